@@ -1,0 +1,213 @@
+"""Drop-in for ac4k_kernel's compiled module `ac4k_kernel._cuda_ops` on B200 (sm_100a).
+
+Same names, argument order and argument checks as the pybind module defined in the
+reference's lib/cuda_bindings.cc:37-97 (C++ prototypes in include/ac4k_kernel/ops.h:27-48).
+Each function validates its tensors the way the reference's host launcher does, then hands
+raw device pointers and the current CUDA stream to the C-ABI library; outputs are
+pre-allocated by the caller and written in place.  A failed check raises RuntimeError, as
+the reference's TORCH_CHECKs do.
+
+Scale-factor layout is inferred from the rank of `sf`: `in.dim() + 1` is the reference's
+[.., K/64, align16(M), 4] layout, `in.dim() + 3` the tensor-memory-ready
+[.., ceil(M/128), K/64, 32, 4, 4] tiles.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import LIB, check
+
+__arch__ = LIB.ac4k_arch().decode()
+__arch_description__ = LIB.ac4k_arch_description().decode()
+__backend__ = LIB.ac4k_backend().decode()
+__version__ = LIB.ac4k_version().decode()
+
+SF_AC4K, SF_TILE128X4 = 0, 1
+_DT = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+_I64x4 = ctypes.c_int64 * 4
+
+
+def _align_up(a, b):
+    return (a + b - 1) // b * b
+
+
+def _ceil_div(a, b):
+    return (a + b - 1) // b
+
+
+def _require(cond, msg):
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _check_tensor(x, dtype, name):
+    _require(isinstance(x, torch.Tensor), f"{name} must be a tensor")
+    _require(x.is_cuda, f"{name} must be a CUDA tensor")
+    _require(x.is_contiguous(), f"{name} must be contiguous")
+    _require(x.dtype == dtype, f"Inconsistency of Tensor type: {name} must be {dtype}")
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _view4(inp: torch.Tensor, cross_dim: int, reduce_dim: int):
+    """Sizes and element strides ordered [outer0, outer1, cross, reduce], rank padded to 4
+    with leading 1s (quantize_nvfp4.cu:226-241)."""
+    nd = inp.dim()
+    others = [i for i in range(nd) if i not in (cross_dim, reduce_dim)]
+    shape = [1] * (2 - len(others)) + [inp.size(i) for i in others]
+    stride = [0] * (2 - len(others)) + [inp.stride(i) for i in others]
+    shape += [inp.size(cross_dim), inp.size(reduce_dim)]
+    stride += [inp.stride(cross_dim), inp.stride(reduce_dim)]
+    return shape, stride, others
+
+
+def _check_quant_common(out, inp, cross_dim, reduce_dim, reduce_align, reduce_div):
+    _require(2 <= inp.dim() <= 4, "in must be 2-4D")
+    _require(0 <= cross_dim < inp.dim(), "cross_dim must be less than in.dim()")
+    _require(0 <= reduce_dim < inp.dim(), "reduce_dim must be less than in.dim()")
+    _require(cross_dim != reduce_dim, "cross_dim and reduce_dim must be different")
+    _require(out.dim() == inp.dim(), "out must be the same dim as in")
+    shape, stride, others = _view4(inp, cross_dim, reduce_dim)
+    for c, i in enumerate(others):
+        _require(out.size(c) == inp.size(i), "out must be the same shape as in")
+    _require(out.size(-2) == shape[2], "meet invalid cross dim size")
+    _require(out.size(-1) == _align_up(shape[3], reduce_align) // reduce_div,
+             "meet invalid reduce dim size")
+    return shape, stride, others
+
+
+def quantize_nvfp4(out, sf, input, global_scale, cross_dim, reduce_dim, swizzle):
+    """bf16 -> NVFP4 (ops.h:27-29; checks of quantize_nvfp4.cu:171-224)."""
+    _check_tensor(input, torch.bfloat16, "in")
+    _check_tensor(global_scale, torch.float32, "global_scale")
+    _require(global_scale.dim() == 0, "global_scale must be a scalar")
+    _check_tensor(out, torch.uint8, "out")
+    _check_tensor(sf, torch.float8_e4m3fn, "sf")
+    shape, stride, others = _check_quant_common(out, input, int(cross_dim), int(reduce_dim), 64, 2)
+    nd = input.dim()
+    kt = _ceil_div(shape[3], 64)
+    if sf.dim() == nd + 1:
+        layout = SF_AC4K
+        want = [input.size(i) for i in others] + [kt, _align_up(shape[2], 16), 4]
+    elif sf.dim() == nd + 3:
+        layout = SF_TILE128X4
+        want = [input.size(i) for i in others] + [_ceil_div(shape[2], 128), kt, 32, 4, 4]
+    else:
+        raise RuntimeError("meet invalid sf rank")
+    _require(list(sf.shape) == want, "meet invalid sf shape")
+    with torch.cuda.device(input.device):
+        check(LIB.ac4k_quantize_nvfp4(out.data_ptr(), sf.data_ptr(), input.data_ptr(),
+                                      global_scale.data_ptr(), _I64x4(*shape), _I64x4(*stride),
+                                      int(bool(swizzle)), layout, _stream(input)),
+              "quantize_nvfp4")
+
+
+def _quantize_rowwise(fn, name, out, sf, input, scale_max, scale_dtype, out_dtype, cross_dim,
+                      reduce_dim, swizzle):
+    _check_tensor(input, torch.bfloat16, "in")
+    _check_tensor(scale_max, scale_dtype, "scale_max")
+    _require(scale_max.dim() == 0, "scale_max must be a scalar")
+    _check_tensor(out, out_dtype, "out")
+    _check_tensor(sf, torch.float32, "sf")
+    shape, stride, others = _check_quant_common(out, input, int(cross_dim), int(reduce_dim), 16, 1)
+    _require(sf.dim() == input.dim() - 1, "meet invalid sf rank")
+    want = [input.size(i) for i in others] + [_align_up(shape[2], 16)]
+    _require(list(sf.shape) == want, "meet invalid sf shape")
+    args = [out.data_ptr(), sf.data_ptr(), input.data_ptr(), scale_max.data_ptr(),
+            _I64x4(*shape), _I64x4(*stride)]
+    if swizzle is not None:
+        args.append(int(bool(swizzle)))
+    with torch.cuda.device(input.device):
+        check(fn(*args, _stream(input)), name)
+
+
+def quantize_fp8(out, sf, input, scale_max, cross_dim, reduce_dim, swizzle):
+    """bf16 -> per-row e4m3 (ops.h:31-33; checks of quantize_fp8.cu:196-247)."""
+    _quantize_rowwise(LIB.ac4k_quantize_fp8, "quantize_fp8", out, sf, input, scale_max,
+                      torch.float32, torch.float8_e4m3fn, cross_dim, reduce_dim, swizzle)
+
+
+def quantize_int8(out, sf, input, scale_max, cross_dim, reduce_dim):
+    """bf16 -> per-row int8, int32 scale_max (ops.h:35-37; quantize_int8.cu:179-230)."""
+    _quantize_rowwise(LIB.ac4k_quantize_int8, "quantize_int8", out, sf, input, scale_max,
+                      torch.int32, torch.int8, cross_dim, reduce_dim, None)
+
+
+def linear_nvfp4(D, A, A_sf, A_global_scale, B, B_sf, B_global_scale, bias):
+    """D = (A_gs*B_gs) * A @ B^T + bias (ops.h:43-48; checks of linear_nvfp4.cu:759-805)."""
+    _require(D.dim() == 2, "d must be a 2d matrix")
+    M, N = D.shape
+    _require(D.dtype in _DT, "d must be bfloat16, half or float")
+    _require(D.is_cuda and D.is_contiguous(), "d must be contiguous")
+    _require(A.dim() == 2, "a must be a 2d matrix")
+    _check_tensor(A, torch.uint8, "a")
+    _require(A.size(0) == M, f"A size(0) must be {M} but see {A.size(0)}")
+    K = A.size(1) * 2
+    _require(K % 16 == 0, f"A size(1)*2 must be multiple of 16 but see {K}")
+    _require(B.dim() == 2, "b must be a 2d matrix")
+    _check_tensor(B, torch.uint8, "b")
+    _require(B.size(0) == N, f"B size(0) must be {N} but see {B.size(0)}")
+    _require(B.size(1) == A.size(1), "B size(1) must equal A size(1)")
+    kt = _ceil_div(K, 64)
+    _check_tensor(A_sf, torch.float8_e4m3fn, "scale_a")
+    _check_tensor(B_sf, torch.float8_e4m3fn, "scale_b")
+    if A_sf.dim() == 3:
+        layout = SF_AC4K
+        _require(list(A_sf.shape) == [kt, _align_up(M, 16), 4], "scale_a has an invalid shape")
+        _require(B_sf.dim() == 3, "scale_b must be a 3d matrix")
+        _require(list(B_sf.shape) == [kt, _align_up(N, 16), 4], "scale_b has an invalid shape")
+    elif A_sf.dim() == 5:
+        layout = SF_TILE128X4
+        _require(list(A_sf.shape) == [_ceil_div(M, 128), kt, 32, 4, 4], "scale_a has an invalid shape")
+        _require(list(B_sf.shape) == [_ceil_div(N, 128), kt, 32, 4, 4], "scale_b has an invalid shape")
+    else:
+        raise RuntimeError("scale_a must be a 3d matrix")
+    _check_tensor(A_global_scale, torch.float32, "global_scale_a")
+    _require(A_global_scale.dim() == 0, "A_global_scale must be a scalar")
+    _check_tensor(B_global_scale, torch.float32, "global_scale_b")
+    _require(B_global_scale.dim() == 0, "B_global_scale must be a scalar")
+    bias_ptr, bias_dt = None, 0
+    if bias is not None:
+        _require(bias.dtype in _DT, "bias must be bfloat16, half or float")
+        _require(bias.is_cuda and bias.is_contiguous(), "bias must be contiguous")
+        _require(bias.dim() == 2, "bias must be a 2d matrix")
+        _require(bias.size(0) == 1, "bias shape[0] must be 1")
+        _require(bias.size(1) == N, f"bias shape[1] must be {N}")
+        bias_ptr, bias_dt = bias.data_ptr(), _DT[bias.dtype]
+    with torch.cuda.device(D.device):
+        check(LIB.ac4k_linear_nvfp4(D.data_ptr(), _DT[D.dtype], A.data_ptr(), A_sf.data_ptr(),
+                                    A_global_scale.data_ptr(), B.data_ptr(), B_sf.data_ptr(),
+                                    B_global_scale.data_ptr(), bias_ptr, bias_dt, M, N, K, layout,
+                                    _stream(D)),
+              "linear_nvfp4")
+
+
+def global_scale_bf16(out, input, max_scale):
+    """out[()] = max|input| / max_scale on the device; stands in for the reference's Triton
+    amax kernel (python/ac4k_kernel/ops/quant.py:21-59)."""
+    _check_tensor(input, torch.bfloat16, "in")
+    _check_tensor(out, torch.float32, "out")
+    _require(out.dim() == 0, "out must be a scalar")
+    with torch.cuda.device(input.device):
+        check(LIB.ac4k_global_scale_bf16(input.data_ptr(), input.numel(), float(max_scale),
+                                         out.data_ptr(), _stream(input)),
+              "global_scale_bf16")
+
+
+def _out_of_scope(name):
+    def fn(*args, **kwargs):
+        raise NotImplementedError(
+            f"{name} is outside the NVFP4 linear path that this sm100 build covers")
+    fn.__name__ = name
+    return fn
+
+
+# Names that ac4k_kernel/__init__.py:19-34 imports eagerly; present so the import succeeds.
+mha_nvfp4_fwd = _out_of_scope("mha_nvfp4_fwd")
+mha_int8_x_fp8_fwd = _out_of_scope("mha_int8_x_fp8_fwd")
+rope3d = _out_of_scope("rope3d")

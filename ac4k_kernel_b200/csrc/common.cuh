@@ -1,0 +1,102 @@
+// Shared host/device helpers for the sm_100a NVFP4 kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ac4k_b200.h"
+
+namespace ac4k {
+
+// ---- host-side error plumbing -----------------------------------------------------------
+void set_last_error(const char *fmt, ...);
+int fail(int code, const char *fmt, ...);     // records the message, returns code
+int cuda_fail(cudaError_t e, const char *what);
+
+#define AC4K_CUDA_TRY(expr)                                                     \
+  do {                                                                          \
+    cudaError_t _e = (expr);                                                    \
+    if (_e != cudaSuccess) return ::ac4k::cuda_fail(_e, #expr);                 \
+  } while (0)
+
+#define AC4K_LAUNCH_CHECK(what)                                                 \
+  do {                                                                          \
+    cudaError_t _e = cudaGetLastError();                                        \
+    if (_e != cudaSuccess) return ::ac4k::cuda_fail(_e, what);                  \
+  } while (0)
+
+// Address of the device status word of the current device (one per device, lives in this
+// library's module); kernels with bounded waits receive it as an argument.  NULL on error.
+unsigned int *device_status_ptr();
+
+// ---- small integer helpers --------------------------------------------------------------
+__host__ __device__ constexpr int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+__host__ __device__ constexpr int64_t align_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
+
+// ---- conversions (device) ---------------------------------------------------------------
+// 8 fp32 -> 8 e2m1 packed in a 32-bit word, element 2j in the low nibble of byte j.
+// `cvt.rn.satfinite.e2m1x2.f32 d, a, b` puts a in the HIGH nibble, b in the low one.
+__device__ __forceinline__ uint32_t f32x8_to_e2m1x8(const float (&v)[8]) {
+  uint32_t r;
+  asm("{\n"
+      ".reg .b8 b0, b1, b2, b3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
+      "mov.b32 %0, {b0, b1, b2, b3};\n"
+      "}"
+      : "=r"(r)
+      : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
+  return r;
+}
+
+// 4 fp32 -> 4 e4m3 (RNE, satfinite), element 0 in the low byte.
+__device__ __forceinline__ uint32_t f32x4_to_e4m3x4(float a, float b, float c, float d) {
+  uint32_t r;
+  asm("{\n"
+      ".reg .b16 lo, hi;\n"
+      "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n"
+      "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n"
+      "mov.b32 %0, {lo, hi};\n"
+      "}"
+      : "=r"(r)
+      : "f"(a), "f"(b), "f"(c), "f"(d));
+  return r;
+}
+
+// one fp32 (>= 0) -> e4m3 byte and its exact fp32 value
+__device__ __forceinline__ uint8_t f32_to_e4m3(float s, float &back) {
+  uint16_t p;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(p) : "f"(0.0f), "f"(s));
+  uint8_t b = (uint8_t)(p & 0xFF);
+  __half_raw h = __nv_cvt_fp8_to_halfraw(b, __NV_E4M3);
+  back = __half2float(__half(h));
+  return b;
+}
+
+__device__ __forceinline__ int8_t f32_to_s8_rni_sat(float x) {
+  int r;
+  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return (int8_t)r;
+}
+
+// |x| of two packed bf16 (clears the sign bits), max of packed bf16 pairs
+__device__ __forceinline__ uint32_t abs_bf16x2(uint32_t v) { return v & 0x7FFF7FFFu; }
+__device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
+  __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162 *>(&a);
+  __nv_bfloat162 y = *reinterpret_cast<__nv_bfloat162 *>(&b);
+  __nv_bfloat162 m = __hmax2(x, y);
+  return *reinterpret_cast<uint32_t *>(&m);
+}
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t lo16) { return __uint_as_float(lo16 << 16); }
+// max of the two halves of an abs'd bf16x2 word, as fp32
+__device__ __forceinline__ float hmax_bf16x2_to_f32(uint32_t v) {
+  uint32_t a = v & 0xFFFFu, b = v >> 16;   // non-negative bf16: integer order == value order
+  return bf16_bits_to_f32(a > b ? a : b);
+}
+
+}  // namespace ac4k

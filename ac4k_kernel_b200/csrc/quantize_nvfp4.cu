@@ -1,0 +1,357 @@
+// BF16 -> NVFP4 quantiser and the global-scale (amax) reduction for sm_100a.
+//
+// Semantics follow ac4k_kernel's lib/cuda/sm120/quantize_nvfp4.cu:49-157 (block of 16,
+// pair of scales packed four to a word, K padded to 64, scale rows padded to 16) with its
+// approximate reciprocals replaced by correctly rounded fp32 operations:
+//     alpha = 1 / g ;  sf = e4m3(alpha * (amax16 * fp32(1/6))) ;
+//     r = sf ? alpha * (1 / float(sf)) : 0 ;  code = e2m1(float(x) * r)
+// Two kernels: a tiled one for rows that are contiguous along K (the linear path), and a
+// strided one (any cross/reduce strides, optional K permutation) for the other callers.
+#include "common.cuh"
+
+namespace ac4k {
+
+static constexpr float kOneSixth = 0.16666667163372040f;
+
+struct BlockScale {
+  float r;       // multiplier applied to the elements
+  uint8_t byte;  // e4m3 scale
+};
+
+__device__ __forceinline__ BlockScale block_scale(float amax, float alpha) {
+  BlockScale o;
+  float s = __fmul_rn(alpha, __fmul_rn(amax, kOneSixth));
+  float sf_f;
+  o.byte = f32_to_e4m3(s, sf_f);
+  o.r = (sf_f != 0.0f) ? __fmul_rn(alpha, __frcp_rn(sf_f)) : 0.0f;
+  return o;
+}
+
+__device__ __forceinline__ float load_alpha(const float *gscale) {
+  float g = __ldg(gscale);
+  return g == 0.0f ? 0.0f : __frcp_rn(g);
+}
+
+__device__ __forceinline__ uint32_t quantize8(const uint4 &v, float r) {
+  float f[8];
+  f[0] = __fmul_rn(__uint_as_float(v.x << 16), r);
+  f[1] = __fmul_rn(__uint_as_float(v.x & 0xFFFF0000u), r);
+  f[2] = __fmul_rn(__uint_as_float(v.y << 16), r);
+  f[3] = __fmul_rn(__uint_as_float(v.y & 0xFFFF0000u), r);
+  f[4] = __fmul_rn(__uint_as_float(v.z << 16), r);
+  f[5] = __fmul_rn(__uint_as_float(v.z & 0xFFFF0000u), r);
+  f[6] = __fmul_rn(__uint_as_float(v.w << 16), r);
+  f[7] = __fmul_rn(__uint_as_float(v.w & 0xFFFF0000u), r);
+  return f32x8_to_e2m1x8(f);
+}
+
+// ----------------------------------------------------------------------------------------
+// Tiled kernel: one CTA = 128 rows x 256 K-elements.  A warp reads 512 contiguous bytes of
+// one row per pass (one 16-byte load per lane), writes 128 contiguous bytes of codes, and
+// drops its scale bytes into a shared-memory image of the scale tile that is written out
+// with full-width stores at the end.
+// ----------------------------------------------------------------------------------------
+static constexpr int kTileRows = 128;
+static constexpr int kTileK = 256;
+static constexpr int kTileKch = kTileK / 64;
+static constexpr int kThreads = 256;
+static constexpr int kUnroll = 8;
+
+template <int SF_LAYOUT>
+__global__ void __launch_bounds__(kThreads)
+nvfp4_quantize_tiled_kernel(uint8_t *__restrict__ out, uint32_t *__restrict__ sf,
+                            const uint16_t *__restrict__ in, const float *__restrict__ gscale,
+                            int64_t M, int64_t K, int64_t d1, int64_t stride0, int64_t stride1,
+                            int64_t row_stride) {
+  __shared__ uint32_t s_sf[kTileKch * kTileRows];
+
+  const int64_t Kp = align_up(K, 64);
+  const int64_t KT = Kp / 64;
+  const int64_t M16 = align_up(M, 16);
+  const int64_t MT = ceil_div(M, 128);
+  const int64_t batch = blockIdx.z;
+  const int64_t r0 = (int64_t)blockIdx.y * kTileRows;
+  const int64_t k0 = (int64_t)blockIdx.x * kTileK;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const uint16_t *in_b = in + (batch / d1) * stride0 + (batch % d1) * stride1;
+  uint8_t *out_b = out + batch * M * (Kp / 2);
+  const float alpha = load_alpha(gscale);
+
+  const int64_t k = k0 + lane * 8;
+  const bool k_live = k < Kp;   // chunk belongs to the (padded) output
+  const bool k_data = k < K;    // chunk has input data (K % 8 == 0 on this path)
+  uint8_t *s_bytes = reinterpret_cast<uint8_t *>(s_sf);
+  const int kch = lane >> 3, blk = (lane >> 1) & 3;
+
+#pragma unroll 1
+  for (int p0 = 0; p0 < kTileRows / 8; p0 += kUnroll) {
+    uint4 v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t row = r0 + (p0 + u) * 8 + warp;
+      v[u] = make_uint4(0, 0, 0, 0);
+      if (row < M && k_data)
+        v[u] = __ldcs(reinterpret_cast<const uint4 *>(in_b + row * row_stride + k));
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int row_l = (p0 + u) * 8 + warp;
+      const int64_t row = r0 + row_l;
+      uint32_t m = max_bf16x2(max_bf16x2(abs_bf16x2(v[u].x), abs_bf16x2(v[u].y)),
+                              max_bf16x2(abs_bf16x2(v[u].z), abs_bf16x2(v[u].w)));
+      m = max_bf16x2(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+      const BlockScale bs = block_scale(hmax_bf16x2_to_f32(m), alpha);
+      if (row < M && k_live)
+        __stcs(reinterpret_cast<uint32_t *>(out_b + row * (Kp / 2) + k / 2), quantize8(v[u], bs.r));
+      if ((lane & 1) == 0) {
+        const uint8_t b = (row < M) ? bs.byte : (uint8_t)0;
+        int off;
+        if (SF_LAYOUT == AC4K_SF_AC4K)
+          off = (kch * kTileRows + row_l) * 4 + blk;
+        else
+          off = kch * 512 + (row_l & 31) * 16 + (row_l >> 5) * 4 + blk;
+        s_bytes[off] = b;
+      }
+    }
+  }
+  __syncthreads();
+
+  // write the scale image: kTileKch groups of 128 words
+  for (int t = threadIdx.x; t < kTileKch * kTileRows; t += kThreads) {
+    const int c = t >> 7, w = t & 127;
+    const int64_t k64 = k0 / 64 + c;
+    if (k64 >= KT) continue;
+    if (SF_LAYOUT == AC4K_SF_AC4K) {
+      const int64_t row = r0 + w;
+      if (row < M16) sf[(batch * KT + k64) * M16 + row] = s_sf[t];
+    } else {
+      sf[((batch * MT + blockIdx.y) * KT + k64) * 128 + w] = s_sf[t];
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// Strided kernel: one thread = one 16-element block, scalar loads with arbitrary element
+// strides; `PERMUTE` applies the K permutation of quantize_nvfp4.cu:86-100 (each group of
+// 32 viewed as [4][4][2] and transposed in its first two modes).  Threads are laid out so
+// that neighbouring lanes walk the dimension with the smaller stride.
+// ----------------------------------------------------------------------------------------
+template <int SF_LAYOUT, bool PERMUTE, bool ROW_FASTEST>
+__global__ void __launch_bounds__(256)
+nvfp4_quantize_strided_kernel(uint8_t *__restrict__ out, uint8_t *__restrict__ sf,
+                              const uint16_t *__restrict__ in, const float *__restrict__ gscale,
+                              int64_t M, int64_t K, int64_t d1, int64_t stride0, int64_t stride1,
+                              int64_t stride_m, int64_t stride_k) {
+  const int64_t Kp = align_up(K, 64);
+  const int64_t KT = Kp / 64;
+  const int64_t nblk = Kp / 16;
+  const int64_t M16 = align_up(M, 16);
+  const int64_t MT = ceil_div(M, 128);
+  const int64_t rows_sf = (SF_LAYOUT == AC4K_SF_AC4K) ? M16 : MT * 128;
+  const int64_t batch = blockIdx.z;
+
+  int64_t row, blk;
+  if (ROW_FASTEST) {   // 32 rows x 8 blocks per CTA
+    row = (int64_t)blockIdx.y * 32 + (threadIdx.x & 31);
+    blk = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  } else {             // 8 rows x 32 blocks per CTA
+    row = (int64_t)blockIdx.y * 8 + (threadIdx.x >> 5);
+    blk = (int64_t)blockIdx.x * 32 + (threadIdx.x & 31);
+  }
+  if (row >= rows_sf || blk >= nblk) return;
+
+  const uint16_t *in_b = in + (batch / d1) * stride0 + (batch % d1) * stride1;
+  const float alpha = load_alpha(gscale);
+
+  uint32_t w[8];
+  uint32_t amax = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    uint32_t pair = 0;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int64_t p = blk * 16 + j * 2 + h;   // position in the (permuted) output row
+      int64_t src = p;
+      if (PERMUTE) {
+        const int64_t q = p & 31;
+        src = (p - q) + 8 * ((q & 7) >> 1) + 2 * (q >> 3) + (q & 1);
+      }
+      uint32_t e = 0;
+      if (row < M && src < K) e = __ldg(in_b + row * stride_m + src * stride_k);
+      pair |= e << (16 * h);
+      const uint32_t a = e & 0x7FFFu;
+      amax = a > amax ? a : amax;
+    }
+    w[j] = pair;
+  }
+  const BlockScale bs = block_scale(bf16_bits_to_f32(amax), alpha);
+
+  if (row < M) {
+    uint4 lo = make_uint4(w[0], w[1], w[2], w[3]), hi = make_uint4(w[4], w[5], w[6], w[7]);
+    uint2 codes = make_uint2(quantize8(lo, bs.r), quantize8(hi, bs.r));
+    *reinterpret_cast<uint2 *>(out + (batch * M + row) * (Kp / 2) + blk * 8) = codes;
+  }
+  const uint8_t b = (row < M) ? bs.byte : (uint8_t)0;
+  const int64_t k64 = blk >> 2;
+  if (SF_LAYOUT == AC4K_SF_AC4K) {
+    sf[((batch * KT + k64) * M16 + row) * 4 + (blk & 3)] = b;
+  } else {
+    const int64_t mt = row >> 7, rl = row & 127;
+    sf[((batch * MT + mt) * KT + k64) * 512 + (rl & 31) * 16 + (rl >> 5) * 4 + (blk & 3)] = b;
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// Global scale: max|x| / max_scale.  Division is monotonic, so each CTA divides its own
+// maximum and combines with an integer atomicMax on the (non-negative) float bits, the
+// same scheme as the reference's Triton kernel (python/ac4k_kernel/ops/quant.py:21-46).
+// ----------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(512)
+global_scale_kernel(const uint16_t *__restrict__ x, int64_t n, float max_scale, float *g_out) {
+  uint32_t m2 = 0;   // packed pair of running maxima (bf16 bits, sign cleared)
+  uint32_t m1 = 0;   // scalar head/tail
+  // head: elements before the first 16-byte boundary
+  const uintptr_t addr = reinterpret_cast<uintptr_t>(x);
+  int64_t head = ((16 - (addr & 15)) & 15) / 2;
+  if (head > n) head = n;
+  const int64_t nvec = (n - head) / 8;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthr = (int64_t)gridDim.x * blockDim.x;
+  const uint4 *xv = reinterpret_cast<const uint4 *>(x + head);
+  int64_t i = tid;
+  for (; i + 3 * nthr < nvec; i += 4 * nthr) {
+    uint4 a = __ldcs(xv + i), b = __ldcs(xv + i + nthr), c = __ldcs(xv + i + 2 * nthr),
+          d = __ldcs(xv + i + 3 * nthr);
+    uint32_t ma = max_bf16x2(max_bf16x2(abs_bf16x2(a.x), abs_bf16x2(a.y)),
+                             max_bf16x2(abs_bf16x2(a.z), abs_bf16x2(a.w)));
+    uint32_t mb = max_bf16x2(max_bf16x2(abs_bf16x2(b.x), abs_bf16x2(b.y)),
+                             max_bf16x2(abs_bf16x2(b.z), abs_bf16x2(b.w)));
+    uint32_t mc = max_bf16x2(max_bf16x2(abs_bf16x2(c.x), abs_bf16x2(c.y)),
+                             max_bf16x2(abs_bf16x2(c.z), abs_bf16x2(c.w)));
+    uint32_t md = max_bf16x2(max_bf16x2(abs_bf16x2(d.x), abs_bf16x2(d.y)),
+                             max_bf16x2(abs_bf16x2(d.z), abs_bf16x2(d.w)));
+    m2 = max_bf16x2(m2, max_bf16x2(max_bf16x2(ma, mb), max_bf16x2(mc, md)));
+  }
+  for (; i < nvec; i += nthr) {
+    uint4 a = __ldcs(xv + i);
+    m2 = max_bf16x2(m2, max_bf16x2(max_bf16x2(abs_bf16x2(a.x), abs_bf16x2(a.y)),
+                                   max_bf16x2(abs_bf16x2(a.z), abs_bf16x2(a.w))));
+  }
+  if (tid < head) m1 = x[tid] & 0x7FFFu;
+  const int64_t tail0 = head + nvec * 8;
+  if (tail0 + tid < n) {
+    uint32_t e = x[tail0 + tid] & 0x7FFFu;
+    m1 = e > m1 ? e : m1;
+  }
+  uint32_t m = max(max(m2 & 0xFFFFu, m2 >> 16), m1);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+  __shared__ uint32_t s_m[16];
+  if ((threadIdx.x & 31) == 0) s_m[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    m = threadIdx.x < (blockDim.x >> 5) ? s_m[threadIdx.x] : 0;
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if (threadIdx.x == 0 && m != 0) {
+      const float g = __fdiv_rn(bf16_bits_to_f32(m), max_scale);
+      atomicMax(reinterpret_cast<int *>(g_out), __float_as_int(g));
+    }
+  }
+}
+
+}  // namespace ac4k
+
+using namespace ac4k;
+
+static int check_view(const int64_t shape[4], const int64_t stride[4]) {
+  if (!shape || !stride) return fail(AC4K_ERR_NULL, "shape/stride is NULL");
+  for (int i = 0; i < 4; ++i)
+    if (shape[i] < 0) return fail(AC4K_ERR_SHAPE, "shape[%d] = %lld is negative", i, (long long)shape[i]);
+  return 0;
+}
+
+extern "C" int ac4k_global_scale_bf16(const void *x, int64_t numel, float max_scale, float *g_out,
+                                      ac4k_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!g_out) return fail(AC4K_ERR_NULL, "g_out is NULL");
+  if (numel < 0) return fail(AC4K_ERR_SHAPE, "numel is negative");
+  if (numel > 0 && !x) return fail(AC4K_ERR_NULL, "x is NULL");
+  if (reinterpret_cast<uintptr_t>(x) & 1) return fail(AC4K_ERR_ALIGN, "x must be 2-byte aligned");
+  if (!(max_scale > 0.0f)) return fail(AC4K_ERR_SHAPE, "max_scale must be positive");
+  AC4K_CUDA_TRY(cudaMemsetAsync(g_out, 0, sizeof(float), stream));
+  if (numel == 0) return 0;
+  const int threads = 512;
+  int64_t blocks = ceil_div(ceil_div(numel, 8), (int64_t)threads * 4);
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  if (blocks < 1) blocks = 1;
+  global_scale_kernel<<<(unsigned)blocks, threads, 0, stream>>>(static_cast<const uint16_t *>(x), numel,
+                                                               max_scale, g_out);
+  AC4K_LAUNCH_CHECK("global_scale_kernel");
+  return 0;
+}
+
+extern "C" int ac4k_quantize_nvfp4(void *out, void *sf, const void *in, const float *global_scale,
+                                   const int64_t shape[4], const int64_t stride[4], int swizzle,
+                                   int sf_layout, ac4k_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (int e = check_view(shape, stride)) return e;
+  if (!out || !sf || !global_scale) return fail(AC4K_ERR_NULL, "out/sf/global_scale is NULL");
+  if (sf_layout != AC4K_SF_AC4K && sf_layout != AC4K_SF_TILE128X4)
+    return fail(AC4K_ERR_ENUM, "unknown sf_layout %d", sf_layout);
+  const int64_t d0 = shape[0], d1 = shape[1], M = shape[2], K = shape[3];
+  const int64_t nbatch = d0 * d1;
+  if (nbatch == 0 || M == 0 || K == 0) return 0;   // nothing to write (padding needs K > 0 rows)
+  if (!in) return fail(AC4K_ERR_NULL, "in is NULL");
+  if (nbatch > 65535) return fail(AC4K_ERR_SHAPE, "outer dims product %lld exceeds 65535", (long long)nbatch);
+  if ((reinterpret_cast<uintptr_t>(out) & 7) || (reinterpret_cast<uintptr_t>(sf) & 3))
+    return fail(AC4K_ERR_ALIGN, "out must be 8-byte and sf 4-byte aligned");
+  const int64_t Kp = align_up(K, 64);
+  const uint16_t *inp = static_cast<const uint16_t *>(in);
+
+  const bool vec_ok = !swizzle && stride[3] == 1 && (K % 8 == 0) && (stride[2] % 8 == 0) &&
+                      (stride[0] % 8 == 0) && (stride[1] % 8 == 0) &&
+                      ((reinterpret_cast<uintptr_t>(in) & 15) == 0);
+  if (vec_ok) {
+    dim3 grid((unsigned)ceil_div(Kp, kTileK), (unsigned)ceil_div(M, kTileRows), (unsigned)nbatch);
+    if (ceil_div(M, kTileRows) > 65535) return fail(AC4K_ERR_SHAPE, "M too large");
+    if (sf_layout == AC4K_SF_AC4K)
+      nvfp4_quantize_tiled_kernel<AC4K_SF_AC4K><<<grid, kThreads, 0, stream>>>(
+          static_cast<uint8_t *>(out), static_cast<uint32_t *>(sf), inp, global_scale, M, K, d1,
+          stride[0], stride[1], stride[2]);
+    else
+      nvfp4_quantize_tiled_kernel<AC4K_SF_TILE128X4><<<grid, kThreads, 0, stream>>>(
+          static_cast<uint8_t *>(out), static_cast<uint32_t *>(sf), inp, global_scale, M, K, d1,
+          stride[0], stride[1], stride[2]);
+    AC4K_LAUNCH_CHECK("nvfp4_quantize_tiled_kernel");
+    return 0;
+  }
+
+  const int64_t rows_sf = (sf_layout == AC4K_SF_AC4K) ? align_up(M, 16) : align_up(M, 128);
+  const bool row_fastest = stride[2] < stride[3];
+  dim3 grid;
+  if (row_fastest)
+    grid = dim3((unsigned)ceil_div(Kp / 16, 8), (unsigned)ceil_div(rows_sf, 32), (unsigned)nbatch);
+  else
+    grid = dim3((unsigned)ceil_div(Kp / 16, 32), (unsigned)ceil_div(rows_sf, 8), (unsigned)nbatch);
+  if (grid.y > 65535) return fail(AC4K_ERR_SHAPE, "M too large for the strided path");
+#define AC4K_LAUNCH_STRIDED(L, P, R)                                                             \
+  nvfp4_quantize_strided_kernel<L, P, R><<<grid, 256, 0, stream>>>(                              \
+      static_cast<uint8_t *>(out), static_cast<uint8_t *>(sf), inp, global_scale, M, K, d1,      \
+      stride[0], stride[1], stride[2], stride[3])
+  const int sel = (sf_layout == AC4K_SF_TILE128X4 ? 4 : 0) | (swizzle ? 2 : 0) | (row_fastest ? 1 : 0);
+  switch (sel) {
+    case 0: AC4K_LAUNCH_STRIDED(AC4K_SF_AC4K, false, false); break;
+    case 1: AC4K_LAUNCH_STRIDED(AC4K_SF_AC4K, false, true); break;
+    case 2: AC4K_LAUNCH_STRIDED(AC4K_SF_AC4K, true, false); break;
+    case 3: AC4K_LAUNCH_STRIDED(AC4K_SF_AC4K, true, true); break;
+    case 4: AC4K_LAUNCH_STRIDED(AC4K_SF_TILE128X4, false, false); break;
+    case 5: AC4K_LAUNCH_STRIDED(AC4K_SF_TILE128X4, false, true); break;
+    case 6: AC4K_LAUNCH_STRIDED(AC4K_SF_TILE128X4, true, false); break;
+    default: AC4K_LAUNCH_STRIDED(AC4K_SF_TILE128X4, true, true); break;
+  }
+#undef AC4K_LAUNCH_STRIDED
+  AC4K_LAUNCH_CHECK("nvfp4_quantize_strided_kernel");
+  return 0;
+}

@@ -1,0 +1,105 @@
+/*
+ * ac4k_b200.h - C ABI of the B200 (sm_100a) NVFP4 linear path.
+ *
+ * A shared library exporting these symbols replaces the compiled half of ac4k_kernel's
+ * `_cuda_ops` extension for the quantise -> NVFP4 GEMM path.  Every entry point takes raw
+ * device pointers, sizes and a CUDA stream; no torch types cross the boundary.  The file
+ * and line given with each declaration is the reference interface it stands in for
+ * (paths inside the ac4k_kernel project).
+ *
+ * Conventions
+ *   - return value: 0 = success; < 0 = rejected argument (see AC4K_ERR_*); > 0 = the
+ *     cudaError_t / CUresult reported by the runtime.  Nothing throws, nothing exits.
+ *     `ac4k_last_error()` returns a thread-local message for the last non-zero return.
+ *   - all work is enqueued on `stream` and is asynchronous; the caller owns every buffer and
+ *     must keep it alive until the stream reaches that point.  Outputs are fully written,
+ *     padding included (callers allocate them uninitialised, like the reference's Python).
+ *   - `shape`/`stride` describe the bf16 input as a 4-D view ordered
+ *     [outer0, outer1, cross (M), reduce (K)], strides in elements; lower ranks are padded
+ *     with leading 1s, exactly like quantize_nvfp4.cu:226-241 does after its checks.
+ *   - scale-factor layouts for NVFP4:
+ *       AC4K_SF_AC4K      [.., ceil(K/64), align16(M), 4]   the reference's wire format
+ *                         (quantize_nvfp4.cu:56-60,150-155)
+ *       AC4K_SF_TILE128X4 [.., ceil(M/128), ceil(K/64), 32, 4, 4]  the 512-byte tiles that
+ *                         `tcgen05.cp.32x128b.warpx4` copies to tensor memory unchanged
+ *                         (the un-layout is test/utils.py:15-23)
+ */
+#ifndef AC4K_B200_H_
+#define AC4K_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *ac4k_stream_t; /* cudaStream_t */
+
+enum {
+  AC4K_OK = 0,
+  AC4K_ERR_NULL = -1,        /* required pointer is NULL                       */
+  AC4K_ERR_SHAPE = -2,       /* negative / inconsistent sizes                  */
+  AC4K_ERR_ALIGN = -3,       /* pointer or stride alignment not supported      */
+  AC4K_ERR_ENUM = -4,        /* unknown dtype / layout code                    */
+  AC4K_ERR_UNSUPPORTED = -5, /* valid in the reference, not built here         */
+  AC4K_ERR_DEVICE = -6,      /* current device is not an sm_100 part           */
+  AC4K_ERR_TIMEOUT = -7      /* a bounded device-side wait gave up (see status) */
+};
+
+enum { AC4K_SF_AC4K = 0, AC4K_SF_TILE128X4 = 1 };
+enum { AC4K_DT_BF16 = 0, AC4K_DT_FP16 = 1, AC4K_DT_FP32 = 2 };
+
+/* Library identity: mirrors the module attributes of lib/cuda_bindings.cc:41-44. */
+const char *ac4k_arch(void);             /* "sm100" */
+const char *ac4k_arch_description(void);
+const char *ac4k_backend(void);          /* "cuda"  */
+const char *ac4k_version(void);          /* "0.1.0" */
+const char *ac4k_last_error(void);
+
+/* Device-side status word of the current device: 0, or the code left by a kernel whose
+ * bounded wait expired.  Synchronises the device.  `clear` != 0 resets it. */
+int ac4k_device_status(uint32_t *status_out, int clear);
+
+/* g_out[0] = max|x| / max_scale over `numel` contiguous bf16 values (0 for numel == 0).
+ * Replaces `_global_scale` + `_triton_global_scale_kernel`,
+ * python/ac4k_kernel/ops/quant.py:21-59. */
+int ac4k_global_scale_bf16(const void *x, int64_t numel, float max_scale, float *g_out,
+                           ac4k_stream_t stream);
+
+/* bf16 -> packed e2m1 + e4m3 block scales, given the fp32 global scale on the device.
+ * Replaces ac4k::quantize_nvfp4, include/ac4k_kernel/ops.h:27-29 and
+ * lib/cuda/sm120/quantize_nvfp4.cu:164-271.
+ *   out: [outer0, outer1, M, align64(K)/2] bytes;  sf: see layouts above. */
+int ac4k_quantize_nvfp4(void *out, void *sf, const void *in, const float *global_scale,
+                        const int64_t shape[4], const int64_t stride[4], int swizzle,
+                        int sf_layout, ac4k_stream_t stream);
+
+/* Per-row (whole reduce dim) e4m3 quantiser.  Replaces ac4k::quantize_fp8,
+ * include/ac4k_kernel/ops.h:31-33, lib/cuda/sm120/quantize_fp8.cu:192-290.
+ *   out: [outer0, outer1, M, align16(K)] e4m3;  sf: [outer0, outer1, align16(M)] fp32. */
+int ac4k_quantize_fp8(void *out, float *sf, const void *in, const float *scale_max,
+                      const int64_t shape[4], const int64_t stride[4], int swizzle,
+                      ac4k_stream_t stream);
+
+/* Per-row int8 quantiser (scale_max is an int32 on the device).  Replaces
+ * ac4k::quantize_int8, include/ac4k_kernel/ops.h:35-37,
+ * lib/cuda/sm120/quantize_int8.cu:175-262. */
+int ac4k_quantize_int8(void *out, float *sf, const void *in, const int32_t *scale_max,
+                       const int64_t shape[4], const int64_t stride[4],
+                       ac4k_stream_t stream);
+
+/* D[M,N] = cast((A_gs*B_gs) * A_fp4[M,K] * B_fp4[N,K]^T + bias[N]).
+ * Replaces ac4k::linear_nvfp4, include/ac4k_kernel/ops.h:43-48,
+ * lib/cuda/sm120/linear_nvfp4.cu:753-901.
+ *   A: [M, K/2] bytes, B: [N, K/2] bytes, K a multiple of 64 (what the quantiser emits);
+ *   A_sf/B_sf in `sf_layout`; A_gs/B_gs: device fp32 scalars; bias: NULL or N values of
+ *   `bias_dtype`; D row-major contiguous of `d_dtype`. */
+int ac4k_linear_nvfp4(void *D, int d_dtype, const void *A, const void *A_sf,
+                      const float *A_gs, const void *B, const void *B_sf, const float *B_gs,
+                      const void *bias, int bias_dtype, int64_t M, int64_t N, int64_t K,
+                      int sf_layout, ac4k_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AC4K_B200_H_ */

@@ -1,0 +1,316 @@
+"""CPU/torch restatement of ac4k_kernel's NVFP4 linear path.  TEST INFRASTRUCTURE ONLY.
+
+This module is the checker for the CUDA kernels: it is imported by the tests, by the
+smoke check and by the CPU-baseline leg of the benchmark, never by the product package.
+Every function works on CPU tensors and (because it only uses elementwise fp32 torch ops,
+which are IEEE round-to-nearest on both devices) on CUDA tensors as well, so full-size
+inputs can be checked on the GPU against the same arithmetic.
+
+Parity status: PINNED.  The reference ships no golden files, but its own test oracles
+(`test/test_quantize_bench.py` `get_ref` / `qunatize_fp8`, `test/test_linear_bench.py`
+`get_torch_results`) were executed on CPU against this restatement; their outputs on seeded
+inputs are stored under tests/golden/ (see tests/golden/make_golden.py).
+
+Reference lines followed (paths inside the ac4k_kernel project):
+  * global scale            python/ac4k_kernel/ops/quant.py:21-59,198-200
+  * NVFP4 quantiser math    lib/cuda/sm120/quantize_nvfp4.cu:73,113-147  (order of fp32 ops)
+  * NVFP4 layouts, padding  lib/cuda/sm120/quantize_nvfp4.cu:56-70,83,107-108,150-155;
+                            test/test_quantize_bench.py:29-83
+  * K permutation "swizzle" lib/cuda/sm120/quantize_nvfp4.cu:86-100; test_quantize_bench.py:60-64
+  * nibble order / LUT      lib/cuda/common/math.cuh:62-85; test/test_linear_bench.py:15-50
+  * dequantise + matmul     test/test_linear_bench.py:53-107; lib/cuda/sm120/linear_nvfp4.cu:586-633
+  * per-token FP8           lib/cuda/sm120/quantize_fp8.cu:91-176; test_quantize_bench.py:256-300
+  * per-token INT8          lib/cuda/sm120/quantize_int8.cu:55-59,125-165
+  * 128x4 scale tile        test/utils.py:15-23
+
+The reference kernels use `rcp.approx.ftz` and `--use_fast_math`; this restatement (and the
+CUDA kernels checked against it) use correctly rounded fp32 operations in the same order, so
+that CPU, GPU-torch and the hand-written kernels agree bit for bit.
+"""
+from __future__ import annotations
+
+import torch
+
+BLOCK = 16            # elements per scale block            (quant.py:190)
+PACK_SF = 4           # scales packed per 32-bit word       (quant.py:192)
+CROSS_ALIGN = 16      # scale rows are padded to 16         (quant.py:193)
+REDUCE_ALIGN = 64     # K is padded to 64                   (quant.py:194)
+E2M1_MAX = 6.0
+E4M3_MAX = 448.0
+ONE_SIXTH = 0.16666667163372040   # fp32(1/6), the literal in quantize_nvfp4.cu:126
+
+E2M1_VALUES = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0,
+               -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0]
+
+
+def ceil_div(a, b):
+    return (a + b - 1) // b
+
+
+def align_up(a, b):
+    return ceil_div(a, b) * b
+
+
+# ----------------------------------------------------------------------------------------
+# scalar format conversions
+# ----------------------------------------------------------------------------------------
+def e4m3_rne_sat_bits(s: torch.Tensor) -> torch.Tensor:
+    """fp32 (>= 0 or NaN) -> e4m3fn byte, round-to-nearest-even, saturating to 448.
+
+    Written with integer/fp32 arithmetic only (no torch fp8 cast) so that it can be checked
+    against torch's own cast.  NaN maps to 0x7F like `cvt.rn.satfinite.e4m3x2.f32`.
+    """
+    s = s.to(torch.float32)
+    nan = torch.isnan(s)
+    neg = torch.signbit(s)
+    a = s.abs().clamp(max=E4M3_MAX)
+    a = torch.where(nan, torch.zeros_like(a), a)
+    # quantum of the e4m3 grid around a: 2^(e-3) for normals (e >= -6), 2^-9 below 2^-6
+    ad = a.double()
+    e = (torch.frexp(ad)[1] - 1).clamp(min=-6).double()     # floor(log2(a)), exact
+    q = torch.ldexp(torch.ones_like(ad), (e - 3.0).to(torch.int32))
+    n = torch.round(ad / q)                  # torch.round is half-to-even; a/q exact in fp64
+    v = n * q                                # value on the grid (may carry into next binade)
+    # encode v
+    ve = (torch.frexp(v)[1] - 1).clamp(min=-6).double()
+    mant = v / torch.ldexp(torch.ones_like(v), ve.to(torch.int32))
+    is_sub = v < 2.0 ** -6
+    exp_field = torch.where(is_sub, torch.zeros_like(ve), ve + 7.0)
+    man_field = torch.where(is_sub, v / 2.0 ** -9, (mant - 1.0) * 8.0)
+    bits = (exp_field * 8.0 + man_field).to(torch.int64)
+    bits = torch.where(v == 0, torch.zeros_like(bits), bits)
+    bits = bits | (neg.to(torch.int64) << 7)
+    bits = torch.where(nan, torch.full_like(bits, 0x7F), bits)
+    return bits.to(torch.uint8)
+
+
+def e4m3_bits_to_float(b: torch.Tensor) -> torch.Tensor:
+    return b.contiguous().view(torch.float8_e4m3fn).to(torch.float32)
+
+
+def e2m1_rne_sat_codes(y: torch.Tensor) -> torch.Tensor:
+    """fp32 -> 4-bit e2m1 code (0..15), RNE, saturate to +-6, sign of zero kept.
+
+    Ties go to the code with an even mantissa bit: 0.25->0, 0.75->1, 1.25->1, 1.75->2,
+    2.5->2, 3.5->4, 5->4.  NaN -> 0x7 (what `cvt.rn.satfinite.e2m1x2.f32` returns).
+    """
+    y = y.to(torch.float32)
+    a = y.abs()
+    code = torch.zeros(y.shape, dtype=torch.uint8, device=y.device)
+    code = torch.where(a > 0.25, torch.full_like(code, 1), code)
+    code = torch.where(a >= 0.75, torch.full_like(code, 2), code)
+    code = torch.where(a > 1.25, torch.full_like(code, 3), code)
+    code = torch.where(a >= 1.75, torch.full_like(code, 4), code)
+    code = torch.where(a > 2.5, torch.full_like(code, 5), code)
+    code = torch.where(a >= 3.5, torch.full_like(code, 6), code)
+    code = torch.where(a > 5.0, torch.full_like(code, 7), code)
+    code = code | (torch.signbit(y).to(torch.uint8) << 3)
+    code = torch.where(torch.isnan(y), torch.full_like(code, 7), code)
+    return code
+
+
+def e2m1_codes_to_float(code: torch.Tensor) -> torch.Tensor:
+    lut = torch.tensor(E2M1_VALUES, dtype=torch.float32, device=code.device)
+    return lut[code.long()]
+
+
+def unpack_fp4(packed: torch.Tensor) -> torch.Tensor:
+    """[..., n] bytes -> [..., 2n] codes; element 2j is the LOW nibble of byte j
+    (test_linear_bench.py:39-49)."""
+    lo = packed & 0x0F
+    hi = (packed >> 4) & 0x0F
+    return torch.stack((lo, hi), dim=-1).reshape(*packed.shape[:-1], packed.shape[-1] * 2)
+
+
+def pack_fp4(codes: torch.Tensor) -> torch.Tensor:
+    c = codes.reshape(*codes.shape[:-1], codes.shape[-1] // 2, 2)
+    return (c[..., 0] | (c[..., 1] << 4)).to(torch.uint8)
+
+
+# ----------------------------------------------------------------------------------------
+# layout helpers
+# ----------------------------------------------------------------------------------------
+def _canonical(x: torch.Tensor, cross_dim: int, reduce_dim: int):
+    """Permute to [others..., cross, reduce] and flatten the others into one batch dim."""
+    nd = x.ndim
+    assert 2 <= nd <= 4
+    if cross_dim < 0:
+        cross_dim += nd
+    if reduce_dim < 0:
+        reduce_dim += nd
+    assert cross_dim != reduce_dim
+    others = [i for i in range(nd) if i not in (cross_dim, reduce_dim)]
+    lead = [x.shape[i] for i in others]
+    xp = x.permute(*others, cross_dim, reduce_dim).contiguous()
+    m, k = x.shape[cross_dim], x.shape[reduce_dim]
+    return xp.reshape(-1, m, k), lead, m, k
+
+
+def sf_ac4k_to_rows(sf: torch.Tensor, m: int, nblk: int) -> torch.Tensor:
+    """[KT, M16, 4] -> [m, nblk]: one scale per (row, 16-block) (test_linear_bench.py:7-12)."""
+    t = sf.permute(1, 0, 2)
+    return t.reshape(t.shape[0], -1)[:m, :nblk]
+
+
+def sf_rows_to_ac4k(rows: torch.Tensor, m16: int, kt: int) -> torch.Tensor:
+    """[m, nblk] (any 1-byte dtype) -> [KT, M16, 4], zero filled padding."""
+    m, nblk = rows.shape
+    full = torch.zeros((m16, kt * 4), dtype=rows.dtype, device=rows.device)
+    full[:m, :nblk] = rows
+    return full.reshape(m16, kt, 4).permute(1, 0, 2).contiguous()
+
+
+def sf_rows_to_tile128x4(rows: torch.Tensor, kt: int) -> torch.Tensor:
+    """[m, nblk] bytes -> [ceil(m/128), KT, 32, 4, 4]; byte (r, b) lands at
+    tile (r/128, b/4), offset (r%32)*16 + ((r%128)/32)*4 + b%4 (test/utils.py:15-23)."""
+    m, nblk = rows.shape
+    mt = ceil_div(m, 128)
+    full = torch.zeros((mt * 128, kt * 4), dtype=rows.dtype, device=rows.device)
+    full[:m, :nblk] = rows
+    t = full.reshape(mt, 4, 32, kt, 4)          # (mt, r/32, r%32, kt, b%4)
+    return t.permute(0, 3, 2, 1, 4).contiguous()  # (mt, kt, r%32, r/32, b%4)
+
+
+def sf_tile128x4_to_rows(sf: torch.Tensor, m: int, nblk: int) -> torch.Tensor:
+    mt, kt = sf.shape[0], sf.shape[1]
+    t = sf.permute(0, 3, 2, 1, 4).reshape(mt * 128, kt * 4)
+    return t[:m, :nblk]
+
+
+def permute_k_nvfp4(x: torch.Tensor) -> torch.Tensor:
+    """K permutation used for attention's V ("swizzle"): every 32 elements are viewed as
+    [4, 4, 2] and transposed to [4(b), 4(a), 2] (test_quantize_bench.py:60-64)."""
+    s = x.shape
+    return x.reshape(-1, 4, 4, 2).permute(0, 2, 1, 3).reshape(s)
+
+
+def permute_k_fp8(x: torch.Tensor) -> torch.Tensor:
+    """FP8 variant: every 16 elements viewed as [2, 4, 2] -> [4, 2, 2]
+    (test_quantize_bench.py:276-280)."""
+    s = x.shape
+    return x.reshape(-1, 2, 4, 2).permute(0, 2, 1, 3).reshape(s)
+
+
+# ----------------------------------------------------------------------------------------
+# NVFP4 quantiser
+# ----------------------------------------------------------------------------------------
+def global_scale_ref(x: torch.Tensor, max_scale: float = E2M1_MAX * E4M3_MAX) -> torch.Tensor:
+    """0-dim fp32: max|x| / max_scale (quant.py:49-59; test_quantize_bench.py:19-20)."""
+    amax = x.abs().amax().to(torch.float32) if x.numel() else torch.zeros((), device=x.device)
+    return amax / torch.tensor(max_scale, dtype=torch.float32, device=x.device)
+
+
+def quantize_nvfp4_ref(x: torch.Tensor, cross_dim: int = 0, reduce_dim: int = 1,
+                       global_scale: torch.Tensor | None = None, swizzle: bool = False,
+                       sf_layout: str = "ac4k", max_scale: float = E2M1_MAX * E4M3_MAX):
+    """bf16 -> (packed u8 [..., M, Kp/2], scales e4m3, global scale fp32 0-dim).
+
+    Arithmetic order (all fp32, round to nearest, no fused multiply-add):
+        alpha = 1 / g                       (0 when g == 0)
+        s     = alpha * (amax_block * fp32(1/6));  sf = e4m3_rne_sat(s)
+        r     = sf == 0 ? 0 : alpha * (1 / float(sf))
+        code  = e2m1_rne_sat(float(x) * r)
+    """
+    assert x.dtype == torch.bfloat16
+    g = global_scale_ref(x, max_scale) if global_scale is None else global_scale.to(torch.float32)
+    xb, lead, m, k = _canonical(x, cross_dim, reduce_dim)
+    kp = align_up(k, REDUCE_ALIGN)
+    nb = xb.shape[0]
+    xf = torch.zeros((nb, m, kp), dtype=torch.float32, device=x.device)
+    xf[:, :, :k] = xb.to(torch.float32)
+    if swizzle:
+        xf = permute_k_nvfp4(xf)
+    one = torch.ones((), dtype=torch.float32, device=x.device)
+    alpha = torch.where(g == 0, torch.zeros_like(g), one / g)
+    blocks = xf.reshape(nb, m, kp // BLOCK, BLOCK)
+    amax_b = blocks.abs().amax(dim=-1)
+    s = alpha * (amax_b * torch.tensor(ONE_SIXTH, dtype=torch.float32, device=x.device))
+    sf_bits = e4m3_rne_sat_bits(s)
+    sf_f = e4m3_bits_to_float(sf_bits)
+    r = torch.where(sf_f == 0, torch.zeros_like(sf_f), alpha * (one / sf_f))
+    codes = e2m1_rne_sat_codes(blocks * r.unsqueeze(-1)).reshape(nb, m, kp)
+    packed = pack_fp4(codes).reshape(*lead, m, kp // 2)
+    kt = kp // REDUCE_ALIGN
+    if sf_layout == "ac4k":
+        m16 = align_up(m, CROSS_ALIGN)
+        sf = torch.stack([sf_rows_to_ac4k(sf_bits[i], m16, kt) for i in range(nb)])
+        sf = sf.reshape(*lead, kt, m16, 4)
+    elif sf_layout == "128x4":
+        sf = torch.stack([sf_rows_to_tile128x4(sf_bits[i], kt) for i in range(nb)])
+        sf = sf.reshape(*lead, ceil_div(m, 128), kt, 32, 4, 4)
+    else:
+        raise ValueError(sf_layout)
+    return packed, sf.view(torch.float8_e4m3fn), g
+
+
+def dequantize_nvfp4_ref(packed: torch.Tensor, sf: torch.Tensor, g: torch.Tensor | None,
+                         sf_layout: str | None = None) -> torch.Tensor:
+    """2-D packed [rows, Kp/2] + scales -> fp32 [rows, Kp]; value = e2m1 * e4m3 (* g)
+    (test_linear_bench.py:53-67 with global_scale passed as 1/g there)."""
+    rows, kp2 = packed.shape
+    kp = kp2 * 2
+    if sf_layout is None:
+        sf_layout = "ac4k" if sf.dim() == 3 else "128x4"
+    sfb = sf.view(torch.uint8)
+    if sf_layout == "ac4k":
+        sr = sf_ac4k_to_rows(sfb, rows, kp // BLOCK)
+    else:
+        sr = sf_tile128x4_to_rows(sfb, rows, kp // BLOCK)
+    vals = e2m1_codes_to_float(unpack_fp4(packed)).reshape(rows, kp // BLOCK, BLOCK)
+    out = (vals * e4m3_bits_to_float(sr).unsqueeze(-1)).reshape(rows, kp)
+    if g is not None:
+        out = out * g.to(torch.float32)
+    return out
+
+
+def linear_nvfp4_ref(a, a_sf, a_g, b, b_sf, b_g, bias=None, out_dtype=torch.bfloat16,
+                     accum_dtype=torch.float32):
+    """out = cast(alpha * dequant(A) @ dequant(B)^T + bias), alpha = a_g * b_g in fp32
+    (linear_nvfp4.cu:586-633; test_linear_bench.py:70-107).  `accum_dtype=torch.float64`
+    gives the exact-accumulation variant used to bound kernel error."""
+    ad = dequantize_nvfp4_ref(a, a_sf, None).to(accum_dtype)
+    bd = dequantize_nvfp4_ref(b, b_sf, None).to(accum_dtype)
+    acc = ad @ bd.t()
+    alpha = (a_g.to(torch.float32) * b_g.to(torch.float32)).to(accum_dtype)
+    acc = acc * alpha
+    if bias is not None:
+        acc = acc + bias.reshape(1, -1).to(accum_dtype)
+    return acc.to(out_dtype)
+
+
+# ----------------------------------------------------------------------------------------
+# per-token FP8 / INT8 quantisers
+# ----------------------------------------------------------------------------------------
+def _rowwise_common(x, cross_dim, reduce_dim, scale_max: float, permute):
+    assert x.dtype == torch.bfloat16
+    xb, lead, m, k = _canonical(x, cross_dim, reduce_dim)
+    kp = align_up(k, 16)
+    m16 = align_up(m, CROSS_ALIGN)
+    nb = xb.shape[0]
+    xf = torch.zeros((nb, m, kp), dtype=torch.float32, device=x.device)
+    xf[:, :, :k] = xb.to(torch.float32)
+    if permute:
+        xf = permute_k_fp8(xf)
+    smax = torch.tensor(float(scale_max), dtype=torch.float32, device=x.device)
+    amax = xf.abs().amax(dim=-1)                           # [nb, m]
+    sf = torch.zeros((nb, m16), dtype=torch.float32, device=x.device)
+    sf[:, :m] = amax / smax                                # quantize_fp8.cu:124
+    recip = smax / amax                                    # quantize_fp8.cu:132 (inf for a zero row)
+    y = xf * recip.unsqueeze(-1)                           # 0 * inf = NaN, as in the reference
+    return y, sf.reshape(*lead, m16), lead, m, kp
+
+
+def quantize_fp8_ref(x, cross_dim=0, reduce_dim=1, scale_max: float = 448.0, swizzle=False):
+    """Per-row e4m3: returns (e4m3 [..., M, align16(K)], fp32 scales [..., align16(M)])."""
+    y, sf, lead, m, kp = _rowwise_common(x, cross_dim, reduce_dim, scale_max, swizzle)
+    # satfinite: +-448 clamp keeps the sign, NaN -> 0x7F
+    bits = e4m3_rne_sat_bits(y)
+    return bits.reshape(*lead, m, kp).view(torch.float8_e4m3fn), sf
+
+
+def quantize_int8_ref(x, cross_dim=0, reduce_dim=1, scale_max: int = 127):
+    """Per-row int8 with `cvt.rni.sat.s8.f32`: round half to even, clamp [-128, 127], NaN -> 0."""
+    y, sf, lead, m, kp = _rowwise_common(x, cross_dim, reduce_dim, float(int(scale_max)), False)
+    q = torch.round(y).clamp(-128, 127)
+    q = torch.where(torch.isnan(y), torch.zeros_like(q), q)
+    return q.to(torch.int8).reshape(*lead, m, kp), sf

@@ -1,0 +1,60 @@
+"""CPU test: the built library exports every symbol that include/ac4k_b200.h declares, and
+the Python mirror exposes the reference module's names.  No compute call is made."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "ac4k_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ac4k_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_exported():
+    from ac4k_kernel_b200 import _lib
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    syms = declared_symbols()
+    assert "ac4k_linear_nvfp4" in syms and "ac4k_quantize_nvfp4" in syms
+    for s in syms:
+        assert hasattr(lib, s), f"{s} declared in the header but not exported"
+    assert set(_lib.SIGNATURES) == set(syms)
+
+
+def test_module_mirrors_reference_names():
+    import ac4k_kernel_b200 as pkg
+    from ac4k_kernel_b200 import _cuda_ops
+    for name in ("mha_nvfp4_fwd", "mha_int8_x_fp8_fwd", "quantize_nvfp4", "quantize_fp8",
+                 "quantize_int8", "linear_nvfp4", "rope3d", "__arch__", "__backend__",
+                 "__arch_description__", "__version__"):
+        assert hasattr(_cuda_ops, name)
+    assert pkg.get_arch() == "sm100" and pkg.get_backend() == "cuda"
+    with pytest.raises(NotImplementedError):
+        _cuda_ops.rope3d()
+
+
+def test_argument_errors_without_gpu():
+    """Rejected arguments return negative codes before anything touches the device."""
+    from ac4k_kernel_b200._lib import LIB, last_error
+    shape = (ctypes.c_int64 * 4)(1, 1, 16, 64)
+    stride = (ctypes.c_int64 * 4)(0, 0, 64, 1)
+    assert LIB.ac4k_quantize_nvfp4(None, None, None, None, shape, stride, 0, 0, None) == -1
+    assert "NULL" in last_error()
+    assert LIB.ac4k_quantize_nvfp4(8, 8, 16, 16, shape, stride, 0, 7, None) == -4
+    assert LIB.ac4k_global_scale_bf16(None, -1, 1.0, 8, None) == -2
+    bad = (ctypes.c_int64 * 4)(1, 1, -3, 64)
+    assert LIB.ac4k_quantize_fp8(8, 8, 16, 16, bad, stride, 0, None) == -2
+
+
+def test_python_checks_mirror_reference():
+    import torch
+    from ac4k_kernel_b200 import _cuda_ops
+    x = torch.zeros((16, 64), dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        _cuda_ops.quantize_nvfp4(torch.zeros((16, 32), dtype=torch.uint8),
+                                 torch.zeros((1, 16, 4), dtype=torch.float8_e4m3fn), x,
+                                 torch.zeros(()), 0, 1, False)
