@@ -1,7 +1,508 @@
-// placeholder until the tcgen05 GEMM lands
+// NVFP4 block-scaled GEMM for sm_100a:  D[M,N] = cast((gA*gB) * A_fp4[M,K] * B_fp4[N,K]^T + bias).
+//
+// Stands in for ac4k_kernel's lib/cuda/sm120/linear_nvfp4.cu:337-901 (an mma.sync kernel that
+// does not assemble for sm_100a).  This one is a persistent, warp-specialised tcgen05 kernel:
+//
+//   warp 0   TMA producer: per K-step of 256 elements, one 128-byte-swizzled box of A
+//            (128 rows x 128 B), one of B (BN rows x 128 B) and the scale bytes of both,
+//            into a multi-stage shared-memory ring guarded by full/empty mbarriers
+//   warp 1   MMA issuer (one lane): copies the scale tiles shared -> tensor memory
+//            (tcgen05.cp.32x128b.warpx4), issues four K=64 tcgen05.mma
+//            kind::mxf4nvf4.block_scale per stage into a TMEM accumulator, and releases the
+//            stage / publishes the accumulator with tcgen05.commit
+//   warp 2   only for the reference's [K/64, rows16, 4] scale layout: turns each 128-word
+//            scale chunk into the 32 x 16-byte image that tcgen05.cp expects
+//   warps 3-6 epilogue: tcgen05.ld of the accumulator (one TMEM lane quarter per warp),
+//            * (gA*gB), + bias, convert, store
+//
+// Scale factors in tensor memory: the four e4m3 scales of row r for one K=64 step sit in lane
+// r % 32 (replicated in all four lane quarters), 32-bit column r / 32, so A (128 rows) takes 4
+// columns and B (BN rows) BN/32 columns per step.
+#include <cuda.h>
+
+#include <mutex>
+#include <vector>
+
 #include "common.cuh"
-extern "C" int ac4k_linear_nvfp4(void *, int, const void *, const void *, const float *, const void *,
-                                 const void *, const float *, const void *, int, int64_t, int64_t, int64_t,
-                                 int, ac4k_stream_t) {
-  return ac4k::fail(AC4K_ERR_UNSUPPORTED, "linear_nvfp4 not built yet");
+#include "sm100_ptx.cuh"
+
+namespace ac4k {
+using namespace ptx;
+
+static constexpr int BM = 128;        // rows of A per tile (= TMEM lanes)
+static constexpr int BKB = 128;       // bytes of packed K per stage (= 256 elements = 4 MMA K-steps)
+static constexpr int K64_PER_STAGE = 4;
+static constexpr int kNumThreads = 224;
+static constexpr int kTmemCols = 512;
+static constexpr int kGroupM = 8;     // tile rasterisation: walk 8 M-tiles per N-tile
+
+enum : unsigned { kStatusTimeoutProducer = 0xA1, kStatusTimeoutMma = 0xA2, kStatusTimeoutSf = 0xA3,
+                  kStatusTimeoutEpilogue = 0xA4 };
+
+template <int BN>
+struct Cfg {
+  static constexpr int A_BYTES = BM * BKB;
+  static constexpr int B_BYTES = BN * BKB;
+  static constexpr int SFA_BYTES = K64_PER_STAGE * 512;
+  static constexpr int SFB_BYTES = (BN / 128) * K64_PER_STAGE * 512;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr int STAGES = (BN == 128) ? 6 : 4;
+  static constexpr int ACC_STAGES = (BN == 128) ? 2 : 1;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 512 /*barriers*/;
+  // tensor-memory columns
+  static constexpr int SFA_COL = ACC_STAGES * BN;
+  static constexpr int SFA_COLS = K64_PER_STAGE * 4;
+  static constexpr int SFB_COL = SFA_COL + 2 * SFA_COLS;
+  static constexpr int SFB_COLS = K64_PER_STAGE * (BN / 32);
+  static_assert(SFB_COL + 2 * SFB_COLS <= kTmemCols, "tensor memory overflow");
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory overflow");
+};
+
+struct GemmArgs {
+  const uint8_t *sfa;
+  const uint8_t *sfb;
+  void *D;
+  const float *a_gs;
+  const float *b_gs;
+  const void *bias;
+  unsigned int *status;
+  int bias_dt;
+  int M, N, K;          // K in elements, multiple of 64
+  int KT;               // K / 64
+  int rows_sfa, rows_sfb;   // padded row counts of the scale tensors (16- or 128-aligned)
+  int tiles_m, tiles_n;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int &tm, int &tn) {
+  const int group = kGroupM * tiles_n;
+  const int g = t / group;
+  const int first_m = g * kGroupM;
+  const int gm = min(tiles_m - first_m, kGroupM);
+  const int r = t - g * group;
+  tm = first_m + r % gm;
+  tn = r / gm;
+}
+
+__device__ __forceinline__ float load_bias(const void *bias, int dt, int n) {
+  if (dt == AC4K_DT_BF16) return __bfloat162float(static_cast<const __nv_bfloat16 *>(bias)[n]);
+  if (dt == AC4K_DT_FP16) return __half2float(static_cast<const __half *>(bias)[n]);
+  return static_cast<const float *>(bias)[n];
+}
+
+template <int OUT_DT>
+struct OutT;
+template <> struct OutT<AC4K_DT_BF16> { using type = __nv_bfloat16; };
+template <> struct OutT<AC4K_DT_FP16> { using type = __half; };
+template <> struct OutT<AC4K_DT_FP32> { using type = float; };
+
+template <int OUT_DT>
+__device__ __forceinline__ void store_row32(void *D, int64_t off, const float (&v)[32], int ncols, bool vec_ok) {
+  using T = typename OutT<OUT_DT>::type;
+  T *dst = static_cast<T *>(D) + off;
+  if (vec_ok && ncols == 32) {
+    if (OUT_DT == AC4K_DT_FP32) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        reinterpret_cast<float4 *>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (OUT_DT == AC4K_DT_BF16) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+            w[j] = *reinterpret_cast<uint32_t *>(&h);
+          } else {
+            __half2 h = __floats2half2_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+            w[j] = *reinterpret_cast<uint32_t *>(&h);
+          }
+        }
+        reinterpret_cast<uint4 *>(dst)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+  } else {
+    for (int i = 0; i < ncols; ++i) {
+      if (OUT_DT == AC4K_DT_BF16) dst[i] = (T)__float2bfloat16_rn(v[i]);
+      else if (OUT_DT == AC4K_DT_FP16) dst[i] = (T)__float2half_rn(v[i]);
+      else dst[i] = (T)v[i];
+    }
+  }
+}
+
+template <int BN, bool SF_TILED, int OUT_DT>
+__global__ void __launch_bounds__(kNumThreads, 1)
+linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                    const GemmArgs p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sA = smem_base;
+  const uint32_t sB = sA + C::STAGES * C::A_BYTES;
+  const uint32_t sSFA = sB + C::STAGES * C::B_BYTES;
+  const uint32_t sSFB = sSFA + C::STAGES * C::SFA_BYTES;
+  const uint32_t bars = sSFB + C::STAGES * C::SFB_BYTES;
+  const uint32_t full_bar = bars, empty_bar = bars + 8 * C::STAGES, sf_bar = bars + 16 * C::STAGES;
+  const uint32_t tfull_bar = bars + 24 * C::STAGES, tempty_bar = tfull_bar + 8 * C::ACC_STAGES;
+  const uint32_t tmem_slot = tempty_bar + 8 * C::ACC_STAGES;
+  uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));   // generic pointer to smem_base
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int k_tiles = (p.KT + K64_PER_STAGE - 1) / K64_PER_STAGE;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(full_bar + 8 * s, 1);
+      mbar_init(empty_bar + 8 * s, 1);
+      mbar_init(sf_bar + 8 * s, 1);
+    }
+    for (int a = 0; a < C::ACC_STAGES; ++a) {
+      mbar_init(tfull_bar + 8 * a, 1);
+      mbar_init(tempty_bar + 8 * a, 4);
+    }
+    fence_barrier_init();
+    prefetch_tmap(&tma_a);
+    prefetch_tmap(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(smem_gen + (tmem_slot - smem_base));
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kt = 0; kt < k_tiles; ++kt) {
+          if (!mbar_wait(empty_bar + 8 * s, ph ^ 1)) { atomicExch(p.status, kStatusTimeoutProducer); ok = false; break; }
+          const int nk = min(K64_PER_STAGE, p.KT - kt * K64_PER_STAGE);
+          uint32_t sfa_bytes, sfb_bytes;
+          if (SF_TILED) {
+            sfa_bytes = nk * 512;
+            const int nb_valid = min(BN / 128, (p.rows_sfb - n0) / 128);
+            sfb_bytes = nb_valid * nk * 512;
+          } else {
+            sfa_bytes = nk * 4 * min(BM, p.rows_sfa - m0);
+            sfb_bytes = nk * 4 * min(BN, p.rows_sfb - n0);
+          }
+          const uint32_t fb = full_bar + 8 * s;
+          mbar_arrive_expect_tx(fb, C::A_BYTES + C::B_BYTES + sfa_bytes + sfb_bytes);
+          tma_load_2d(sA + s * C::A_BYTES, &tma_a, kt * BKB, m0, fb);
+          tma_load_2d(sB + s * C::B_BYTES, &tma_b, kt * BKB, n0, fb);
+          const int64_t k64 = (int64_t)kt * K64_PER_STAGE;
+          if (SF_TILED) {
+            // [row tile of 128][K/64][512 B]: the nk chunks of one row tile are contiguous
+            bulk_load_1d(sSFA + s * C::SFA_BYTES, p.sfa + ((int64_t)tm * p.KT + k64) * 512, nk * 512, fb);
+            for (int nb = 0; nb < BN / 128; ++nb) {
+              const int64_t nt = n0 / 128 + nb;
+              if (nt * 128 < p.rows_sfb)
+                bulk_load_1d(sSFB + s * C::SFB_BYTES + nb * (K64_PER_STAGE * 512),
+                             p.sfb + (nt * p.KT + k64) * 512, nk * 512, fb);
+            }
+          } else {
+            // [K/64][rows16][4 B]: one chunk of (rows x 4 B) per K=64 step
+            const uint32_t ra = 4 * min(BM, p.rows_sfa - m0), rb = 4 * min(BN, p.rows_sfb - n0);
+            for (int j = 0; j < nk; ++j) {
+              bulk_load_1d(sSFA + s * C::SFA_BYTES + j * 512, p.sfa + ((k64 + j) * p.rows_sfa + m0) * 4, ra, fb);
+              bulk_load_1d(sSFB + s * C::SFB_BYTES + j * (BN / 128) * 512,
+                           p.sfb + ((k64 + j) * p.rows_sfb + n0) * 4, rb, fb);
+            }
+          }
+          if (++s == C::STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_mxf4nvf4(BM, BN);
+      uint32_t s = 0, ph = 0, acc = 0, acc_ph = 0, sfbuf = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(tempty_bar + 8 * acc, acc_ph ^ 1)) { atomicExch(p.status, kStatusTimeoutMma); break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kt = 0; kt < k_tiles; ++kt) {
+          if (!mbar_wait(full_bar + 8 * s, ph) || (!SF_TILED && !mbar_wait(sf_bar + 8 * s, ph))) {
+            atomicExch(p.status, kStatusTimeoutMma); ok = false; break;
+          }
+          tc_fence_after();
+          const int nk = min(K64_PER_STAGE, p.KT - kt * K64_PER_STAGE);
+          const uint32_t t_sfa = tmem_base + C::SFA_COL + sfbuf * C::SFA_COLS;
+          const uint32_t t_sfb = tmem_base + C::SFB_COL + sfbuf * C::SFB_COLS;
+          for (int j = 0; j < nk; ++j) {
+            tmem_cp_32x128b_warpx4(t_sfa + j * 4,
+                                   make_smem_desc(sSFA + s * C::SFA_BYTES + j * 512, 0, 128, kSwizzleNone));
+#pragma unroll
+            for (int nb = 0; nb < BN / 128; ++nb) {
+              const uint32_t off = SF_TILED ? (nb * K64_PER_STAGE + j) * 512 : (j * (BN / 128) + nb) * 512;
+              tmem_cp_32x128b_warpx4(t_sfb + j * (BN / 32) + nb * 4,
+                                     make_smem_desc(sSFB + s * C::SFB_BYTES + off, 0, 128, kSwizzleNone));
+            }
+          }
+          const uint64_t adesc = make_smem_desc(sA + s * C::A_BYTES, 16, 1024, kSwizzle128B);
+          const uint64_t bdesc = make_smem_desc(sB + s * C::B_BYTES, 16, 1024, kSwizzle128B);
+          for (int j = 0; j < nk; ++j) {
+            // +32 bytes of K per step inside the 128-byte swizzle atom: start-address field += 2
+            mma_mxf4nvf4(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, t_sfa + j * 4, t_sfb + j * (BN / 32),
+                         (kt > 0 || j > 0) ? 1u : 0u);
+          }
+          tc_commit(empty_bar + 8 * s);
+          sfbuf ^= 1;
+          if (++s == C::STAGES) { s = 0; ph ^= 1; }
+        }
+        if (ok) tc_commit(tfull_bar + 8 * acc);
+        if (++acc == C::ACC_STAGES) { acc = 0; acc_ph ^= 1; }
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ scale re-layout
+    if (!SF_TILED) {
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        for (int kt = 0; kt < k_tiles; ++kt) {
+          if (!mbar_wait(full_bar + 8 * s, ph)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutSf); ok = false; break; }
+          const int nk = min(K64_PER_STAGE, p.KT - kt * K64_PER_STAGE);
+          // chunks of this stage: nk for A, nk * BN/128 for B, each 128 words: word r -> image
+          // word (r % 32) * 4 + r / 32
+          uint32_t *base_a = reinterpret_cast<uint32_t *>(smem_gen + (sSFA + s * C::SFA_BYTES - smem_base));
+          uint32_t *base_b = reinterpret_cast<uint32_t *>(smem_gen + (sSFB + s * C::SFB_BYTES - smem_base));
+          const int nchunks = nk * (1 + BN / 128);
+          for (int c = 0; c < nchunks; ++c) {
+            uint32_t *chunk = (c < nk) ? base_a + c * 128 : base_b + (c - nk) * 128;
+            uint4 v = make_uint4(chunk[lane], chunk[lane + 32], chunk[lane + 64], chunk[lane + 96]);
+            __syncwarp();
+            reinterpret_cast<uint4 *>(chunk)[lane] = v;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sf_bar + 8 * s);
+          if (++s == C::STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;                   // TMEM lane quarter this warp may read
+    uint32_t acc = 0, acc_ph = 0;
+    const float alpha = __fmul_rn(__ldg(p.a_gs), __ldg(p.b_gs));
+    const bool vec_ok = (OUT_DT == AC4K_DT_FP32) ? (p.N % 4 == 0) : (p.N % 8 == 0);
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      int tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      if (!mbar_wait(tfull_bar + 8 * acc, acc_ph)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue); break; }
+      tc_fence_after();
+      const int row = tm * BM + q * 32 + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c, r);
+        tmem_ld_wait();
+        const int col = tn * BN + c;
+        const int ncols = min(32, p.N - col);
+        if (row < p.M && ncols > 0) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __fmul_rn(__uint_as_float(r[i]), alpha);
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < ncols) v[i] = __fadd_rn(v[i], load_bias(p.bias, p.bias_dt, col + i));
+          }
+          store_row32<OUT_DT>(p.D, (int64_t)row * p.N + col, v, ncols, vec_ok);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar + 8 * acc);
+      if (++acc == C::ACC_STAGES) { acc = 0; acc_ph ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+struct TmapKey {
+  const void *ptr;
+  int64_t rows, row_bytes;
+  int box_rows, dev;
+  bool operator==(const TmapKey &o) const {
+    return ptr == o.ptr && rows == o.rows && row_bytes == o.row_bytes && box_rows == o.box_rows && dev == o.dev;
+  }
+};
+struct TmapEntry { TmapKey key; CUtensorMap map; };
+
+// Tensor maps depend only on (pointer, shape, box); encoding costs a driver call, so the last
+// few are kept.  The reference re-encodes five per call (linear_nvfp4.cu:842-886).
+static int get_tmap(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUtensorMap *out) {
+  static std::mutex mu;
+  static std::vector<TmapEntry> cache;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  TmapKey key{ptr, rows, row_bytes, box_rows, dev};
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    for (auto &e : cache)
+      if (e.key == key) { *out = e.map; return 0; }
+  }
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return fail(AC4K_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)row_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)BKB, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), gdim, gstride, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail((int)r > 0 ? (int)r : 999, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    if (cache.size() >= 64) cache.erase(cache.begin());
+    cache.push_back({key, m});
+  }
+  *out = m;
+  return 0;
+}
+
+struct DeviceInfo { int sms = 0; int cc_major = 0; bool ok = false; };
+static int get_device_info(DeviceInfo *out) {
+  static DeviceInfo info[64];
+  int dev = 0;
+  AC4K_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(AC4K_ERR_DEVICE, "device index %d out of range", dev);
+  if (!info[dev].ok) {
+    AC4K_CUDA_TRY(cudaDeviceGetAttribute(&info[dev].sms, cudaDevAttrMultiProcessorCount, dev));
+    AC4K_CUDA_TRY(cudaDeviceGetAttribute(&info[dev].cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+    info[dev].ok = true;
+  }
+  *out = info[dev];
+  return 0;
+}
+
+template <int BN, bool SF_TILED, int OUT_DT>
+static int launch(const CUtensorMap &ta, const CUtensorMap &tb, const GemmArgs &args, int sms, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  auto kern = linear_nvfp4_kernel<BN, SF_TILED, OUT_DT>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev]) {
+    AC4K_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    attr_set[dev] = true;
+  }
+  const int num_tiles = args.tiles_m * args.tiles_n;
+  const int grid = num_tiles < sms ? num_tiles : sms;
+  kern<<<grid, kNumThreads, C::SMEM_BYTES, stream>>>(ta, tb, args);
+  AC4K_LAUNCH_CHECK("linear_nvfp4_kernel");
+  return 0;
+}
+
+template <int BN, bool SF_TILED>
+static int launch_dt(int d_dtype, const CUtensorMap &ta, const CUtensorMap &tb, const GemmArgs &a, int sms,
+                     cudaStream_t st) {
+  switch (d_dtype) {
+    case AC4K_DT_BF16: return launch<BN, SF_TILED, AC4K_DT_BF16>(ta, tb, a, sms, st);
+    case AC4K_DT_FP16: return launch<BN, SF_TILED, AC4K_DT_FP16>(ta, tb, a, sms, st);
+    default: return launch<BN, SF_TILED, AC4K_DT_FP32>(ta, tb, a, sms, st);
+  }
+}
+
+}  // namespace ac4k
+
+using namespace ac4k;
+
+// Tile width override for experiments: 0 = automatic.
+static int g_force_bn = 0;
+extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_tile_n(int bn) { g_force_bn = bn; }
+
+extern "C" int ac4k_linear_nvfp4(void *D, int d_dtype, const void *A, const void *A_sf, const float *A_gs,
+                                 const void *B, const void *B_sf, const float *B_gs, const void *bias,
+                                 int bias_dtype, int64_t M, int64_t N, int64_t K, int sf_layout,
+                                 ac4k_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M < 0 || N < 0 || K < 0) return fail(AC4K_ERR_SHAPE, "negative dimension");
+  if (d_dtype < 0 || d_dtype > 2) return fail(AC4K_ERR_ENUM, "unknown d_dtype %d", d_dtype);
+  if (bias && (bias_dtype < 0 || bias_dtype > 2)) return fail(AC4K_ERR_ENUM, "unknown bias_dtype %d", bias_dtype);
+  if (sf_layout != AC4K_SF_AC4K && sf_layout != AC4K_SF_TILE128X4)
+    return fail(AC4K_ERR_ENUM, "unknown sf_layout %d", sf_layout);
+  if (M == 0 || N == 0) return 0;
+  if (!D || !A || !B || !A_sf || !B_sf || !A_gs || !B_gs) return fail(AC4K_ERR_NULL, "a required pointer is NULL");
+  if (K == 0 || K % 64 != 0)
+    return fail(AC4K_ERR_SHAPE, "K = %lld must be a positive multiple of 64 (the quantiser pads K to 64)", (long long)K);
+  if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return fail(AC4K_ERR_SHAPE, "dimension too large");
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
+      (reinterpret_cast<uintptr_t>(A_sf) & 15) || (reinterpret_cast<uintptr_t>(B_sf) & 15) ||
+      (reinterpret_cast<uintptr_t>(D) & 15))
+    return fail(AC4K_ERR_ALIGN, "A, B, A_sf, B_sf and D must be 16-byte aligned");
+  DeviceInfo di;
+  if (int e = get_device_info(&di)) return e;
+  if (di.cc_major != 10) return fail(AC4K_ERR_DEVICE, "linear_nvfp4 needs an sm_100 device (found sm_%d0)", di.cc_major);
+  unsigned int *status = device_status_ptr();
+  if (!status) return fail(AC4K_ERR_DEVICE, "cannot resolve the device status word");
+
+  int bn = g_force_bn ? g_force_bn : 128;
+  CUtensorMap ta, tb;
+  if (int e = get_tmap(A, M, K / 2, BM, &ta)) return e;
+  if (int e = get_tmap(B, N, K / 2, bn, &tb)) return e;
+
+  GemmArgs a;
+  a.sfa = static_cast<const uint8_t *>(A_sf);
+  a.sfb = static_cast<const uint8_t *>(B_sf);
+  a.D = D;
+  a.a_gs = A_gs;
+  a.b_gs = B_gs;
+  a.bias = bias;
+  a.status = status;
+  a.bias_dt = bias_dtype;
+  a.M = (int)M; a.N = (int)N; a.K = (int)K;
+  a.KT = (int)(K / 64);
+  const int pad = sf_layout == AC4K_SF_AC4K ? 16 : 128;
+  a.rows_sfa = (int)align_up(M, pad);
+  a.rows_sfb = (int)align_up(N, pad);
+  a.tiles_m = (int)ceil_div(M, BM);
+  a.tiles_n = (int)ceil_div(N, bn);
+  const bool tiled = sf_layout == AC4K_SF_TILE128X4;
+  if (bn == 256)
+    return tiled ? launch_dt<256, true>(d_dtype, ta, tb, a, di.sms, stream)
+                 : launch_dt<256, false>(d_dtype, ta, tb, a, di.sms, stream);
+  return tiled ? launch_dt<128, true>(d_dtype, ta, tb, a, di.sms, stream)
+               : launch_dt<128, false>(d_dtype, ta, tb, a, di.sms, stream);
 }
