@@ -6,13 +6,14 @@
 //   warp 0   TMA producer: per K-step of 256 elements, one 128-byte-swizzled box of A
 //            (128 rows x 128 B), one of B (BN rows x 128 B) and the scale bytes of both,
 //            into a multi-stage shared-memory ring guarded by full/empty mbarriers
-//   warp 1   MMA issuer (one lane): copies the scale tiles shared -> tensor memory
-//            (tcgen05.cp.32x128b.warpx4), issues four K=64 tcgen05.mma
-//            kind::mxf4nvf4.block_scale per stage into a TMEM accumulator, and releases the
-//            stage / publishes the accumulator with tcgen05.commit
-//   warp 2   only for the reference's [K/64, rows16, 4] scale layout: turns each 128-word
-//            scale chunk into the 32 x 16-byte image that tcgen05.cp expects
-//   warps 3-6 epilogue: tcgen05.ld of the accumulator (one TMEM lane quarter per warp),
+//   warp 1   MMA issuer (one lane): four K=64 tcgen05.mma kind::mxf4nvf4.block_scale per
+//            stage into a TMEM accumulator; releases the stage / publishes the accumulator
+//            with tcgen05.commit
+//   warps 2-5 scale warps: move the stage's scale bytes shared memory -> registers -> tensor
+//            memory with tcgen05.st, one TMEM lane quarter per warp.  (tcgen05.cp was measured
+//            at ~62 cycles per 512-byte copy, more than the MMAs it feeds; one tcgen05.st per
+//            operand and stage is far cheaper.)
+//   warps 6-9 epilogue: tcgen05.ld of the accumulator (one TMEM lane quarter per warp),
 //            * (gA*gB), + bias, convert, store
 //
 // Scale factors in tensor memory: the four e4m3 scales of row r for one K=64 step sit in lane
@@ -32,7 +33,7 @@ using namespace ptx;
 static constexpr int BM = 128;        // rows of A per tile (= TMEM lanes)
 static constexpr int BKB = 128;       // bytes of packed K per stage (= 256 elements = 4 MMA K-steps)
 static constexpr int K64_PER_STAGE = 4;
-static constexpr int kNumThreads = 224;
+static constexpr int kNumThreads = 320;
 static constexpr int kTmemCols = 512;
 static constexpr int kGroupM = 8;     // tile rasterisation: walk 8 M-tiles per N-tile
 
@@ -49,12 +50,12 @@ struct Cfg {
   static constexpr int STAGES = (BN == 128) ? 6 : 4;
   static constexpr int ACC_STAGES = (BN == 128) ? 2 : 1;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 512 /*barriers*/;
-  // tensor-memory columns
+  // tensor-memory columns: accumulators, then one scale buffer per shared-memory stage
   static constexpr int SFA_COL = ACC_STAGES * BN;
   static constexpr int SFA_COLS = K64_PER_STAGE * 4;
-  static constexpr int SFB_COL = SFA_COL + 2 * SFA_COLS;
+  static constexpr int SFB_COL = SFA_COL + STAGES * SFA_COLS;
   static constexpr int SFB_COLS = K64_PER_STAGE * (BN / 32);
-  static_assert(SFB_COL + 2 * SFB_COLS <= kTmemCols, "tensor memory overflow");
+  static_assert(SFB_COL + STAGES * SFB_COLS <= kTmemCols, "tensor memory overflow");
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory overflow");
 };
 
@@ -71,6 +72,7 @@ struct GemmArgs {
   int KT;               // K / 64
   int rows_sfa, rows_sfb;   // padded row counts of the scale tensors (16- or 128-aligned)
   int tiles_m, tiles_n;
+  int dbg;              // experiment switches, 0 in production
 };
 
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int &tm, int &tn) {
@@ -155,7 +157,7 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(full_bar + 8 * s, 1);
       mbar_init(empty_bar + 8 * s, 1);
-      mbar_init(sf_bar + 8 * s, 1);
+      mbar_init(sf_bar + 8 * s, 4);
     }
     for (int a = 0; a < C::ACC_STAGES; ++a) {
       mbar_init(tfull_bar + 8 * a, 1);
@@ -226,30 +228,20 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_mxf4nvf4(BM, BN);
-      uint32_t s = 0, ph = 0, acc = 0, acc_ph = 0, sfbuf = 0;
+      uint32_t s = 0, ph = 0, acc = 0, acc_ph = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         if (!mbar_wait(tempty_bar + 8 * acc, acc_ph ^ 1)) { atomicExch(p.status, kStatusTimeoutMma); break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kt = 0; kt < k_tiles; ++kt) {
-          if (!mbar_wait(full_bar + 8 * s, ph) || (!SF_TILED && !mbar_wait(sf_bar + 8 * s, ph))) {
+          if (!mbar_wait(full_bar + 8 * s, ph) || !mbar_wait(sf_bar + 8 * s, ph)) {
             atomicExch(p.status, kStatusTimeoutMma); ok = false; break;
           }
           tc_fence_after();
           const int nk = min(K64_PER_STAGE, p.KT - kt * K64_PER_STAGE);
-          const uint32_t t_sfa = tmem_base + C::SFA_COL + sfbuf * C::SFA_COLS;
-          const uint32_t t_sfb = tmem_base + C::SFB_COL + sfbuf * C::SFB_COLS;
-          for (int j = 0; j < nk; ++j) {
-            tmem_cp_32x128b_warpx4(t_sfa + j * 4,
-                                   make_smem_desc(sSFA + s * C::SFA_BYTES + j * 512, 0, 128, kSwizzleNone));
-#pragma unroll
-            for (int nb = 0; nb < BN / 128; ++nb) {
-              const uint32_t off = SF_TILED ? (nb * K64_PER_STAGE + j) * 512 : (j * (BN / 128) + nb) * 512;
-              tmem_cp_32x128b_warpx4(t_sfb + j * (BN / 32) + nb * 4,
-                                     make_smem_desc(sSFB + s * C::SFB_BYTES + off, 0, 128, kSwizzleNone));
-            }
-          }
+          const uint32_t t_sfa = tmem_base + C::SFA_COL + s * C::SFA_COLS;
+          const uint32_t t_sfb = tmem_base + C::SFB_COL + s * C::SFB_COLS;
           const uint64_t adesc = make_smem_desc(sA + s * C::A_BYTES, 16, 1024, kSwizzle128B);
           const uint64_t bdesc = make_smem_desc(sB + s * C::B_BYTES, 16, 1024, kSwizzle128B);
           for (int j = 0; j < nk; ++j) {
@@ -258,38 +250,64 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                          (kt > 0 || j > 0) ? 1u : 0u);
           }
           tc_commit(empty_bar + 8 * s);
-          sfbuf ^= 1;
           if (++s == C::STAGES) { s = 0; ph ^= 1; }
         }
         if (ok) tc_commit(tfull_bar + 8 * acc);
         if (++acc == C::ACC_STAGES) { acc = 0; acc_ph ^= 1; }
       }
     }
-  } else if (warp == 2) {
-    // ------------------------------------------------------------------ scale re-layout
-    if (!SF_TILED) {
-      uint32_t s = 0, ph = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        for (int kt = 0; kt < k_tiles; ++kt) {
-          if (!mbar_wait(full_bar + 8 * s, ph)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutSf); ok = false; break; }
-          const int nk = min(K64_PER_STAGE, p.KT - kt * K64_PER_STAGE);
-          // chunks of this stage: nk for A, nk * BN/128 for B, each 128 words: word r -> image
-          // word (r % 32) * 4 + r / 32
-          uint32_t *base_a = reinterpret_cast<uint32_t *>(smem_gen + (sSFA + s * C::SFA_BYTES - smem_base));
-          uint32_t *base_b = reinterpret_cast<uint32_t *>(smem_gen + (sSFB + s * C::SFB_BYTES - smem_base));
-          const int nchunks = nk * (1 + BN / 128);
-          for (int c = 0; c < nchunks; ++c) {
-            uint32_t *chunk = (c < nk) ? base_a + c * 128 : base_b + (c - nk) * 128;
-            uint4 v = make_uint4(chunk[lane], chunk[lane + 32], chunk[lane + 64], chunk[lane + 96]);
-            __syncwarp();
-            reinterpret_cast<uint4 *>(chunk)[lane] = v;
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ scale warps
+    // Lane l of the warp owning TMEM lane quarter q writes, for K-step j and row group g, the
+    // 32-bit word of row 32 g + l into column (j * groups + g) of lane 32 q + l; all four
+    // quarters hold the same words.
+    const int q = warp & 3;
+    uint32_t s = 0, ph = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int kt = 0; kt < k_tiles; ++kt) {
+        if (!mbar_wait(full_bar + 8 * s, ph)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutSf); ok = false; break; }
+        const uint8_t *a_src = smem_gen + (sSFA + s * C::SFA_BYTES - smem_base);
+        const uint8_t *b_src = smem_gen + (sSFB + s * C::SFB_BYTES - smem_base);
+        uint32_t ra[16];
+        uint32_t rb[C::SFB_COLS];
+        if (SF_TILED) {
+          // 512-byte tiles [32 lanes][4 groups] words: one 16-byte load per K-step
+#pragma unroll
+          for (int j = 0; j < K64_PER_STAGE; ++j) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(a_src + j * 512 + lane * 16);
+            ra[j * 4 + 0] = v.x; ra[j * 4 + 1] = v.y; ra[j * 4 + 2] = v.z; ra[j * 4 + 3] = v.w;
+#pragma unroll
+            for (int nb = 0; nb < BN / 128; ++nb) {
+              const uint4 w = *reinterpret_cast<const uint4 *>(b_src + (nb * K64_PER_STAGE + j) * 512 + lane * 16);
+              rb[j * (BN / 32) + nb * 4 + 0] = w.x; rb[j * (BN / 32) + nb * 4 + 1] = w.y;
+              rb[j * (BN / 32) + nb * 4 + 2] = w.z; rb[j * (BN / 32) + nb * 4 + 3] = w.w;
+            }
           }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(sf_bar + 8 * s);
-          if (++s == C::STAGES) { s = 0; ph ^= 1; }
+        } else {
+          // [K-step][row] words
+#pragma unroll
+          for (int j = 0; j < K64_PER_STAGE; ++j) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              ra[j * 4 + g] = reinterpret_cast<const uint32_t *>(a_src + j * 512)[g * 32 + lane];
+#pragma unroll
+            for (int g = 0; g < BN / 32; ++g)
+              rb[j * (BN / 32) + g] = reinterpret_cast<const uint32_t *>(b_src + j * (BN / 128) * 512)[g * 32 + lane];
+          }
         }
+        const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+        tmem_st_32x32b_x16(lane_base + C::SFA_COL + s * C::SFA_COLS, ra);
+        if constexpr (BN == 256) {
+          tmem_st_32x32b_x32(lane_base + C::SFB_COL + s * C::SFB_COLS, reinterpret_cast<uint32_t (&)[32]>(rb));
+        } else {
+          tmem_st_32x32b_x16(lane_base + C::SFB_COL + s * C::SFB_COLS, reinterpret_cast<uint32_t (&)[16]>(rb));
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sf_bar + 8 * s);
+        if (++s == C::STAGES) { s = 0; ph ^= 1; }
       }
     }
   } else {
@@ -312,7 +330,7 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         tmem_ld_wait();
         const int col = tn * BN + c;
         const int ncols = min(32, p.N - col);
-        if (row < p.M && ncols > 0) {
+        if (row < p.M && ncols > 0 && !(p.dbg & 8)) {
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __fmul_rn(__uint_as_float(r[i]), alpha);
@@ -451,6 +469,8 @@ using namespace ac4k;
 
 // Tile width override for experiments: 0 = automatic.
 static int g_force_bn = 0;
+static int g_dbg = 0;
+extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_flags(int f) { g_dbg = f; }
 extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_tile_n(int bn) { g_force_bn = bn; }
 
 extern "C" int ac4k_linear_nvfp4(void *D, int d_dtype, const void *A, const void *A_sf, const float *A_gs,
@@ -499,6 +519,7 @@ extern "C" int ac4k_linear_nvfp4(void *D, int d_dtype, const void *A, const void
   a.rows_sfb = (int)align_up(N, pad);
   a.tiles_m = (int)ceil_div(M, BM);
   a.tiles_n = (int)ceil_div(N, bn);
+  a.dbg = g_dbg;
   const bool tiled = sf_layout == AC4K_SF_TILE128X4;
   if (bn == 256)
     return tiled ? launch_dt<256, true>(d_dtype, ta, tb, a, di.sms, stream)

@@ -1,0 +1,228 @@
+"""GPU parity tests of the NVFP4 GEMM: CUDA path (through the C ABI, via the reference-shaped
+`quantize` / `linear` wrappers) vs the restatement in oracle/.
+
+Tolerance (stated by the target this build follows): relative L2 <= 2e-3 against
+cast(alpha * dequant(A) @ dequant(B)^T + bias), and per element at most 2 ulps of the output
+dtype.  The products of e2m1 values and e4m3 scales are exact in fp32, so the only error
+sources are the accumulation order and the final rounding; the oracle accumulates in fp64.
+Where an output suffers cancellation (|out| far below the magnitude of its partial sums) an
+ulp of the *result* is not a meaningful yardstick, so the per-element bound also allows
+2^-22 of sum_k |a_k b_k| (a few fp32 roundings of the largest partial sum).
+"""
+import os
+import random
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import emulation as emu
+from tests.helpers import bf16_from_bits, gaussian
+
+pytestmark = pytest.mark.gpu
+
+ULP_REL = {torch.bfloat16: 2.0 ** -7, torch.float16: 2.0 ** -10, torch.float32: 2.0 ** -23}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from ac4k_kernel_b200 import ops as o
+    return o
+
+
+def gemm_reference(a4, asf, ag, b4, bsf, bg, bias, out_dtype, device):
+    """fp64-accumulated oracle and the magnitude sum_k |a_k b_k| * alpha, on `device`."""
+    to = lambda t: t.to(device)
+    ad = emu.dequantize_nvfp4_ref(to(a4), to(asf), None).double()
+    bd = emu.dequantize_nvfp4_ref(to(b4), to(bsf), None).double()
+    alpha = (to(ag).float() * to(bg).float()).double()
+    acc = ad @ bd.t() * alpha
+    mag = ad.abs() @ bd.abs().t() * alpha
+    if bias is not None:
+        acc = acc + to(bias).reshape(1, -1).double()
+        mag = mag + to(bias).reshape(1, -1).double().abs()
+    return acc, mag
+
+
+def assert_gemm_close(out, acc64, mag64, out_dtype):
+    ref = acc64.to(out_dtype)
+    o = out.double()
+    r = ref.double()
+    assert not bool(torch.isnan(o).any()), "NaN in output"
+    rel = float((o - r).norm() / r.norm().clamp(min=1e-300))
+    assert rel <= 2e-3, f"relative L2 {rel}"
+    # ulp of the output dtype at |ref|
+    e = torch.frexp(r.abs().clamp(min=1e-300))[1] - 1
+    ulp = torch.ldexp(torch.ones_like(r), e) * ULP_REL[out_dtype]
+    tol = 2 * ulp + mag64 * 2.0 ** -22
+    bad = (o - r).abs() > tol
+    assert not bool(bad.any()), f"{int(bad.sum())} of {bad.numel()} elements off by more than 2 ulps"
+    return rel, float(((o - r).abs() / ulp).max())
+
+
+def run_case(ops, m, n, k, seed=0, layout="ac4k", bias_dtype=None, out_dtype=None, a=None, b=None,
+             oracle_device="cpu"):
+    a = gaussian((m, k), seed=seed) if a is None else a
+    b = gaussian((n, k), seed=seed + 1) if b is None else b
+    ad, bd = a.cuda(), b.cuda()
+    a4, asf, ag = ops.quantize(ad, 0, 1, sf_layout=layout)
+    b4, bsf, bg = ops.quantize(bd, 0, 1, sf_layout=layout)
+    bias = None
+    if bias_dtype is not None:
+        bias = gaussian((1, n), seed=seed + 2).to(bias_dtype).cuda()
+    out = None
+    if out_dtype is not None:
+        out = torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda")
+    res = ops.linear(a4, asf, ag, b4, bsf, bg, bias=bias, out=out)
+    torch.cuda.synchronize()
+    from ac4k_kernel_b200 import _lib
+    assert _lib.device_status() == 0
+    odt = torch.bfloat16 if out_dtype is None else out_dtype
+    assert res.dtype == odt and tuple(res.shape) == (m, n)
+    acc, mag = gemm_reference(a4, asf, ag, b4, bsf, bg, bias, odt, oracle_device)
+    return assert_gemm_close(res.to(oracle_device), acc, mag, odt)
+
+
+@pytest.mark.parametrize("layout", ["ac4k", "128x4"])
+def test_config1(ops, layout):
+    """BASELINE config 1: A [128,512], B [256,512], N(0,1), seed 0; operands bit-exact, GEMM in tolerance."""
+    g = torch.Generator().manual_seed(0)
+    A = torch.randn((128, 512), generator=g).bfloat16()
+    B = torch.randn((256, 512), generator=g).bfloat16()
+    a4, asf, ag = ops.quantize(A.cuda(), 0, 1, sf_layout=layout)
+    ra4, rasf, rag = emu.quantize_nvfp4_ref(A, sf_layout=layout)
+    assert torch.equal(a4.cpu(), ra4) and torch.equal(asf.view(torch.uint8).cpu(), rasf.view(torch.uint8))
+    assert torch.equal(ag.cpu(), rag)
+    run_case(ops, 128, 256, 512, layout=layout, a=A, b=B)
+
+
+# the reference's own shape list (test/test_linear_bench.py:167-177)
+REF_SHAPES = [(128, 128, 128), (10, 512, 512), (1024, 1024, 384), (130, 384, 256), (666, 768, 512),
+              (123, 321, 256), (10, 15, 512), (1, 4, 256), (64, 64, 128), (12, 23, 55)]
+
+
+@pytest.mark.parametrize("layout", ["ac4k", "128x4"])
+@pytest.mark.parametrize("shape", REF_SHAPES)
+def test_reference_shapes(ops, shape, layout):
+    run_case(ops, *shape, seed=9567, layout=layout)
+
+
+@pytest.mark.parametrize("m,n,k,odt,bdt", [
+    (12, 23, 5, torch.float32, None),
+    (1, 2, 50, torch.float16, torch.bfloat16), (1, 2, 50, torch.float16, torch.float16),
+    (2, 3, 51, torch.float16, torch.float32), (3, 2, 50, torch.bfloat16, torch.bfloat16),
+    (4, 2, 50, torch.bfloat16, torch.float16), (5, 3, 51, torch.bfloat16, torch.float32),
+    (1, 21, 50, torch.float32, torch.bfloat16), (1, 22, 50, torch.float32, torch.float16),
+    (2, 33, 51, torch.float32, torch.float32),
+    (200, 264, 320, torch.float16, torch.float32), (130, 136, 192, torch.float32, torch.bfloat16),
+])
+def test_bias_and_output_dtypes(ops, m, n, k, odt, bdt):
+    """test/test_linear_bench.py:178-205 plus two tile-crossing shapes."""
+    run_case(ops, m, n, k, seed=3, bias_dtype=bdt, out_dtype=odt)
+
+
+def test_random_shapes(ops):
+    """test/test_linear_bench.py:156-161: 20 random M, N, K in [2, 555]."""
+    rng = random.Random(9567)
+    for i in range(20):
+        m, n, k = rng.randint(2, 555), rng.randint(2, 555), rng.randint(2, 555)
+        run_case(ops, m, n, k, seed=100 + i, layout="ac4k" if i % 2 else "128x4")
+
+
+def test_bias_1d_and_default_output(ops):
+    a = gaussian((40, 128), seed=1).cuda()
+    b = gaussian((72, 128), seed=2).cuda()
+    bias = gaussian((72,), seed=3).cuda()
+    a4, asf, ag = ops.quantize(a, 0, 1)
+    b4, bsf, bg = ops.quantize(b, 0, 1)
+    out = ops.linear(a4, asf, ag, b4, bsf, bg, bias=bias)
+    acc, mag = gemm_reference(a4, asf, ag, b4, bsf, bg, bias.reshape(1, -1), torch.bfloat16, "cuda")
+    assert_gemm_close(out, acc, mag, torch.bfloat16)
+
+
+def test_golden_reference_emulation(ops, golden_dir):
+    """Outputs of the reference's get_torch_results (tests/golden/make_golden.py) vs the CUDA path,
+    at the reference's own tolerance (test_linear_bench.py:152)."""
+    z = np.load(os.path.join(golden_dir, "nvfp4_linear_reference_emulation.npz"))
+    for i in range(int(z["n_cases"])):
+        a = bf16_from_bits(z[f"l{i}_a"]).cuda()
+        b = bf16_from_bits(z[f"l{i}_b"]).cuda()
+        bias = None
+        if f"l{i}_bias" in z:
+            bias = torch.from_numpy(z[f"l{i}_bias"]).to(eval(str(z[f"l{i}_bias_dtype"]))).cuda()
+        odt = eval(str(z[f"l{i}_out_dtype"]))
+        a4, asf, ag = ops.quantize(a, 0, 1)
+        b4, bsf, bg = ops.quantize(b, 0, 1)
+        out = torch.empty((a.shape[0], b.shape[0]), dtype=odt, device="cuda")
+        ops.linear(a4, asf, ag, b4, bsf, bg, bias=bias, out=out)
+        ref = torch.from_numpy(z[f"l{i}_out"])
+        torch.testing.assert_close(out.float().cpu(), ref, atol=1e-2, rtol=1e-2)
+        assert float((out.float().cpu() - ref).norm() / ref.norm()) < 2e-3
+
+
+def test_argument_checks(ops):
+    a = gaussian((16, 64), seed=1).cuda()
+    a4, asf, ag = ops.quantize(a, 0, 1)
+    with pytest.raises(RuntimeError, match="B size"):
+        ops.linear(a4, asf, ag, a4[:, :16].contiguous(), asf, ag)
+    with pytest.raises(RuntimeError, match="bias shape"):
+        ops.linear(a4, asf, ag, a4, asf, ag, bias=torch.zeros((1, 5), device="cuda"))
+    with pytest.raises(RuntimeError, match="scalar"):
+        ops.linear(a4, asf, ag.reshape(1), a4, asf, ag)
+
+
+# ------------------------------------------------------------------ full-size configurations
+def _outlier_activations(shape, seed, frac, mul):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(shape, generator=g, device="cuda")
+    mask = torch.rand(shape, generator=g, device="cuda") < frac
+    return torch.where(mask, x * mul, x).bfloat16()
+
+
+def _weights(shape, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, generator=g, device="cuda") * 0.02).bfloat16()
+
+
+@pytest.mark.parametrize("layout", ["ac4k", "128x4"])
+def test_config2_full(ops, layout):
+    """BASELINE config 2: 4096^3, activations N(0,1) with 0.5% x30 outliers, weights N(0,0.02)."""
+    run_case(ops, 4096, 4096, 4096, layout=layout, oracle_device="cuda",
+             a=_outlier_activations((4096, 4096), 0, 0.005, 30.0), b=_weights((4096, 4096), 1))
+
+
+@pytest.mark.parametrize("m", [1, 16, 64])
+def test_config3_decode_shapes(ops, m):
+    """BASELINE config 3: M in {1,16,64}, K = N = 8192."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn((m, 8192), generator=g, device="cuda").bfloat16()
+    run_case(ops, m, 8192, 8192, layout="128x4", oracle_device="cuda", a=x, b=_weights((8192, 8192), 1))
+
+
+def test_reference_8192_cube(ops):
+    """test/test_linear_bench.py:174."""
+    g = torch.Generator(device="cuda").manual_seed(9567)
+    a = torch.randn((8192, 8192), generator=g, device="cuda").bfloat16()
+    b = torch.randn((8192, 8192), generator=g, device="cuda").bfloat16()
+    run_case(ops, 8192, 8192, 8192, oracle_device="cuda", a=a, b=b)
+
+
+def test_config5_single_gpu_linearity(ops):
+    """BASELINE config 5 at full size on one GPU: M=8192, K=8192, N=28672.  Besides the
+    tolerance check, the column-parallel property the multi-GPU variant relies on: computing
+    any N-shard alone gives bit-identical columns."""
+    a = _outlier_activations((8192, 8192), 0, 0.005, 30.0)
+    w = _weights((28672, 8192), 1)
+    a4, asf, ag = ops.quantize(a, 0, 1, sf_layout="128x4")
+    w4, wsf, wg = ops.quantize(w, 0, 1, sf_layout="128x4")
+    out = ops.linear(a4, asf, ag, w4, wsf, wg)
+    acc, mag = gemm_reference(a4, asf, ag, w4, wsf, wg, None, torch.bfloat16, "cuda")
+    assert_gemm_close(out, acc, mag, torch.bfloat16)
+    del acc, mag
+    for world in (2, 8):
+        ns = 28672 // world
+        r = world - 1
+        shard = ops.linear(a4, asf, ag, w4[r * ns:(r + 1) * ns], wsf[r * ns // 128:(r + 1) * ns // 128], wg)
+        assert torch.equal(shard, out[:, r * ns:(r + 1) * ns])
+    out2 = ops.linear(a4, asf, ag, w4, wsf, wg)
+    assert torch.equal(out, out2)
