@@ -1,0 +1,83 @@
+"""Column-parallel NVFP4 linear over the GPUs of one node (one process per GPU).
+
+The reference has no multi-GPU code; this module defines the variant the B200 build adds:
+the weight [N, K] is split by rows (output columns) over the ranks, activations are
+replicated, every rank computes D[:, r*N/w : (r+1)*N/w] with the single-GPU kernel and the
+bf16 outputs are all-gathered over NVLink with NCCL.  For the result to equal the single-GPU
+result bit for bit, every shard must be quantised with the global scale of the WHOLE weight:
+the per-shard amax scales are combined with one all-reduce(max) of a single float (exact and
+order independent).
+
+Only the collective plumbing lives here; it works with any torch.distributed backend, which is
+how the CPU tests exercise it (gloo, world size 2).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(n: int, rank: int, world: int, align: int = 128):
+    """Rows [lo, hi) of the weight owned by `rank`.  N must split into `world` equal parts that
+    are multiples of `align` (128 keeps every shard on whole 128-row scale tiles)."""
+    if n % world != 0 or (n // world) % align != 0:
+        raise ValueError(f"N={n} does not split into {world} shards of a multiple of {align} rows")
+    per = n // world
+    return rank * per, (rank + 1) * per
+
+
+def allreduce_max_scale(local_scale: torch.Tensor, group=None) -> torch.Tensor:
+    """max over ranks of a 0-dim fp32 scale, in place.  amax/max_scale is monotonic in amax, so
+    the max of the per-shard global scales is the global scale of the whole tensor."""
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(local_scale, op=dist.ReduceOp.MAX, group=group)
+    return local_scale
+
+
+def quantize_weight_shard(w_shard: torch.Tensor, group=None, sf_layout: str = "128x4"):
+    """Quantise this rank's rows of the weight with the whole-tensor global scale.
+    Returns (packed, scales, global_scale) like `ops.quantize`."""
+    from .ops.quant import _global_scale, quantize_nvfp4, FLOAT4_E2M1_MAX, FLOAT8_E4M3_MAX
+    from .ops.utils import align_up, ceil_div
+    g = _global_scale(w_shard, FLOAT4_E2M1_MAX * FLOAT8_E4M3_MAX)
+    allreduce_max_scale(g, group)
+    n, k = w_shard.shape
+    kp = align_up(k, 64)
+    out = torch.empty((n, kp // 2), dtype=torch.uint8, device=w_shard.device)
+    if sf_layout == "ac4k":
+        sf_shape = (kp // 64, align_up(n, 16), 4)
+    else:
+        sf_shape = (ceil_div(n, 128), kp // 64, 32, 4, 4)
+    sf = torch.empty(sf_shape, dtype=torch.float8_e4m3fn, device=w_shard.device)
+    quantize_nvfp4(out, sf, w_shard, g, 0, 1, False)
+    return out, sf, g
+
+
+def gather_columns(local_out: torch.Tensor, gathered: torch.Tensor | None = None, group=None):
+    """All-gather the [M, N/w] outputs of all ranks into a [w, M, N/w] tensor (rank-major slabs,
+    the layout NCCL writes without an extra pass).  `columns_view` gives the [M, N] ordering."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    m, ns = local_out.shape
+    if gathered is None:
+        gathered = torch.empty((world, m, ns), dtype=local_out.dtype, device=local_out.device)
+    if world == 1:
+        gathered[0].copy_(local_out)
+    else:
+        dist.all_gather_into_tensor(gathered.view(world * m, ns), local_out.contiguous(), group=group)
+    return gathered
+
+
+def columns_view(gathered: torch.Tensor) -> torch.Tensor:
+    """[w, M, N/w] -> [M, N] (a strided view; call .contiguous() for row-major memory)."""
+    w, m, ns = gathered.shape
+    return gathered.permute(1, 0, 2).reshape(m, w * ns)
+
+
+def column_parallel_linear(x, x_scale, x_global_scale, w_shard, w_shard_scale, w_global_scale,
+                           bias_shard=None, local_out=None, gathered=None, group=None):
+    """One step of the column-parallel layer: local NVFP4 GEMM on this rank's shard, then the
+    all-gather of the bf16 output.  Returns (gathered [w, M, N/w], local_out)."""
+    from .ops.linear import linear
+    local_out = linear(x, x_scale, x_global_scale, w_shard, w_shard_scale, w_global_scale,
+                       bias=bias_shard, out=local_out)
+    return gather_columns(local_out, gathered, group), local_out

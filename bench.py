@@ -1,0 +1,465 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 linear path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload ...]
+
+N = 1 (default): the square single-GPU GEMM the headline metric is quoted on (M = N = K = 4096,
+activations N(0,1) with 0.5 % x30 outliers, weights N(0,0.02), both quantised to NVFP4).  One
+step = one `linear()` call on operands already resident in HBM; `value` is 2*M*N*K / step time
+in TFLOP/s.  The same run also measures the quantiser bandwidth on bf16 [32768, 8192], the
+end-to-end number (host buffers -> H2D -> quantize -> linear -> D2H) and the CPU emulation.
+
+N > 1 (launched with torchrun): the column-parallel MLP up/gate GEMM (M = 8192, K = 8192,
+N = 28672 split over the ranks) followed by the NCCL all-gather of the bf16 output; total work
+is fixed, so "scaling" is "strong".
+
+`--impl reference` times the reference's CPU-runnable form of this path (the torch emulation its
+own tests use as the oracle: dequantise -> fp32 matmul -> cast) on the host cores.
+
+Rank 0 prints exactly one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+L2_BYTES = 126 * 1024 * 1024
+NOMINAL_FP4_TFLOPS = 9000.0     # dense FP4, vendor figure
+NOMINAL_HBM_GBS = 8000.0
+METRIC = "NVFP4 GEMM TFLOP/s at 4096^3 (% of FP4 peak); quantize HBM GB/s (% of 8 TB/s)"
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------------------------------
+# clock sampling through NVML while the timed region runs
+# ------------------------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, index: int):
+        self.samples = []
+        self.stop = threading.Event()
+        self.thread = None
+        self.max_mhz = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(vis.split(",")[index]) if vis and vis.split(",")[index].isdigit() else index
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        while not self.stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                try:
+                    reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.samples.append((time.perf_counter(), mhz, reasons))
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self.thread = threading.Thread(target=self._run, daemon=True)
+            self.thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self.stop.set()
+        if self.thread is not None:
+            self.thread.join()
+
+    def summary(self, t0=None, t1=None):
+        if self.nv is None or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0,
+                    "note": "NVML unavailable"}
+        window = "timed"
+        sel = [s for s in self.samples if t0 is not None and t0 <= s[0] <= t1]
+        if len(sel) < 3:
+            sel, window = self.samples, "warmup+timed"
+        mhz = sorted(s[1] for s in sel)
+        bits = 0
+        for s in sel:
+            bits |= s[2]
+        reasons = [name for bit, name in self.REASONS.items() if bits & bit]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                "samples": len(sel), "window": window}
+
+
+# ------------------------------------------------------------------------------------------
+# synthetic inputs
+# ------------------------------------------------------------------------------------------
+def activations(shape, seed, frac, mul, device):
+    g = torch.Generator(device=device).manual_seed(seed)
+    x = torch.randn(shape, generator=g, device=device)
+    if frac > 0:
+        mask = torch.rand(shape, generator=g, device=device) < frac
+        x = torch.where(mask, x * mul, x)
+    return x.bfloat16()
+
+
+def weights(shape, seed, device):
+    g = torch.Generator(device=device).manual_seed(seed)
+    return (torch.randn(shape, generator=g, device=device) * 0.02).bfloat16()
+
+
+def time_graph(fn_step, n_sets, steps, warmup, barrier=None):
+    """Capture `steps` calls of fn_step(i % n_sets) in a CUDA graph and time one replay with
+    events (launch overhead of the Python wrapper would otherwise dominate 20-microsecond
+    kernels).  Returns (seconds for the K steps, host t0, host t1)."""
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for i in range(max(warmup, 3)):
+            fn_step(i % n_sets)
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        for i in range(steps):
+            fn_step(i % n_sets)
+    graph.replay()                      # one untimed replay: graph upload, caches
+    torch.cuda.synchronize()
+    if barrier is not None:
+        barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    return e0.elapsed_time(e1) * 1e-3, t0, t1
+
+
+def time_eager(fn, reps, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e-3 / reps
+
+
+# ------------------------------------------------------------------------------------------
+# CPU emulation (the reference's CPU-runnable form of the path)
+# ------------------------------------------------------------------------------------------
+def cpu_emulation_c2(budget_s=15.0, reps=None):
+    """dequantise -> fp32 matmul -> bf16 on a row sample of the 4096^3 workload, all host threads.
+    Returns (TFLOP/s, cores, sample description, seconds per rep, reps)."""
+    from oracle import emulation as emu
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    n = k = 4096
+    g = torch.Generator().manual_seed(0)
+    w = (torch.randn((n, k), generator=g) * 0.02).bfloat16()
+    w4, wsf, wg = emu.quantize_nvfp4_ref(w)
+    rows = 256
+    a = torch.randn((rows, k), generator=g).bfloat16()
+    a4, asf, ag = emu.quantize_nvfp4_ref(a)
+    t = time.perf_counter()
+    emu.linear_nvfp4_ref(a4, asf, ag, w4, wsf, wg)
+    first = time.perf_counter() - t
+    if reps is None:
+        reps = max(1, min(10, int(budget_s / max(first, 1e-3))))
+    t = time.perf_counter()
+    for _ in range(reps):
+        emu.linear_nvfp4_ref(a4, asf, ag, w4, wsf, wg)
+    dt = (time.perf_counter() - t) / reps
+    tflops = 2.0 * rows * n * k / dt / 1e12
+    sample = f"{rows} of 4096 activation rows x full 4096x4096 weight, dequantise + fp32 matmul + cast, {reps} reps"
+    return tflops, cores, sample, dt, reps
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, args.steps)
+    from oracle import emulation as emu
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    n = k = 4096
+    rows = 256
+    g = torch.Generator().manual_seed(0)
+    w = (torch.randn((n, k), generator=g) * 0.02).bfloat16()
+    w4, wsf, wg = emu.quantize_nvfp4_ref(w)
+    a = torch.randn((rows, k), generator=g).bfloat16()
+    a4, asf, ag = emu.quantize_nvfp4_ref(a)
+    for _ in range(min(args.warmup, 2)):
+        emu.linear_nvfp4_ref(a4, asf, ag, w4, wsf, wg)
+    t = time.perf_counter()
+    done = 0
+    for _ in range(steps):
+        emu.linear_nvfp4_ref(a4, asf, ag, w4, wsf, wg)
+        done += 1
+        if time.perf_counter() - t > 150:
+            break
+    dt = (time.perf_counter() - t) / done
+    tflops = 2.0 * rows * n * k / dt / 1e12
+    sample = (f"each step = {rows} of 4096 activation rows x full 4096x4096 weight through the torch "
+              f"emulation (dequantise, fp32 matmul, bf16 cast); {done} steps timed")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": done, "warmup": min(args.warmup, 2), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3 block scales, fp32 accumulate)",
+        "data": "synthetic",
+        "config": {"workload": "single-GPU square NVFP4 GEMM M=N=K=4096 (row sample on CPU)"},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference's GEMM kernel is sm_120a-only and cannot run on a B200; its CPU-runnable "
+                "form is the torch emulation from its tests, restated in oracle/emulation.py",
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------
+def quantize_bandwidth(peaks):
+    """BASELINE config 4: bf16 [32768, 8192] with 1 % x50 outliers."""
+    from ac4k_kernel_b200 import _cuda_ops, ops
+    from ac4k_kernel_b200.ops.quant import _global_scale
+    m, k = 32768, 8192
+    x = activations((m, k), 0, 0.01, 50.0, "cuda")
+    g = _global_scale(x, 2688.0)
+    out = torch.empty((m, k // 2), dtype=torch.uint8, device="cuda")
+    res = {}
+    for name, shape in (("ac4k", (k // 64, m, 4)), ("128x4", (m // 128, k // 64, 32, 4, 4))):
+        sf = torch.empty(shape, dtype=torch.float8_e4m3fn, device="cuda")
+        t = time_eager(lambda: _cuda_ops.quantize_nvfp4(out, sf, x, g, 0, 1, False), 20)
+        res[f"nvfp4_{name}_gbs"] = m * k * 2.5625 / t / 1e9
+    t = time_eager(lambda: _global_scale(x, 2688.0), 20)
+    res["global_scale_gbs"] = m * k * 2 / t / 1e9
+    t = time_eager(lambda: ops.quantize(x, 0, 1), 10)
+    res["quantize_call_us"] = t * 1e6
+    for prec in ("fp8e4m3", "int8"):
+        t = time_eager(lambda: ops.quantize(x, 0, 1, precision=prec), 10)
+        res[f"{prec}_gbs"] = (m * k * 3 + m * 4) / t / 1e9
+    best = max(res["nvfp4_ac4k_gbs"], res["nvfp4_128x4_gbs"])
+    res["nvfp4_frac_of_8tbs"] = best / NOMINAL_HBM_GBS
+    res["nvfp4_frac_of_measured_copy"] = best / peaks["hbm_gbs"]
+    res["workload"] = "bf16 [32768, 8192] N(0,1) with 1% x50 outliers; 688 MB per launch (larger than L2)"
+    return res
+
+
+def run_single(args, peaks):
+    from ac4k_kernel_b200 import _cuda_ops, ops
+    torch.cuda.set_device(0)
+    m = n = k = 4096
+    flops = 2.0 * m * n * k
+    a = activations((m, k), 0, 0.005, 30.0, "cuda")
+    w = weights((n, k), 1, "cuda")
+    set_bytes = m * k // 2 + n * k // 2 + (m + n) * k // 16 + m * n * 2
+    n_sets = 2 * L2_BYTES // set_bytes + 1          # rotate operand sets: > 2 x L2 in total
+    sets = {}
+    for layout in ("128x4", "ac4k"):
+        a4, asf, ag = ops.quantize(a, 0, 1, sf_layout=layout)
+        w4, wsf, wg = ops.quantize(w, 0, 1, sf_layout=layout)
+        sets[layout] = [(a4.clone(), asf.clone(), ag, w4.clone(), wsf.clone(), wg,
+                         torch.empty((m, n), dtype=torch.bfloat16, device="cuda")) for _ in range(n_sets)]
+
+    def step(layout):
+        def f(i):
+            a4, asf, ag, w4, wsf, wg, out = sets[layout][i]
+            _cuda_ops.linear_nvfp4(out, a4, asf, ag, w4, wsf, wg, None)
+        return f
+
+    with ClockSampler(0) as clk:
+        secs, t0, t1 = time_graph(step("128x4"), n_sets, args.steps, args.warmup)
+    clocks = clk.summary(t0, t1)
+    secs_ac4k, _, _ = time_graph(step("ac4k"), n_sets, args.steps, args.warmup)
+    ms_per_step = secs / args.steps * 1e3
+    value = flops / (secs / args.steps) / 1e12
+    del sets["ac4k"]
+
+    # end to end through the public API with host buffers: H2D of the step's activations,
+    # quantize (global scale + quantiser), linear against resident NVFP4 weights, D2H of the result
+    a_host = a.cpu().pin_memory()
+    out_host = torch.empty((m, n), dtype=torch.bfloat16).pin_memory()
+    a_dev = torch.empty_like(a)
+    _, _, _, w4, wsf, wg, out_dev = sets["128x4"][0]
+
+    def e2e_step():
+        a_dev.copy_(a_host, non_blocking=True)
+        a4, asf, ag = ops.quantize(a_dev, 0, 1, sf_layout="128x4")
+        ops.linear(a4, asf, ag, w4, wsf, wg, out=out_dev)
+        out_host.copy_(out_dev, non_blocking=True)
+
+    e2e_reps = max(5, min(args.steps, 50))
+    t_e2e = time_eager(e2e_step, e2e_reps)
+    e2e = {"value": flops / t_e2e / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": a_host.numel() * 2,
+           "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": t_e2e * 1e3,
+           "path": "pinned host bf16 activations -> H2D -> quantize() -> linear() vs resident NVFP4 weights -> D2H of bf16 output"}
+    del sets, a_host, out_host
+
+    quant = quantize_bandwidth(peaks)
+    cpu_tflops, cores, sample, _, _ = cpu_emulation_c2()
+
+    fp4_proxy_peak = 4.0 * peaks["bf16_tflops"]
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3 block scales, fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": "single-GPU square NVFP4 GEMM M=N=K=4096, activations N(0,1) + 0.5% x30 outliers, "
+                               "weights N(0,0.02), 128x4 scale tiles, bf16 out, alpha = gA*gB",
+                   "l2": f"{n_sets} operand/output sets rotated ({n_sets * set_bytes >> 20} MiB > 2 x L2)",
+                   "timing": "K steps captured in one CUDA graph, CUDA events around the replay"},
+        "frac_of_nominal_fp4_peak": value / NOMINAL_FP4_TFLOPS,
+        "value_reference_scale_layout": flops / (secs_ac4k / args.steps) / 1e12,
+        "roofline": {"bound": "tensor", "achieved": value, "peak": fp4_proxy_peak, "unit": "TFLOP/s",
+                     "frac": value / fp4_proxy_peak,
+                     "traffic": None,
+                     "peak_note": f"4 x {peaks['source']} bf16 burst ({peaks['bf16_tflops']} TFLOP/s): no FP4 figure is "
+                                  "measured on this pool; nominal dense FP4 is 9000 TFLOP/s",
+                     "algorithmic_flops_per_launch": flops},
+        "quantize": quant,
+        "cpu_baseline": {"value": cpu_tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": e2e,
+        "clocks": clocks,
+        "gpu_launches": args.steps,
+    }
+    print(json.dumps(line))
+
+
+def run_multi(args, peaks):
+    import torch.distributed as dist
+    from ac4k_kernel_b200 import ops, parallel, _cuda_ops
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    m, k, n = 8192, 8192, 28672
+    flops = 2.0 * m * n * k
+    lo, hi = parallel.shard_bounds(n, rank, world)
+    ns = hi - lo
+    a = activations((m, k), 0, 0.005, 30.0, "cuda")          # replicated: same seed on every rank
+    # this rank's rows of the weight, drawn from a per-shard seed (the full matrix is never built)
+    w_shard = weights((ns, k), 1000 + rank, "cuda")
+    a4, asf, ag = ops.quantize(a, 0, 1, sf_layout="128x4")
+    w4, wsf, wg = parallel.quantize_weight_shard(w_shard, None, "128x4")
+    del a, w_shard
+    set_bytes = ns * k // 2 + ns * k // 16 + m * ns * 2
+    n_sets = max(2, 2 * L2_BYTES // set_bytes + 1)
+    wsets = [(w4.clone(), wsf.clone(), torch.empty((m, ns), dtype=torch.bfloat16, device="cuda"))
+             for _ in range(n_sets)]
+    gathered = torch.empty((world, m, ns), dtype=torch.bfloat16, device="cuda")
+
+    def gemm_only(i):
+        wq, ws, out = wsets[i]
+        _cuda_ops.linear_nvfp4(out, a4, asf, ag, wq, ws, wg, None)
+
+    def full_step(i):
+        wq, ws, out = wsets[i]
+        _cuda_ops.linear_nvfp4(out, a4, asf, ag, wq, ws, wg, None)
+        dist.all_gather_into_tensor(gathered.view(world * m, ns), out)
+
+    def barrier():
+        dist.barrier()
+
+    # GEMM alone (graph), then GEMM + all-gather (eager: NCCL collectives are enqueued directly)
+    secs_gemm, _, _ = time_graph(gemm_only, n_sets, args.steps, args.warmup, barrier)
+    for i in range(max(args.warmup, 3)):
+        full_step(i % n_sets)
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    with ClockSampler(local) as clk:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for i in range(args.steps):
+            full_step(i % n_sets)
+        e1.record()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+    secs = e0.elapsed_time(e1) * 1e-3
+    t = torch.tensor([secs, secs_gemm], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    secs, secs_gemm = float(t[0]), float(t[1])
+    dist.barrier()
+    if rank == 0:
+        value = flops / (secs / args.steps) / 1e12
+        gemm_tflops = flops / (secs_gemm / args.steps) / 1e12
+        recv_bytes = (world - 1) * m * ns * 2
+        gather_s = max(secs - secs_gemm, 1e-9) / args.steps
+        fp4_proxy_peak = 4.0 * peaks["bf16_tflops"] * world
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None,
+            "dtype": "nvfp4 (e2m1 x ue4m3 block scales, fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": f"column-parallel NVFP4 GEMM M=8192 K=8192 N=28672 over {world} GPUs "
+                                   f"(N/{world} = {ns} columns per rank) + NCCL all-gather of the bf16 output",
+                       "l2": f"{n_sets} weight/output sets rotated per rank",
+                       "timing": "CUDA events on each rank, max over ranks"},
+            "gemm_only_tflops": gemm_tflops,
+            "gemm_only_per_gpu_frac_of_nominal_fp4": gemm_tflops / world / NOMINAL_FP4_TFLOPS,
+            "all_gather": {"recv_bytes_per_gpu": recv_bytes, "exposed_ms": gather_s * 1e3,
+                           "recv_gbs_per_gpu": recv_bytes / gather_s / 1e9},
+            "roofline": {"bound": "tensor", "achieved": gemm_tflops, "peak": fp4_proxy_peak, "unit": "TFLOP/s",
+                         "frac": gemm_tflops / fp4_proxy_peak, "traffic": None,
+                         "peak_note": f"{world} x 4 x {peaks['source']} bf16 burst; GEMM-only"},
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                    "note": "activations and weights are layer-resident in this variant; see the 1-GPU line for host copies"},
+            "clocks": clk.summary(t0, t1),
+            "gpu_launches": args.steps,
+        }
+        print(json.dumps(line))
+    dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback "
+                         "(use --impl reference for the CPU emulation)")
+    peaks = load_peaks()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        run_multi(args, peaks)
+    else:
+        run_single(args, peaks)
+
+
+if __name__ == "__main__":
+    main()
