@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the NVFP4 linear path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload ...]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--profile-case NAME]
 
 N = 1 (default): the square single-GPU GEMM the headline metric is quoted on (M = N = K = 4096,
 activations N(0,1) with 0.5 % x30 outliers, weights N(0,0.02), both quantised to NVFP4).  One
@@ -440,13 +440,48 @@ def run_multi(args, peaks):
     dist.destroy_process_group()
 
 
+def run_profile_case(case):
+    """One small workload, three launches, no timing: the command line that ncu wraps."""
+    from ac4k_kernel_b200 import _cuda_ops, _lib, ops
+    from ac4k_kernel_b200.ops.quant import _global_scale
+    torch.cuda.set_device(0)
+    if case.startswith("gemm"):
+        dims = {"gemm-c2": (4096, 4096, 4096), "gemm-8k": (8192, 8192, 8192), "gemm-decode": (16, 8192, 8192)}[case]
+        m, n, k = dims
+        a = activations((m, k), 0, 0.005, 30.0, "cuda")
+        w = weights((n, k), 1, "cuda")
+        a4, asf, ag = ops.quantize(a, 0, 1, sf_layout="128x4")
+        w4, wsf, wg = ops.quantize(w, 0, 1, sf_layout="128x4")
+        out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        for _ in range(3):
+            _cuda_ops.linear_nvfp4(out, a4, asf, ag, w4, wsf, wg, None)
+    else:
+        m, k = 32768, 8192
+        x = activations((m, k), 0, 0.01, 50.0, "cuda")
+        for _ in range(3):
+            if case == "quant-c4":
+                ops.quantize(x, 0, 1, sf_layout="128x4")
+            elif case == "quant-c4-fp8":
+                ops.quantize(x, 0, 1, precision="fp8e4m3")
+            else:
+                ops.quantize(x, 0, 1, precision="int8")
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": case, "device_status": _lib.device_status()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--profile-case", default=None,
+                    choices=["gemm-c2", "gemm-8k", "gemm-decode", "quant-c4", "quant-c4-fp8", "quant-c4-int8"],
+                    help="run one small workload three times and exit (for ncu)")
     args = ap.parse_args()
+    if args.profile_case:
+        run_profile_case(args.profile_case)
+        return
     if args.impl == "reference":
         run_reference(args)
         return
