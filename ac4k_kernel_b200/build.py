@@ -20,7 +20,8 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 OBJ_DIR = os.path.join(PKG_DIR, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libac4k_b200.so")
 
-SOURCES = ["cabi.cu", "quantize_nvfp4.cu", "quantize_rowwise.cu", "linear_nvfp4.cu"]
+SOURCES = ["cabi.cu", "quantize_nvfp4.cu", "quantize_rowwise.cu", "linear_nvfp4.cu",
+           "linear_nvfp4_2cta.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
@@ -56,7 +57,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
         objs.append(obj)
         if force or not _newer(obj, [src] + headers):
-            cmd = [nvcc, *NVCC_FLAGS, "-c", src, "-o", obj]
+            cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("AC4K_NVCC_EXTRA", "").split(), "-c", src, "-o", obj]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append(cmd)

@@ -1,0 +1,126 @@
+// Pieces shared by the 1-CTA and 2-CTA NVFP4 GEMM kernels: tile constants, kernel arguments,
+// tile rasterisation, epilogue helpers, and the host-side tensor-map cache.
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace ac4k {
+using namespace ptx;
+
+static constexpr int BM = 128;        // rows of A per tile (= TMEM lanes)
+static constexpr int BKB = 128;       // bytes of packed K per stage (= 256 elements = 4 MMA K-steps)
+static constexpr int K64_PER_STAGE = 4;
+static constexpr int kNumThreads = 320;
+static constexpr int kTmemCols = 512;
+static constexpr int kGroupM = 8;     // tile rasterisation: walk 8 M-tiles per N-tile
+
+enum : unsigned { kStatusTimeoutProducer = 0xA1, kStatusTimeoutMma = 0xA2, kStatusTimeoutSf = 0xA3,
+                  kStatusTimeoutEpilogue = 0xA4 };
+
+template <int BN>
+struct Cfg {
+  static constexpr int A_BYTES = BM * BKB;
+  static constexpr int B_BYTES = BN * BKB;
+  static constexpr int SFA_BYTES = K64_PER_STAGE * 512;
+  static constexpr int SFB_BYTES = (BN / 128) * K64_PER_STAGE * 512;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr int STAGES = (BN == 128) ? 6 : 4;
+  static constexpr int ACC_STAGES = (BN == 128) ? 2 : 1;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 512 /*barriers*/;
+  // tensor-memory columns: accumulators, then one scale buffer per shared-memory stage
+  static constexpr int SFA_COL = ACC_STAGES * BN;
+  static constexpr int SFA_COLS = K64_PER_STAGE * 4;
+  static constexpr int SFB_COL = SFA_COL + STAGES * SFA_COLS;
+  static constexpr int SFB_COLS = K64_PER_STAGE * (BN / 32);
+  static_assert(SFB_COL + STAGES * SFB_COLS <= kTmemCols, "tensor memory overflow");
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory overflow");
+};
+
+struct GemmArgs {
+  const uint8_t *sfa;
+  const uint8_t *sfb;
+  void *D;
+  const float *a_gs;
+  const float *b_gs;
+  const void *bias;
+  unsigned int *status;
+  int bias_dt;
+  int M, N, K;          // K in elements, multiple of 64
+  int KT;               // K / 64
+  int rows_sfa, rows_sfb;   // padded row counts of the scale tensors (16- or 128-aligned)
+  int tiles_m, tiles_n;
+  int dbg;              // experiment switches, 0 in production
+  unsigned long long *trace;   // experiment: per-stage timestamps of cluster 0, NULL in production
+};
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int &tm, int &tn) {
+  const int group = kGroupM * tiles_n;
+  const int g = t / group;
+  const int first_m = g * kGroupM;
+  const int gm = min(tiles_m - first_m, kGroupM);
+  const int r = t - g * group;
+  tm = first_m + r % gm;
+  tn = r / gm;
+}
+
+__device__ __forceinline__ float load_bias(const void *bias, int dt, int n) {
+  if (dt == AC4K_DT_BF16) return __bfloat162float(static_cast<const __nv_bfloat16 *>(bias)[n]);
+  if (dt == AC4K_DT_FP16) return __half2float(static_cast<const __half *>(bias)[n]);
+  return static_cast<const float *>(bias)[n];
+}
+
+template <int OUT_DT>
+struct OutT;
+template <> struct OutT<AC4K_DT_BF16> { using type = __nv_bfloat16; };
+template <> struct OutT<AC4K_DT_FP16> { using type = __half; };
+template <> struct OutT<AC4K_DT_FP32> { using type = float; };
+
+template <int OUT_DT>
+__device__ __forceinline__ void store_row32(void *D, int64_t off, const float (&v)[32], int ncols, bool vec_ok) {
+  using T = typename OutT<OUT_DT>::type;
+  T *dst = static_cast<T *>(D) + off;
+  if (vec_ok && ncols == 32) {
+    if (OUT_DT == AC4K_DT_FP32) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        reinterpret_cast<float4 *>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (OUT_DT == AC4K_DT_BF16) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+            w[j] = *reinterpret_cast<uint32_t *>(&h);
+          } else {
+            __half2 h = __floats2half2_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+            w[j] = *reinterpret_cast<uint32_t *>(&h);
+          }
+        }
+        reinterpret_cast<uint4 *>(dst)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+  } else {
+    for (int i = 0; i < ncols; ++i) {
+      if (OUT_DT == AC4K_DT_BF16) dst[i] = (T)__float2bfloat16_rn(v[i]);
+      else if (OUT_DT == AC4K_DT_FP16) dst[i] = (T)__float2half_rn(v[i]);
+      else dst[i] = (T)v[i];
+    }
+  }
+}
+
+
+// host helpers (linear_nvfp4.cu)
+struct DeviceInfo { int sms = 0; int cc_major = 0; bool ok = false; };
+int get_device_info(DeviceInfo *out);
+// 2-D byte tensor map [rows, row_bytes] with a (128 B x box_rows) box and 128-byte swizzle
+int get_tmap(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUtensorMap *out);
+// 2-CTA kernel launcher (linear_nvfp4_2cta.cu); D must be bf16/fp16 with N % 8 == 0
+int launch_linear_2cta(int d_dtype, bool sf_tiled, const CUtensorMap &ta, const CUtensorMap &tb,
+                       const CUtensorMap &td, GemmArgs args, cudaStream_t stream);
+
+}  // namespace ac4k

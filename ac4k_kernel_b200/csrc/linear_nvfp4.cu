@@ -19,118 +19,13 @@
 // Scale factors in tensor memory: the four e4m3 scales of row r for one K=64 step sit in lane
 // r % 32 (replicated in all four lane quarters), 32-bit column r / 32, so A (128 rows) takes 4
 // columns and B (BN rows) BN/32 columns per step.
-#include <cuda.h>
-
 #include <mutex>
 #include <vector>
 
-#include "common.cuh"
-#include "sm100_ptx.cuh"
+#include "gemm_common.cuh"
 
 namespace ac4k {
 using namespace ptx;
-
-static constexpr int BM = 128;        // rows of A per tile (= TMEM lanes)
-static constexpr int BKB = 128;       // bytes of packed K per stage (= 256 elements = 4 MMA K-steps)
-static constexpr int K64_PER_STAGE = 4;
-static constexpr int kNumThreads = 320;
-static constexpr int kTmemCols = 512;
-static constexpr int kGroupM = 8;     // tile rasterisation: walk 8 M-tiles per N-tile
-
-enum : unsigned { kStatusTimeoutProducer = 0xA1, kStatusTimeoutMma = 0xA2, kStatusTimeoutSf = 0xA3,
-                  kStatusTimeoutEpilogue = 0xA4 };
-
-template <int BN>
-struct Cfg {
-  static constexpr int A_BYTES = BM * BKB;
-  static constexpr int B_BYTES = BN * BKB;
-  static constexpr int SFA_BYTES = K64_PER_STAGE * 512;
-  static constexpr int SFB_BYTES = (BN / 128) * K64_PER_STAGE * 512;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
-  static constexpr int STAGES = (BN == 128) ? 6 : 4;
-  static constexpr int ACC_STAGES = (BN == 128) ? 2 : 1;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 512 /*barriers*/;
-  // tensor-memory columns: accumulators, then one scale buffer per shared-memory stage
-  static constexpr int SFA_COL = ACC_STAGES * BN;
-  static constexpr int SFA_COLS = K64_PER_STAGE * 4;
-  static constexpr int SFB_COL = SFA_COL + STAGES * SFA_COLS;
-  static constexpr int SFB_COLS = K64_PER_STAGE * (BN / 32);
-  static_assert(SFB_COL + STAGES * SFB_COLS <= kTmemCols, "tensor memory overflow");
-  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory overflow");
-};
-
-struct GemmArgs {
-  const uint8_t *sfa;
-  const uint8_t *sfb;
-  void *D;
-  const float *a_gs;
-  const float *b_gs;
-  const void *bias;
-  unsigned int *status;
-  int bias_dt;
-  int M, N, K;          // K in elements, multiple of 64
-  int KT;               // K / 64
-  int rows_sfa, rows_sfb;   // padded row counts of the scale tensors (16- or 128-aligned)
-  int tiles_m, tiles_n;
-  int dbg;              // experiment switches, 0 in production
-};
-
-__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int &tm, int &tn) {
-  const int group = kGroupM * tiles_n;
-  const int g = t / group;
-  const int first_m = g * kGroupM;
-  const int gm = min(tiles_m - first_m, kGroupM);
-  const int r = t - g * group;
-  tm = first_m + r % gm;
-  tn = r / gm;
-}
-
-__device__ __forceinline__ float load_bias(const void *bias, int dt, int n) {
-  if (dt == AC4K_DT_BF16) return __bfloat162float(static_cast<const __nv_bfloat16 *>(bias)[n]);
-  if (dt == AC4K_DT_FP16) return __half2float(static_cast<const __half *>(bias)[n]);
-  return static_cast<const float *>(bias)[n];
-}
-
-template <int OUT_DT>
-struct OutT;
-template <> struct OutT<AC4K_DT_BF16> { using type = __nv_bfloat16; };
-template <> struct OutT<AC4K_DT_FP16> { using type = __half; };
-template <> struct OutT<AC4K_DT_FP32> { using type = float; };
-
-template <int OUT_DT>
-__device__ __forceinline__ void store_row32(void *D, int64_t off, const float (&v)[32], int ncols, bool vec_ok) {
-  using T = typename OutT<OUT_DT>::type;
-  T *dst = static_cast<T *>(D) + off;
-  if (vec_ok && ncols == 32) {
-    if (OUT_DT == AC4K_DT_FP32) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        reinterpret_cast<float4 *>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint32_t w[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (OUT_DT == AC4K_DT_BF16) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
-            w[j] = *reinterpret_cast<uint32_t *>(&h);
-          } else {
-            __half2 h = __floats2half2_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
-            w[j] = *reinterpret_cast<uint32_t *>(&h);
-          }
-        }
-        reinterpret_cast<uint4 *>(dst)[i] = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-    }
-  } else {
-    for (int i = 0; i < ncols; ++i) {
-      if (OUT_DT == AC4K_DT_BF16) dst[i] = (T)__float2bfloat16_rn(v[i]);
-      else if (OUT_DT == AC4K_DT_FP16) dst[i] = (T)__float2half_rn(v[i]);
-      else dst[i] = (T)v[i];
-    }
-  }
-}
 
 template <int BN, bool SF_TILED, int OUT_DT>
 __global__ void __launch_bounds__(kNumThreads, 1)
@@ -389,7 +284,7 @@ struct TmapEntry { TmapKey key; CUtensorMap map; };
 
 // Tensor maps depend only on (pointer, shape, box); encoding costs a driver call, so the last
 // few are kept.  The reference re-encodes five per call (linear_nvfp4.cu:842-886).
-static int get_tmap(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUtensorMap *out) {
+int get_tmap(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUtensorMap *out) {
   static std::mutex mu;
   static std::vector<TmapEntry> cache;
   int dev = 0;
@@ -420,8 +315,7 @@ static int get_tmap(const void *ptr, int64_t rows, int64_t row_bytes, int box_ro
   return 0;
 }
 
-struct DeviceInfo { int sms = 0; int cc_major = 0; bool ok = false; };
-static int get_device_info(DeviceInfo *out) {
+int get_device_info(DeviceInfo *out) {
   static DeviceInfo info[64];
   int dev = 0;
   AC4K_CUDA_TRY(cudaGetDevice(&dev));
@@ -470,6 +364,8 @@ using namespace ac4k;
 // Tile width override for experiments: 0 = automatic.
 static int g_force_bn = 0;
 static int g_dbg = 0;
+static unsigned long long *g_trace = nullptr;
+extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_trace(void *p) { g_trace = static_cast<unsigned long long *>(p); }
 extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_flags(int f) { g_dbg = f; }
 extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_tile_n(int bn) { g_force_bn = bn; }
 
@@ -498,10 +394,19 @@ extern "C" int ac4k_linear_nvfp4(void *D, int d_dtype, const void *A, const void
   unsigned int *status = device_status_ptr();
   if (!status) return fail(AC4K_ERR_DEVICE, "cannot resolve the device status word");
 
-  int bn = g_force_bn ? g_force_bn : 128;
-  CUtensorMap ta, tb;
+  // kernel choice: CTA pairs (256 x 256 tiles, TMA-store epilogue) when there are at least two row
+  // tiles to pair and the output can be stored by TMA; otherwise single CTAs with 128 x 256 or
+  // 128 x 128 tiles.  g_force_bn: 128 / 256 force the single-CTA kernel, 512 forces pairs.
+  const bool pair_ok = d_dtype != AC4K_DT_FP32 && (N % 8 == 0);
+  bool use_pair = pair_ok && M > 128 && N > 128;
+  int bn = N > 128 ? 256 : 128;
+  if (g_force_bn == 128 || g_force_bn == 256) { use_pair = false; bn = g_force_bn; }
+  if (g_force_bn == 512 && pair_ok) use_pair = true;
+  CUtensorMap ta, tb, td;
   if (int e = get_tmap(A, M, K / 2, BM, &ta)) return e;
-  if (int e = get_tmap(B, N, K / 2, bn, &tb)) return e;
+  if (int e = get_tmap(B, N, K / 2, use_pair ? 128 : bn, &tb)) return e;
+  if (use_pair)
+    if (int e = get_tmap(D, M, N * 2, 128, &td)) return e;
 
   GemmArgs a;
   a.sfa = static_cast<const uint8_t *>(A_sf);
@@ -520,7 +425,9 @@ extern "C" int ac4k_linear_nvfp4(void *D, int d_dtype, const void *A, const void
   a.tiles_m = (int)ceil_div(M, BM);
   a.tiles_n = (int)ceil_div(N, bn);
   a.dbg = g_dbg;
+  a.trace = g_trace;
   const bool tiled = sf_layout == AC4K_SF_TILE128X4;
+  if (use_pair) return launch_linear_2cta(d_dtype, tiled, ta, tb, td, a, stream);
   if (bn == 256)
     return tiled ? launch_dt<256, true>(d_dtype, ta, tb, a, di.sms, stream)
                  : launch_dt<256, false>(d_dtype, ta, tb, a, di.sms, stream);
