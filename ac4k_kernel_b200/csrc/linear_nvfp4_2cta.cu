@@ -27,6 +27,11 @@ using namespace ptx;
     if (p.trace != nullptr && cluster_id == 0 && (it) < 128)                                \
       p.trace[((size_t)rank * 128 + (it)) * 8 + (ev)] = clock64();                          \
   } while (0)
+#define AC4K_TRACES(it, ev)                                                                 \
+  do {                                                                                      \
+    if (p.trace != nullptr && cluster_id == 0 && rank == 0 && warp == 2 && lane == 0 && (it) < 128) \
+      p.trace[((size_t)2 * 128 + (it)) * 8 + (ev)] = clock64();                             \
+  } while (0)
 #define AC4K_TRACE(it, ev)                                                                  \
   do {                                                                                      \
     if (p.trace != nullptr && cluster_id == 0 && (it) < 128)                                \
@@ -35,6 +40,7 @@ using namespace ptx;
 
 #else
 #define AC4K_TRACEC(it, ev) do { } while (0)
+#define AC4K_TRACES(it, ev) do { } while (0)
 #define AC4K_TRACE(it, ev) do { } while (0)
 #endif
 
@@ -134,7 +140,7 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         const int nb0 = tn * BN + (int)rank * 128;        // this CTA's rows of B
         for (int kt = 0; kt < k_tiles; ++kt) {
           if (!mbar_wait(empty_bar + 8 * s, ph ^ 1)) { atomicExch(p.status, kStatusTimeoutProducer); ok = false; break; }
-          AC4K_TRACE(it, 0);
+          AC4K_TRACEC(it, 2);
           ++it;
           const uint32_t leader_full = map_to_cta(full_bar + 8 * s, 0);
           if (rank == 0) mbar_arrive_expect_tx(full_bar + 8 * s, ((p.dbg & 512) ? 1 : 2) * (A_BYTES + B_BYTES));
@@ -200,7 +206,6 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           tc_commit_pair_both(empty_bar + 8 * s, 3);                 // stage free in both CTAs
           if (kt == k_tiles - 1) tc_commit_pair_both(tfull_bar, 3);  // accumulator complete in both CTAs
           AC4K_TRACEC(it, 5);
-          AC4K_TRACE(it, 7);
           ++it;
           if (++s == STAGES) s = 0;
         }
@@ -221,6 +226,7 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         }
         ok = ok && mbar_wait(full_bar + 8 * s, ph);
         if (!ok) break;
+        AC4K_TRACEC(count, 4);
         st_shared_release(ready_word, ++count);
         if (++s == STAGES) { s = 0; ph ^= 1; }
       }
@@ -275,7 +281,9 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     bool ok = true;
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
     for (StageCursor cur(cluster_id, num_clusters, num_tiles, k_tiles); cur.valid() && ok; cur.next()) {
+      AC4K_TRACES(it, 0);
       if (!mbar_wait(sffull_bar + 8 * s, ph)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutSf); ok = false; break; }
+      AC4K_TRACES(it, 1);
       const uint8_t *a_src = smem_gen + (sSFA + s * SFA_BYTES - smem_base);
       const uint8_t *b_src = smem_gen + (sSFB + s * SFB_BYTES - smem_base);
       uint32_t ra[16], rb[32];
@@ -302,14 +310,19 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(sffree_bar + 8 * s);      // this warp holds the slot in registers
+      AC4K_TRACES(it, 2);
       // tensor-memory slot s is free once the MMAs of the step that last used it are done
       if (!mbar_wait(empty_bar + 8 * s, ph ^ 1)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutSf); ok = false; break; }
+      AC4K_TRACES(it, 3);
       tc_fence_after();
       tmem_st_32x32b_x16(lane_base + SFA_COL + s * SFA_COLS, ra);
       tmem_st_32x32b_x32(lane_base + SFB_COL + s * SFB_COLS, rb);
+      AC4K_TRACES(it, 4);
       tmem_st_wait();
+      AC4K_TRACES(it, 5);
       tc_fence_before();
       __syncwarp();
+      if (warp == 2 && lane == 0) AC4K_TRACEC(it, 6);
       ++it;
       if (lane == 0) mbar_arrive_cluster(map_to_cta(full_bar + 8 * s, 0));
       if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -336,7 +349,7 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       const int m0 = tm * BMP + (int)rank * 128, n0 = tn * BN;
       if (!mbar_wait(tfull_bar, acc_ph)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue); break; }
       tc_fence_after();
-      if (warp == 6 && lane == 0) AC4K_TRACEC(120 + ti, 4);
+      if (warp == 6 && lane == 0) AC4K_TRACEC(120 + ti, 7);
       uint32_t w[64];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -362,7 +375,7 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       }
       tc_fence_before();
       __syncwarp();
-      if (warp == 6 && lane == 0) AC4K_TRACEC(120 + ti, 6);
+      if (warp == 6 && lane == 0 && p.trace != nullptr && cluster_id == 0) p.trace[((size_t)rank * 128 + 112 + ti) * 8 + 7] = clock64();
       if (lane == 0) mbar_arrive_cluster(leader_tempty);
       if (!(p.dbg & 8)) {
         // staging buffer `half` holds columns [half*128 + round*64, +64) in round `round`
