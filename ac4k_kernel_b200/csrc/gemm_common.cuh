@@ -52,6 +52,9 @@ struct GemmArgs {
   int KT;               // K / 64
   int rows_sfa, rows_sfb;   // padded row counts of the scale tensors (16- or 128-aligned)
   int tiles_m, tiles_n;
+  int splits;           // split-K factor (1-CTA kernel only); > 1 writes fp32 partials to `ws`
+  int kt_per_split;     // K stages (of 256 elements) per split
+  float *ws;            // [splits, M, N] fp32 partial sums when splits > 1
   int dbg;              // experiment switches, 0 in production
   unsigned long long *trace;   // experiment: per-stage timestamps of cluster 0, NULL in production
 };

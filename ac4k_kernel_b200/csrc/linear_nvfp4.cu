@@ -45,8 +45,11 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));   // generic pointer to smem_base
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // work item = (tile, K split); consecutive items walk the tiles first so that concurrent CTAs
+  // stream different weight rows
   const int num_tiles = p.tiles_m * p.tiles_n;
-  const int k_tiles = (p.KT + K64_PER_STAGE - 1) / K64_PER_STAGE;
+  const int num_work = num_tiles * p.splits;
+  const int k_tiles_all = (p.KT + K64_PER_STAGE - 1) / K64_PER_STAGE;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -76,11 +79,13 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     if (lane == 0) {
       uint32_t s = 0, ph = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
+        const int t = wi % num_tiles, split = wi / num_tiles;
+        const int kt0 = split * p.kt_per_split, kt1 = min(k_tiles_all, kt0 + p.kt_per_split);
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
-        for (int kt = 0; kt < k_tiles; ++kt) {
+        for (int kt = kt0; kt < kt1; ++kt) {
           if (!mbar_wait(empty_bar + 8 * s, ph ^ 1)) { atomicExch(p.status, kStatusTimeoutProducer); ok = false; break; }
           const int nk = min(K64_PER_STAGE, p.KT - kt * K64_PER_STAGE);
           uint32_t sfa_bytes, sfb_bytes;
@@ -125,11 +130,13 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       constexpr uint32_t idesc = make_idesc_mxf4nvf4(BM, BN);
       uint32_t s = 0, ph = 0, acc = 0, acc_ph = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
+        const int split = wi / num_tiles;
+        const int kt0 = split * p.kt_per_split, kt1 = min(k_tiles_all, kt0 + p.kt_per_split);
         if (!mbar_wait(tempty_bar + 8 * acc, acc_ph ^ 1)) { atomicExch(p.status, kStatusTimeoutMma); break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kt = 0; kt < k_tiles; ++kt) {
+        for (int kt = kt0; kt < kt1; ++kt) {
           if (!mbar_wait(full_bar + 8 * s, ph) || !mbar_wait(sf_bar + 8 * s, ph)) {
             atomicExch(p.status, kStatusTimeoutMma); ok = false; break;
           }
@@ -142,7 +149,7 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           for (int j = 0; j < nk; ++j) {
             // +32 bytes of K per step inside the 128-byte swizzle atom: start-address field += 2
             mma_mxf4nvf4(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, t_sfa + j * 4, t_sfb + j * (BN / 32),
-                         (kt > 0 || j > 0) ? 1u : 0u);
+                         (kt > kt0 || j > 0) ? 1u : 0u);
           }
           tc_commit(empty_bar + 8 * s);
           if (++s == C::STAGES) { s = 0; ph ^= 1; }
@@ -159,8 +166,10 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     const int q = warp & 3;
     uint32_t s = 0, ph = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-      for (int kt = 0; kt < k_tiles; ++kt) {
+    for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
+      const int split = wi / num_tiles;
+      const int kt0 = split * p.kt_per_split, kt1 = min(k_tiles_all, kt0 + p.kt_per_split);
+      for (int kt = kt0; kt < kt1; ++kt) {
         if (!mbar_wait(full_bar + 8 * s, ph)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutSf); ok = false; break; }
         const uint8_t *a_src = smem_gen + (sSFA + s * C::SFA_BYTES - smem_base);
         const uint8_t *b_src = smem_gen + (sSFB + s * C::SFB_BYTES - smem_base);
@@ -211,7 +220,8 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     uint32_t acc = 0, acc_ph = 0;
     const float alpha = __fmul_rn(__ldg(p.a_gs), __ldg(p.b_gs));
     const bool vec_ok = (OUT_DT == AC4K_DT_FP32) ? (p.N % 4 == 0) : (p.N % 8 == 0);
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    for (int wi = blockIdx.x; wi < num_work; wi += gridDim.x) {
+      const int t = wi % num_tiles, split = wi / num_tiles;
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
       if (!mbar_wait(tfull_bar + 8 * acc, acc_ph)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue); break; }
@@ -225,7 +235,16 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         tmem_ld_wait();
         const int col = tn * BN + c;
         const int ncols = min(32, p.N - col);
-        if (row < p.M && ncols > 0 && !(p.dbg & 8)) {
+        if (p.splits > 1) {
+          // split-K: raw fp32 partial sums go to the workspace; alpha, bias and the cast are applied
+          // by the reduction kernel
+          if (row < p.M && ncols > 0) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+            store_row32<AC4K_DT_FP32>(p.ws, ((int64_t)split * p.M + row) * p.N + col, v, ncols, p.N % 4 == 0);
+          }
+        } else if (row < p.M && ncols > 0 && !(p.dbg & 8)) {
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __fmul_rn(__uint_as_float(r[i]), alpha);
@@ -249,6 +268,42 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// out[m, n] = cast(alpha * sum_s ws[s, m, n] + bias[n]) for the split-K path; one thread per
+// four consecutive columns (N % 4 == 0 on this path).
+template <int OUT_DT>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(void *__restrict__ D, const float *__restrict__ ws, const float *__restrict__ a_gs,
+                     const float *__restrict__ b_gs, const void *__restrict__ bias, int bias_dt, int splits,
+                     int64_t M, int64_t N) {
+  using T = typename OutT<OUT_DT>::type;
+  const int64_t i4 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t total4 = M * N / 4;
+  if (i4 >= total4) return;
+  const float alpha = __fmul_rn(__ldg(a_gs), __ldg(b_gs));
+  float4 acc = __ldcs(reinterpret_cast<const float4 *>(ws) + i4);
+  for (int s = 1; s < splits; ++s) {
+    const float4 v = __ldcs(reinterpret_cast<const float4 *>(ws + (int64_t)s * M * N) + i4);
+    acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y);
+    acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+  }
+  float o[4] = {__fmul_rn(acc.x, alpha), __fmul_rn(acc.y, alpha), __fmul_rn(acc.z, alpha), __fmul_rn(acc.w, alpha)};
+  if (bias != nullptr) {
+    const int n = (int)((i4 * 4) % N);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = __fadd_rn(o[j], load_bias(bias, bias_dt, n + j));
+  }
+  T *dst = static_cast<T *>(D) + i4 * 4;
+  if (OUT_DT == AC4K_DT_FP32) {
+    *reinterpret_cast<float4 *>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+  } else if (OUT_DT == AC4K_DT_BF16) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+    *reinterpret_cast<uint2 *>(dst) = make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
+  } else {
+    __half2 lo = __floats2half2_rn(o[0], o[1]), hi = __floats2half2_rn(o[2], o[3]);
+    *reinterpret_cast<uint2 *>(dst) = make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
   }
 }
 
@@ -340,8 +395,8 @@ static int launch(const CUtensorMap &ta, const CUtensorMap &tb, const GemmArgs &
     AC4K_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     attr_set[dev] = true;
   }
-  const int num_tiles = args.tiles_m * args.tiles_n;
-  const int grid = num_tiles < sms ? num_tiles : sms;
+  const int num_work = args.tiles_m * args.tiles_n * args.splits;
+  const int grid = num_work < sms ? num_work : sms;
   kern<<<grid, kNumThreads, C::SMEM_BYTES, stream>>>(ta, tb, args);
   AC4K_LAUNCH_CHECK("linear_nvfp4_kernel");
   return 0;
@@ -363,17 +418,38 @@ using namespace ac4k;
 
 // Tile width override for experiments: 0 = automatic.
 static int g_force_bn = 0;
+static int g_force_splits = 0;   // 0 = automatic, 1 = never split, n > 1 = force n K slices
+extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_splits(int n) { g_force_splits = n; }
 static int g_dbg = 0;
 static unsigned long long *g_trace = nullptr;
 extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_trace(void *p) { g_trace = static_cast<unsigned long long *>(p); }
 extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_flags(int f) { g_dbg = f; }
 extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_tile_n(int bn) { g_force_bn = bn; }
 
-extern "C" int ac4k_linear_nvfp4(void *D, int d_dtype, const void *A, const void *A_sf, const float *A_gs,
-                                 const void *B, const void *B_sf, const float *B_gs, const void *bias,
-                                 int bias_dtype, int64_t M, int64_t N, int64_t K, int sf_layout,
-                                 ac4k_stream_t stream_) {
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+// Split-K plan for shapes with too few output tiles to occupy the GPU (decode: M <= 128): how many
+// K slices, and the fp32 workspace [splits, M, N] they need.  splits == 1 means no workspace.
+struct SplitPlan { int splits; int kt_per_split; size_t ws_bytes; };
+
+static SplitPlan plan_split(int64_t M, int64_t N, int64_t K, int bn, int sms) {
+  SplitPlan pl{1, (int)ceil_div(K / 64, K64_PER_STAGE), 0};
+  const int64_t tiles = ceil_div(M, BM) * ceil_div(N, bn);
+  const int k_tiles = pl.kt_per_split;
+  if (g_force_splits == 1 || N % 4 != 0 || tiles * 2 > sms || k_tiles < 8) return pl;
+  int splits = g_force_splits > 1 ? g_force_splits : (int)(sms / tiles);
+  if (splits > k_tiles / 4) splits = k_tiles / 4;      // at least four pipeline stages per slice
+  if (splits < 2) return pl;
+  pl.kt_per_split = (int)ceil_div(k_tiles, splits);
+  pl.splits = (int)ceil_div(k_tiles, pl.kt_per_split);
+  pl.ws_bytes = (size_t)pl.splits * (size_t)M * (size_t)N * sizeof(float);
+  return pl;
+}
+
+// ws_mode: 0 = workspace from the stream-ordered allocator (cudaMallocAsync / cudaFreeAsync),
+//          1 = caller-provided workspace of ws_capacity bytes (no allocation in this call)
+static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, const float *A_gs,
+                       const void *B, const void *B_sf, const float *B_gs, const void *bias,
+                       int bias_dtype, int64_t M, int64_t N, int64_t K, int sf_layout,
+                       cudaStream_t stream, int ws_mode, float *ws_fixed, size_t ws_capacity) {
   if (M < 0 || N < 0 || K < 0) return fail(AC4K_ERR_SHAPE, "negative dimension");
   if (d_dtype < 0 || d_dtype > 2) return fail(AC4K_ERR_ENUM, "unknown d_dtype %d", d_dtype);
   if (bias && (bias_dtype < 0 || bias_dtype > 2)) return fail(AC4K_ERR_ENUM, "unknown bias_dtype %d", bias_dtype);
@@ -402,6 +478,15 @@ extern "C" int ac4k_linear_nvfp4(void *D, int d_dtype, const void *A, const void
   int bn = N > 128 ? 256 : 128;
   if (g_force_bn == 128 || g_force_bn == 256) { use_pair = false; bn = g_force_bn; }
   if (g_force_bn == 512 && pair_ok) use_pair = true;
+  SplitPlan pl{1, (int)ceil_div(K / 64, K64_PER_STAGE), 0};
+  if (!use_pair) {
+    // few output tiles (decode shapes): narrower tiles and K slices put more SMs on the weight stream
+    if (g_force_bn == 0 && ceil_div(M, BM) * ceil_div(N, 256) * 2 <= di.sms) bn = 128;
+    pl = plan_split(M, N, K, bn, di.sms);
+    if (ws_mode == 1 && pl.ws_bytes > ws_capacity)
+      return fail(AC4K_ERR_SHAPE, "split-K workspace of %zu bytes exceeds the fixed scratch of %zu bytes",
+                  pl.ws_bytes, ws_capacity);
+  }
   CUtensorMap ta, tb, td;
   if (int e = get_tmap(A, M, K / 2, BM, &ta)) return e;
   if (int e = get_tmap(B, N, K / 2, use_pair ? 128 : bn, &tb)) return e;
@@ -426,11 +511,56 @@ extern "C" int ac4k_linear_nvfp4(void *D, int d_dtype, const void *A, const void
   a.tiles_n = (int)ceil_div(N, bn);
   a.dbg = g_dbg;
   a.trace = g_trace;
+  a.splits = pl.splits;
+  a.kt_per_split = pl.kt_per_split;
+  a.ws = nullptr;
   const bool tiled = sf_layout == AC4K_SF_TILE128X4;
   if (use_pair) return launch_linear_2cta(d_dtype, tiled, ta, tb, td, a, stream);
+  if (pl.splits > 1) {
+    if (ws_mode == 1) {
+      a.ws = ws_fixed;
+    } else {
+      void *wsp = nullptr;
+      AC4K_CUDA_TRY(cudaMallocAsync(&wsp, pl.ws_bytes, stream));
+      a.ws = static_cast<float *>(wsp);
+    }
+  }
+  int rc;
   if (bn == 256)
-    return tiled ? launch_dt<256, true>(d_dtype, ta, tb, a, di.sms, stream)
-                 : launch_dt<256, false>(d_dtype, ta, tb, a, di.sms, stream);
-  return tiled ? launch_dt<128, true>(d_dtype, ta, tb, a, di.sms, stream)
+    rc = tiled ? launch_dt<256, true>(d_dtype, ta, tb, a, di.sms, stream)
+               : launch_dt<256, false>(d_dtype, ta, tb, a, di.sms, stream);
+  else
+    rc = tiled ? launch_dt<128, true>(d_dtype, ta, tb, a, di.sms, stream)
                : launch_dt<128, false>(d_dtype, ta, tb, a, di.sms, stream);
+  if (pl.splits > 1) {
+    if (rc == 0) {
+      const int64_t total4 = M * N / 4;
+      const unsigned blocks = (unsigned)ceil_div(total4, 256);
+      switch (d_dtype) {
+        case AC4K_DT_BF16:
+          splitk_reduce_kernel<AC4K_DT_BF16><<<blocks, 256, 0, stream>>>(D, a.ws, A_gs, B_gs, bias, bias_dtype, pl.splits, M, N);
+          break;
+        case AC4K_DT_FP16:
+          splitk_reduce_kernel<AC4K_DT_FP16><<<blocks, 256, 0, stream>>>(D, a.ws, A_gs, B_gs, bias, bias_dtype, pl.splits, M, N);
+          break;
+        default:
+          splitk_reduce_kernel<AC4K_DT_FP32><<<blocks, 256, 0, stream>>>(D, a.ws, A_gs, B_gs, bias, bias_dtype, pl.splits, M, N);
+      }
+      cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) rc = cuda_fail(e, "splitk_reduce_kernel");
+    }
+    if (ws_mode == 0) {
+      cudaError_t e = cudaFreeAsync(a.ws, stream);
+      if (e != cudaSuccess && rc == 0) rc = cuda_fail(e, "cudaFreeAsync");
+    }
+  }
+  return rc;
+}
+
+extern "C" int ac4k_linear_nvfp4(void *D, int d_dtype, const void *A, const void *A_sf, const float *A_gs,
+                                 const void *B, const void *B_sf, const float *B_gs, const void *bias,
+                                 int bias_dtype, int64_t M, int64_t N, int64_t K, int sf_layout,
+                                 ac4k_stream_t stream_) {
+  return linear_impl(D, d_dtype, A, A_sf, A_gs, B, B_sf, B_gs, bias, bias_dtype, M, N, K, sf_layout,
+                     static_cast<cudaStream_t>(stream_), 0, nullptr, 0);
 }

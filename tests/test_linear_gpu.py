@@ -199,6 +199,19 @@ def test_config3_decode_shapes(ops, m):
     run_case(ops, m, 8192, 8192, layout="128x4", oracle_device="cuda", a=x, b=_weights((8192, 8192), 1))
 
 
+@pytest.mark.parametrize("m,n,k,odt,bdt", [
+    (5, 2048, 4096, torch.bfloat16, torch.float32),     # 16 tiles -> 4 K slices
+    (33, 1024, 8192, torch.float16, torch.bfloat16),    # 8 tiles -> 8 K slices
+    (128, 512, 4096, torch.float32, None),              # 4 tiles, fp32 output
+    (3, 4100, 2048, torch.bfloat16, None),              # N % 128 != 0, N % 4 == 0
+])
+def test_split_k_decode_path(ops, m, n, k, odt, bdt):
+    """Few output tiles and a long K: the library slices K over more CTAs, sums fp32 partials from a
+    scratch buffer and applies alpha / bias / cast in a second kernel."""
+    run_case(ops, m, n, k, seed=21, layout="128x4", bias_dtype=bdt, out_dtype=odt, oracle_device="cuda")
+    run_case(ops, m, n, k, seed=22, layout="ac4k", bias_dtype=bdt, out_dtype=odt, oracle_device="cuda")
+
+
 def test_reference_8192_cube(ops):
     """test/test_linear_bench.py:174."""
     g = torch.Generator(device="cuda").manual_seed(9567)
