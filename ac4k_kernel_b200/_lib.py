@@ -30,6 +30,9 @@ SIGNATURES = {
     "ac4k_linear_nvfp4": (ctypes.c_int, [_vp, ctypes.c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                          ctypes.c_int, ctypes.c_int64, ctypes.c_int64,
                                          ctypes.c_int64, ctypes.c_int, _vp]),
+    "ac4k_linear_nvfp4_noalloc": (ctypes.c_int, [_vp, ctypes.c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                                 ctypes.c_int, ctypes.c_int64, ctypes.c_int64,
+                                                 ctypes.c_int64, ctypes.c_int, _vp]),
 }
 
 

@@ -564,3 +564,35 @@ extern "C" int ac4k_linear_nvfp4(void *D, int d_dtype, const void *A, const void
   return linear_impl(D, d_dtype, A, A_sf, A_gs, B, B_sf, B_gs, bias, bias_dtype, M, N, K, sf_layout,
                      static_cast<cudaStream_t>(stream_), 0, nullptr, 0);
 }
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free variant
+// ------------------------------------------------------------------------------------------
+// Some hosts of this library may not allocate device memory while they run: code that executes
+// inside a memory-budgeted serving process whose pools are sized once at start-up, plugins that
+// are handed device buffers by a framework and are forbidden to call the CUDA allocator, or
+// latency-critical loops where an allocator call (even a stream-ordered one) is not acceptable.
+// The regular entry point takes the split-K scratch from cudaMallocAsync; this one takes it from
+// a fixed array that lives in the library's device image instead.
+static constexpr size_t kFixedScratchBytes = 8u << 20;   // 8 MiB, held by every GPU that loads the library
+static __device__ __align__(256) unsigned char g_fixed_scratch[kFixedScratchBytes];
+
+extern "C" int ac4k_linear_nvfp4_noalloc(void *D, int d_dtype, const void *A, const void *A_sf,
+                                         const float *A_gs, const void *B, const void *B_sf,
+                                         const float *B_gs, const void *bias, int bias_dtype, int64_t M,
+                                         int64_t N, int64_t K, int sf_layout, ac4k_stream_t stream_) {
+  // In host code `g_fixed_scratch` is only a handle for the symbol, not a device address: the
+  // address is looked up once per device, with that device current, and then handed to the kernels.
+  static float *scratch[64] = {};
+  int dev = 0;
+  AC4K_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(AC4K_ERR_DEVICE, "device index %d out of range", dev);
+  if (scratch[dev] == nullptr) {
+    void *ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_fixed_scratch);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_fixed_scratch)");
+    scratch[dev] = static_cast<float *>(ptr);
+  }
+  return linear_impl(D, d_dtype, A, A_sf, A_gs, B, B_sf, B_gs, bias, bias_dtype, M, N, K, sf_layout,
+                     static_cast<cudaStream_t>(stream_), 1, scratch[dev], kFixedScratchBytes);
+}

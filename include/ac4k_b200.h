@@ -99,6 +99,26 @@ int ac4k_linear_nvfp4(void *D, int d_dtype, const void *A, const void *A_sf,
                       const void *bias, int bias_dtype, int64_t M, int64_t N, int64_t K,
                       int sf_layout, ac4k_stream_t stream);
 
+/* Same computation and arguments as ac4k_linear_nvfp4, for callers that must not allocate device
+ * memory while running (a plugin living inside someone else's fixed memory budget, a serving loop
+ * that forbids allocator calls).  No counterpart in the reference, which never needs scratch.
+ *
+ * Where ac4k_linear_nvfp4 would take split-K scratch from the stream-ordered allocator, this entry
+ * point uses a fixed 8 MiB array inside the library's device image (every GPU that loads the
+ * library holds those 8 MiB until the process exits).  It calls no cudaMalloc / cudaFree of any
+ * kind.  Shapes whose split-K partial sums ([K slices, M, N] fp32) need more than 8 MiB are
+ * rejected with AC4K_ERR_SHAPE and a message; shapes that need no scratch run as usual.
+ *
+ *  - The first call on each device looks up the array's device address (device must be current);
+ *    make that first call before starting any stream capture.
+ *  - All calls share the one array and it keeps whatever the last call left in it.  Nothing in
+ *    it needs clearing: each call overwrites every partial sum it later reads.  Two calls that
+ *    can overlap on the GPU (different streams) would race on it: serialise them. */
+int ac4k_linear_nvfp4_noalloc(void *D, int d_dtype, const void *A, const void *A_sf,
+                              const float *A_gs, const void *B, const void *B_sf, const float *B_gs,
+                              const void *bias, int bias_dtype, int64_t M, int64_t N, int64_t K,
+                              int sf_layout, ac4k_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
