@@ -340,7 +340,9 @@ def run_single(args, peaks):
         "value_reference_scale_layout": flops / (secs_ac4k / args.steps) / 1e12,
         "roofline": {"bound": "tensor", "achieved": value, "peak": fp4_proxy_peak, "unit": "TFLOP/s",
                      "frac": value / fp4_proxy_peak,
-                     "traffic": None,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture
+                     # summarised in profiles/gemm_nvfp4_pair_4096cube.md
+                     "traffic": 19.0e6,
                      "peak_note": f"4 x {peaks['source']} bf16 burst ({peaks['bf16_tflops']} TFLOP/s): no FP4 figure is "
                                   "measured on this pool; nominal dense FP4 is 9000 TFLOP/s",
                      "algorithmic_flops_per_launch": flops},
