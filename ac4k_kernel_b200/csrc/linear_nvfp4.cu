@@ -231,8 +231,7 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
-        tmem_ld_32x32b_x32(t_row + c, r);
-        tmem_ld_wait();
+        tmem_ld_32x32b_x32_sync(t_row + c, r);
         const int col = tn * BN + c;
         const int ncols = min(32, p.N - col);
         if (p.splits > 1) {

@@ -5,94 +5,80 @@
 // CTA issues one tcgen05.mma over both (M = 256, N = 256, each CTA accumulating its 128 rows x
 // 256 columns in its own tensor memory, the B halves read from both CTAs' shared memory).  Per
 // FLOP this moves a third less operand data from L2 into shared memory than 128 x 256 tiles of
-// single CTAs, which is what bounds the single-CTA kernel (measured: its TMA stream alone takes
-// longer than its MMAs).  No multicast loads are used.
+// single CTAs.  No multicast loads are used.
 //
-// Roles per CTA (512 threads): warp 0 TMA producer (A, B), warp 1 MMA issuer (leader CTA only),
-// warps 2-5 scale warps (shared memory -> tcgen05.st -> tensor memory), warp 10 scale feeder
-// (bulk copies of scale bytes, running ahead of the operands), warp 11 barrier watcher (leader
-// CTA only), warps 6-9 and 12-15 epilogue (tcgen05.ld, *alpha, +bias, convert, 128-byte-swizzled
-// staging in shared memory, TMA store).
-// Barriers that gate the MMA (operands landed, scales written, accumulator drained) live in the
-// leader CTA and are signalled by both CTAs; barriers that release shared-memory stages and
-// publish the accumulator exist in both CTAs and are signalled by two tcgen05.commit each.
+// A pipeline stage is K = 512 elements (8 MMAs of K = 64): every role's per-stage bookkeeping
+// (mbarrier waits ~75-100 cycles each, tcgen05.commit ~110, a tcgen05.mma issue ~75-125, remote
+// arrives) was measured to be latency-bound, so fewer, larger stages keep each role's loop shorter
+// than the 1024 cycles the tensor pipe needs per stage.
+//
+// Roles per CTA (512 threads):
+//   warp 0      TMA producer: A and B of this CTA, 4 boxes of 128 rows x 128 B per stage, 3 stages
+//   warp 1      MMA issuer (leader CTA only): 8 MMAs + 1 commit per stage; learns that a stage is
+//               ready from a counter in shared memory instead of waiting on mbarriers itself
+//   warps 2-5   scale warps: scale bytes shared memory -> registers -> tensor memory (tcgen05.st),
+//               one TMEM lane quarter each; 2-deep rings in shared and in tensor memory
+//   warp 10     scale feeder: bulk copies of scale bytes, as soon as the scale warps freed a slot
+//   warp 11     barrier watcher (leader CTA only): waits for accumulator hand-back and for each
+//               stage's operands + scales, publishes the count of ready stages
+//   warps 6-9, 12-15  epilogue: tcgen05.ld of 128 accumulator columns per warp into registers
+//               (* alpha, + bias, packed to 16 bit), hand the accumulator back, then store
+// Barriers that gate the MMA live in the leader CTA and are signalled by both CTAs; barriers that
+// release stages / publish the accumulator exist in both CTAs and are signalled by one
+// tcgen05.commit whose arrival fans out to both.
 #include "gemm_common.cuh"
 
 namespace ac4k {
 using namespace ptx;
 
 #ifdef AC4K_TRACE_ENABLED
-#define AC4K_TRACEC(it, ev)                                                                 \
+// region 0: MMA issuer, region 1: epilogue warp 6, region 2: scale warp 2 (all leader CTA, cluster 0)
+#define AC4K_TR(region, it, ev)                                                              \
   do {                                                                                      \
-    if (p.trace != nullptr && cluster_id == 0 && (it) < 128)                                \
-      p.trace[((size_t)rank * 128 + (it)) * 8 + (ev)] = clock64();                          \
+    if (p.trace != nullptr && cluster_id == 0 && rank == 0 && (it) < 128)                   \
+      p.trace[((size_t)(region) * 128 + (it)) * 8 + (ev)] = clock64();                      \
   } while (0)
-#define AC4K_TRACES(it, ev)                                                                 \
-  do {                                                                                      \
-    if (p.trace != nullptr && cluster_id == 0 && rank == 0 && warp == 2 && lane == 0 && (it) < 128) \
-      p.trace[((size_t)2 * 128 + (it)) * 8 + (ev)] = clock64();                             \
-  } while (0)
-#define AC4K_TRACE(it, ev)                                                                  \
-  do {                                                                                      \
-    if (p.trace != nullptr && cluster_id == 0 && (it) < 128)                                \
-      p.trace[((size_t)rank * 128 + (it)) * 8 + (ev)] = globaltimer();                      \
-  } while (0)
-
 #else
-#define AC4K_TRACEC(it, ev) do { } while (0)
-#define AC4K_TRACES(it, ev) do { } while (0)
-#define AC4K_TRACE(it, ev) do { } while (0)
+#define AC4K_TR(region, it, ev) do { } while (0)
 #endif
 
 namespace pair {
 static constexpr int BN = 256;                      // output columns of the pair tile
 static constexpr int BMP = 256;                     // output rows of the pair tile
-static constexpr int A_BYTES = 128 * BKB;           // this CTA's 128 rows of A
-static constexpr int B_BYTES = 128 * BKB;           // this CTA's 128 rows of B
-static constexpr int SFA_BYTES = K64_PER_STAGE * 512;
-static constexpr int SFB_BYTES = 2 * K64_PER_STAGE * 512;
-static constexpr int STAGES = 5;                    // operand ring, scale ring and TMEM scale ring
-static constexpr int OUT_CHUNK_BYTES = 128 * 128;   // 128 rows x 64 16-bit columns
-static constexpr int OUT_CHUNKS = 2;                // double-buffered staging of the epilogue
-static constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES) +
-                                  OUT_CHUNKS * OUT_CHUNK_BYTES + 1024 + 512;
-static constexpr int SFA_COL = 256, SFA_COLS = 16, SFB_COL = SFA_COL + STAGES * SFA_COLS, SFB_COLS = 32;
-static_assert(SFB_COL + STAGES * SFB_COLS <= kTmemCols, "tensor memory overflow");
+static constexpr int KS = 8;                        // K = 64 steps per stage
+static constexpr int HALF_BYTES = 128 * BKB;        // one 128-row x 128-byte box
+static constexpr int A_BYTES = 2 * HALF_BYTES;      // this CTA's 128 rows of A, K = 512
+static constexpr int B_BYTES = 2 * HALF_BYTES;      // this CTA's 128 rows of B, K = 512
+static constexpr int SFA_BYTES = KS * 512;
+static constexpr int SFB_BYTES = 2 * KS * 512;
+static constexpr int STAGES = 3;                    // operand ring
+static constexpr int SF_STAGES = 2;                 // scale rings (shared memory and tensor memory)
+static constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + SF_STAGES * (SFA_BYTES + SFB_BYTES) + 1024 + 512;
+static constexpr int SFA_COL = 256, SFA_COLS = KS * 4, SFB_COL = SFA_COL + SF_STAGES * SFA_COLS, SFB_COLS = KS * 8;
+static_assert(SFB_COL + SF_STAGES * SFB_COLS <= kTmemCols, "tensor memory overflow");
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory overflow");
-static constexpr int kThreadsPair = 512;           // 16 warps, see the role list in the kernel
+static constexpr int kThreadsPair = 512;
 }  // namespace pair
-
-// Walks the (tile, K-step) sequence of one cluster.
-struct StageCursor {
-  int t, kt, k_tiles, num_tiles, step;
-  __device__ StageCursor(int first_tile, int step_, int num_tiles_, int k_tiles_)
-      : t(first_tile), kt(0), k_tiles(k_tiles_), num_tiles(num_tiles_), step(step_) {}
-  __device__ bool valid() const { return t < num_tiles; }
-  __device__ void next() {
-    if (++kt == k_tiles) { kt = 0; t += step; }
-  }
-};
 
 template <bool SF_TILED, int OUT_DT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreadsPair, 1)
 linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                         const __grid_constant__ CUtensorMap tma_d, const GemmArgs p) {
+                         const GemmArgs p) {
   using namespace pair;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sA = smem_base;
   const uint32_t sB = sA + STAGES * A_BYTES;
-  const uint32_t sOut = sB + STAGES * B_BYTES;
-  const uint32_t sSFA = sOut + OUT_CHUNKS * OUT_CHUNK_BYTES;
-  const uint32_t sSFB = sSFA + STAGES * SFA_BYTES;
-  const uint32_t bars = sSFB + STAGES * SFB_BYTES;
-  const uint32_t full_bar = bars;                     // [STAGES] leader: A/B of both CTAs landed and all scales in TMEM
-  const uint32_t sffull_bar = bars + 8 * STAGES;      // [STAGES] local: scale bytes landed
-  const uint32_t empty_bar = bars + 24 * STAGES;      // [STAGES] local: MMAs that used the stage are done
-  const uint32_t tfull_bar = bars + 32 * STAGES;      // local: accumulator complete
-  const uint32_t tempty_bar = tfull_bar + 8;          // leader: 8 epilogue warps drained the accumulator
-  const uint32_t sffree_bar = tempty_bar + 8;         // [STAGES] local: 4 scale warps have read the slot
-  const uint32_t ready_word = sffree_bar + 8 * STAGES;   // leader: number of stages the watcher has seen complete
+  const uint32_t sSFA = sB + STAGES * B_BYTES;
+  const uint32_t sSFB = sSFA + SF_STAGES * SFA_BYTES;
+  const uint32_t bars = sSFB + SF_STAGES * SFB_BYTES;
+  const uint32_t full_bar = bars;                     // [STAGES] leader: operands of both CTAs landed + all scales in TMEM
+  const uint32_t empty_bar = full_bar + 8 * STAGES;   // [STAGES] both: MMAs that used the stage are done
+  const uint32_t sffull_bar = empty_bar + 8 * STAGES; // [SF_STAGES] local: scale bytes landed
+  const uint32_t sffree_bar = sffull_bar + 8 * SF_STAGES;   // [SF_STAGES] local: 4 scale warps have read the slot
+  const uint32_t tfull_bar = sffree_bar + 8 * SF_STAGES;    // both: accumulator complete
+  const uint32_t tempty_bar = tfull_bar + 8;          // leader: 16 epilogue warps drained the accumulator
+  const uint32_t ready_word = tempty_bar + 8;         // leader: stages the watcher has seen complete
   const uint32_t tmem_slot = ready_word + 8;
   uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
@@ -100,22 +86,24 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   const uint32_t rank = cluster_ctarank();
   const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
   const int num_tiles = p.tiles_m * p.tiles_n;
-  const int k_tiles = (p.KT + K64_PER_STAGE - 1) / K64_PER_STAGE;
+  const int k_tiles = (p.KT + KS - 1) / KS;
+  const int last_nk = p.KT - (k_tiles - 1) * KS;      // K = 64 steps in the last stage of a tile
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar + 8 * s, 9);          // producer's expect_tx arrival + 8 scale warps
-      mbar_init(sffull_bar + 8 * s, 1);
+      mbar_init(full_bar + 8 * s, 9);           // producer's expect_tx arrival + 8 scale warps
       mbar_init(empty_bar + 8 * s, 1);
+    }
+    for (int s = 0; s < SF_STAGES; ++s) {
+      mbar_init(sffull_bar + 8 * s, 1);
       mbar_init(sffree_bar + 8 * s, 4);
     }
     mbar_init(tfull_bar, 1);
-    mbar_init(tempty_bar, 16);          // 8 epilogue warps in each CTA
+    mbar_init(tempty_bar, 16);                  // 8 epilogue warps in each CTA
     st_shared_release(ready_word, 0);
     fence_barrier_init();
     prefetch_tmap(&tma_a);
     prefetch_tmap(&tma_b);
-    prefetch_tmap(&tma_d);
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, kTmemCols);
@@ -131,8 +119,10 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     // ------------------------------------------------------------------ TMA producer (A and B)
     if (lane == 0) {
       uint32_t s = 0, ph = 0;
-      int it = 0;
       bool ok = true;
+      uint32_t leader_full[STAGES];
+#pragma unroll
+      for (int i = 0; i < STAGES; ++i) leader_full[i] = map_to_cta(full_bar + 8 * i, 0);
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
@@ -140,18 +130,13 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         const int nb0 = tn * BN + (int)rank * 128;        // this CTA's rows of B
         for (int kt = 0; kt < k_tiles; ++kt) {
           if (!mbar_wait(empty_bar + 8 * s, ph ^ 1)) { atomicExch(p.status, kStatusTimeoutProducer); ok = false; break; }
-          AC4K_TRACEC(it, 2);
-          ++it;
-          const uint32_t leader_full = map_to_cta(full_bar + 8 * s, 0);
-          if (rank == 0) mbar_arrive_expect_tx(full_bar + 8 * s, ((p.dbg & 512) ? 1 : 2) * (A_BYTES + B_BYTES));
-          if ((p.dbg & 512) && rank == 1) { if (++s == STAGES) { s = 0; ph ^= 1; } continue; }
-          if ((p.dbg & 256) && rank == 0) {
-            tma_load_2d_local(sA + s * A_BYTES, &tma_a, kt * BKB, m0, full_bar + 8 * s);
-            tma_load_2d_local(sB + s * B_BYTES, &tma_b, kt * BKB, nb0, full_bar + 8 * s);
-          } else {
-            tma_load_2d_pair(sA + s * A_BYTES, &tma_a, kt * BKB, m0, leader_full);
-            tma_load_2d_pair(sB + s * B_BYTES, &tma_b, kt * BKB, nb0, leader_full);
-          }
+          const uint32_t lf = s == 0 ? leader_full[0] : (s == 1 ? leader_full[1] : leader_full[2]);
+          if (rank == 0) mbar_arrive_expect_tx(full_bar + 8 * s, 2 * (A_BYTES + B_BYTES));
+          const int kb = kt * (2 * BKB);
+          tma_load_2d_pair(sA + s * A_BYTES, &tma_a, kb, m0, lf);
+          tma_load_2d_pair(sB + s * B_BYTES, &tma_b, kb, nb0, lf);
+          tma_load_2d_pair(sA + s * A_BYTES + HALF_BYTES, &tma_a, kb + BKB, m0, lf);
+          tma_load_2d_pair(sB + s * B_BYTES + HALF_BYTES, &tma_b, kb + BKB, nb0, lf);
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
@@ -159,54 +144,53 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA)
     if (lane == 0 && rank == 0) {
-      // The MMA pipe accepts a new instruction only as an earlier one retires (about every 128
-      // cycles at N = 256), and whatever this thread does between two issues that takes longer
-      // than that becomes a bubble in the pipe.  So the per-stage bookkeeping is spread over the
-      // gaps between the four MMAs of a stage: the wait for the NEXT stage sits after the first
-      // MMA, the commit after the last.
       constexpr uint32_t idesc = make_idesc_mxf4nvf4(BMP, BN);
-      // Every mbarrier or tcgen05 instruction holds this thread for roughly 75-110 cycles, and four
-      // MMAs (4 x ~92) plus a commit (~109) already fill most of the 512 cycles a stage takes in the
-      // pipe.  Waiting on the stage's barriers is therefore delegated to the watcher warp, which
-      // publishes a running count of ready stages in shared memory; polling that word costs a
-      // shared-memory load (~30 cycles).
-      uint32_t s = 0, it = 0;
+      uint32_t s = 0, sf = 0, it = 0;
       bool ok = true;
       const uint64_t adesc0 = make_smem_desc(sA, 16, 1024, kSwizzle128B);
       const uint64_t bdesc0 = make_smem_desc(sB, 16, 1024, kSwizzle128B);
-      const int last_nk = p.KT - (k_tiles - 1) * K64_PER_STAGE;
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
         for (int kt = 0; kt < k_tiles; ++kt) {
-          AC4K_TRACEC(it, 0);
+          AC4K_TR(0, it, 0);
           uint32_t seen = ld_shared_volatile(ready_word);
           if (seen <= it) {
             const unsigned long long t0 = globaltimer();
             while ((seen = ld_shared_volatile(ready_word)) <= it) {
+              // back off: a hot spin here takes issue slots from the epilogue and scale warps that
+              // share this scheduler, which is exactly what the issuer is waiting for
+              __nanosleep(40);
               if (globaltimer() - t0 > kWaitTimeoutNs) { seen = 0xFFFFFFFFu; break; }
             }
           }
           if (seen == 0xFFFFFFFFu) { ok = false; break; }
           tc_fence_after();
-          const uint32_t t_sfa = tmem_base + SFA_COL + s * SFA_COLS;
-          const uint32_t t_sfb = tmem_base + SFB_COL + s * SFB_COLS;
+          AC4K_TR(0, it, 1);
+          const uint32_t t_sfa = tmem_base + SFA_COL + sf * SFA_COLS;
+          const uint32_t t_sfb = tmem_base + SFB_COL + sf * SFB_COLS;
           const uint64_t adesc = adesc0 + (uint64_t)(s * (A_BYTES >> 4));
           const uint64_t bdesc = bdesc0 + (uint64_t)(s * (B_BYTES >> 4));
-          AC4K_TRACEC(it, 1);
-          if (kt + 1 < k_tiles || last_nk == K64_PER_STAGE) {
-            mma_mxf4nvf4_pair(tmem_base, adesc, bdesc, idesc, t_sfa, t_sfb, kt > 0 ? 1u : 0u);
-            mma_mxf4nvf4_pair(tmem_base, adesc + 2, bdesc + 2, idesc, t_sfa + 4, t_sfb + 8, 1u);
-            mma_mxf4nvf4_pair(tmem_base, adesc + 4, bdesc + 4, idesc, t_sfa + 8, t_sfb + 16, 1u);
-            mma_mxf4nvf4_pair(tmem_base, adesc + 6, bdesc + 6, idesc, t_sfa + 12, t_sfb + 24, 1u);
-          } else {
-            for (int j = 0; j < last_nk; ++j)
-              mma_mxf4nvf4_pair(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, t_sfa + j * 4, t_sfb + j * 8,
+          const int nk = (kt + 1 < k_tiles) ? KS : last_nk;
+          if (nk == KS) {
+#pragma unroll
+            for (int j = 0; j < KS; ++j) {
+              // K step j: box j / 4 of the stage, 32 bytes further inside the 128-byte swizzle atom per step
+              const uint32_t off = (j >> 2) * (HALF_BYTES >> 4) + 2 * (j & 3);
+              mma_mxf4nvf4_pair(tmem_base, adesc + off, bdesc + off, idesc, t_sfa + j * 4, t_sfb + j * 8,
                                 (kt > 0 || j > 0) ? 1u : 0u);
+            }
+          } else {
+            for (int j = 0; j < nk; ++j) {
+              const uint32_t off = (j >> 2) * (HALF_BYTES >> 4) + 2 * (j & 3);
+              mma_mxf4nvf4_pair(tmem_base, adesc + off, bdesc + off, idesc, t_sfa + j * 4, t_sfb + j * 8,
+                                (kt > 0 || j > 0) ? 1u : 0u);
+            }
           }
-          AC4K_TRACEC(it, 3);
+          AC4K_TR(0, it, 3);
           tc_commit_pair_both(empty_bar + 8 * s, 3);                 // stage free in both CTAs
           if (kt == k_tiles - 1) tc_commit_pair_both(tfull_bar, 3);  // accumulator complete in both CTAs
-          AC4K_TRACEC(it, 5);
+          AC4K_TR(0, it, 5);
           ++it;
+          sf ^= 1;
           if (++s == STAGES) s = 0;
         }
       }
@@ -214,21 +198,18 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     }
   } else if (warp == 11) {
     // ------------------------------------------------------------------ barrier watcher (leader CTA)
-    // Waits, in the order the MMA issuer consumes them, for the accumulator hand-back (first stage
-    // of a tile) and for each stage's operands and scales, and publishes the count.
     if (lane == 0 && rank == 0) {
       uint32_t s = 0, ph = 0, acc_ph = 0, count = 0;
       bool ok = true;
-      for (StageCursor c(cluster_id, num_clusters, num_tiles, k_tiles); c.valid(); c.next()) {
-        if (c.kt == 0) {
-          ok = mbar_wait(tempty_bar, acc_ph ^ 1);
-          acc_ph ^= 1;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+        ok = mbar_wait(tempty_bar, acc_ph ^ 1);
+        acc_ph ^= 1;
+        for (int kt = 0; kt < k_tiles && ok; ++kt) {
+          ok = mbar_wait(full_bar + 8 * s, ph);
+          if (!ok) break;
+          st_shared_release(ready_word, ++count);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
-        ok = ok && mbar_wait(full_bar + 8 * s, ph);
-        if (!ok) break;
-        AC4K_TRACEC(count, 4);
-        st_shared_release(ready_word, ++count);
-        if (++s == STAGES) { s = 0; ph ^= 1; }
       }
       if (!ok) {
         atomicExch(p.status, kStatusTimeoutMma);
@@ -237,107 +218,118 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     }
   } else if (warp == 10) {
     // ------------------------------------------------------------------ scale feeder
-    // Issues the bulk copies of the scale bytes into the shared-memory scale ring as soon as the
-    // four scale warps have read a slot into registers: the scales run ahead of the operands
-    // and never sit on the MMA's critical path.
     if (lane == 0) {
       uint32_t s = 0, ph = 0;
-      for (StageCursor c(cluster_id, num_clusters, num_tiles, k_tiles); c.valid(); c.next()) {
-        if (!mbar_wait(sffree_bar + 8 * s, ph ^ 1)) { atomicExch(p.status, kStatusTimeoutSf); break; }
+      bool ok = true;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
         int tm, tn;
-        tile_coords(c.t, p.tiles_m, p.tiles_n, tm, tn);
+        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
         const int m0 = tm * BMP + (int)rank * 128, n0 = tn * BN;
-        const int nk = min(K64_PER_STAGE, p.KT - c.kt * K64_PER_STAGE);
-        const uint32_t bar = sffull_bar + 8 * s;
-        const int64_t k64 = (int64_t)c.kt * K64_PER_STAGE;
-        if (SF_TILED) {
-          const int64_t mt = m0 / 128;
-          const bool a_ok = mt * 128 < p.rows_sfa;
-          const int nb_valid = min(2, (p.rows_sfb - n0) / 128);
-          mbar_arrive_expect_tx(bar, (a_ok ? nk * 512 : 0) + nb_valid * nk * 512);
-          if (a_ok) bulk_load_1d_local(sSFA + s * SFA_BYTES, p.sfa + (mt * p.KT + k64) * 512, nk * 512, bar);
-          for (int nb = 0; nb < nb_valid; ++nb)
-            bulk_load_1d_local(sSFB + s * SFB_BYTES + nb * (K64_PER_STAGE * 512),
-                               p.sfb + ((int64_t)(n0 / 128 + nb) * p.KT + k64) * 512, nk * 512, bar);
-        } else {
-          const int ra = 4 * max(0, min(128, p.rows_sfa - m0)), rb = 4 * min(BN, p.rows_sfb - n0);
-          mbar_arrive_expect_tx(bar, nk * (ra + rb));
-          for (int j = 0; j < nk; ++j) {
-            if (ra > 0)
-              bulk_load_1d_local(sSFA + s * SFA_BYTES + j * 512, p.sfa + ((k64 + j) * p.rows_sfa + m0) * 4, ra, bar);
-            bulk_load_1d_local(sSFB + s * SFB_BYTES + j * 1024, p.sfb + ((k64 + j) * p.rows_sfb + n0) * 4, rb, bar);
+        const int64_t mt = m0 / 128;
+        const bool a_ok = SF_TILED ? (mt * 128 < p.rows_sfa) : (m0 < p.rows_sfa);
+        const int nb_valid = min(2, (p.rows_sfb - n0) / 128);                       // tiled layout
+        const int ra = 4 * max(0, min(128, p.rows_sfa - m0)), rb = 4 * min(BN, p.rows_sfb - n0);   // row layout
+        for (int kt = 0; kt < k_tiles; ++kt) {
+          if (!mbar_wait(sffree_bar + 8 * s, ph ^ 1)) { atomicExch(p.status, kStatusTimeoutSf); ok = false; break; }
+          const int nk = (kt + 1 < k_tiles) ? KS : last_nk;
+          const uint32_t bar = sffull_bar + 8 * s;
+          const int64_t k64 = (int64_t)kt * KS;
+          if (SF_TILED) {
+            mbar_arrive_expect_tx(bar, ((a_ok ? 1 : 0) + nb_valid) * nk * 512);
+            if (a_ok) bulk_load_1d_local(sSFA + s * SFA_BYTES, p.sfa + (mt * p.KT + k64) * 512, nk * 512, bar);
+            for (int nb = 0; nb < nb_valid; ++nb)
+              bulk_load_1d_local(sSFB + s * SFB_BYTES + nb * (KS * 512),
+                                 p.sfb + ((int64_t)(n0 / 128 + nb) * p.KT + k64) * 512, nk * 512, bar);
+          } else {
+            mbar_arrive_expect_tx(bar, nk * (ra + rb));
+            for (int j = 0; j < nk; ++j) {
+              if (ra > 0)
+                bulk_load_1d_local(sSFA + s * SFA_BYTES + j * 512, p.sfa + ((k64 + j) * p.rows_sfa + m0) * 4, ra, bar);
+              bulk_load_1d_local(sSFB + s * SFB_BYTES + j * 1024, p.sfb + ((k64 + j) * p.rows_sfb + n0) * 4, rb, bar);
+            }
           }
+          if (++s == SF_STAGES) { s = 0; ph ^= 1; }
         }
-        if (++s == STAGES) { s = 0; ph ^= 1; }
       }
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------------ scale warps
-    // shared memory -> registers -> tensor memory.  A slot of the tensor-memory scale ring is
-    // rewritten once the MMAs that used it have completed (the stage's `empty` barrier).
+    // Lane l of the warp owning TMEM lane quarter q writes, for K step j and row group g, the word
+    // of row 32 g + l into column (j * groups + g) of lane 32 q + l.  A tensor-memory slot is
+    // rewritten once the MMAs of the stage that used it two stages ago are done.
     const int q = warp & 3;
-    uint32_t s = 0, ph = 0;
-    int it = 0;
+    uint32_t s = 0, ph = 0;          // scale rings (depth 2)
+    uint32_t os = 0, oph = 0;        // operand ring position of the current stage (depth 3)
+    uint32_t ps = 0, pph = 0;        // operand ring position of the stage two stages back
+    uint32_t it = 0;
     bool ok = true;
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
-    for (StageCursor cur(cluster_id, num_clusters, num_tiles, k_tiles); cur.valid() && ok; cur.next()) {
-      AC4K_TRACES(it, 0);
-      if (!mbar_wait(sffull_bar + 8 * s, ph)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutSf); ok = false; break; }
-      AC4K_TRACES(it, 1);
-      const uint8_t *a_src = smem_gen + (sSFA + s * SFA_BYTES - smem_base);
-      const uint8_t *b_src = smem_gen + (sSFB + s * SFB_BYTES - smem_base);
-      uint32_t ra[16], rb[32];
-      if (SF_TILED) {
+    uint32_t leader_full[STAGES];
 #pragma unroll
-        for (int j = 0; j < K64_PER_STAGE; ++j) {
-          const uint4 v = *reinterpret_cast<const uint4 *>(a_src + j * 512 + lane * 16);
-          ra[j * 4 + 0] = v.x; ra[j * 4 + 1] = v.y; ra[j * 4 + 2] = v.z; ra[j * 4 + 3] = v.w;
+    for (int i = 0; i < STAGES; ++i) leader_full[i] = map_to_cta(full_bar + 8 * i, 0);
+    for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+      for (int kt = 0; kt < k_tiles; ++kt) {
+        if (warp == 2 && lane == 0) AC4K_TR(2, it, 0);
+        if (!mbar_wait(sffull_bar + 8 * s, ph)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutSf); ok = false; break; }
+        if (warp == 2 && lane == 0) AC4K_TR(2, it, 1);
+        const uint8_t *a_src = smem_gen + (sSFA + s * SFA_BYTES - smem_base);
+        const uint8_t *b_src = smem_gen + (sSFB + s * SFB_BYTES - smem_base);
+        uint32_t ra[32], rb[64];
+        if (SF_TILED) {
 #pragma unroll
-          for (int nb = 0; nb < 2; ++nb) {
-            const uint4 w = *reinterpret_cast<const uint4 *>(b_src + (nb * K64_PER_STAGE + j) * 512 + lane * 16);
-            rb[j * 8 + nb * 4 + 0] = w.x; rb[j * 8 + nb * 4 + 1] = w.y;
-            rb[j * 8 + nb * 4 + 2] = w.z; rb[j * 8 + nb * 4 + 3] = w.w;
+          for (int j = 0; j < KS; ++j) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(a_src + j * 512 + lane * 16);
+            ra[j * 4 + 0] = v.x; ra[j * 4 + 1] = v.y; ra[j * 4 + 2] = v.z; ra[j * 4 + 3] = v.w;
+#pragma unroll
+            for (int nb = 0; nb < 2; ++nb) {
+              const uint4 w = *reinterpret_cast<const uint4 *>(b_src + (nb * KS + j) * 512 + lane * 16);
+              rb[j * 8 + nb * 4 + 0] = w.x; rb[j * 8 + nb * 4 + 1] = w.y;
+              rb[j * 8 + nb * 4 + 2] = w.z; rb[j * 8 + nb * 4 + 3] = w.w;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < KS; ++j) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) ra[j * 4 + g] = reinterpret_cast<const uint32_t *>(a_src + j * 512)[g * 32 + lane];
+#pragma unroll
+            for (int g = 0; g < 8; ++g) rb[j * 8 + g] = reinterpret_cast<const uint32_t *>(b_src + j * 1024)[g * 32 + lane];
           }
         }
-      } else {
-#pragma unroll
-        for (int j = 0; j < K64_PER_STAGE; ++j) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) ra[j * 4 + g] = reinterpret_cast<const uint32_t *>(a_src + j * 512)[g * 32 + lane];
-#pragma unroll
-          for (int g = 0; g < 8; ++g) rb[j * 8 + g] = reinterpret_cast<const uint32_t *>(b_src + j * 1024)[g * 32 + lane];
+        if (warp == 2 && lane == 0) AC4K_TR(2, it, 2);
+        if (it >= SF_STAGES) {
+          if (!mbar_wait(empty_bar + 8 * ps, pph)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutSf); ok = false; break; }
+          if (++ps == STAGES) { ps = 0; pph ^= 1; }
         }
+        if (warp == 2 && lane == 0) AC4K_TR(2, it, 3);
+        tc_fence_after();
+        tmem_st_32x32b_x32(lane_base + SFA_COL + s * SFA_COLS, ra);
+        tmem_st_32x32b_x64(lane_base + SFB_COL + s * SFB_COLS, rb);
+        tmem_st_wait();
+        if (warp == 2 && lane == 0) AC4K_TR(2, it, 5);
+        tc_fence_before();
+        __syncwarp();
+        // The shared-memory slot goes back to the feeder only now, after tcgen05.st has consumed the
+        // registers: an arrive issued right behind the loads can overtake them (they queue behind the
+        // tensor core's operand reads for hundreds of cycles), and the refill then landed under a
+        // warp that was still reading - seen as scales of two stages ahead in one lane quarter.
+        if (lane == 0) mbar_arrive(sffree_bar + 8 * s);
+        if (lane == 0) mbar_arrive_cluster(os == 0 ? leader_full[0] : (os == 1 ? leader_full[1] : leader_full[2]));
+        ++it;
+        if (++s == SF_STAGES) { s = 0; ph ^= 1; }
+        if (++os == STAGES) { os = 0; oph ^= 1; }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(sffree_bar + 8 * s);      // this warp holds the slot in registers
-      AC4K_TRACES(it, 2);
-      // tensor-memory slot s is free once the MMAs of the step that last used it are done
-      if (!mbar_wait(empty_bar + 8 * s, ph ^ 1)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutSf); ok = false; break; }
-      AC4K_TRACES(it, 3);
-      tc_fence_after();
-      tmem_st_32x32b_x16(lane_base + SFA_COL + s * SFA_COLS, ra);
-      tmem_st_32x32b_x32(lane_base + SFB_COL + s * SFB_COLS, rb);
-      AC4K_TRACES(it, 4);
-      tmem_st_wait();
-      AC4K_TRACES(it, 5);
-      tc_fence_before();
-      __syncwarp();
-      if (warp == 2 && lane == 0) AC4K_TRACEC(it, 6);
-      ++it;
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(full_bar + 8 * s, 0));
-      if (++s == STAGES) { s = 0; ph ^= 1; }
     }
+    (void)oph;
   } else {
     // ------------------------------------------------------------------ epilogue (warps 6-9, 12-15)
-    // Two warps per tensor-memory lane quarter, each draining 128 of the 256 accumulator columns.
-    // Phase 1: tcgen05.ld, * alpha, + bias, pack to 16 bit, all into registers, then the
-    // accumulator is handed back to the MMA issuer at once.  Phase 2 (two rounds of swizzled
-    // staging + TMA store per tile) overlaps the next tile's main loop.
+    // Two warps per tensor-memory lane quarter, 128 accumulator columns each.  Phase 1: tcgen05.ld,
+    // * alpha, + bias, pack to 16 bit, all into registers; then the accumulator goes back to the
+    // MMA issuer.  Phase 2: each thread stores its 256-byte row segment; it overlaps the next
+    // tile's main loop.
     using T = typename OutT<OUT_DT>::type;
     const int q = warp & 3;
     const int half = warp >= 12 ? 1 : 0;
-    const int row_l = q * 32 + lane;
-    const bool store_thread = (warp == 6 && lane == 0);
     uint32_t acc_ph = 0;
     int ti = 0;
     const float alpha = __fmul_rn(__ldg(p.a_gs), __ldg(p.b_gs));
@@ -346,68 +338,73 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     for (int t = cluster_id; t < num_tiles; t += num_clusters) {
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
-      const int m0 = tm * BMP + (int)rank * 128, n0 = tn * BN;
+      const int row = tm * BMP + (int)rank * 128 + q * 32 + lane;
+      const int col0 = tn * BN + half * 128;
       if (!mbar_wait(tfull_bar, acc_ph)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue); break; }
       tc_fence_after();
-      if (warp == 6 && lane == 0) AC4K_TRACEC(120 + ti, 7);
+      if (warp == 6 && lane == 0) AC4K_TR(1, ti, 0);
       uint32_t w[64];
+      if (p.bias == nullptr) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_row + c * 32, r);
-        tmem_ld_wait();
-        const int col = n0 + half * 128 + c * 32;
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32_sync(t_row + c * 32, r);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float v0 = __fmul_rn(__uint_as_float(r[2 * i]), alpha), v1 = __fmul_rn(__uint_as_float(r[2 * i + 1]), alpha);
-          if (p.bias != nullptr) {
+          for (int i = 0; i < 16; ++i)
+            w[c * 16 + i] = (OUT_DT == AC4K_DT_BF16) ? scale_pack_bf16x2(r[2 * i], r[2 * i + 1], alpha)
+                                                     : scale_pack_f16x2(r[2 * i], r[2 * i + 1], alpha);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32_sync(t_row + c * 32, r);
+          const int col = col0 + c * 32;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float v0 = __fmul_rn(__uint_as_float(r[2 * i]), alpha), v1 = __fmul_rn(__uint_as_float(r[2 * i + 1]), alpha);
             if (col + 2 * i < p.N) v0 = __fadd_rn(v0, load_bias(p.bias, p.bias_dt, col + 2 * i));
             if (col + 2 * i + 1 < p.N) v1 = __fadd_rn(v1, load_bias(p.bias, p.bias_dt, col + 2 * i + 1));
-          }
-          if (OUT_DT == AC4K_DT_BF16) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
-            w[c * 16 + i] = *reinterpret_cast<uint32_t *>(&h);
-          } else {
-            __half2 h = __floats2half2_rn(v0, v1);
-            w[c * 16 + i] = *reinterpret_cast<uint32_t *>(&h);
+            if (OUT_DT == AC4K_DT_BF16) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+              w[c * 16 + i] = *reinterpret_cast<uint32_t *>(&h);
+            } else {
+              __half2 h = __floats2half2_rn(v0, v1);
+              w[c * 16 + i] = *reinterpret_cast<uint32_t *>(&h);
+            }
           }
         }
       }
       tc_fence_before();
       __syncwarp();
-      if (warp == 6 && lane == 0 && p.trace != nullptr && cluster_id == 0) p.trace[((size_t)rank * 128 + 112 + ti) * 8 + 7] = clock64();
+      if (warp == 6 && lane == 0) AC4K_TR(1, ti, 1);
       if (lane == 0) mbar_arrive_cluster(leader_tempty);
-      if (!(p.dbg & 8)) {
-        // staging buffer `half` holds columns [half*128 + round*64, +64) in round `round`
-#pragma unroll
-        for (int round = 0; round < 2; ++round) {
-          if (store_thread) bulk_wait_group_read0();     // earlier stores have finished reading the staging
-          named_barrier_sync(1, 256);
-          // 128-byte-swizzled staging: 16-byte chunk index XOR (row % 8), as the TMA store expects
-          uint8_t *buf = smem_gen + (sOut + half * OUT_CHUNK_BYTES - smem_base) + row_l * 128;
+      if (row < p.M && !(p.dbg & 8)) {
+        T *dst = static_cast<T *>(p.D) + (int64_t)row * p.N + col0;
+        // Each lane owns one row, so a store instruction touches 32 different rows however it is
+        // shaped; 32-byte stores make every one of those touches a full sector, and a short pause
+        // between them keeps the SM's memory pipe free for the barrier and shared-memory traffic of
+        // the warps that run the next tile's main loop (the stores have a whole tile time to finish).
+        const bool row_aligned = ((int64_t)p.N * sizeof(T)) % 32 == 0 && (reinterpret_cast<uintptr_t>(p.D) & 31) == 0;
+        if (col0 + 128 <= p.N && row_aligned) {
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const int chunk = i ^ (row_l & 7);
-            *reinterpret_cast<uint4 *>(buf + chunk * 16) =
-                make_uint4(w[round * 32 + 4 * i], w[round * 32 + 4 * i + 1], w[round * 32 + 4 * i + 2],
-                           w[round * 32 + 4 * i + 3]);
+            st_global_v8(reinterpret_cast<uint8_t *>(dst) + 32 * i, w[8 * i], w[8 * i + 1], w[8 * i + 2], w[8 * i + 3],
+                         w[8 * i + 4], w[8 * i + 5], w[8 * i + 6], w[8 * i + 7]);
+            __nanosleep(200);
           }
-          fence_proxy_async_smem();
-          named_barrier_sync(1, 256);
-          if (store_thread) {
+        } else {
+          // ragged right edge or 16-byte-aligned rows (N % 8 == 0 on this path): 16-byte groups
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int col0 = n0 + h * 128 + round * 64;
-              if (m0 < p.M && col0 < p.N) tma_store_2d(&tma_d, col0 * (int)sizeof(T), m0, sOut + h * OUT_CHUNK_BYTES);
-            }
-            bulk_commit_group();
-          }
+          for (int i = 0; i < 16; ++i)
+            if (col0 + 8 * i < p.N)
+              __stcs(reinterpret_cast<uint4 *>(dst) + i, make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]));
         }
       }
-      if (ti < 7) ++ti;
+      if (warp == 6 && lane == 0) AC4K_TR(1, ti, 2);
+      ++ti;
       acc_ph ^= 1;
     }
-    if (store_thread) bulk_wait_group0();
   }
 
   tc_fence_before();
@@ -420,8 +417,8 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
 }
 
 template <bool SF_TILED, int OUT_DT>
-static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &td, const GemmArgs &args,
-                       int sms, cudaStream_t stream) {
+static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const GemmArgs &args, int sms,
+                       cudaStream_t stream) {
   auto kern = linear_nvfp4_2cta_kernel<SF_TILED, OUT_DT>;
   static bool attr_set[64] = {};
   int dev = 0;
@@ -453,23 +450,24 @@ static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUten
   const int num_tiles = args.tiles_m * args.tiles_n;
   int clusters = max_clusters[dev];
   if (num_tiles < clusters) clusters = num_tiles;
-  kern<<<2 * clusters, pair::kThreadsPair, pair::SMEM_BYTES, stream>>>(ta, tb, td, args);
+  kern<<<2 * clusters, pair::kThreadsPair, pair::SMEM_BYTES, stream>>>(ta, tb, args);
   AC4K_LAUNCH_CHECK("linear_nvfp4_2cta_kernel");
   return 0;
 }
 
 int launch_linear_2cta(int d_dtype, bool sf_tiled, const CUtensorMap &ta, const CUtensorMap &tb,
                        const CUtensorMap &td, GemmArgs args, cudaStream_t stream) {
+  (void)td;
   DeviceInfo di;
   if (int e = get_device_info(&di)) return e;
   args.tiles_m = (int)ceil_div(args.M, pair::BMP);
   args.tiles_n = (int)ceil_div(args.N, pair::BN);
   if (d_dtype == AC4K_DT_BF16)
-    return sf_tiled ? launch_pair<true, AC4K_DT_BF16>(ta, tb, td, args, di.sms, stream)
-                    : launch_pair<false, AC4K_DT_BF16>(ta, tb, td, args, di.sms, stream);
+    return sf_tiled ? launch_pair<true, AC4K_DT_BF16>(ta, tb, args, di.sms, stream)
+                    : launch_pair<false, AC4K_DT_BF16>(ta, tb, args, di.sms, stream);
   if (d_dtype == AC4K_DT_FP16)
-    return sf_tiled ? launch_pair<true, AC4K_DT_FP16>(ta, tb, td, args, di.sms, stream)
-                    : launch_pair<false, AC4K_DT_FP16>(ta, tb, td, args, di.sms, stream);
+    return sf_tiled ? launch_pair<true, AC4K_DT_FP16>(ta, tb, args, di.sms, stream)
+                    : launch_pair<false, AC4K_DT_FP16>(ta, tb, args, di.sms, stream);
   return fail(AC4K_ERR_UNSUPPORTED, "the CTA-pair kernel stores 16-bit outputs only");
 }
 

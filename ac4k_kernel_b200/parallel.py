@@ -81,3 +81,46 @@ def column_parallel_linear(x, x_scale, x_global_scale, w_shard, w_shard_scale, w
     local_out = linear(x, x_scale, x_global_scale, w_shard, w_shard_scale, w_global_scale,
                        bias=bias_shard, out=local_out)
     return gather_columns(local_out, gathered, group), local_out
+
+
+def column_parallel_linear_pipelined(x, x_scale, x_global_scale, w_shard, w_shard_scale, w_global_scale,
+                                     gathered, bias_shard=None, chunks=4, group=None, comm_stream=None):
+    """Column-parallel step with the exchange overlapped with the GEMM.
+
+    The M rows are cut into `chunks` blocks (multiples of 128 rows, so 128x4 scale tiles slice
+    cleanly).  Block i is computed straight into this rank's slab of `gathered` ([w, M, N/w]) and
+    then sent to every peer with grouped NCCL send/recv on `comm_stream` while block i+1 is being
+    computed.  Results are identical to `column_parallel_linear`.  Returns `gathered`; the caller
+    must wait on `comm_stream` (the function leaves the current stream waiting on it).
+    """
+    from .ops.linear import linear
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    m = x.shape[0]
+    if x_scale.dim() != 5:
+        raise ValueError("the pipelined variant slices activations by 128-row scale tiles (sf_layout='128x4')")
+    per = -(-m // chunks)
+    per = -(-per // 128) * 128
+    main = torch.cuda.current_stream()
+    if comm_stream is None:
+        comm_stream = torch.cuda.Stream()
+    for r0 in range(0, m, per):
+        r1 = min(m, r0 + per)
+        out_view = gathered[rank, r0:r1]
+        linear(x[r0:r1], x_scale[r0 // 128:-(-r1 // 128)], x_global_scale, w_shard, w_shard_scale,
+               w_global_scale, bias=bias_shard, out=out_view)
+        if world > 1:
+            ready = torch.cuda.Event()
+            ready.record(main)
+            with torch.cuda.stream(comm_stream):
+                comm_stream.wait_event(ready)
+                ops = []
+                for peer in range(world):
+                    if peer == rank:
+                        continue
+                    ops.append(dist.P2POp(dist.isend, out_view, peer, group))
+                    ops.append(dist.P2POp(dist.irecv, gathered[peer, r0:r1], peer, group))
+                for req in dist.batch_isend_irecv(ops):
+                    req.wait()
+    main.wait_stream(comm_stream)
+    return gathered
