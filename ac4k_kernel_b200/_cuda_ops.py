@@ -187,6 +187,47 @@ def linear_nvfp4(D, A, A_sf, A_global_scale, B, B_sf, B_global_scale, bias):
               "linear_nvfp4")
 
 
+def linear_nvfp4_gather(dst_ptrs, ldd, col_off, D_local, A, A_sf, A_global_scale, B, B_sf, B_global_scale, bias):
+    """The GEMM of `linear_nvfp4` storing every tile to several [M, ldd] buffers at columns
+    [col_off, col_off + N): the all-gather of the column-parallel layer fused into the epilogue
+    (no counterpart in the reference).  `dst_ptrs`: device addresses of the destinations, this GPU's
+    own buffer first; `D_local`: this GPU's buffer as a [M, ldd] tensor (for dtype, device, stream).
+    N is taken from B."""
+    _require(D_local.dim() == 2 and D_local.is_cuda and D_local.is_contiguous(), "d must be a contiguous 2d matrix")
+    _require(D_local.dtype in (torch.bfloat16, torch.float16), "d must be bfloat16 or half")
+    M = D_local.size(0)
+    _require(D_local.size(1) == ldd, "ldd must be the row length of d")
+    _check_tensor(A, torch.uint8, "a")
+    _check_tensor(B, torch.uint8, "b")
+    _require(A.dim() == 2 and B.dim() == 2 and A.size(0) == M and A.size(1) == B.size(1), "a / b shapes do not match")
+    N, K = B.size(0), A.size(1) * 2
+    kt = _ceil_div(K, 64)
+    _check_tensor(A_sf, torch.float8_e4m3fn, "scale_a")
+    _check_tensor(B_sf, torch.float8_e4m3fn, "scale_b")
+    if A_sf.dim() == 3:
+        layout = SF_AC4K
+        _require(list(A_sf.shape) == [kt, _align_up(M, 16), 4], "scale_a has an invalid shape")
+        _require(list(B_sf.shape) == [kt, _align_up(N, 16), 4], "scale_b has an invalid shape")
+    else:
+        layout = SF_TILE128X4
+        _require(list(A_sf.shape) == [_ceil_div(M, 128), kt, 32, 4, 4], "scale_a has an invalid shape")
+        _require(list(B_sf.shape) == [_ceil_div(N, 128), kt, 32, 4, 4], "scale_b has an invalid shape")
+    _check_tensor(A_global_scale, torch.float32, "global_scale_a")
+    _check_tensor(B_global_scale, torch.float32, "global_scale_b")
+    bias_ptr, bias_dt = None, 0
+    if bias is not None:
+        _require(bias.dtype in _DT and bias.is_cuda and bias.is_contiguous(), "bias must be a contiguous cuda tensor")
+        _require(bias.dim() == 2 and bias.size(0) == 1 and bias.size(1) == N, f"bias must be [1, {N}]")
+        bias_ptr, bias_dt = bias.data_ptr(), _DT[bias.dtype]
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*[int(p) for p in dst_ptrs])
+    with torch.cuda.device(D_local.device):
+        check(LIB.ac4k_linear_nvfp4_gather(arr, len(dst_ptrs), int(ldd), int(col_off), _DT[D_local.dtype],
+                                           A.data_ptr(), A_sf.data_ptr(), A_global_scale.data_ptr(),
+                                           B.data_ptr(), B_sf.data_ptr(), B_global_scale.data_ptr(),
+                                           bias_ptr, bias_dt, M, N, K, layout, _stream(D_local)),
+              "linear_nvfp4_gather")
+
+
 def global_scale_bf16(out, input, max_scale):
     """out[()] = max|input| / max_scale on the device; stands in for the reference's Triton
     amax kernel (python/ac4k_kernel/ops/quant.py:21-59)."""

@@ -39,10 +39,16 @@ struct Cfg {
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory overflow");
 };
 
+static constexpr int kMaxDst = 8;     // output destinations of one launch (this GPU + up to 7 peers)
+
 struct GemmArgs {
   const uint8_t *sfa;
   const uint8_t *sfb;
-  void *D;
+  void *D;              // first (or only) destination
+  void *D_more[kMaxDst - 1];   // further destinations of the same tile stores (pair kernel only), n_dst - 1 used
+  int n_dst;            // 1 for the plain GEMM
+  int64_t ldd;          // leading dimension of every destination, in elements (N for the plain GEMM)
+  int64_t col_off;      // first destination column of this launch's N columns (0 for the plain GEMM)
   const float *a_gs;
   const float *b_gs;
   const void *bias;
@@ -124,6 +130,6 @@ int get_device_info(DeviceInfo *out);
 int get_tmap(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUtensorMap *out);
 // 2-CTA kernel launcher (linear_nvfp4_2cta.cu); D must be bf16/fp16 with N % 8 == 0
 int launch_linear_2cta(int d_dtype, bool sf_tiled, const CUtensorMap &ta, const CUtensorMap &tb,
-                       const CUtensorMap &td, GemmArgs args, cudaStream_t stream);
+                       GemmArgs args, cudaStream_t stream);
 
 }  // namespace ac4k

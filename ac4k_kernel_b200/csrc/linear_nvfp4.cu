@@ -22,6 +22,8 @@
 #include <mutex>
 #include <vector>
 
+#include <cstring>
+
 #include "gemm_common.cuh"
 
 namespace ac4k {
@@ -445,10 +447,16 @@ static SplitPlan plan_split(int64_t M, int64_t N, int64_t K, int bn, int sms) {
 
 // ws_mode: 0 = workspace from the stream-ordered allocator (cudaMallocAsync / cudaFreeAsync),
 //          1 = caller-provided workspace of ws_capacity bytes (no allocation in this call)
+// `more`: further destinations that receive the same tile stores (the fused all-gather), each a
+// [M, ldd] buffer written at columns [col_off, col_off + N); NULL / 0 for the plain GEMM, which
+// writes D as a dense [M, N] matrix.
+struct OutSpec { void *const *more; int n_more; int64_t ldd; int64_t col_off; };
+
 static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, const float *A_gs,
                        const void *B, const void *B_sf, const float *B_gs, const void *bias,
                        int bias_dtype, int64_t M, int64_t N, int64_t K, int sf_layout,
-                       cudaStream_t stream, int ws_mode, float *ws_fixed, size_t ws_capacity) {
+                       cudaStream_t stream, int ws_mode, float *ws_fixed, size_t ws_capacity,
+                       const OutSpec *out = nullptr) {
   if (M < 0 || N < 0 || K < 0) return fail(AC4K_ERR_SHAPE, "negative dimension");
   if (d_dtype < 0 || d_dtype > 2) return fail(AC4K_ERR_ENUM, "unknown d_dtype %d", d_dtype);
   if (bias && (bias_dtype < 0 || bias_dtype > 2)) return fail(AC4K_ERR_ENUM, "unknown bias_dtype %d", bias_dtype);
@@ -474,8 +482,13 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
   // 128 x 128 tiles.  g_force_bn: 128 / 256 force the single-CTA kernel, 512 forces pairs.
   const bool pair_ok = d_dtype != AC4K_DT_FP32 && (N % 8 == 0);
   bool use_pair = pair_ok && M > 128 && N > 128;
+  if (out) {
+    // strided / multi-destination output exists in the pair kernel only
+    if (!pair_ok) return fail(AC4K_ERR_UNSUPPORTED, "the gathered output needs a 16-bit output type and N %% 8 == 0");
+    use_pair = true;
+  }
   int bn = N > 128 ? 256 : 128;
-  if (g_force_bn == 128 || g_force_bn == 256) { use_pair = false; bn = g_force_bn; }
+  if (!out && (g_force_bn == 128 || g_force_bn == 256)) { use_pair = false; bn = g_force_bn; }
   if (g_force_bn == 512 && pair_ok) use_pair = true;
   SplitPlan pl{1, (int)ceil_div(K / 64, K64_PER_STAGE), 0};
   if (!use_pair) {
@@ -486,16 +499,24 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
       return fail(AC4K_ERR_SHAPE, "split-K workspace of %zu bytes exceeds the fixed scratch of %zu bytes",
                   pl.ws_bytes, ws_capacity);
   }
-  CUtensorMap ta, tb, td;
+  CUtensorMap ta, tb;
   if (int e = get_tmap(A, M, K / 2, BM, &ta)) return e;
   if (int e = get_tmap(B, N, K / 2, use_pair ? 128 : bn, &tb)) return e;
-  if (use_pair)
-    if (int e = get_tmap(D, M, N * 2, 128, &td)) return e;
 
   GemmArgs a;
   a.sfa = static_cast<const uint8_t *>(A_sf);
   a.sfb = static_cast<const uint8_t *>(B_sf);
   a.D = D;
+  a.n_dst = 1;
+  a.ldd = N;
+  a.col_off = 0;
+  for (int i = 0; i < kMaxDst - 1; ++i) a.D_more[i] = nullptr;
+  if (out) {
+    a.n_dst = 1 + out->n_more;
+    a.ldd = out->ldd;
+    a.col_off = out->col_off;
+    for (int i = 0; i < out->n_more; ++i) a.D_more[i] = out->more[i];
+  }
   a.a_gs = A_gs;
   a.b_gs = B_gs;
   a.bias = bias;
@@ -514,7 +535,7 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
   a.kt_per_split = pl.kt_per_split;
   a.ws = nullptr;
   const bool tiled = sf_layout == AC4K_SF_TILE128X4;
-  if (use_pair) return launch_linear_2cta(d_dtype, tiled, ta, tb, td, a, stream);
+  if (use_pair) return launch_linear_2cta(d_dtype, tiled, ta, tb, a, stream);
   if (pl.splits > 1) {
     if (ws_mode == 1) {
       a.ws = ws_fixed;
@@ -594,4 +615,65 @@ extern "C" int ac4k_linear_nvfp4_noalloc(void *D, int d_dtype, const void *A, co
   }
   return linear_impl(D, d_dtype, A, A_sf, A_gs, B, B_sf, B_gs, bias, bias_dtype, M, N, K, sf_layout,
                      static_cast<cudaStream_t>(stream_), 1, scratch[dev], kFixedScratchBytes);
+}
+
+// ------------------------------------------------------------------------------------------
+// GEMM with the all-gather of its output fused into the epilogue
+// ------------------------------------------------------------------------------------------
+extern "C" int ac4k_linear_nvfp4_gather(void *const *D_dsts, int n_dst, int64_t ldd, int64_t col_off, int d_dtype,
+                                        const void *A, const void *A_sf, const float *A_gs, const void *B,
+                                        const void *B_sf, const float *B_gs, const void *bias, int bias_dtype,
+                                        int64_t M, int64_t N, int64_t K, int sf_layout, ac4k_stream_t stream_) {
+  if (!D_dsts) return fail(AC4K_ERR_NULL, "D_dsts is NULL");
+  if (n_dst < 1 || n_dst > kMaxDst) return fail(AC4K_ERR_SHAPE, "n_dst = %d, must be 1..%d", n_dst, kMaxDst);
+  if (N < 0 || col_off < 0 || ldd < col_off + N) return fail(AC4K_ERR_SHAPE, "columns [col_off, col_off + N) do not fit in ldd");
+  if (ldd % 8 != 0 || col_off % 8 != 0)
+    return fail(AC4K_ERR_ALIGN, "ldd and col_off must be multiples of 8 elements (16-byte row segments)");
+  for (int i = 0; i < n_dst; ++i) {
+    if (!D_dsts[i]) return fail(AC4K_ERR_NULL, "destination %d is NULL", i);
+    if (reinterpret_cast<uintptr_t>(D_dsts[i]) & 15) return fail(AC4K_ERR_ALIGN, "destination %d is not 16-byte aligned", i);
+  }
+  OutSpec out{D_dsts + 1, n_dst - 1, ldd, col_off};
+  return linear_impl(D_dsts[0], d_dtype, A, A_sf, A_gs, B, B_sf, B_gs, bias, bias_dtype, M, N, K, sf_layout,
+                     static_cast<cudaStream_t>(stream_), 0, nullptr, 0, &out);
+}
+
+// ------------------------------------------------------------------------------------------
+// Device buffers that other processes of the node can map (CUDA IPC)
+// ------------------------------------------------------------------------------------------
+extern "C" int ac4k_peer_alloc(int64_t bytes, void **ptr_out, unsigned char handle_out[64]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  if (!ptr_out || !handle_out) return fail(AC4K_ERR_NULL, "a required pointer is NULL");
+  if (bytes <= 0) return fail(AC4K_ERR_SHAPE, "bytes must be positive");
+  void *p = nullptr;
+  AC4K_CUDA_TRY(cudaMalloc(&p, (size_t)bytes));
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return cuda_fail(e, "cudaIpcGetMemHandle");
+  }
+  memcpy(handle_out, &h, 64);
+  *ptr_out = p;
+  return 0;
+}
+
+extern "C" int ac4k_peer_free(void *ptr) {
+  if (ptr) AC4K_CUDA_TRY(cudaFree(ptr));
+  return 0;
+}
+
+extern "C" int ac4k_peer_open(const unsigned char handle[64], void **ptr_out) {
+  if (!handle || !ptr_out) return fail(AC4K_ERR_NULL, "a required pointer is NULL");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  void *p = nullptr;
+  AC4K_CUDA_TRY(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  *ptr_out = p;
+  return 0;
+}
+
+extern "C" int ac4k_peer_close(void *ptr) {
+  if (ptr) AC4K_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+  return 0;
 }

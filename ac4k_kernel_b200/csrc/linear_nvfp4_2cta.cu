@@ -380,25 +380,32 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       if (warp == 6 && lane == 0) AC4K_TR(1, ti, 1);
       if (lane == 0) mbar_arrive_cluster(leader_tempty);
       if (row < p.M && !(p.dbg & 8)) {
-        T *dst = static_cast<T *>(p.D) + (int64_t)row * p.N + col0;
         // Each lane owns one row, so a store instruction touches 32 different rows however it is
         // shaped; 32-byte stores make every one of those touches a full sector, and a short pause
         // between them keeps the SM's memory pipe free for the barrier and shared-memory traffic of
         // the warps that run the next tile's main loop (the stores have a whole tile time to finish).
-        const bool row_aligned = ((int64_t)p.N * sizeof(T)) % 32 == 0 && (reinterpret_cast<uintptr_t>(p.D) & 31) == 0;
-        if (col0 + 128 <= p.N && row_aligned) {
+        // With several destinations (this GPU's buffer and its peers', reached through NVLink) the
+        // same registers are stored once per destination: the all-gather of the output happens here.
+        const int64_t off = (int64_t)row * p.ldd + p.col_off + col0;
+        const bool vec32 = col0 + 128 <= p.N && ((p.ldd | p.col_off) * (int64_t)sizeof(T)) % 32 == 0;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            st_global_v8(reinterpret_cast<uint8_t *>(dst) + 32 * i, w[8 * i], w[8 * i + 1], w[8 * i + 2], w[8 * i + 3],
-                         w[8 * i + 4], w[8 * i + 5], w[8 * i + 6], w[8 * i + 7]);
-            __nanosleep(200);
+        for (int d = 0; d < kMaxDst; ++d) {
+          if (d >= p.n_dst) break;
+          T *dst = static_cast<T *>(d == 0 ? p.D : p.D_more[d - 1]) + off;
+          if (vec32 && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              st_global_v8(reinterpret_cast<uint8_t *>(dst) + 32 * i, w[8 * i], w[8 * i + 1], w[8 * i + 2], w[8 * i + 3],
+                           w[8 * i + 4], w[8 * i + 5], w[8 * i + 6], w[8 * i + 7]);
+              __nanosleep(200);
+            }
+          } else {
+            // ragged right edge or rows that are only 16-byte aligned: 16-byte groups
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (col0 + 8 * i < p.N)
+                __stcs(reinterpret_cast<uint4 *>(dst) + i, make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]));
           }
-        } else {
-          // ragged right edge or 16-byte-aligned rows (N % 8 == 0 on this path): 16-byte groups
-#pragma unroll
-          for (int i = 0; i < 16; ++i)
-            if (col0 + 8 * i < p.N)
-              __stcs(reinterpret_cast<uint4 *>(dst) + i, make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]));
         }
       }
       if (warp == 6 && lane == 0) AC4K_TR(1, ti, 2);
@@ -456,8 +463,7 @@ static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const GemmA
 }
 
 int launch_linear_2cta(int d_dtype, bool sf_tiled, const CUtensorMap &ta, const CUtensorMap &tb,
-                       const CUtensorMap &td, GemmArgs args, cudaStream_t stream) {
-  (void)td;
+                       GemmArgs args, cudaStream_t stream) {
   DeviceInfo di;
   if (int e = get_device_info(&di)) return e;
   args.tiles_m = (int)ceil_div(args.M, pair::BMP);

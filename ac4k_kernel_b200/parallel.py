@@ -124,3 +124,83 @@ def column_parallel_linear_pipelined(x, x_scale, x_global_scale, w_shard, w_shar
                     req.wait()
     main.wait_stream(comm_stream)
     return gathered
+
+
+class PeerOutput:
+    """The gathered output [M, N] (row-major, whole matrix) of the column-parallel layer, one copy
+    per rank, every copy mapped into every rank's process so that a GEMM epilogue can store its
+    tiles to all of them over NVLink.
+
+    The memory comes from the library's `ac4k_peer_alloc` (plain cudaMalloc + CUDA IPC handle); the
+    handles travel through `all_gather_object` of the process group.  `tensor` is this rank's copy
+    as a torch tensor; `ptrs[i]` is the device address, in this process, of rank i's copy.
+    Call `close()` (collective) before the process group is destroyed.
+    """
+
+    def __init__(self, m: int, n: int, dtype=torch.bfloat16, group=None):
+        import ctypes
+        from ._lib import LIB, check
+        if not dist.is_initialized():
+            raise RuntimeError("PeerOutput needs an initialised process group")
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.m, self.n, self.dtype = m, n, dtype
+        nbytes = m * n * torch.empty((), dtype=dtype).element_size()
+        ptr = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        check(LIB.ac4k_peer_alloc(nbytes, ctypes.byref(ptr), handle), "ac4k_peer_alloc")
+        self._own = ptr.value
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle.raw, group=group)
+        self.ptrs = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.ptrs.append(self._own)
+                continue
+            q = ctypes.c_void_p()
+            check(LIB.ac4k_peer_open(h, ctypes.byref(q)), f"ac4k_peer_open(rank {r})")
+            self.ptrs.append(q.value)
+        # this rank's copy as a tensor (CUDA array interface: no copy, this object keeps it alive)
+        typestr = {torch.bfloat16: "<i2", torch.float16: "<f2"}[dtype]
+        holder = type("_Mem", (), {})()
+        holder.__cuda_array_interface__ = {"shape": (m, n), "typestr": typestr, "data": (self._own, False),
+                                           "version": 3, "strides": None}
+        t = torch.as_tensor(holder, device=torch.device("cuda", torch.cuda.current_device()))
+        self.tensor = t.view(dtype) if t.dtype != dtype else t
+        self._holder = holder
+
+    def destinations(self):
+        """Device addresses ordered for this rank: own copy first, then the peers starting with the
+        next rank, so that at any moment different ranks are storing to different peers."""
+        return [self.ptrs[(self.rank + i) % self.world] for i in range(self.world)]
+
+    def close(self):
+        from ._lib import LIB, check
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)              # nobody is still storing into a peer
+        for r, p in enumerate(self.ptrs):
+            if r != self.rank and p is not None:
+                check(LIB.ac4k_peer_close(p), "ac4k_peer_close")
+        self.ptrs = []
+        dist.barrier(group=self.group)              # every mapping is closed before the owners free
+        self.tensor = None
+        if self._own is not None:
+            check(LIB.ac4k_peer_free(self._own), "ac4k_peer_free")
+            self._own = None
+
+
+def column_parallel_linear_fused(x, x_scale, x_global_scale, w_shard, w_shard_scale, w_global_scale,
+                                 peer_out: PeerOutput, bias_shard=None, sync: torch.Tensor | None = None):
+    """Column-parallel step with the all-gather fused into the GEMM epilogue: this rank's kernel
+    stores each finished tile of its [M, N/w] columns into every rank's [M, N] buffer.  A one-element
+    all-reduce on the same stream then orders every rank's reads after every rank's stores.
+    Returns this rank's full [M, N] output (valid on the current stream after the call)."""
+    from . import _cuda_ops
+    lo, _ = shard_bounds(peer_out.n, peer_out.rank, peer_out.world, align=8)
+    _cuda_ops.linear_nvfp4_gather(peer_out.destinations(), peer_out.n, lo, peer_out.tensor, x, x_scale,
+                                  x_global_scale, w_shard, w_shard_scale, w_global_scale, bias_shard)
+    if peer_out.world > 1:
+        if sync is None:
+            sync = torch.zeros(1, dtype=torch.float32, device=x.device)
+        dist.all_reduce(sync, group=peer_out.group)
+    return peer_out.tensor

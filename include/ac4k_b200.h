@@ -119,6 +119,33 @@ int ac4k_linear_nvfp4_noalloc(void *D, int d_dtype, const void *A, const void *A
                               const void *bias, int bias_dtype, int64_t M, int64_t N, int64_t K,
                               int sf_layout, ac4k_stream_t stream);
 
+/* The GEMM of ac4k_linear_nvfp4 with the all-gather of its output fused into the epilogue: every
+ * finished tile is stored to `n_dst` destinations (1..8) instead of one.  No counterpart in the
+ * reference, which is single-GPU; this is the exchange step of the column-parallel layer, where
+ * rank r owns N of the `ldd` output columns and every rank wants the whole [M, ldd] matrix.
+ *   D_dsts[i]: base of a row-major [M, ldd] buffer of `d_dtype` (bf16 or fp16), 16-byte aligned;
+ *              entry 0 is normally this GPU's own buffer, the others are peers' buffers mapped into
+ *              this process (see ac4k_peer_open).  The launch writes columns
+ *              [col_off, col_off + N) of every destination; ldd and col_off are multiples of 8.
+ * Peer stores travel over NVLink as plain st.global (no TMA, no multicast).  They are complete
+ * when the kernel has finished; a peer may read its buffer after it has synchronised with this
+ * GPU's stream past the launch (e.g. a stream-ordered barrier among the ranks). */
+int ac4k_linear_nvfp4_gather(void *const *D_dsts, int n_dst, int64_t ldd, int64_t col_off, int d_dtype,
+                             const void *A, const void *A_sf, const float *A_gs, const void *B,
+                             const void *B_sf, const float *B_gs, const void *bias, int bias_dtype,
+                             int64_t M, int64_t N, int64_t K, int sf_layout, ac4k_stream_t stream);
+
+/* Device buffers that the other processes of the node can map (CUDA IPC), for the destinations of
+ * ac4k_linear_nvfp4_gather.  No counterpart in the reference.
+ *   ac4k_peer_alloc: cudaMalloc on the current device + its 64-byte IPC handle.
+ *   ac4k_peer_open:  maps a buffer another process allocated (handle received by any host-side
+ *                    channel) into this process, enabling peer access; returns its address here.
+ *   ac4k_peer_close / ac4k_peer_free: undo the above (close every mapping before the owner frees). */
+int ac4k_peer_alloc(int64_t bytes, void **ptr_out, unsigned char handle_out[64]);
+int ac4k_peer_open(const unsigned char handle[64], void **ptr_out);
+int ac4k_peer_close(void *ptr);
+int ac4k_peer_free(void *ptr);
+
 #ifdef __cplusplus
 }
 #endif
