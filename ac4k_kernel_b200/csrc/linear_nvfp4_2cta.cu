@@ -60,7 +60,7 @@ static_assert(SMEM_BYTES <= 227 * 1024, "shared memory overflow");
 static constexpr int kThreadsPair = 512;
 }  // namespace pair
 
-template <bool SF_TILED, int OUT_DT>
+template <bool SF_TILED, int OUT_DT, bool GATHER>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreadsPair, 1)
 linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                          const GemmArgs p) {
@@ -379,32 +379,55 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       __syncwarp();
       if (warp == 6 && lane == 0) AC4K_TR(1, ti, 1);
       if (lane == 0) mbar_arrive_cluster(leader_tempty);
+      const int64_t col_base = p.col_off + col0;
       if (row < p.M && !(p.dbg & 8)) {
         // Each lane owns one row, so a store instruction touches 32 different rows however it is
         // shaped; 32-byte stores make every one of those touches a full sector, and a short pause
         // between them keeps the SM's memory pipe free for the barrier and shared-memory traffic of
         // the warps that run the next tile's main loop (the stores have a whole tile time to finish).
-        // With several destinations (this GPU's buffer and its peers', reached through NVLink) the
-        // same registers are stored once per destination: the all-gather of the output happens here.
-        const int64_t off = (int64_t)row * p.ldd + p.col_off + col0;
-        const bool vec32 = col0 + 128 <= p.N && ((p.ldd | p.col_off) * (int64_t)sizeof(T)) % 32 == 0;
+        T *dst = static_cast<T *>(p.D) + (int64_t)row * p.ldd + col_base;
+        const bool vec32 = col0 + 128 <= p.N && ((p.ldd | p.col_off) * (int64_t)sizeof(T)) % 32 == 0 &&
+                           (reinterpret_cast<uintptr_t>(p.D) & 31) == 0;
+        if (vec32) {
 #pragma unroll
-        for (int d = 0; d < kMaxDst; ++d) {
+          for (int i = 0; i < 8; ++i) {
+            st_global_v8(reinterpret_cast<uint8_t *>(dst) + 32 * i, w[8 * i], w[8 * i + 1], w[8 * i + 2], w[8 * i + 3],
+                         w[8 * i + 4], w[8 * i + 5], w[8 * i + 6], w[8 * i + 7]);
+            __nanosleep(200);
+          }
+        } else {
+          // ragged right edge or rows that are only 16-byte aligned: 16-byte groups
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (col0 + 8 * i < p.N)
+              __stcs(reinterpret_cast<uint4 *>(dst) + i, make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]));
+        }
+      }
+      if (GATHER && p.n_dst > 1 && !(p.dbg & 8)) {
+        // Fused all-gather: forward this warp's 32 rows x 256 bytes to the other destinations (peer
+        // GPUs' buffers, reached over NVLink).  The registers hold one row per lane, which would make
+        // every peer store a scatter of 32-byte pieces; NVLink wants long contiguous writes.  So the
+        // block is read back from this GPU's L2 in the other orientation - 16 lanes x 16 bytes cover a
+        // row's 256 bytes, two rows per instruction - and stored to each peer in that shape.
+        __syncwarp();                               // the warp's own stores above are ordered before its loads
+        const int row0 = tm * BMP + (int)rank * 128 + q * 32 + (lane >> 4);
+        const int cchunk = (lane & 15) * 8;         // first column of this lane's 16-byte piece
+        const bool col_ok = col0 + cchunk < p.N;
+        const T *src = static_cast<const T *>(p.D) + col_base + cchunk;
+        uint4 v[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int r = row0 + 2 * i;
+          if (col_ok && r < p.M) v[i] = ld_global_cg_v4(src + (int64_t)r * p.ldd);
+        }
+#pragma unroll
+        for (int d = 1; d < kMaxDst; ++d) {
           if (d >= p.n_dst) break;
-          T *dst = static_cast<T *>(d == 0 ? p.D : p.D_more[d - 1]) + off;
-          if (vec32 && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+          T *peer = static_cast<T *>(p.D_more[d - 1]) + col_base + cchunk;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              st_global_v8(reinterpret_cast<uint8_t *>(dst) + 32 * i, w[8 * i], w[8 * i + 1], w[8 * i + 2], w[8 * i + 3],
-                           w[8 * i + 4], w[8 * i + 5], w[8 * i + 6], w[8 * i + 7]);
-              __nanosleep(200);
-            }
-          } else {
-            // ragged right edge or rows that are only 16-byte aligned: 16-byte groups
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              if (col0 + 8 * i < p.N)
-                __stcs(reinterpret_cast<uint4 *>(dst) + i, make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]));
+          for (int i = 0; i < 16; ++i) {
+            const int r = row0 + 2 * i;
+            if (col_ok && r < p.M) st_global_v4(peer + (int64_t)r * p.ldd, v[i]);
           }
         }
       }
@@ -423,10 +446,10 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   }
 }
 
-template <bool SF_TILED, int OUT_DT>
+template <bool SF_TILED, int OUT_DT, bool GATHER>
 static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const GemmArgs &args, int sms,
                        cudaStream_t stream) {
-  auto kern = linear_nvfp4_2cta_kernel<SF_TILED, OUT_DT>;
+  auto kern = linear_nvfp4_2cta_kernel<SF_TILED, OUT_DT, GATHER>;
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -468,12 +491,23 @@ int launch_linear_2cta(int d_dtype, bool sf_tiled, const CUtensorMap &ta, const 
   if (int e = get_device_info(&di)) return e;
   args.tiles_m = (int)ceil_div(args.M, pair::BMP);
   args.tiles_n = (int)ceil_div(args.N, pair::BN);
-  if (d_dtype == AC4K_DT_BF16)
-    return sf_tiled ? launch_pair<true, AC4K_DT_BF16>(ta, tb, args, di.sms, stream)
-                    : launch_pair<false, AC4K_DT_BF16>(ta, tb, args, di.sms, stream);
-  if (d_dtype == AC4K_DT_FP16)
-    return sf_tiled ? launch_pair<true, AC4K_DT_FP16>(ta, tb, args, di.sms, stream)
-                    : launch_pair<false, AC4K_DT_FP16>(ta, tb, args, di.sms, stream);
+  // the instantiation that forwards tiles to further destinations is separate: its extra registers
+  // and code would otherwise slow the plain GEMM down
+  const bool gather = args.n_dst > 1;
+  if (d_dtype == AC4K_DT_BF16) {
+    if (gather)
+      return sf_tiled ? launch_pair<true, AC4K_DT_BF16, true>(ta, tb, args, di.sms, stream)
+                      : launch_pair<false, AC4K_DT_BF16, true>(ta, tb, args, di.sms, stream);
+    return sf_tiled ? launch_pair<true, AC4K_DT_BF16, false>(ta, tb, args, di.sms, stream)
+                    : launch_pair<false, AC4K_DT_BF16, false>(ta, tb, args, di.sms, stream);
+  }
+  if (d_dtype == AC4K_DT_FP16) {
+    if (gather)
+      return sf_tiled ? launch_pair<true, AC4K_DT_FP16, true>(ta, tb, args, di.sms, stream)
+                      : launch_pair<false, AC4K_DT_FP16, true>(ta, tb, args, di.sms, stream);
+    return sf_tiled ? launch_pair<true, AC4K_DT_FP16, false>(ta, tb, args, di.sms, stream)
+                    : launch_pair<false, AC4K_DT_FP16, false>(ta, tb, args, di.sms, stream);
+  }
   return fail(AC4K_ERR_UNSUPPORTED, "the CTA-pair kernel stores 16-bit outputs only");
 }
 

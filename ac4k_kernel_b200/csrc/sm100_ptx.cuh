@@ -264,6 +264,17 @@ __device__ __forceinline__ void st_global_v8(void *p, uint32_t a, uint32_t b, ui
                : "memory");
 }
 
+// 16-byte global load served by L2 (never by this SM's L1, which may hold a stale line)
+__device__ __forceinline__ uint4 ld_global_cg_v4(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+// 16-byte global store without L1 allocation (used for peer memory)
+__device__ __forceinline__ void st_global_v4(void *p, uint4 v) {
+  asm volatile("st.global.L1::no_allocate.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
 // ---- CTA pairs (cta_group::2) and clusters ----------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
