@@ -19,8 +19,8 @@
 //   warps 2-5   scale warps: scale bytes shared memory -> registers -> tensor memory (tcgen05.st),
 //               one TMEM lane quarter each; 2-deep rings in shared and in tensor memory
 //   warp 10     scale feeder: bulk copies of scale bytes, as soon as the scale warps freed a slot
-//   warp 11     barrier watcher (leader CTA only): waits for accumulator hand-back and for each
-//               stage's operands + scales, publishes the count of ready stages
+//   warp 11     barrier watcher (leader CTA only): waits for each stage's operands + scales and
+//               publishes the count of ready stages
 //   warps 6-9, 12-15  epilogue: tcgen05.ld of 128 accumulator columns per warp into registers
 //               (* alpha, + bias, packed to 16 bit), hand the accumulator back, then store
 // Barriers that gate the MMA live in the leader CTA and are signalled by both CTAs; barriers that
@@ -38,8 +38,15 @@ using namespace ptx;
     if (p.trace != nullptr && cluster_id == 0 && rank == 0 && (it) < 128)                   \
       p.trace[((size_t)(region) * 128 + (it)) * 8 + (ev)] = clock64();                      \
   } while (0)
+// wall-clock (ns) stamps, comparable across the two CTAs of cluster 0
+#define AC4K_TRG(region, it, ev)                                                             \
+  do {                                                                                      \
+    if (p.trace != nullptr && cluster_id == 0 && (it) < 128)                                \
+      p.trace[((size_t)(region) * 128 + (it)) * 8 + (ev)] = globaltimer();                  \
+  } while (0)
 #else
 #define AC4K_TR(region, it, ev) do { } while (0)
+#define AC4K_TRG(region, it, ev) do { } while (0)
 #endif
 
 namespace pair {
@@ -89,6 +96,7 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   const int k_tiles = (p.KT + KS - 1) / KS;
   const int last_nk = p.KT - (k_tiles - 1) * KS;      // K = 64 steps in the last stage of a tile
 
+  if (threadIdx.x == 0) AC4K_TR(3, 0, 0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar + 8 * s, 9);           // producer's expect_tx arrival + 8 scale warps
@@ -114,6 +122,7 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   cluster_sync();          // peer's barriers are initialised before anything is signalled remotely
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(smem_gen + (tmem_slot - smem_base));
+  if (threadIdx.x == 0) AC4K_TR(3, 0, 1);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (A and B)
@@ -149,7 +158,14 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       bool ok = true;
       const uint64_t adesc0 = make_smem_desc(sA, 16, 1024, kSwizzle128B);
       const uint64_t bdesc0 = make_smem_desc(sB, 16, 1024, kSwizzle128B);
+      uint32_t acc_ph = 0;
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+        // the accumulator must have been drained by all 16 epilogue warps of the pair; waited for
+        // here and not through the watcher: it is the last link of the chain between two tiles
+        AC4K_TRG(0, it, 6);
+        if (!mbar_wait(tempty_bar, acc_ph ^ 1)) { ok = false; break; }
+        AC4K_TRG(0, it, 7);
+        acc_ph ^= 1;
         for (int kt = 0; kt < k_tiles; ++kt) {
           AC4K_TR(0, it, 0);
           uint32_t seen = ld_shared_volatile(ready_word);
@@ -165,6 +181,7 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           if (seen == 0xFFFFFFFFu) { ok = false; break; }
           tc_fence_after();
           AC4K_TR(0, it, 1);
+          if (it == 0) AC4K_TR(3, 0, 2);
           const uint32_t t_sfa = tmem_base + SFA_COL + sf * SFA_COLS;
           const uint32_t t_sfb = tmem_base + SFB_COL + sf * SFB_COLS;
           const uint64_t adesc = adesc0 + (uint64_t)(s * (A_BYTES >> 4));
@@ -199,11 +216,9 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   } else if (warp == 11) {
     // ------------------------------------------------------------------ barrier watcher (leader CTA)
     if (lane == 0 && rank == 0) {
-      uint32_t s = 0, ph = 0, acc_ph = 0, count = 0;
+      uint32_t s = 0, ph = 0, count = 0;
       bool ok = true;
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
-        ok = mbar_wait(tempty_bar, acc_ph ^ 1);
-        acc_ph ^= 1;
         for (int kt = 0; kt < k_tiles && ok; ++kt) {
           ok = mbar_wait(full_bar + 8 * s, ph);
           if (!ok) break;
@@ -343,15 +358,18 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       if (!mbar_wait(tfull_bar, acc_ph)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue); break; }
       tc_fence_after();
       if (warp == 6 && lane == 0) AC4K_TR(1, ti, 0);
+      if (lane == 0 && ti < 16) AC4K_TRG(4 + rank, ti * 8 + q + 4 * half, 0);
       uint32_t w[64];
       if (p.bias == nullptr) {
+        // two 64-column loads: each load-and-wait costs a full tensor-memory round trip, and this
+        // drain is on the critical path between two tiles
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32_sync(t_row + c * 32, r);
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[64];
+          tmem_ld_32x32b_x64_sync(t_row + c * 64, r);
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            w[c * 16 + i] = (OUT_DT == AC4K_DT_BF16) ? scale_pack_bf16x2(r[2 * i], r[2 * i + 1], alpha)
+          for (int i = 0; i < 32; ++i)
+            w[c * 32 + i] = (OUT_DT == AC4K_DT_BF16) ? scale_pack_bf16x2(r[2 * i], r[2 * i + 1], alpha)
                                                      : scale_pack_f16x2(r[2 * i], r[2 * i + 1], alpha);
         }
       } else {
@@ -379,7 +397,9 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       __syncwarp();
       if (warp == 6 && lane == 0) AC4K_TR(1, ti, 1);
       if (lane == 0) mbar_arrive_cluster(leader_tempty);
+      if (lane == 0 && ti < 16) AC4K_TRG(4 + rank, ti * 8 + q + 4 * half, 1);
       const int64_t col_base = p.col_off + col0;
+      const bool last_tile = t + num_clusters >= num_tiles;
       if (row < p.M && !(p.dbg & 8)) {
         // Each lane owns one row, so a store instruction touches 32 different rows however it is
         // shaped; 32-byte stores make every one of those touches a full sector, and a short pause
@@ -393,7 +413,7 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           for (int i = 0; i < 8; ++i) {
             st_global_v8(reinterpret_cast<uint8_t *>(dst) + 32 * i, w[8 * i], w[8 * i + 1], w[8 * i + 2], w[8 * i + 3],
                          w[8 * i + 4], w[8 * i + 5], w[8 * i + 6], w[8 * i + 7]);
-            __nanosleep(200);
+            if (!last_tile) __nanosleep(200);      // nothing left to make room for after the last tile
           }
         } else {
           // ragged right edge or rows that are only 16-byte aligned: 16-byte groups
@@ -432,11 +452,13 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         }
       }
       if (warp == 6 && lane == 0) AC4K_TR(1, ti, 2);
+      if (warp == 6 && lane == 0) AC4K_TR(3, 0, 3);
       ++ti;
       acc_ph ^= 1;
     }
   }
 
+  if (threadIdx.x == 0) AC4K_TR(3, 0, 4);
   tc_fence_before();
   __syncthreads();
   cluster_sync();          // neither CTA leaves while the other may still read its memory or barriers
@@ -444,6 +466,7 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, kTmemCols);
   }
+  if (threadIdx.x == 0) AC4K_TR(3, 0, 5);
 }
 
 template <bool SF_TILED, int OUT_DT, bool GATHER>
