@@ -51,6 +51,13 @@ def build(force: bool = False, verbose: bool = False) -> str:
     headers.append(os.path.join(ROOT, "include", "ac4k_b200.h"))
     headers.append(os.path.abspath(__file__))
     srcs = [os.path.join(CSRC, s) for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
+    # objects built with other extra flags (a debug or trace build) are stale
+    extra = os.environ.get("AC4K_NVCC_EXTRA", "")
+    stamp = os.path.join(OBJ_DIR, "flags.txt")
+    if not os.path.exists(stamp) or open(stamp).read() != extra:
+        force = True
+    with open(stamp, "w") as f:
+        f.write(extra)
     objs = []
     jobs = []
     for src in srcs:

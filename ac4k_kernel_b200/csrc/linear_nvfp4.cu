@@ -427,6 +427,37 @@ extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_trace(void
 extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_flags(int f) { g_dbg = f; }
 extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_tile_n(int bn) { g_force_bn = bn; }
 
+// Scale factors in the reference's row layout [K/64, rows16, 4] -> 128 x 4 tiles
+// [ceil(rows/128), K/64, 32, 4, 4] for both operands in one launch.  The pair kernel moves tiled
+// scales with 16-byte shared-memory loads and three bulk copies per stage; fed with the row layout
+// it needs 4-byte loads and sixteen small copies, which costs far more than this pass (the scales
+// are 1/9 of the operand bytes).  One thread writes one 16-byte piece: the four scale words of rows
+// l, l + 32, l + 64, l + 96 of a tile at one K step.
+__global__ void __launch_bounds__(256)
+sf_rows_to_tiles_kernel(const uint32_t *__restrict__ src_a, int rows16_a, int tiles_a, uint4 *__restrict__ dst_a,
+                        const uint32_t *__restrict__ src_b, int rows16_b, int tiles_b, uint4 *__restrict__ dst_b,
+                        int KT) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t na = (int64_t)tiles_a * KT * 32;
+  const int64_t nb = (int64_t)tiles_b * KT * 32;
+  if (idx >= na + nb) return;
+  const bool is_b = idx >= na;
+  const int64_t i = is_b ? idx - na : idx;
+  const uint32_t *src = is_b ? src_b : src_a;
+  const int rows16 = is_b ? rows16_b : rows16_a;
+  const int l = (int)(i & 31);
+  const int64_t tk = i >> 5;
+  const int kt = (int)(tk % KT);
+  const int rt = (int)(tk / KT);
+  uint32_t w[4];
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const int row = rt * 128 + 32 * g + l;
+    w[g] = row < rows16 ? __ldg(src + (int64_t)kt * rows16 + row) : 0u;
+  }
+  (is_b ? dst_b : dst_a)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // Split-K plan for shapes with too few output tiles to occupy the GPU (decode: M <= 128): how many
 // K slices, and the fp32 workspace [splits, M, N] they need.  splits == 1 means no workspace.
 struct SplitPlan { int splits; int kt_per_split; size_t ws_bytes; };
@@ -535,7 +566,38 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
   a.kt_per_split = pl.kt_per_split;
   a.ws = nullptr;
   const bool tiled = sf_layout == AC4K_SF_TILE128X4;
-  if (use_pair) return launch_linear_2cta(d_dtype, tiled, ta, tb, a, stream);
+  if (use_pair) {
+    // row-layout scales of a large problem are re-tiled first (see sf_rows_to_tiles_kernel); the
+    // scratch comes from the stream-ordered allocator, or from the caller's fixed scratch if it fits
+    const int64_t tiles_a = ceil_div(M, 128), tiles_b = ceil_div(N, 128);
+    const size_t conv_bytes = (size_t)(tiles_a + tiles_b) * (size_t)a.KT * 512;
+    const bool convert = !tiled && !(g_dbg & 16) && (double)M * (double)N * (double)K >= 2147483648.0 &&
+                         (ws_mode == 0 || conv_bytes <= ws_capacity);
+    if (!convert) return launch_linear_2cta(d_dtype, tiled, ta, tb, a, stream);
+    void *scratch = ws_fixed;
+    if (ws_mode == 0) AC4K_CUDA_TRY(cudaMallocAsync(&scratch, conv_bytes, stream));
+    uint8_t *ta_sf = static_cast<uint8_t *>(scratch);
+    uint8_t *tb_sf = ta_sf + (size_t)tiles_a * a.KT * 512;
+    const int64_t pieces = (tiles_a + tiles_b) * a.KT * 32;
+    sf_rows_to_tiles_kernel<<<(unsigned)ceil_div(pieces, 256), 256, 0, stream>>>(
+        reinterpret_cast<const uint32_t *>(A_sf), a.rows_sfa, (int)tiles_a, reinterpret_cast<uint4 *>(ta_sf),
+        reinterpret_cast<const uint32_t *>(B_sf), a.rows_sfb, (int)tiles_b, reinterpret_cast<uint4 *>(tb_sf), a.KT);
+    int rc = 0;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) rc = cuda_fail(e, "sf_rows_to_tiles_kernel");
+    if (rc == 0) {
+      a.sfa = ta_sf;
+      a.sfb = tb_sf;
+      a.rows_sfa = (int)(tiles_a * 128);
+      a.rows_sfb = (int)(tiles_b * 128);
+      rc = launch_linear_2cta(d_dtype, true, ta, tb, a, stream);
+    }
+    if (ws_mode == 0) {
+      e = cudaFreeAsync(scratch, stream);
+      if (e != cudaSuccess && rc == 0) rc = cuda_fail(e, "cudaFreeAsync");
+    }
+    return rc;
+  }
   if (pl.splits > 1) {
     if (ws_mode == 1) {
       a.ws = ws_fixed;
