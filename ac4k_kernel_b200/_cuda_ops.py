@@ -228,6 +228,52 @@ def linear_nvfp4_gather(dst_ptrs, ldd, col_off, D_local, A, A_sf, A_global_scale
               "linear_nvfp4_gather")
 
 
+def linear_nvfp4_requant(out, out_sf, out_global_scale, A, A_sf, A_global_scale, B, B_sf, B_global_scale, bias):
+    """NVFP4 GEMM whose epilogue quantises the bf16 result to NVFP4 with the given global scale
+    (no counterpart in the reference's linear path).  `out`: [M, N/2] uint8, `out_sf`: e4m3 scales in
+    either layout (3-d [N/64, align16(M), 4] or 5-d [ceil(M/128), N/64, 32, 4, 4])."""
+    _check_tensor(out, torch.uint8, "out")
+    _require(out.dim() == 2, "out must be a 2d matrix")
+    M, N = out.size(0), out.size(1) * 2
+    _check_tensor(A, torch.uint8, "a")
+    _check_tensor(B, torch.uint8, "b")
+    _require(A.dim() == 2 and B.dim() == 2 and A.size(0) == M and B.size(0) == N and A.size(1) == B.size(1),
+             "a / b / out shapes do not match")
+    K = A.size(1) * 2
+    kt = _ceil_div(K, 64)
+    for t, nm in ((A_sf, "scale_a"), (B_sf, "scale_b"), (out_sf, "out_sf")):
+        _check_tensor(t, torch.float8_e4m3fn, nm)
+    if A_sf.dim() == 3:
+        layout = SF_AC4K
+        _require(list(A_sf.shape) == [kt, _align_up(M, 16), 4], "scale_a has an invalid shape")
+        _require(list(B_sf.shape) == [kt, _align_up(N, 16), 4], "scale_b has an invalid shape")
+    else:
+        layout = SF_TILE128X4
+        _require(list(A_sf.shape) == [_ceil_div(M, 128), kt, 32, 4, 4], "scale_a has an invalid shape")
+        _require(list(B_sf.shape) == [_ceil_div(N, 128), kt, 32, 4, 4], "scale_b has an invalid shape")
+    _require(N % 64 == 0, "N must be a multiple of 64")
+    if out_sf.dim() == 3:
+        out_layout = SF_AC4K
+        _require(list(out_sf.shape) == [N // 64, _align_up(M, 16), 4], "out_sf has an invalid shape")
+    else:
+        out_layout = SF_TILE128X4
+        _require(list(out_sf.shape) == [_ceil_div(M, 128), N // 64, 32, 4, 4], "out_sf has an invalid shape")
+    for t, nm in ((A_global_scale, "global_scale_a"), (B_global_scale, "global_scale_b"), (out_global_scale, "out_global_scale")):
+        _check_tensor(t, torch.float32, nm)
+        _require(t.dim() == 0, f"{nm} must be a scalar")
+    bias_ptr, bias_dt = None, 0
+    if bias is not None:
+        _require(bias.dtype in _DT and bias.is_cuda and bias.is_contiguous(), "bias must be a contiguous cuda tensor")
+        _require(bias.dim() == 2 and bias.size(0) == 1 and bias.size(1) == N, f"bias must be [1, {N}]")
+        bias_ptr, bias_dt = bias.data_ptr(), _DT[bias.dtype]
+    with torch.cuda.device(out.device):
+        check(LIB.ac4k_linear_nvfp4_requant(out.data_ptr(), out_sf.data_ptr(), out_global_scale.data_ptr(), out_layout,
+                                            A.data_ptr(), A_sf.data_ptr(), A_global_scale.data_ptr(),
+                                            B.data_ptr(), B_sf.data_ptr(), B_global_scale.data_ptr(),
+                                            bias_ptr, bias_dt, M, N, K, layout, _stream(out)),
+              "linear_nvfp4_requant")
+
+
 def global_scale_bf16(out, input, max_scale):
     """out[()] = max|input| / max_scale on the device; stands in for the reference's Triton
     amax kernel (python/ac4k_kernel/ops/quant.py:21-59)."""

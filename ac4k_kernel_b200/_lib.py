@@ -36,6 +36,9 @@ SIGNATURES = {
     "ac4k_linear_nvfp4_gather": (ctypes.c_int, [ctypes.POINTER(_vp), ctypes.c_int, ctypes.c_int64, ctypes.c_int64,
                                                 ctypes.c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_int,
                                                 ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int, _vp]),
+    "ac4k_linear_nvfp4_requant": (ctypes.c_int, [_vp, _vp, _vp, ctypes.c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                                 ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                                 ctypes.c_int, _vp]),
     "ac4k_peer_alloc": (ctypes.c_int, [ctypes.c_int64, ctypes.POINTER(_vp), ctypes.c_char_p]),
     "ac4k_peer_open": (ctypes.c_int, [ctypes.c_char_p, ctypes.POINTER(_vp)]),
     "ac4k_peer_close": (ctypes.c_int, [_vp]),

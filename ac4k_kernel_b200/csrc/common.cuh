@@ -99,4 +99,62 @@ __device__ __forceinline__ float hmax_bf16x2_to_f32(uint32_t v) {
   return bf16_bits_to_f32(a > b ? a : b);
 }
 
+// ---- NVFP4 block quantisation (shared by the quantiser and the GEMM's re-quantising epilogue) ----
+static constexpr float kOneSixth = 0.16666667163372040f;
+
+struct BlockScale {
+  float r;       // multiplier applied to the elements
+  uint8_t byte;  // e4m3 scale
+};
+
+__device__ __forceinline__ BlockScale block_scale(float amax, float alpha) {
+  BlockScale o;
+  float s = __fmul_rn(alpha, __fmul_rn(amax, kOneSixth));
+  float sf_f;
+  o.byte = f32_to_e4m3(s, sf_f);
+  o.r = (sf_f != 0.0f) ? __fmul_rn(alpha, __frcp_rn(sf_f)) : 0.0f;
+  return o;
+}
+
+__device__ __forceinline__ float load_alpha(const float *gscale) {
+  float g = __ldg(gscale);
+  return g == 0.0f ? 0.0f : __frcp_rn(g);
+}
+
+// four packed bf16 pairs -> 8 e2m1 codes (one word); products in fp32, round to nearest
+__device__ __forceinline__ uint32_t quantize8_x2(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, float r) {
+  uint32_t out;
+  asm("{\n"
+      ".reg .b64 rr, p0, p1, p2, p3;\n"
+      ".reg .b32 l0, l1, l2, l3, h0, h1, h2, h3;\n"
+      ".reg .f32 x0, x1, x2, x3, y0, y1, y2, y3;\n"
+      ".reg .b8 b0, b1, b2, b3;\n"
+      "mov.b64 rr, {%5, %5};\n"
+      "shl.b32 l0, %1, 16;\n and.b32 h0, %1, 0xFFFF0000;\n mov.b64 p0, {l0, h0};\n"
+      "shl.b32 l1, %2, 16;\n and.b32 h1, %2, 0xFFFF0000;\n mov.b64 p1, {l1, h1};\n"
+      "shl.b32 l2, %3, 16;\n and.b32 h2, %3, 0xFFFF0000;\n mov.b64 p2, {l2, h2};\n"
+      "shl.b32 l3, %4, 16;\n and.b32 h3, %4, 0xFFFF0000;\n mov.b64 p3, {l3, h3};\n"
+      "mul.rn.f32x2 p0, p0, rr;\n mul.rn.f32x2 p1, p1, rr;\n"
+      "mul.rn.f32x2 p2, p2, rr;\n mul.rn.f32x2 p3, p3, rr;\n"
+      "mov.b64 {x0, y0}, p0;\n mov.b64 {x1, y1}, p1;\n mov.b64 {x2, y2}, p2;\n mov.b64 {x3, y3}, p3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, y0, x0;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, y1, x1;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, y2, x2;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, y3, x3;\n"
+      "mov.b32 %0, {b0, b1, b2, b3};\n"
+      "}"
+      : "=r"(out)
+      : "r"(w0), "r"(w1), "r"(w2), "r"(w3), "f"(r));
+  return out;
+}
+
+// amax of 16 packed bf16 values (8 words) as fp32
+__device__ __forceinline__ float amax16_bf16(const uint32_t *w) {
+  const uint32_t m = max_bf16x2(max_bf16x2(max_bf16x2(abs_bf16x2(w[0]), abs_bf16x2(w[1])),
+                                           max_bf16x2(abs_bf16x2(w[2]), abs_bf16x2(w[3]))),
+                                max_bf16x2(max_bf16x2(abs_bf16x2(w[4]), abs_bf16x2(w[5])),
+                                           max_bf16x2(abs_bf16x2(w[6]), abs_bf16x2(w[7]))));
+  return hmax_bf16x2_to_f32(m);
+}
+
 }  // namespace ac4k

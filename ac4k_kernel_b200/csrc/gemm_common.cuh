@@ -39,6 +39,7 @@ struct Cfg {
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory overflow");
 };
 
+enum { EPI_PLAIN = 0, EPI_GATHER = 1, EPI_REQUANT = 2 };   // epilogue variants of the pair kernel
 static constexpr int kMaxDst = 8;     // output destinations of one launch (this GPU + up to 7 peers)
 
 struct GemmArgs {
@@ -49,6 +50,13 @@ struct GemmArgs {
   int n_dst;            // 1 for the plain GEMM
   int64_t ldd;          // leading dimension of every destination, in elements (N for the plain GEMM)
   int64_t col_off;      // first destination column of this launch's N columns (0 for the plain GEMM)
+  // re-quantising epilogue (pair kernel, EPI_REQUANT): the bf16 result is not stored but quantised to
+  // NVFP4 with the given global scale, exactly as the quantiser would quantise the stored bf16 matrix
+  uint8_t *q_out;       // [M, N / 2] packed e2m1
+  uint8_t *q_sf;        // block scales of the output in q_layout
+  const float *q_gs;    // global scale of the output (device scalar)
+  int q_layout;         // AC4K_SF_AC4K or AC4K_SF_TILE128X4
+  int q_rows;           // padded row count of q_sf (16- or 128-aligned M)
   const float *a_gs;
   const float *b_gs;
   const void *bias;

@@ -481,7 +481,9 @@ static SplitPlan plan_split(int64_t M, int64_t N, int64_t K, int bn, int sms) {
 // `more`: further destinations that receive the same tile stores (the fused all-gather), each a
 // [M, ldd] buffer written at columns [col_off, col_off + N); NULL / 0 for the plain GEMM, which
 // writes D as a dense [M, N] matrix.
-struct OutSpec { void *const *more; int n_more; int64_t ldd; int64_t col_off; };
+struct OutSpec { void *const *more; int n_more; int64_t ldd; int64_t col_off;
+                 // re-quantising epilogue: packed output, its scales, its global scale, scale layout
+                 uint8_t *q_out = nullptr; uint8_t *q_sf = nullptr; const float *q_gs = nullptr; int q_layout = 0; };
 
 static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, const float *A_gs,
                        const void *B, const void *B_sf, const float *B_gs, const void *bias,
@@ -494,7 +496,8 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
   if (sf_layout != AC4K_SF_AC4K && sf_layout != AC4K_SF_TILE128X4)
     return fail(AC4K_ERR_ENUM, "unknown sf_layout %d", sf_layout);
   if (M == 0 || N == 0) return 0;
-  if (!D || !A || !B || !A_sf || !B_sf || !A_gs || !B_gs) return fail(AC4K_ERR_NULL, "a required pointer is NULL");
+  const bool requant = out && out->q_out;
+  if ((!D && !requant) || !A || !B || !A_sf || !B_sf || !A_gs || !B_gs) return fail(AC4K_ERR_NULL, "a required pointer is NULL");
   if (K == 0 || K % 64 != 0)
     return fail(AC4K_ERR_SHAPE, "K = %lld must be a positive multiple of 64 (the quantiser pads K to 64)", (long long)K);
   if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return fail(AC4K_ERR_SHAPE, "dimension too large");
@@ -542,11 +545,16 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
   a.ldd = N;
   a.col_off = 0;
   for (int i = 0; i < kMaxDst - 1; ++i) a.D_more[i] = nullptr;
+  a.q_out = nullptr; a.q_sf = nullptr; a.q_gs = nullptr; a.q_layout = 0; a.q_rows = 0;
   if (out) {
     a.n_dst = 1 + out->n_more;
     a.ldd = out->ldd;
     a.col_off = out->col_off;
     for (int i = 0; i < out->n_more; ++i) a.D_more[i] = out->more[i];
+    if (out->q_out) {
+      a.q_out = out->q_out; a.q_sf = out->q_sf; a.q_gs = out->q_gs; a.q_layout = out->q_layout;
+      a.q_rows = (int)align_up(M, out->q_layout == AC4K_SF_AC4K ? 16 : 128);
+    }
   }
   a.a_gs = A_gs;
   a.b_gs = B_gs;
@@ -738,4 +746,27 @@ extern "C" int ac4k_peer_open(const unsigned char handle[64], void **ptr_out) {
 extern "C" int ac4k_peer_close(void *ptr) {
   if (ptr) AC4K_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
   return 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// GEMM whose epilogue re-quantises the bf16 result to NVFP4 (input of the next linear layer)
+// ------------------------------------------------------------------------------------------
+extern "C" int ac4k_linear_nvfp4_requant(void *out_fp4, void *out_sf, const float *out_gs, int out_sf_layout,
+                                         const void *A, const void *A_sf, const float *A_gs, const void *B,
+                                         const void *B_sf, const float *B_gs, const void *bias, int bias_dtype,
+                                         int64_t M, int64_t N, int64_t K, int sf_layout, ac4k_stream_t stream_) {
+  if (!out_fp4 || !out_sf || !out_gs) return fail(AC4K_ERR_NULL, "a required output pointer is NULL");
+  if (out_sf_layout != AC4K_SF_AC4K && out_sf_layout != AC4K_SF_TILE128X4)
+    return fail(AC4K_ERR_ENUM, "unknown out_sf_layout %d", out_sf_layout);
+  if (N % 64 != 0) return fail(AC4K_ERR_UNSUPPORTED, "the re-quantising epilogue needs N %% 64 == 0 (N = %lld)", (long long)N);
+  if ((reinterpret_cast<uintptr_t>(out_fp4) & 15) || (reinterpret_cast<uintptr_t>(out_sf) & 15))
+    return fail(AC4K_ERR_ALIGN, "out_fp4 and out_sf must be 16-byte aligned");
+  OutSpec out{nullptr, 0, N, 0};
+  out.q_out = static_cast<uint8_t *>(out_fp4);
+  out.q_sf = static_cast<uint8_t *>(out_sf);
+  out.q_gs = out_gs;
+  out.q_layout = out_sf_layout;
+  // D is not written in this mode; the packed output stands in for the alignment checks
+  return linear_impl(out_fp4, AC4K_DT_BF16, A, A_sf, A_gs, B, B_sf, B_gs, bias, bias_dtype, M, N, K, sf_layout,
+                     static_cast<cudaStream_t>(stream_), 0, nullptr, 0, &out);
 }

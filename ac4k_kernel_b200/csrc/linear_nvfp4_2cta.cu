@@ -67,7 +67,7 @@ static_assert(SMEM_BYTES <= 227 * 1024, "shared memory overflow");
 static constexpr int kThreadsPair = 512;
 }  // namespace pair
 
-template <bool SF_TILED, int OUT_DT, bool GATHER>
+template <bool SF_TILED, int OUT_DT, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreadsPair, 1)
 linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                          const GemmArgs p) {
@@ -400,6 +400,48 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       if (lane == 0 && ti < 16) AC4K_TRG(4 + rank, ti * 8 + q + 4 * half, 1);
       const int64_t col_base = p.col_off + col0;
       const bool last_tile = t + num_clusters >= num_tiles;
+      if (EPI == EPI_REQUANT) {
+        // w[] holds this row's 128 outputs as packed bf16 - the quantiser's input format.  Quantise
+        // them here (8 blocks of 16 along N, which is the next layer's K) instead of storing them.
+        if (row < p.q_rows) {
+          const float g = __ldg(p.q_gs);
+          const float alpha_o = g == 0.0f ? 0.0f : __frcp_rn(g);
+          uint32_t codes[16];
+          uint32_t sfw[2] = {0u, 0u};
+#pragma unroll
+          for (int b = 0; b < 8; ++b) {
+            const float amax = amax16_bf16(&w[8 * b]);
+            const float s = __fmul_rn(alpha_o, __fmul_rn(amax, kOneSixth));
+            uint16_t pk;
+            asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pk) : "f"(0.0f), "f"(s));
+            const uint32_t sb = pk & 0x7Fu;
+            const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)sb, __NV_E4M3);
+            const float r = sb ? __fmul_rn(alpha_o, __frcp_rn(__half2float(__half(h)))) : 0.0f;
+            codes[2 * b] = quantize8_x2(w[8 * b], w[8 * b + 1], w[8 * b + 2], w[8 * b + 3], r);
+            codes[2 * b + 1] = quantize8_x2(w[8 * b + 4], w[8 * b + 5], w[8 * b + 6], w[8 * b + 7], r);
+            sfw[b >> 2] |= (row < p.M ? sb : 0u) << (8 * (b & 3));
+          }
+          const int kt_out = p.N / 64;
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {
+            const int c64 = col0 + 64 * h2;
+            if (c64 >= p.N) break;
+            if (row < p.M) {
+              uint4 *dst = reinterpret_cast<uint4 *>(p.q_out + (int64_t)row * (p.N / 2) + c64 / 2);
+              __stcs(dst, make_uint4(codes[8 * h2], codes[8 * h2 + 1], codes[8 * h2 + 2], codes[8 * h2 + 3]));
+              __stcs(dst + 1, make_uint4(codes[8 * h2 + 4], codes[8 * h2 + 5], codes[8 * h2 + 6], codes[8 * h2 + 7]));
+            }
+            const int k64 = c64 / 64;
+            uint32_t *sfp;
+            if (p.q_layout == AC4K_SF_AC4K)
+              sfp = reinterpret_cast<uint32_t *>(p.q_sf) + (int64_t)k64 * p.q_rows + row;
+            else
+              sfp = reinterpret_cast<uint32_t *>(p.q_sf) + ((int64_t)(row / 128) * kt_out + k64) * 128 + (row & 31) * 4 +
+                    ((row & 127) >> 5);
+            *sfp = sfw[h2];
+          }
+        }
+      } else
       if (row < p.M && !(p.dbg & 8)) {
         // Each lane owns one row, so a store instruction touches 32 different rows however it is
         // shaped; 32-byte stores make every one of those touches a full sector, and a short pause
@@ -423,7 +465,7 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
               __stcs(reinterpret_cast<uint4 *>(dst) + i, make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]));
         }
       }
-      if (GATHER && p.n_dst > 1 && !(p.dbg & 8)) {
+      if (EPI == EPI_GATHER && p.n_dst > 1 && !(p.dbg & 8)) {
         // Fused all-gather: forward this warp's 32 rows x 256 bytes to the other destinations (peer
         // GPUs' buffers, reached over NVLink).  The registers hold one row per lane, which would make
         // every peer store a scatter of 32-byte pieces; NVLink wants long contiguous writes.  So the
@@ -469,10 +511,10 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   if (threadIdx.x == 0) AC4K_TR(3, 0, 5);
 }
 
-template <bool SF_TILED, int OUT_DT, bool GATHER>
+template <bool SF_TILED, int OUT_DT, int EPI>
 static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const GemmArgs &args, int sms,
                        cudaStream_t stream) {
-  auto kern = linear_nvfp4_2cta_kernel<SF_TILED, OUT_DT, GATHER>;
+  auto kern = linear_nvfp4_2cta_kernel<SF_TILED, OUT_DT, EPI>;
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -514,22 +556,27 @@ int launch_linear_2cta(int d_dtype, bool sf_tiled, const CUtensorMap &ta, const 
   if (int e = get_device_info(&di)) return e;
   args.tiles_m = (int)ceil_div(args.M, pair::BMP);
   args.tiles_n = (int)ceil_div(args.N, pair::BN);
-  // the instantiation that forwards tiles to further destinations is separate: its extra registers
-  // and code would otherwise slow the plain GEMM down
+  // the instantiations that forward tiles to further destinations or re-quantise the output are
+  // separate: their extra registers and code would otherwise slow the plain GEMM down
+  if (args.q_out != nullptr) {
+    if (d_dtype != AC4K_DT_BF16) return fail(AC4K_ERR_UNSUPPORTED, "the re-quantising epilogue rounds to bf16 first");
+    return sf_tiled ? launch_pair<true, AC4K_DT_BF16, EPI_REQUANT>(ta, tb, args, di.sms, stream)
+                    : launch_pair<false, AC4K_DT_BF16, EPI_REQUANT>(ta, tb, args, di.sms, stream);
+  }
   const bool gather = args.n_dst > 1;
   if (d_dtype == AC4K_DT_BF16) {
     if (gather)
-      return sf_tiled ? launch_pair<true, AC4K_DT_BF16, true>(ta, tb, args, di.sms, stream)
-                      : launch_pair<false, AC4K_DT_BF16, true>(ta, tb, args, di.sms, stream);
-    return sf_tiled ? launch_pair<true, AC4K_DT_BF16, false>(ta, tb, args, di.sms, stream)
-                    : launch_pair<false, AC4K_DT_BF16, false>(ta, tb, args, di.sms, stream);
+      return sf_tiled ? launch_pair<true, AC4K_DT_BF16, EPI_GATHER>(ta, tb, args, di.sms, stream)
+                      : launch_pair<false, AC4K_DT_BF16, EPI_GATHER>(ta, tb, args, di.sms, stream);
+    return sf_tiled ? launch_pair<true, AC4K_DT_BF16, EPI_PLAIN>(ta, tb, args, di.sms, stream)
+                    : launch_pair<false, AC4K_DT_BF16, EPI_PLAIN>(ta, tb, args, di.sms, stream);
   }
   if (d_dtype == AC4K_DT_FP16) {
     if (gather)
-      return sf_tiled ? launch_pair<true, AC4K_DT_FP16, true>(ta, tb, args, di.sms, stream)
-                      : launch_pair<false, AC4K_DT_FP16, true>(ta, tb, args, di.sms, stream);
-    return sf_tiled ? launch_pair<true, AC4K_DT_FP16, false>(ta, tb, args, di.sms, stream)
-                    : launch_pair<false, AC4K_DT_FP16, false>(ta, tb, args, di.sms, stream);
+      return sf_tiled ? launch_pair<true, AC4K_DT_FP16, EPI_GATHER>(ta, tb, args, di.sms, stream)
+                      : launch_pair<false, AC4K_DT_FP16, EPI_GATHER>(ta, tb, args, di.sms, stream);
+    return sf_tiled ? launch_pair<true, AC4K_DT_FP16, EPI_PLAIN>(ta, tb, args, di.sms, stream)
+                    : launch_pair<false, AC4K_DT_FP16, EPI_PLAIN>(ta, tb, args, di.sms, stream);
   }
   return fail(AC4K_ERR_UNSUPPORTED, "the CTA-pair kernel stores 16-bit outputs only");
 }

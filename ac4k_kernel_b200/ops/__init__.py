@@ -1,6 +1,6 @@
 """Operators of the NVFP4 linear path (mirrors python/ac4k_kernel/ops/__init__.py for the
 names this build covers)."""
-from .linear import linear, linear_nvfp4
+from .linear import linear, linear_nvfp4, linear_requant
 from .quant import quantize, quantize_nvfp4, quantize_fp8, quantize_int8
 
-__all__ = ["quantize", "linear", "quantize_nvfp4", "quantize_fp8", "quantize_int8", "linear_nvfp4"]
+__all__ = ["quantize", "linear", "quantize_nvfp4", "quantize_fp8", "quantize_int8", "linear_nvfp4", "linear_requant"]

@@ -35,3 +35,26 @@ def linear(x, x_scale, x_global_scale, weight, weight_scale, weight_global_scale
     [M, N] bf16/fp16/fp32 (bf16 when allocated here).  Returns out."""
     return _OP(x, x_scale, x_global_scale, weight, weight_scale, weight_global_scale, bias,
                out=out)
+
+
+def linear_requant(x, x_scale, x_global_scale, weight, weight_scale, weight_global_scale,
+                   out_global_scale, bias=None, sf_layout="128x4"):
+    """`linear()` followed by `quantize(..., global_scale=out_global_scale)` in one kernel: the GEMM's
+    epilogue rounds the result to bf16 and quantises it to NVFP4 (blocks of 16 along N), so the output
+    can feed the next `linear()` directly.  Bit-identical to the two-call sequence; the reference has
+    no counterpart.  Returns (packed [M, N/2] u8, block scales in `sf_layout`, out_global_scale)."""
+    from .utils import align_up, ceil_div
+    if (bias is not None) and (bias.ndim == 1):
+        bias = bias.reshape(1, -1)
+    m, n = x.shape[0], weight.shape[0]
+    out = torch.empty((m, n // 2), dtype=torch.uint8, device=x.device)
+    if sf_layout == "ac4k":
+        sf_shape = (n // 64, align_up(m, 16), 4)
+    elif sf_layout == "128x4":
+        sf_shape = (ceil_div(m, 128), n // 64, 32, 4, 4)
+    else:
+        raise ValueError(f"unknown sf_layout {sf_layout!r}")
+    out_sf = torch.empty(sf_shape, dtype=torch.float8_e4m3fn, device=x.device)
+    _cuda_ops.linear_nvfp4_requant(out, out_sf, out_global_scale, x, x_scale, x_global_scale, weight,
+                                   weight_scale, weight_global_scale, bias)
+    return out, out_sf, out_global_scale

@@ -137,6 +137,21 @@ int ac4k_linear_nvfp4_gather(void *const *D_dsts, int n_dst, int64_t ldd, int64_
                              const void *B_sf, const float *B_gs, const void *bias, int bias_dtype,
                              int64_t M, int64_t N, int64_t K, int sf_layout, ac4k_stream_t stream);
 
+/* The GEMM of ac4k_linear_nvfp4 whose epilogue re-quantises the result to NVFP4 instead of storing
+ * it: out = quantize_nvfp4(bf16(alpha * A * B^T + bias), out_gs) with blocks of 16 along N, i.e. the
+ * activation operand of the next linear layer, bit-identical to running ac4k_linear_nvfp4 (bf16
+ * output) followed by ac4k_quantize_nvfp4 with the same global scale.  The reference has no such
+ * entry point for the linear path (it re-quantises in registers only inside its attention kernel,
+ * lib/cuda/sm120/mha_nvfp4.cu:246-319); this saves the bf16 round trip through HBM and two launches.
+ *   out_fp4: [M, N / 2] bytes; out_sf: block scales in `out_sf_layout` ([N/64, align16(M), 4] or
+ *   [ceil(M/128), N/64, 32, 4, 4]), padding rows written as 0; out_gs: device fp32 scalar, chosen by
+ *   the caller (calibrated), since the amax of the output is not known before the GEMM has run.
+ *   N must be a multiple of 64. */
+int ac4k_linear_nvfp4_requant(void *out_fp4, void *out_sf, const float *out_gs, int out_sf_layout,
+                              const void *A, const void *A_sf, const float *A_gs, const void *B,
+                              const void *B_sf, const float *B_gs, const void *bias, int bias_dtype,
+                              int64_t M, int64_t N, int64_t K, int sf_layout, ac4k_stream_t stream);
+
 /* Device buffers that the other processes of the node can map (CUDA IPC), for the destinations of
  * ac4k_linear_nvfp4_gather.  No counterpart in the reference.
  *   ac4k_peer_alloc: cudaMalloc on the current device + its 64-byte IPC handle.

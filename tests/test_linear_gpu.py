@@ -298,3 +298,50 @@ def test_gather_argument_checks(ops):
         _cuda_ops.linear_nvfp4_gather([buf.data_ptr()], 512, 4, buf, a4, asf, ag, a4, asf, ag, None)
     with pytest.raises(RuntimeError):      # too many destinations
         _cuda_ops.linear_nvfp4_gather([buf.data_ptr()] * 9, 512, 0, buf, a4, asf, ag, a4, asf, ag, None)
+
+
+@pytest.mark.parametrize("in_layout,out_layout", [("128x4", "128x4"), ("128x4", "ac4k"), ("ac4k", "128x4")])
+@pytest.mark.parametrize("m,n,k,with_bias", [
+    (512, 512, 1024, False),
+    (300, 320, 256, True),          # ragged row tile, N = 64 * 5
+    (100, 192, 512, False),         # fewer rows than one tile
+    (4096, 4096, 4096, False),      # config 2
+])
+def test_requant_epilogue_equals_linear_then_quantize(ops, in_layout, out_layout, m, n, k, with_bias):
+    """linear_requant == quantize(linear(...) in bf16, given global scale), bit for bit: packed
+    codes, block scales and their zero padding."""
+    from ac4k_kernel_b200 import _cuda_ops
+    from ac4k_kernel_b200.ops.utils import align_up, ceil_div
+    a = gaussian((m, k), seed=21).cuda()
+    b = (gaussian((n, k), seed=22) * 0.05).bfloat16().cuda()
+    a4, asf, ag = ops.quantize(a, 0, 1, sf_layout=in_layout)
+    b4, bsf, bg = ops.quantize(b, 0, 1, sf_layout=in_layout)
+    bias = gaussian((1, n), seed=23).cuda() if with_bias else None
+    y = ops.linear(a4, asf, ag, b4, bsf, bg, bias=bias)                    # bf16 [m, n]
+    # the caller's calibrated output scale: here the true one, scaled so that some blocks saturate
+    g_out = (y.float().abs().max() / (6.0 * 448.0) * 0.75).reshape(()).contiguous()
+    ref4 = torch.empty((m, n // 2), dtype=torch.uint8, device="cuda")
+    if out_layout == "ac4k":
+        ref_sf = torch.empty((n // 64, align_up(m, 16), 4), dtype=torch.float8_e4m3fn, device="cuda")
+    else:
+        ref_sf = torch.empty((ceil_div(m, 128), n // 64, 32, 4, 4), dtype=torch.float8_e4m3fn, device="cuda")
+    _cuda_ops.quantize_nvfp4(ref4, ref_sf, y, g_out, 0, 1, False)
+    out4, out_sf, _ = ops.linear_requant(a4, asf, ag, b4, bsf, bg, g_out, bias=bias, sf_layout=out_layout)
+    torch.cuda.synchronize()
+    assert torch.equal(out4, ref4)
+    assert torch.equal(out_sf.view(torch.uint8), ref_sf.view(torch.uint8))
+    # and the fused output feeds the next layer like the two-call output does
+    w2 = (gaussian((256, n), seed=24) * 0.05).bfloat16().cuda()
+    w24, w2sf, w2g = ops.quantize(w2, 0, 1, sf_layout=out_layout)
+    z_ref = ops.linear(ref4, ref_sf, g_out, w24, w2sf, w2g)
+    z = ops.linear(out4, out_sf, g_out, w24, w2sf, w2g)
+    assert torch.equal(z, z_ref)
+
+
+def test_requant_argument_checks(ops):
+    a = gaussian((256, 256), seed=3).cuda()
+    a4, asf, ag = ops.quantize(a, 0, 1, sf_layout="128x4")
+    b = gaussian((96, 256), seed=4).cuda()              # N = 96 is not a multiple of 64
+    b4, bsf, bg = ops.quantize(b, 0, 1, sf_layout="128x4")
+    with pytest.raises(RuntimeError):
+        ops.linear_requant(a4, asf, ag, b4, bsf, bg, ag)
