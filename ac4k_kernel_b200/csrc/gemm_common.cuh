@@ -69,6 +69,8 @@ struct GemmArgs {
   int splits;           // split-K factor (1-CTA kernel only); > 1 writes fp32 partials to `ws`
   int kt_per_split;     // K stages (of 256 elements) per split
   float *ws;            // [splits, M, N] fp32 partial sums when splits > 1
+  int cluster_reduce;   // 1: the `splits` K slices of a tile run as one cluster and are added through
+                        // distributed shared memory (one work item per CTA); no workspace, no second kernel
   int dbg;              // experiment switches, 0 in production
   unsigned long long *trace;   // experiment: per-stage timestamps of cluster 0, NULL in production
 };

@@ -29,6 +29,17 @@
 namespace ac4k {
 using namespace ptx;
 
+#ifdef AC4K_TRACE_ENABLED
+// per-stage clock64 stamps of CTA 0 (region 0: MMA issuer, region 1: epilogue warp 6, region 3: kernel phases)
+#define AC4K_TR1(region, it, ev)                                                             \
+  do {                                                                                      \
+    if (p.trace != nullptr && blockIdx.x == 0 && (it) < 128)                                \
+      p.trace[((size_t)(region) * 128 + (it)) * 8 + (ev)] = clock64();                      \
+  } while (0)
+#else
+#define AC4K_TR1(region, it, ev) do { } while (0)
+#endif
+
 template <int BN, bool SF_TILED, int OUT_DT>
 __global__ void __launch_bounds__(kNumThreads, 1)
 linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -52,7 +63,13 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int num_work = num_tiles * p.splits;
   const int k_tiles_all = (p.KT + K64_PER_STAGE - 1) / K64_PER_STAGE;
+  // with cluster_reduce the K slices of one tile are the consecutive CTAs of a cluster
+  auto work_item = [&](int wi, int &t, int &split) {
+    if (p.cluster_reduce) { t = wi / p.splits; split = wi % p.splits; }
+    else { t = wi % num_tiles; split = wi / num_tiles; }
+  };
 
+  if (threadIdx.x == 0) AC4K_TR1(3, 0, 0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(full_bar + 8 * s, 1);
@@ -75,6 +92,7 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(smem_gen + (tmem_slot - smem_base));
+  if (threadIdx.x == 0) AC4K_TR1(3, 0, 1);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -82,7 +100,8 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       uint32_t s = 0, ph = 0;
       bool ok = true;
       for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
-        const int t = wi % num_tiles, split = wi / num_tiles;
+        int t, split;
+        work_item(wi, t, split);
         const int kt0 = split * p.kt_per_split, kt1 = min(k_tiles_all, kt0 + p.kt_per_split);
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
@@ -132,28 +151,45 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       constexpr uint32_t idesc = make_idesc_mxf4nvf4(BM, BN);
       uint32_t s = 0, ph = 0, acc = 0, acc_ph = 0;
       bool ok = true;
+      int it = 0;
+      const uint64_t adesc0 = make_smem_desc(sA, 16, 1024, kSwizzle128B);
+      const uint64_t bdesc0 = make_smem_desc(sB, 16, 1024, kSwizzle128B);
       for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
-        const int split = wi / num_tiles;
+        int t_unused, split;
+        work_item(wi, t_unused, split);
         const int kt0 = split * p.kt_per_split, kt1 = min(k_tiles_all, kt0 + p.kt_per_split);
         if (!mbar_wait(tempty_bar + 8 * acc, acc_ph ^ 1)) { atomicExch(p.status, kStatusTimeoutMma); break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kt = kt0; kt < kt1; ++kt) {
-          if (!mbar_wait(full_bar + 8 * s, ph) || !mbar_wait(sf_bar + 8 * s, ph)) {
-            atomicExch(p.status, kStatusTimeoutMma); ok = false; break;
-          }
+          AC4K_TR1(0, it, 0);
+          if (!mbar_wait(full_bar + 8 * s, ph)) { atomicExch(p.status, kStatusTimeoutMma); ok = false; break; }
+          AC4K_TR1(0, it, 1);
+          if (!mbar_wait(sf_bar + 8 * s, ph)) { atomicExch(p.status, kStatusTimeoutMma); ok = false; break; }
           tc_fence_after();
+          AC4K_TR1(0, it, 2);
           const int nk = min(K64_PER_STAGE, p.KT - kt * K64_PER_STAGE);
           const uint32_t t_sfa = tmem_base + C::SFA_COL + s * C::SFA_COLS;
           const uint32_t t_sfb = tmem_base + C::SFB_COL + s * C::SFB_COLS;
-          const uint64_t adesc = make_smem_desc(sA + s * C::A_BYTES, 16, 1024, kSwizzle128B);
-          const uint64_t bdesc = make_smem_desc(sB + s * C::B_BYTES, 16, 1024, kSwizzle128B);
-          for (int j = 0; j < nk; ++j) {
-            // +32 bytes of K per step inside the 128-byte swizzle atom: start-address field += 2
-            mma_mxf4nvf4(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, t_sfa + j * 4, t_sfb + j * (BN / 32),
-                         (kt > kt0 || j > 0) ? 1u : 0u);
+          const uint64_t adesc = adesc0 + (uint64_t)(s * (C::A_BYTES >> 4));
+          const uint64_t bdesc = bdesc0 + (uint64_t)(s * (C::B_BYTES >> 4));
+          // +32 bytes of K per step inside the 128-byte swizzle atom: start-address field += 2.
+          // The full stage is unrolled: every cycle this thread spends between two issues shows up
+          // as time per stage on shapes that only stream weights.
+          if (nk == K64_PER_STAGE) {
+#pragma unroll
+            for (int j = 0; j < K64_PER_STAGE; ++j)
+              mma_mxf4nvf4(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, t_sfa + j * 4, t_sfb + j * (BN / 32),
+                           (kt > kt0 || j > 0) ? 1u : 0u);
+          } else {
+            for (int j = 0; j < nk; ++j)
+              mma_mxf4nvf4(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, t_sfa + j * 4, t_sfb + j * (BN / 32),
+                           (kt > kt0 || j > 0) ? 1u : 0u);
           }
+          AC4K_TR1(0, it, 3);
           tc_commit(empty_bar + 8 * s);
+          AC4K_TR1(0, it, 4);
+          ++it;
           if (++s == C::STAGES) { s = 0; ph ^= 1; }
         }
         if (ok) tc_commit(tfull_bar + 8 * acc);
@@ -169,7 +205,8 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     uint32_t s = 0, ph = 0;
     bool ok = true;
     for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
-      const int split = wi / num_tiles;
+      int t_unused, split;
+      work_item(wi, t_unused, split);
       const int kt0 = split * p.kt_per_split, kt1 = min(k_tiles_all, kt0 + p.kt_per_split);
       for (int kt = kt0; kt < kt1; ++kt) {
         if (!mbar_wait(full_bar + 8 * s, ph)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutSf); ok = false; break; }
@@ -223,13 +260,72 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     const float alpha = __fmul_rn(__ldg(p.a_gs), __ldg(p.b_gs));
     const bool vec_ok = (OUT_DT == AC4K_DT_FP32) ? (p.N % 4 == 0) : (p.N % 8 == 0);
     for (int wi = blockIdx.x; wi < num_work; wi += gridDim.x) {
-      const int t = wi % num_tiles, split = wi / num_tiles;
+      int t, split;
+      work_item(wi, t, split);
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
-      if (!mbar_wait(tfull_bar + 8 * acc, acc_ph)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue); break; }
+      const bool tfull_ok = mbar_wait(tfull_bar + 8 * acc, acc_ph);
+      if (!tfull_ok && lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue);
+      if (!tfull_ok && !p.cluster_reduce) break;
       tc_fence_after();
+      if (warp == 6 && lane == 0) AC4K_TR1(1, 0, 0);
       const int row = tm * BM + q * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      if constexpr (BN == 128) {
+        if (p.cluster_reduce) {
+          // K slices of this tile sit in the CTAs of this cluster (slice = rank).  Every CTA reads its
+          // accumulator into registers; once all of them are past their MMAs (first cluster barrier)
+          // the operand buffers of the leader are free and the other slices write their partial sums
+          // there; after the second barrier the leader adds them in slice order - the same order of
+          // additions as the workspace path - and stores the result.
+          float v[BN];
+          if (tfull_ok) {
+#pragma unroll
+            for (int c = 0; c < BN; c += 32) {
+              uint32_t r[32];
+              tmem_ld_32x32b_x32_sync(t_row + c, r);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[c + i] = __uint_as_float(r[i]);
+            }
+          }
+          const int row_l = q * 32 + lane;
+          const uint32_t rank = cluster_ctarank();
+          cluster_sync();
+          if (rank != 0 && row < p.M) {
+            const uint32_t dst = map_to_cta(sA + ((rank - 1) * BM + row_l) * (BN * 4), 0);
+#pragma unroll
+            for (int c = 0; c < BN / 4; ++c)      // 16-byte pieces, rotated by the row to spread the banks
+              st_shared_cluster_v4(dst + (((c + row_l) & (BN / 4 - 1)) << 4), v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+          }
+          cluster_sync();
+          if (rank == 0 && row < p.M && tfull_ok) {
+            for (int sl = 1; sl < p.splits; ++sl) {
+              const float4 *src = reinterpret_cast<const float4 *>(smem_gen + (sA - smem_base) + ((sl - 1) * BM + row_l) * (BN * 4));
+#pragma unroll
+              for (int c = 0; c < BN / 4; ++c) {
+                const float4 w = src[(c + row_l) & (BN / 4 - 1)];
+                v[4 * c] = __fadd_rn(v[4 * c], w.x); v[4 * c + 1] = __fadd_rn(v[4 * c + 1], w.y);
+                v[4 * c + 2] = __fadd_rn(v[4 * c + 2], w.z); v[4 * c + 3] = __fadd_rn(v[4 * c + 3], w.w);
+              }
+            }
+#pragma unroll
+            for (int c = 0; c < BN; c += 32) {
+              const int col = tn * BN + c;
+              const int ncols = min(32, p.N - col);
+              float o[32];
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __fmul_rn(v[c + i], alpha);
+              if (p.bias != nullptr) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (i < ncols) o[i] = __fadd_rn(o[i], load_bias(p.bias, p.bias_dt, col + i));
+              }
+              if (ncols > 0) store_row32<OUT_DT>(p.D, (int64_t)row * p.N + col, o, ncols, vec_ok);
+            }
+          }
+          break;      // one work item per CTA in this mode
+        }
+      }
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
@@ -257,6 +353,7 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           store_row32<OUT_DT>(p.D, (int64_t)row * p.N + col, v, ncols, vec_ok);
         }
       }
+      if (warp == 6 && lane == 0) AC4K_TR1(1, 0, 1);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar + 8 * acc);
@@ -264,12 +361,18 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     }
   }
 
+  if (threadIdx.x == 0) AC4K_TR1(3, 0, 4);
+  if (p.cluster_reduce && warp < 6) {      // the epilogue warps pass the same two barriers inside their role
+    cluster_sync();
+    cluster_sync();
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (threadIdx.x == 0) AC4K_TR1(3, 0, 5);
 }
 
 // out[m, n] = cast(alpha * sum_s ws[s, m, n] + bias[n]) for the split-K path; one thread per
@@ -398,6 +501,22 @@ static int launch(const CUtensorMap &ta, const CUtensorMap &tb, const GemmArgs &
   }
   const int num_work = args.tiles_m * args.tiles_n * args.splits;
   const int grid = num_work < sms ? num_work : sms;
+  if (args.cluster_reduce) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(num_work);
+    cfg.blockDim = dim3(kNumThreads);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = args.splits;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    AC4K_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, args));
+    return 0;
+  }
   kern<<<grid, kNumThreads, C::SMEM_BYTES, stream>>>(ta, tb, args);
   AC4K_LAUNCH_CHECK("linear_nvfp4_kernel");
   return 0;
@@ -529,9 +648,6 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
     // few output tiles (decode shapes): narrower tiles and K slices put more SMs on the weight stream
     if (g_force_bn == 0 && ceil_div(M, BM) * ceil_div(N, 256) * 2 <= di.sms) bn = 128;
     pl = plan_split(M, N, K, bn, di.sms);
-    if (ws_mode == 1 && pl.ws_bytes > ws_capacity)
-      return fail(AC4K_ERR_SHAPE, "split-K workspace of %zu bytes exceeds the fixed scratch of %zu bytes",
-                  pl.ws_bytes, ws_capacity);
   }
   CUtensorMap ta, tb;
   if (int e = get_tmap(A, M, K / 2, BM, &ta)) return e;
@@ -573,6 +689,17 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
   a.splits = pl.splits;
   a.kt_per_split = pl.kt_per_split;
   a.ws = nullptr;
+  // K slices as a cluster with an in-kernel reduction: every work item needs its own CTA, the other
+  // slices' partial sums ([slices - 1, 128 rows, 128] fp32) must fit the leader's operand buffers, and
+  // a cluster has at most 8 CTAs
+  a.cluster_reduce = 0;
+  if (!use_pair && pl.splits > 1 && pl.splits <= 8 && bn == 128 && M <= BM && !(g_dbg & 32) &&
+      ceil_div(N, bn) * pl.splits <= di.sms &&
+      (size_t)(pl.splits - 1) * BM * 128 * 4 <= (size_t)Cfg<128>::STAGES * (Cfg<128>::A_BYTES + Cfg<128>::B_BYTES))
+    a.cluster_reduce = 1;
+  if (!use_pair && pl.splits > 1 && !a.cluster_reduce && ws_mode == 1 && pl.ws_bytes > ws_capacity)
+    return fail(AC4K_ERR_SHAPE, "split-K workspace of %zu bytes exceeds the fixed scratch of %zu bytes",
+                pl.ws_bytes, ws_capacity);
   const bool tiled = sf_layout == AC4K_SF_TILE128X4;
   if (use_pair) {
     // row-layout scales of a large problem are re-tiled first (see sf_rows_to_tiles_kernel); the
@@ -606,7 +733,7 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
     }
     return rc;
   }
-  if (pl.splits > 1) {
+  if (pl.splits > 1 && !a.cluster_reduce) {
     if (ws_mode == 1) {
       a.ws = ws_fixed;
     } else {
@@ -622,7 +749,7 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
   else
     rc = tiled ? launch_dt<128, true>(d_dtype, ta, tb, a, di.sms, stream)
                : launch_dt<128, false>(d_dtype, ta, tb, a, di.sms, stream);
-  if (pl.splits > 1) {
+  if (pl.splits > 1 && !a.cluster_reduce) {
     if (rc == 0) {
       const int64_t total4 = M * N / 4;
       const unsigned blocks = (unsigned)ceil_div(total4, 256);

@@ -38,8 +38,11 @@ def _operands(m, n, k, seed, layout):
 @pytest.mark.parametrize("layout_name,layout", [("128x4", 1), ("ac4k", 0)])
 def test_noalloc_matches_regular_entry_point_twice(layout_name, layout):
     from ac4k_kernel_b200._lib import LIB, device_status, last_error
-    # two different decode-shaped problems, both on the split-K (scratch-using) path, back to back
-    cases = [(16, 2048, 4096, torch.bfloat16, None), (64, 8192, 8192, torch.float16, torch.float32)]
+    # decode-shaped and split-K problems back to back
+    # (the first two now add their K slices inside the kernel and need no scratch at all; the fp32 one
+    # has two row tiles, which keeps it on the workspace path: 4 slices x 256 x 1024 fp32 = 4 MiB)
+    cases = [(16, 2048, 4096, torch.bfloat16, None), (64, 8192, 8192, torch.float16, torch.float32),
+             (256, 1024, 4096, torch.float32, None), (200, 1024, 8192, torch.float32, torch.bfloat16)]
     for i, (m, n, k, odt, bdt) in enumerate(cases):
         a4, asf, ag, b4, bsf, bg = _operands(m, n, k, 40 + i, layout_name)
         bias = None if bdt is None else torch.randn((1, n), device="cuda").to(bdt)
@@ -68,10 +71,10 @@ def test_noalloc_large_shape_needs_no_scratch():
 
 
 def test_noalloc_rejects_scratch_beyond_its_maximum():
-    """[2 slices, 128, 9216] fp32 = 9 MiB of partial sums does not fit the 8 MiB array."""
+    """[8 slices, 128, 2304] fp32 = 9 MiB of partial sums does not fit the 8 MiB array."""
     from ac4k_kernel_b200._lib import LIB, last_error
-    a4, asf, ag, b4, bsf, bg = _operands(128, 9216, 8192, 9, "128x4")
-    out = torch.empty((128, 9216), dtype=torch.bfloat16, device="cuda")
+    a4, asf, ag, b4, bsf, bg = _operands(128, 2304, 8192, 9, "128x4")
+    out = torch.empty((128, 2304), dtype=torch.bfloat16, device="cuda")
     rc = _call(LIB.ac4k_linear_nvfp4_noalloc, out, a4, asf, ag, b4, bsf, bg, None, 1)
     assert rc == -2 and "exceeds the fixed scratch" in last_error()
     # the regular entry point handles the same shape
