@@ -210,8 +210,18 @@ def run_reference(args):
     from oracle import emulation as emu
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    n = k = 4096
-    rows = 256
+    if args.gpus > 1:
+        # the N > 1 line of the other arm is the column-parallel config (M = K = 8192, N = 28672)
+        n, k, rows = 4096, 8192, 256
+        workload = (f"column-parallel NVFP4 GEMM M=8192 K=8192 N=28672 over {args.gpus} GPUs "
+                    "(row and column sample on CPU)")
+        what = f"{rows} of 8192 activation rows x {n} of 28672 weight rows (K = 8192 in full)"
+        scaling = "strong"
+    else:
+        n, k, rows = 4096, 4096, 256
+        workload = "single-GPU square NVFP4 GEMM M=N=K=4096 (row sample on CPU)"
+        what = f"{rows} of 4096 activation rows x full 4096x4096 weight"
+        scaling = "weak"
     g = torch.Generator().manual_seed(0)
     w = (torch.randn((n, k), generator=g) * 0.02).bfloat16()
     w4, wsf, wg = emu.quantize_nvfp4_ref(w)
@@ -228,14 +238,14 @@ def run_reference(args):
             break
     dt = (time.perf_counter() - t) / done
     tflops = 2.0 * rows * n * k / dt / 1e12
-    sample = (f"each step = {rows} of 4096 activation rows x full 4096x4096 weight through the torch "
+    sample = (f"each step = {what} through the torch "
               f"emulation (dequantise, fp32 matmul, bf16 cast); {done} steps timed")
     line = {
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": done, "warmup": min(args.warmup, 2), "ms_per_step": dt * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3 block scales, fp32 accumulate)",
+        "scaling": scaling, "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3 block scales, fp32 accumulate)",
         "data": "synthetic",
-        "config": {"workload": "single-GPU square NVFP4 GEMM M=N=K=4096 (row sample on CPU)"},
+        "config": {"workload": workload},
         "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference's GEMM kernel is sm_120a-only and cannot run on a B200; its CPU-runnable "
