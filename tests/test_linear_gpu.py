@@ -345,3 +345,60 @@ def test_requant_argument_checks(ops):
     b4, bsf, bg = ops.quantize(b, 0, 1, sf_layout="128x4")
     with pytest.raises(RuntimeError):
         ops.linear_requant(a4, asf, ag, b4, bsf, bg, ag)
+
+
+@pytest.mark.parametrize("layout", ["ac4k", "128x4"])
+@pytest.mark.parametrize("m,n,k,bdt", [
+    (129, 136, 64, None),              # pair kernel, one K step, one ragged tile in both directions
+    (257, 264, 576, torch.float32),    # 9 K steps: full stage of 8 + ragged stage of 1; two row tiles
+    (512, 136, 1088, None),            # 17 K steps, narrow ragged N
+    (300, 520, 4160, torch.bfloat16),  # 65 K steps (8 full stages + 1), three column tiles
+    (2048, 2048, 2048, None),          # whole tiles, more tiles than clusters
+])
+def test_pair_kernel_edges(ops, layout, m, n, k, bdt):
+    """Shapes that take the CTA-pair kernel (M, N > 128, N % 8 == 0) at its edges: ragged last
+    pipeline stage, ragged tiles, a single K step."""
+    run_case(ops, m, n, k, seed=31, layout=layout, bias_dtype=bdt, oracle_device="cuda")
+
+
+def test_graph_capture_and_two_streams(ops):
+    """The calls are asynchronous on the caller's stream and capturable: a CUDA graph of
+    quantize + linear replays to the eager result, and two streams running different problems
+    at the same time (one of them on the split-K path) do not disturb each other."""
+    from ac4k_kernel_b200 import _lib
+    a = gaussian((512, 1024), seed=41).cuda()
+    b = gaussian((768, 1024), seed=42).cuda()
+    b4, bsf, bg = ops.quantize(b, 0, 1, sf_layout="128x4")
+    a4, asf, ag = ops.quantize(a, 0, 1, sf_layout="128x4")
+    eager = ops.linear(a4, asf, ag, b4, bsf, bg)
+    out = torch.empty_like(eager)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        with torch.cuda.graph(g, stream=st):
+            qa, qsf, qg = ops.quantize(a, 0, 1, sf_layout="128x4")
+            ops.linear(qa, qsf, qg, b4, bsf, bg, out=out)
+    for _ in range(3):
+        out.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, eager)
+    # two streams
+    a2 = gaussian((16, 4096), seed=43).cuda()
+    b2 = gaussian((2048, 4096), seed=44).cuda()
+    a24, a2sf, a2g = ops.quantize(a2, 0, 1, sf_layout="ac4k")
+    b24, b2sf, b2g = ops.quantize(b2, 0, 1, sf_layout="ac4k")
+    ref2 = ops.linear(a24, a2sf, a2g, b24, b2sf, b2g)
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    outs1, outs2 = [], []
+    for _ in range(10):
+        with torch.cuda.stream(s1):
+            outs1.append(ops.linear(a4, asf, ag, b4, bsf, bg))
+        with torch.cuda.stream(s2):
+            outs2.append(ops.linear(a24, a2sf, a2g, b24, b2sf, b2g))
+    torch.cuda.synchronize()
+    assert all(torch.equal(o, eager) for o in outs1)
+    assert all(torch.equal(o, ref2) for o in outs2)
+    assert _lib.device_status() == 0
