@@ -92,6 +92,9 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(smem_gen + (tmem_slot - smem_base));
+  // set-up done on this CTA's own resources only; global memory is touched from here on
+  grid_launch_dependents();
+  grid_dependency_wait();
   if (threadIdx.x == 0) AC4K_TR1(3, 0, 1);
 
   if (warp == 0) {
@@ -501,24 +504,25 @@ static int launch(const CUtensorMap &ta, const CUtensorMap &tb, const GemmArgs &
   }
   const int num_work = args.tiles_m * args.tiles_n * args.splits;
   const int grid = num_work < sms ? num_work : sms;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(args.cluster_reduce ? num_work : grid);
+  cfg.blockDim = dim3(kNumThreads);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  // set-up may overlap the previous kernel's tail (see grid_dependency_wait)
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = (args.dbg & 64) ? 0 : 1;
+  cfg.numAttrs = 1;
   if (args.cluster_reduce) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(num_work);
-    cfg.blockDim = dim3(kNumThreads);
-    cfg.dynamicSmemBytes = C::SMEM_BYTES;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = args.splits;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    AC4K_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, args));
-    return 0;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = args.splits;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
   }
-  kern<<<grid, kNumThreads, C::SMEM_BYTES, stream>>>(ta, tb, args);
-  AC4K_LAUNCH_CHECK("linear_nvfp4_kernel");
+  cfg.attrs = attr;
+  AC4K_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, args));
   return 0;
 }
 

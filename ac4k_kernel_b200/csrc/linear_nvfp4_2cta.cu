@@ -122,6 +122,10 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   cluster_sync();          // peer's barriers are initialised before anything is signalled remotely
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(smem_gen + (tmem_slot - smem_base));
+  // Everything above touched only this CTA's own resources, so it may overlap the tail of the kernel
+  // before this one in the stream; from here on global memory is read and written.
+  grid_launch_dependents();
+  grid_dependency_wait();
   if (threadIdx.x == 0) AC4K_TR(3, 0, 1);
 
   if (warp == 0) {
@@ -545,8 +549,18 @@ static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const GemmA
   const int num_tiles = args.tiles_m * args.tiles_n;
   int clusters = max_clusters[dev];
   if (num_tiles < clusters) clusters = num_tiles;
-  kern<<<2 * clusters, pair::kThreadsPair, pair::SMEM_BYTES, stream>>>(ta, tb, args);
-  AC4K_LAUNCH_CHECK("linear_nvfp4_2cta_kernel");
+  // launched so that its set-up may overlap the previous kernel's tail (see grid_dependency_wait)
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * clusters);
+  cfg.blockDim = dim3(pair::kThreadsPair);
+  cfg.dynamicSmemBytes = pair::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = (args.dbg & 64) ? 0 : 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  AC4K_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, args));
   return 0;
 }
 
