@@ -32,6 +32,14 @@ int cuda_fail(cudaError_t e, const char *what);
 // library's module); kernels with bounded waits receive it as an argument.  NULL on error.
 unsigned int *device_status_ptr();
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization
+// attribute may start while the kernel before it in the stream is still running; it must execute
+// grid_dependency_wait() before it touches memory that the earlier kernel reads or writes (the wait
+// returns at once if the kernel was launched normally).  grid_launch_dependents() lets the NEXT
+// kernel of the stream be scheduled onto SMs as this grid's CTAs leave them.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- small integer helpers --------------------------------------------------------------
 __host__ __device__ constexpr int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 __host__ __device__ constexpr int64_t align_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }

@@ -299,14 +299,6 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
   return r;
 }
-// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization
-// attribute may start while the kernel before it in the stream is still running; it must execute
-// grid_dependency_wait() before it touches memory that the earlier kernel reads or writes (the wait
-// returns at once if the kernel was launched normally).  grid_launch_dependents() lets the NEXT
-// kernel of the stream be scheduled onto SMs as this grid's CTAs leave them.
-__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
 // 16-byte store into the shared memory of a CTA of this cluster (address from map_to_cta)
 __device__ __forceinline__ void st_shared_cluster_v4(uint32_t addr, float a, float b, float c, float d) {
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
