@@ -600,7 +600,8 @@ static SplitPlan plan_split(int64_t M, int64_t N, int64_t K, int bn, int sms) {
 }
 
 // ws_mode: 0 = workspace from the stream-ordered allocator (cudaMallocAsync / cudaFreeAsync),
-//          1 = caller-provided workspace of ws_capacity bytes (no allocation in this call)
+//          1 = fixed workspace of ws_capacity bytes, its address obtained from ws_fixed() only when a
+//              call really needs scratch (no allocation in this call)
 // `more`: further destinations that receive the same tile stores (the fused all-gather), each a
 // [M, ldd] buffer written at columns [col_off, col_off + N); NULL / 0 for the plain GEMM, which
 // writes D as a dense [M, N] matrix.
@@ -611,7 +612,7 @@ struct OutSpec { void *const *more; int n_more; int64_t ldd; int64_t col_off;
 static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, const float *A_gs,
                        const void *B, const void *B_sf, const float *B_gs, const void *bias,
                        int bias_dtype, int64_t M, int64_t N, int64_t K, int sf_layout,
-                       cudaStream_t stream, int ws_mode, float *ws_fixed, size_t ws_capacity,
+                       cudaStream_t stream, int ws_mode, int (*ws_fixed)(float **), size_t ws_capacity,
                        const OutSpec *out = nullptr) {
   if (M < 0 || N < 0 || K < 0) return fail(AC4K_ERR_SHAPE, "negative dimension");
   if (d_dtype < 0 || d_dtype > 2) return fail(AC4K_ERR_ENUM, "unknown d_dtype %d", d_dtype);
@@ -713,8 +714,14 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
     const bool convert = !tiled && !(g_dbg & 16) && (double)M * (double)N * (double)K >= 2147483648.0 &&
                          (ws_mode == 0 || conv_bytes <= ws_capacity);
     if (!convert) return launch_linear_2cta(d_dtype, tiled, ta, tb, a, stream);
-    void *scratch = ws_fixed;
-    if (ws_mode == 0) AC4K_CUDA_TRY(cudaMallocAsync(&scratch, conv_bytes, stream));
+    void *scratch = nullptr;
+    if (ws_mode == 0) {
+      AC4K_CUDA_TRY(cudaMallocAsync(&scratch, conv_bytes, stream));
+    } else {
+      float *f = nullptr;
+      if (int e = ws_fixed(&f)) return e;
+      scratch = f;
+    }
     uint8_t *ta_sf = static_cast<uint8_t *>(scratch);
     uint8_t *tb_sf = ta_sf + (size_t)tiles_a * a.KT * 512;
     const int64_t pieces = (tiles_a + tiles_b) * a.KT * 32;
@@ -739,7 +746,7 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
   }
   if (pl.splits > 1 && !a.cluster_reduce) {
     if (ws_mode == 1) {
-      a.ws = ws_fixed;
+      if (int e = ws_fixed(&a.ws)) return e;
     } else {
       void *wsp = nullptr;
       AC4K_CUDA_TRY(cudaMallocAsync(&wsp, pl.ws_bytes, stream));
@@ -798,12 +805,9 @@ extern "C" int ac4k_linear_nvfp4(void *D, int d_dtype, const void *A, const void
 static constexpr size_t kFixedScratchBytes = 8u << 20;   // 8 MiB, held by every GPU that loads the library
 static __device__ __align__(256) unsigned char g_fixed_scratch[kFixedScratchBytes];
 
-extern "C" int ac4k_linear_nvfp4_noalloc(void *D, int d_dtype, const void *A, const void *A_sf,
-                                         const float *A_gs, const void *B, const void *B_sf,
-                                         const float *B_gs, const void *bias, int bias_dtype, int64_t M,
-                                         int64_t N, int64_t K, int sf_layout, ac4k_stream_t stream_) {
-  // In host code `g_fixed_scratch` is only a handle for the symbol, not a device address: the
-  // address is looked up once per device, with that device current, and then handed to the kernels.
+// In host code `g_fixed_scratch` is only a handle for the symbol, not a device address: the address
+// is looked up once per device, with that device current, and then handed to the kernels.
+static int fixed_scratch_ptr(float **out) {
   static float *scratch[64] = {};
   int dev = 0;
   AC4K_CUDA_TRY(cudaGetDevice(&dev));
@@ -814,8 +818,16 @@ extern "C" int ac4k_linear_nvfp4_noalloc(void *D, int d_dtype, const void *A, co
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_fixed_scratch)");
     scratch[dev] = static_cast<float *>(ptr);
   }
+  *out = scratch[dev];
+  return 0;
+}
+
+extern "C" int ac4k_linear_nvfp4_noalloc(void *D, int d_dtype, const void *A, const void *A_sf,
+                                         const float *A_gs, const void *B, const void *B_sf,
+                                         const float *B_gs, const void *bias, int bias_dtype, int64_t M,
+                                         int64_t N, int64_t K, int sf_layout, ac4k_stream_t stream_) {
   return linear_impl(D, d_dtype, A, A_sf, A_gs, B, B_sf, B_gs, bias, bias_dtype, M, N, K, sf_layout,
-                     static_cast<cudaStream_t>(stream_), 1, scratch[dev], kFixedScratchBytes);
+                     static_cast<cudaStream_t>(stream_), 1, fixed_scratch_ptr, kFixedScratchBytes);
 }
 
 // ------------------------------------------------------------------------------------------

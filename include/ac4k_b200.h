@@ -111,8 +111,8 @@ int ac4k_linear_nvfp4(void *D, int d_dtype, const void *A, const void *A_sf,
  * AC4K_ERR_SHAPE and a message; scale factors that do not fit are simply not re-tiled (same
  * result, a slower kernel path); shapes that need no scratch run as usual.
  *
- *  - The first call on each device looks up the array's device address (device must be current);
- *    make that first call before starting any stream capture.
+ *  - The first call on each device that needs scratch looks up the array's device address (device
+ *    must be current); make such a call before starting any stream capture.
  *  - All calls share the one array and it keeps whatever the last call left in it.  Nothing in
  *    it needs clearing: each call overwrites every partial sum it later reads.  Two calls that
  *    can overlap on the GPU (different streams) would race on it: serialise them. */

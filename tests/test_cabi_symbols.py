@@ -58,3 +58,43 @@ def test_python_checks_mirror_reference():
         _cuda_ops.quantize_nvfp4(torch.zeros((16, 32), dtype=torch.uint8),
                                  torch.zeros((1, 16, 4), dtype=torch.float8_e4m3fn), x,
                                  torch.zeros(()), 0, 1, False)
+
+
+def test_gemm_argument_errors_without_gpu():
+    """The GEMM entry points (plain, allocation-free, gather, re-quantising) reject bad sizes,
+    codes, alignments and NULLs with negative codes and a message, before any CUDA call."""
+    from ac4k_kernel_b200._lib import LIB, last_error
+    P = 4096                                   # any 16-byte-aligned non-NULL value; never dereferenced
+    lin = lambda fn, *a: fn(*a)
+    # (D, d_dtype, A, A_sf, A_gs, B, B_sf, B_gs, bias, bias_dtype, M, N, K, sf_layout, stream)
+    for fn in (LIB.ac4k_linear_nvfp4, LIB.ac4k_linear_nvfp4_noalloc):
+        assert fn(P, 0, P, P, P, P, P, P, None, 0, -1, 8, 64, 0, None) == -2          # negative M
+        assert fn(P, 9, P, P, P, P, P, P, None, 0, 8, 8, 64, 0, None) == -4           # unknown d_dtype
+        assert fn(P, 0, P, P, P, P, P, P, None, 0, 8, 8, 64, 5, None) == -4           # unknown sf_layout
+        assert fn(P, 0, P, P, P, P, P, P, None, 0, 0, 8, 64, 0, None) == 0            # empty output: nothing to do
+        assert fn(None, 0, P, P, P, P, P, P, None, 0, 8, 8, 64, 0, None) == -1        # NULL D
+        assert fn(P, 0, P, P, P, P, P, P, None, 0, 8, 8, 80, 0, None) == -2           # K not a multiple of 64
+        assert "multiple of 64" in last_error()
+        assert fn(P + 4, 0, P, P, P, P, P, P, None, 0, 8, 8, 64, 0, None) == -3       # misaligned D
+    dst = (ctypes.c_void_p * 2)(P, P)
+    g = LIB.ac4k_linear_nvfp4_gather
+    # (D_dsts, n_dst, ldd, col_off, d_dtype, A, A_sf, A_gs, B, B_sf, B_gs, bias, bias_dtype, M, N, K, layout, stream)
+    assert g(None, 1, 64, 0, 0, P, P, P, P, P, P, None, 0, 8, 64, 64, 1, None) == -1
+    assert g(dst, 0, 64, 0, 0, P, P, P, P, P, P, None, 0, 8, 64, 64, 1, None) == -2        # no destination
+    assert g(dst, 9, 64, 0, 0, P, P, P, P, P, P, None, 0, 8, 64, 64, 1, None) == -2        # more than 8
+    assert g(dst, 2, 64, 8, 0, P, P, P, P, P, P, None, 0, 8, 64, 64, 1, None) == -2        # columns do not fit
+    assert g(dst, 2, 132, 4, 0, P, P, P, P, P, P, None, 0, 8, 64, 64, 1, None) == -3       # ldd / col_off not % 8
+    bad = (ctypes.c_void_p * 2)(P, None)
+    assert g(bad, 2, 64, 0, 0, P, P, P, P, P, P, None, 0, 8, 64, 64, 1, None) == -1        # NULL destination
+    r = LIB.ac4k_linear_nvfp4_requant
+    # (out_fp4, out_sf, out_gs, out_layout, A, A_sf, A_gs, B, B_sf, B_gs, bias, bias_dtype, M, N, K, layout, stream)
+    assert r(None, P, P, 1, P, P, P, P, P, P, None, 0, 8, 64, 64, 1, None) == -1
+    assert r(P, P, P, 3, P, P, P, P, P, P, None, 0, 8, 64, 64, 1, None) == -4              # unknown output layout
+    assert r(P, P, P, 1, P, P, P, P, P, P, None, 0, 8, 96, 64, 1, None) == -5              # N not a multiple of 64
+    assert "64" in last_error()
+    ptr = ctypes.c_void_p()
+    handle = ctypes.create_string_buffer(64)
+    assert LIB.ac4k_peer_alloc(0, ctypes.byref(ptr), handle) == -2
+    assert LIB.ac4k_peer_alloc(1024, None, handle) == -1
+    assert LIB.ac4k_peer_open(None, ctypes.byref(ptr)) == -1
+    assert LIB.ac4k_peer_close(None) == 0 and LIB.ac4k_peer_free(None) == 0
