@@ -528,7 +528,8 @@ def run_multi(args, peaks):
             "scaling": "strong", "vs_baseline": None,
             "dtype": "nvfp4 (e2m1 x ue4m3 block scales, fp32 accumulate)", "data": "synthetic",
             "config": {"workload": f"column-parallel NVFP4 GEMM M=8192 K=8192 N=28672 over {world} GPUs "
-                                   f"(N/{world} = {ns} columns per rank) + NCCL all-gather of the bf16 output",
+                                   f"(N/{world} = {ns} columns per rank) + all-gather of the bf16 output "
+                                   "(fused into the GEMM epilogue: peer stores over NVLink)",
                        "l2": f"{n_sets} weight/output sets rotated per rank",
                        "timing": "CUDA events on each rank, max over ranks"},
             "gemm_only_tflops": gemm_tflops,
