@@ -98,3 +98,23 @@ def test_gemm_argument_errors_without_gpu():
     assert LIB.ac4k_peer_alloc(1024, None, handle) == -1
     assert LIB.ac4k_peer_open(None, ctypes.byref(ptr)) == -1
     assert LIB.ac4k_peer_close(None) == 0 and LIB.ac4k_peer_free(None) == 0
+
+
+def test_header_is_valid_c_and_links_from_c(tmp_path):
+    """include/ac4k_b200.h compiled by a C compiler (not C++), linked against the built library and
+    run: identity strings and argument rejections through the C ABI, no Python in between."""
+    import shutil
+    import subprocess
+    from ac4k_kernel_b200 import _lib
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    exe = str(tmp_path / "use_from_c")
+    src = os.path.join(ROOT, "tests", "c_abi", "use_from_c.c")
+    libdir = os.path.dirname(_lib.LIB_PATH)
+    cmd = [gcc, "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), src, "-o", exe,
+           "-L", libdir, "-l:libac4k_b200.so", f"-Wl,-rpath,{libdir}"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and r.stdout.strip() == "ok", r.stdout + r.stderr
