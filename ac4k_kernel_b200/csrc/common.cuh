@@ -92,6 +92,25 @@ __device__ __forceinline__ int8_t f32_to_s8_rni_sat(float x) {
   return (int8_t)r;
 }
 
+// 4 fp32 -> 4 int8 (round to nearest even, saturating), element 0 in the low byte.  The float ->
+// s32 conversions clamp and map NaN to 0 exactly like cvt.rni.sat.s8.f32 does; cvt.pack saturates
+// two s32 to s8, puts them in the low half-word (first operand in the upper byte) and moves the low
+// half-word of its third operand to the top: 6 instructions for 4 values instead of 4 conversions
+// plus shifts, masks and ors.
+__device__ __forceinline__ uint32_t f32x4_to_s8x4(float a, float b, float c, float d) {
+  uint32_t r;
+  asm("{\n"
+      ".reg .s32 ia, ib, ic, id;\n"
+      ".reg .b32 hi;\n"
+      "cvt.rni.s32.f32 ia, %1;\n cvt.rni.s32.f32 ib, %2;\n cvt.rni.s32.f32 ic, %3;\n cvt.rni.s32.f32 id, %4;\n"
+      "cvt.pack.sat.s8.s32.b32 hi, id, ic, 0;\n"
+      "cvt.pack.sat.s8.s32.b32 %0, ib, ia, hi;\n"
+      "}"
+      : "=r"(r)
+      : "f"(a), "f"(b), "f"(c), "f"(d));
+  return r;
+}
+
 // |x| of two packed bf16 (clears the sign bits), max of packed bf16 pairs
 __device__ __forceinline__ uint32_t abs_bf16x2(uint32_t v) { return v & 0x7FFF7FFFu; }
 __device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {

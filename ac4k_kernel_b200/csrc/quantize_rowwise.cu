@@ -29,10 +29,8 @@ __device__ __forceinline__ uint2 convert8(const uint4 &v, float r) {
     o.x = f32x4_to_e4m3x4(f[0], f[1], f[2], f[3]);
     o.y = f32x4_to_e4m3x4(f[4], f[5], f[6], f[7]);
   } else {
-    o.x = (uint32_t)(uint8_t)f32_to_s8_rni_sat(f[0]) | ((uint32_t)(uint8_t)f32_to_s8_rni_sat(f[1]) << 8) |
-          ((uint32_t)(uint8_t)f32_to_s8_rni_sat(f[2]) << 16) | ((uint32_t)(uint8_t)f32_to_s8_rni_sat(f[3]) << 24);
-    o.y = (uint32_t)(uint8_t)f32_to_s8_rni_sat(f[4]) | ((uint32_t)(uint8_t)f32_to_s8_rni_sat(f[5]) << 8) |
-          ((uint32_t)(uint8_t)f32_to_s8_rni_sat(f[6]) << 16) | ((uint32_t)(uint8_t)f32_to_s8_rni_sat(f[7]) << 24);
+    o.x = f32x4_to_s8x4(f[0], f[1], f[2], f[3]);
+    o.y = f32x4_to_s8x4(f[4], f[5], f[6], f[7]);
   }
   return o;
 }
