@@ -540,7 +540,16 @@ static int launch_dt(int d_dtype, const CUtensorMap &ta, const CUtensorMap &tb, 
 
 using namespace ac4k;
 
-// Tile width override for experiments: 0 = automatic.
+// Measurement switches (process-wide, not part of the C ABI header, all 0 in production).  They let
+// one build time a kernel choice against its alternative:
+//   ac4k_debug_set_tile_n(bn)   0 automatic; 128 / 256 force the single-CTA kernel with that tile
+//                               width; 512 forces the CTA-pair kernel
+//   ac4k_debug_set_splits(n)    0 automatic; 1 never cut K into slices; n > 1 force n slices
+//   ac4k_debug_set_flags(bits)  8 skip the epilogue's stores; 16 read row-layout scales in the kernel
+//                               instead of re-tiling them first; 32 add K slices through the workspace
+//                               and the reduction kernel instead of inside a cluster; 64 launch without
+//                               the programmatic-stream-serialization attribute
+//   ac4k_debug_set_trace(ptr)   device buffer for the clock stamps of builds with -DAC4K_TRACE_ENABLED
 static int g_force_bn = 0;
 static int g_force_splits = 0;   // 0 = automatic, 1 = never split, n > 1 = force n K slices
 extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_splits(int n) { g_force_splits = n; }
