@@ -413,7 +413,9 @@ def run_multi(args, peaks):
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    # a rank that fails must not leave the others waiting for long: collectives give up after 3 minutes
+    import datetime
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=180))
     m, k, n = 8192, 8192, 28672
     flops = 2.0 * m * n * k
     lo, hi = parallel.shard_bounds(n, rank, world)
