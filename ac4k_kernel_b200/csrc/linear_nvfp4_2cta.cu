@@ -60,7 +60,8 @@ static constexpr int SFA_BYTES = KS * 512;
 static constexpr int SFB_BYTES = 2 * KS * 512;
 static constexpr int STAGES = 3;                    // operand ring
 static constexpr int SF_STAGES = 2;                 // scale rings (shared memory and tensor memory)
-static constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + SF_STAGES * (SFA_BYTES + SFB_BYTES) + 1024 + 512;
+static constexpr int BIAS_BYTES = 8 * 128 * 4;          // one tile's bias as fp32, 128 columns per epilogue warp
+static constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + SF_STAGES * (SFA_BYTES + SFB_BYTES) + 1024 + 512 + BIAS_BYTES;
 static constexpr int SFA_COL = 256, SFA_COLS = KS * 4, SFB_COL = SFA_COL + SF_STAGES * SFA_COLS, SFB_COLS = KS * 8;
 static_assert(SFB_COL + SF_STAGES * SFB_COLS <= kTmemCols, "tensor memory overflow");
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory overflow");
@@ -87,6 +88,7 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   const uint32_t tempty_bar = tfull_bar + 8;          // leader: 16 epilogue warps drained the accumulator
   const uint32_t ready_word = tempty_bar + 8;         // leader: stages the watcher has seen complete
   const uint32_t tmem_slot = ready_word + 8;
+  const uint32_t sBias = bars + 512;                  // [8 epilogue warps][128] fp32
   uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -359,6 +361,19 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
       const int row = tm * BMP + (int)rank * 128 + q * 32 + lane;
       const int col0 = tn * BN + half * 128;
+      const uint32_t bias_s = sBias + (uint32_t)(half * 4 + q) * 512u;
+      if (p.bias != nullptr) {
+        // this warp's 128 bias values go to shared memory while the tile's MMAs are still running, so
+        // that the drain below - which sits between two tiles - only adds broadcast shared-memory loads
+        float b4[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int n = col0 + lane * 4 + i;
+          b4[i] = n < p.N ? load_bias(p.bias, p.bias_dt, n) : 0.0f;
+        }
+        st_shared_v4f(bias_s + lane * 16, b4[0], b4[1], b4[2], b4[3]);
+        __syncwarp();
+      }
       if (!mbar_wait(tfull_bar, acc_ph)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue); break; }
       tc_fence_after();
       if (warp == 6 && lane == 0) AC4K_TR(1, ti, 0);
@@ -378,21 +393,18 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32_sync(t_row + c * 32, r);
-          const int col = col0 + c * 32;
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[64];
+          tmem_ld_32x32b_x64_sync(t_row + c * 64, r);
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            float v0 = __fmul_rn(__uint_as_float(r[2 * i]), alpha), v1 = __fmul_rn(__uint_as_float(r[2 * i + 1]), alpha);
-            if (col + 2 * i < p.N) v0 = __fadd_rn(v0, load_bias(p.bias, p.bias_dt, col + 2 * i));
-            if (col + 2 * i + 1 < p.N) v1 = __fadd_rn(v1, load_bias(p.bias, p.bias_dt, col + 2 * i + 1));
+            const float4 bb = ld_shared_v4f(bias_s + (c * 16 + i) * 16);
             if (OUT_DT == AC4K_DT_BF16) {
-              __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
-              w[c * 16 + i] = *reinterpret_cast<uint32_t *>(&h);
+              w[c * 32 + 2 * i] = scale_bias_pack_bf16x2(r[4 * i], r[4 * i + 1], alpha, bb.x, bb.y);
+              w[c * 32 + 2 * i + 1] = scale_bias_pack_bf16x2(r[4 * i + 2], r[4 * i + 3], alpha, bb.z, bb.w);
             } else {
-              __half2 h = __floats2half2_rn(v0, v1);
-              w[c * 16 + i] = *reinterpret_cast<uint32_t *>(&h);
+              w[c * 32 + 2 * i] = scale_bias_pack_f16x2(r[4 * i], r[4 * i + 1], alpha, bb.x, bb.y);
+              w[c * 32 + 2 * i + 1] = scale_bias_pack_f16x2(r[4 * i + 2], r[4 * i + 3], alpha, bb.z, bb.w);
             }
           }
         }

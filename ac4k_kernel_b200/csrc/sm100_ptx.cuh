@@ -246,6 +246,14 @@ __device__ __forceinline__ uint32_t ld_shared_volatile(uint32_t addr) {
   asm volatile("ld.volatile.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
   return v;
 }
+__device__ __forceinline__ void st_shared_v4f(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cta.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ float4 ld_shared_v4f(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cta.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
 __device__ __forceinline__ void st_shared_release(uint32_t addr, uint32_t v) {
   asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
@@ -257,6 +265,25 @@ __device__ __forceinline__ uint32_t scale_pack_bf16x2(uint32_t a0, uint32_t a1, 
       "mov.b64 p, {%1, %2};\n mov.b64 ss, {%3, %3};\n mul.rn.f32x2 p, p, ss;\n mov.b64 {x, y}, p;\n"
       "cvt.rn.bf16x2.f32 %0, y, x;\n}"
       : "=r"(out) : "r"(a0), "r"(a1), "f"(s));
+  return out;
+}
+// ((a0 * s) + b0, (a1 * s) + b1): product and sum each rounded to nearest in fp32, packed to bf16 / fp16
+__device__ __forceinline__ uint32_t scale_bias_pack_bf16x2(uint32_t a0, uint32_t a1, float s, float b0, float b1) {
+  uint32_t out;
+  asm("{\n.reg .b64 p, ss, bb;\n.reg .f32 x, y;\n"
+      "mov.b64 p, {%1, %2};\n mov.b64 ss, {%3, %3};\n mov.b64 bb, {%4, %5};\n"
+      "mul.rn.f32x2 p, p, ss;\n add.rn.f32x2 p, p, bb;\n mov.b64 {x, y}, p;\n"
+      "cvt.rn.bf16x2.f32 %0, y, x;\n}"
+      : "=r"(out) : "r"(a0), "r"(a1), "f"(s), "f"(b0), "f"(b1));
+  return out;
+}
+__device__ __forceinline__ uint32_t scale_bias_pack_f16x2(uint32_t a0, uint32_t a1, float s, float b0, float b1) {
+  uint32_t out;
+  asm("{\n.reg .b64 p, ss, bb;\n.reg .f32 x, y;\n"
+      "mov.b64 p, {%1, %2};\n mov.b64 ss, {%3, %3};\n mov.b64 bb, {%4, %5};\n"
+      "mul.rn.f32x2 p, p, ss;\n add.rn.f32x2 p, p, bb;\n mov.b64 {x, y}, p;\n"
+      "cvt.rn.f16x2.f32 %0, y, x;\n}"
+      : "=r"(out) : "r"(a0), "r"(a1), "f"(s), "f"(b0), "f"(b1));
   return out;
 }
 __device__ __forceinline__ uint32_t scale_pack_f16x2(uint32_t a0, uint32_t a1, float s) {
