@@ -139,7 +139,9 @@ int get_device_info(DeviceInfo *out);
 // 2-D byte tensor map [rows, row_bytes] with a (128 B x box_rows) box and 128-byte swizzle
 int get_tmap(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUtensorMap *out);
 // 2-CTA kernel launcher (linear_nvfp4_2cta.cu); D must be bf16/fp16 with N % 8 == 0
+// tsa / tsb: tensor maps of row-layout scales (get_tmap_sf); ignored when sf_tiled
+int get_tmap_sf(const void *ptr, int64_t rows16, int64_t kt, int box_rows, int box_ksteps, CUtensorMap *out);
 int launch_linear_2cta(int d_dtype, bool sf_tiled, const CUtensorMap &ta, const CUtensorMap &tb,
-                       GemmArgs args, cudaStream_t stream);
+                       const CUtensorMap &tsa, const CUtensorMap &tsb, GemmArgs args, cudaStream_t stream);
 
 }  // namespace ac4k

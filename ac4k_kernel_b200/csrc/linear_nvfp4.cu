@@ -43,6 +43,7 @@ using namespace ptx;
 template <int BN, bool SF_TILED, int OUT_DT>
 __global__ void __launch_bounds__(kNumThreads, 1)
 linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                    const __grid_constant__ CUtensorMap tma_sfa, const __grid_constant__ CUtensorMap tma_sfb,
                     const GemmArgs p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -83,6 +84,10 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     fence_barrier_init();
     prefetch_tmap(&tma_a);
     prefetch_tmap(&tma_b);
+    if (!SF_TILED) {
+      prefetch_tmap(&tma_sfa);
+      prefetch_tmap(&tma_sfb);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -118,8 +123,10 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             const int nb_valid = min(BN / 128, (p.rows_sfb - n0) / 128);
             sfb_bytes = nb_valid * nk * 512;
           } else {
-            sfa_bytes = nk * 4 * min(BM, p.rows_sfa - m0);
-            sfb_bytes = nk * 4 * min(BN, p.rows_sfb - n0);
+            // one box of [4 K steps][rows] words per operand; rows and K steps outside the tensor
+            // arrive as zeros and count towards the transaction bytes
+            sfa_bytes = K64_PER_STAGE * BM * 4;
+            sfb_bytes = K64_PER_STAGE * BN * 4;
           }
           const uint32_t fb = full_bar + 8 * s;
           mbar_arrive_expect_tx(fb, C::A_BYTES + C::B_BYTES + sfa_bytes + sfb_bytes);
@@ -136,13 +143,9 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                              p.sfb + (nt * p.KT + k64) * 512, nk * 512, fb);
             }
           } else {
-            // [K/64][rows16][4 B]: one chunk of (rows x 4 B) per K=64 step
-            const uint32_t ra = 4 * min(BM, p.rows_sfa - m0), rb = 4 * min(BN, p.rows_sfb - n0);
-            for (int j = 0; j < nk; ++j) {
-              bulk_load_1d(sSFA + s * C::SFA_BYTES + j * 512, p.sfa + ((k64 + j) * p.rows_sfa + m0) * 4, ra, fb);
-              bulk_load_1d(sSFB + s * C::SFB_BYTES + j * (BN / 128) * 512,
-                           p.sfb + ((k64 + j) * p.rows_sfb + n0) * 4, rb, fb);
-            }
+            // [K/64][rows16] words: a box of 4 K steps x the tile's rows per operand
+            tma_load_2d(sSFA + s * C::SFA_BYTES, &tma_sfa, m0, (int)k64, fb);
+            tma_load_2d(sSFB + s * C::SFB_BYTES, &tma_sfb, n0, (int)k64, fb);
           }
           if (++s == C::STAGES) { s = 0; ph ^= 1; }
         }
@@ -477,6 +480,23 @@ int get_tmap(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUt
   return 0;
 }
 
+// Row-layout scale factors [K/64][rows16] as 32-bit words (the four scales of a row at one K step):
+// a box of `box_rows` words x `box_ksteps` K steps lands in shared memory as [K step][row], which is
+// what the kernels' scale warps read.  Not swizzled; out-of-range rows and K steps read as zero.
+int get_tmap_sf(const void *ptr, int64_t rows16, int64_t kt, int box_rows, int box_ksteps, CUtensorMap *out) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return fail(AC4K_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[2] = {(cuuint64_t)rows16, (cuuint64_t)kt};
+  cuuint64_t gstride[1] = {(cuuint64_t)rows16 * 4};
+  cuuint32_t box[2] = {(cuuint32_t)box_rows, (cuuint32_t)box_ksteps};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(ptr), gdim, gstride, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail((int)r > 0 ? (int)r : 999, "cuTensorMapEncodeTiled (scales) failed with CUresult %d", (int)r);
+  return 0;
+}
+
 int get_device_info(DeviceInfo *out) {
   static DeviceInfo info[64];
   int dev = 0;
@@ -492,7 +512,8 @@ int get_device_info(DeviceInfo *out) {
 }
 
 template <int BN, bool SF_TILED, int OUT_DT>
-static int launch(const CUtensorMap &ta, const CUtensorMap &tb, const GemmArgs &args, int sms, cudaStream_t stream) {
+static int launch(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tsa, const CUtensorMap &tsb,
+                  const GemmArgs &args, int sms, cudaStream_t stream) {
   using C = Cfg<BN>;
   auto kern = linear_nvfp4_kernel<BN, SF_TILED, OUT_DT>;
   static bool attr_set[64] = {};
@@ -522,17 +543,17 @@ static int launch(const CUtensorMap &ta, const CUtensorMap &tb, const GemmArgs &
     cfg.numAttrs = 2;
   }
   cfg.attrs = attr;
-  AC4K_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, args));
+  AC4K_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, tsa, tsb, args));
   return 0;
 }
 
 template <int BN, bool SF_TILED>
-static int launch_dt(int d_dtype, const CUtensorMap &ta, const CUtensorMap &tb, const GemmArgs &a, int sms,
-                     cudaStream_t st) {
+static int launch_dt(int d_dtype, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tsa,
+                     const CUtensorMap &tsb, const GemmArgs &a, int sms, cudaStream_t st) {
   switch (d_dtype) {
-    case AC4K_DT_BF16: return launch<BN, SF_TILED, AC4K_DT_BF16>(ta, tb, a, sms, st);
-    case AC4K_DT_FP16: return launch<BN, SF_TILED, AC4K_DT_FP16>(ta, tb, a, sms, st);
-    default: return launch<BN, SF_TILED, AC4K_DT_FP32>(ta, tb, a, sms, st);
+    case AC4K_DT_BF16: return launch<BN, SF_TILED, AC4K_DT_BF16>(ta, tb, tsa, tsb, a, sms, st);
+    case AC4K_DT_FP16: return launch<BN, SF_TILED, AC4K_DT_FP16>(ta, tb, tsa, tsb, a, sms, st);
+    default: return launch<BN, SF_TILED, AC4K_DT_FP32>(ta, tb, tsa, tsb, a, sms, st);
   }
 }
 
@@ -545,8 +566,7 @@ using namespace ac4k;
 //   ac4k_debug_set_tile_n(bn)   0 automatic; 128 / 256 force the single-CTA kernel with that tile
 //                               width; 512 forces the CTA-pair kernel
 //   ac4k_debug_set_splits(n)    0 automatic; 1 never cut K into slices; n > 1 force n slices
-//   ac4k_debug_set_flags(bits)  8 skip the epilogue's stores; 16 read row-layout scales in the kernel
-//                               instead of re-tiling them first; 32 add K slices through the workspace
+//   ac4k_debug_set_flags(bits)  8 skip the epilogue's stores; 32 add K slices through the workspace
 //                               and the reduction kernel instead of inside a cluster; 64 launch without
 //                               the programmatic-stream-serialization attribute
 //   ac4k_debug_set_trace(ptr)   device buffer for the clock stamps of builds with -DAC4K_TRACE_ENABLED
@@ -559,37 +579,6 @@ extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_trace(void
 extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_flags(int f) { g_dbg = f; }
 extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_tile_n(int bn) { g_force_bn = bn; }
 
-// Scale factors in the reference's row layout [K/64, rows16, 4] -> 128 x 4 tiles
-// [ceil(rows/128), K/64, 32, 4, 4] for both operands in one launch.  The pair kernel moves tiled
-// scales with 16-byte shared-memory loads and three bulk copies per stage; fed with the row layout
-// it needs 4-byte loads and sixteen small copies, which costs far more than this pass (the scales
-// are 1/9 of the operand bytes).  One thread writes one 16-byte piece: the four scale words of rows
-// l, l + 32, l + 64, l + 96 of a tile at one K step.
-__global__ void __launch_bounds__(256)
-sf_rows_to_tiles_kernel(const uint32_t *__restrict__ src_a, int rows16_a, int tiles_a, uint4 *__restrict__ dst_a,
-                        const uint32_t *__restrict__ src_b, int rows16_b, int tiles_b, uint4 *__restrict__ dst_b,
-                        int KT) {
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t na = (int64_t)tiles_a * KT * 32;
-  const int64_t nb = (int64_t)tiles_b * KT * 32;
-  if (idx >= na + nb) return;
-  const bool is_b = idx >= na;
-  const int64_t i = is_b ? idx - na : idx;
-  const uint32_t *src = is_b ? src_b : src_a;
-  const int rows16 = is_b ? rows16_b : rows16_a;
-  const int l = (int)(i & 31);
-  const int64_t tk = i >> 5;
-  const int kt = (int)(tk % KT);
-  const int rt = (int)(tk / KT);
-  uint32_t w[4];
-#pragma unroll
-  for (int g = 0; g < 4; ++g) {
-    const int row = rt * 128 + 32 * g + l;
-    w[g] = row < rows16 ? __ldg(src + (int64_t)kt * rows16 + row) : 0u;
-  }
-  (is_b ? dst_b : dst_a)[i] = make_uint4(w[0], w[1], w[2], w[3]);
-}
-
 // Split-K plan for shapes with too few output tiles to occupy the GPU (decode: M <= 128): how many
 // K slices, and the fp32 workspace [splits, M, N] they need.  splits == 1 means no workspace.
 struct SplitPlan { int splits; int kt_per_split; size_t ws_bytes; };
@@ -598,7 +587,13 @@ static SplitPlan plan_split(int64_t M, int64_t N, int64_t K, int bn, int sms) {
   SplitPlan pl{1, (int)ceil_div(K / 64, K64_PER_STAGE), 0};
   const int64_t tiles = ceil_div(M, BM) * ceil_div(N, bn);
   const int k_tiles = pl.kt_per_split;
-  if (g_force_splits == 1 || N % 4 != 0 || tiles * 2 > sms || k_tiles < 8) return pl;
+  if (g_force_splits == 1 || N % 4 != 0 || tiles * 2 > sms) return pl;
+  // Measured on decode-like shapes (graph timing): with K = 4096 (16 stages) no split wins for any tile
+  // count (9.0 vs 9.5 - 12.6 us at 64 x 4096 x 4096); with K = 8192 slices pay when few tiles would
+  // leave most SMs idle (32 x 2048 x 8192: 13.5 -> 9.1 us with 8 slices) and, at 64 tiles, only for a
+  // small M, whose partial sums are cheap to add (16 rows: 15.9 -> 14.4 us; 128 rows: 16.1 -> 17.1 us)
+  if (g_force_splits == 0 && (k_tiles < 32 || (M > 64 && tiles >= 32))) return pl;
+  if (k_tiles < 8) return pl;
   int splits = g_force_splits > 1 ? g_force_splits : (int)(sms / tiles);
   if (splits > k_tiles / 4) splits = k_tiles / 4;      // at least four pipeline stages per slice
   if (splits < 2) return pl;
@@ -703,11 +698,12 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
   a.splits = pl.splits;
   a.kt_per_split = pl.kt_per_split;
   a.ws = nullptr;
-  // K slices as a cluster with an in-kernel reduction: every work item needs its own CTA, the other
-  // slices' partial sums ([slices - 1, 128 rows, 128] fp32) must fit the leader's operand buffers, and
-  // a cluster has at most 8 CTAs
+  // Two K slices run as a cluster with an in-kernel reduction: every work item needs its own CTA and
+  // the other slice's partial sums ([128 rows, 128] fp32) must fit the leader's operand buffers.  More
+  // slices go through the workspace: one leader adding three or more partial tiles was measured slower
+  // than the reduction kernel (64 x 4096 x 4096 with 4 slices: 12.6 against 9.5 us)
   a.cluster_reduce = 0;
-  if (!use_pair && pl.splits > 1 && pl.splits <= 8 && bn == 128 && M <= BM && !(g_dbg & 32) &&
+  if (!use_pair && pl.splits == 2 && bn == 128 && M <= BM && !(g_dbg & 32) &&
       ceil_div(N, bn) * pl.splits <= di.sms &&
       (size_t)(pl.splits - 1) * BM * 128 * 4 <= (size_t)Cfg<128>::STAGES * (Cfg<128>::A_BYTES + Cfg<128>::B_BYTES))
     a.cluster_reduce = 1;
@@ -716,42 +712,13 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
                 pl.ws_bytes, ws_capacity);
   const bool tiled = sf_layout == AC4K_SF_TILE128X4;
   if (use_pair) {
-    // row-layout scales of a large problem are re-tiled first (see sf_rows_to_tiles_kernel); the
-    // scratch comes from the stream-ordered allocator, or from the caller's fixed scratch if it fits
-    const int64_t tiles_a = ceil_div(M, 128), tiles_b = ceil_div(N, 128);
-    const size_t conv_bytes = (size_t)(tiles_a + tiles_b) * (size_t)a.KT * 512;
-    const bool convert = !tiled && !(g_dbg & 16) && (double)M * (double)N * (double)K >= 2147483648.0 &&
-                         (ws_mode == 0 || conv_bytes <= ws_capacity);
-    if (!convert) return launch_linear_2cta(d_dtype, tiled, ta, tb, a, stream);
-    void *scratch = nullptr;
-    if (ws_mode == 0) {
-      AC4K_CUDA_TRY(cudaMallocAsync(&scratch, conv_bytes, stream));
-    } else {
-      float *f = nullptr;
-      if (int e = ws_fixed(&f)) return e;
-      scratch = f;
+    // scales in the reference's row layout are fed by two more tensor maps (one box per operand and stage)
+    CUtensorMap tsa = ta, tsb = tb;      // placeholders when the scales are tiled (not used by the kernel then)
+    if (!tiled) {
+      if (int e = get_tmap_sf(A_sf, a.rows_sfa, a.KT, 128, 8, &tsa)) return e;
+      if (int e = get_tmap_sf(B_sf, a.rows_sfb, a.KT, 256, 8, &tsb)) return e;
     }
-    uint8_t *ta_sf = static_cast<uint8_t *>(scratch);
-    uint8_t *tb_sf = ta_sf + (size_t)tiles_a * a.KT * 512;
-    const int64_t pieces = (tiles_a + tiles_b) * a.KT * 32;
-    sf_rows_to_tiles_kernel<<<(unsigned)ceil_div(pieces, 256), 256, 0, stream>>>(
-        reinterpret_cast<const uint32_t *>(A_sf), a.rows_sfa, (int)tiles_a, reinterpret_cast<uint4 *>(ta_sf),
-        reinterpret_cast<const uint32_t *>(B_sf), a.rows_sfb, (int)tiles_b, reinterpret_cast<uint4 *>(tb_sf), a.KT);
-    int rc = 0;
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) rc = cuda_fail(e, "sf_rows_to_tiles_kernel");
-    if (rc == 0) {
-      a.sfa = ta_sf;
-      a.sfb = tb_sf;
-      a.rows_sfa = (int)(tiles_a * 128);
-      a.rows_sfb = (int)(tiles_b * 128);
-      rc = launch_linear_2cta(d_dtype, true, ta, tb, a, stream);
-    }
-    if (ws_mode == 0) {
-      e = cudaFreeAsync(scratch, stream);
-      if (e != cudaSuccess && rc == 0) rc = cuda_fail(e, "cudaFreeAsync");
-    }
-    return rc;
+    return launch_linear_2cta(d_dtype, tiled, ta, tb, tsa, tsb, a, stream);
   }
   if (pl.splits > 1 && !a.cluster_reduce) {
     if (ws_mode == 1) {
@@ -762,13 +729,18 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
       a.ws = static_cast<float *>(wsp);
     }
   }
+  CUtensorMap tsa = ta, tsb = tb;        // placeholders when the scales are tiled
+  if (!tiled) {
+    if (int e = get_tmap_sf(A_sf, a.rows_sfa, a.KT, BM, K64_PER_STAGE, &tsa)) return e;
+    if (int e = get_tmap_sf(B_sf, a.rows_sfb, a.KT, bn, K64_PER_STAGE, &tsb)) return e;
+  }
   int rc;
   if (bn == 256)
-    rc = tiled ? launch_dt<256, true>(d_dtype, ta, tb, a, di.sms, stream)
-               : launch_dt<256, false>(d_dtype, ta, tb, a, di.sms, stream);
+    rc = tiled ? launch_dt<256, true>(d_dtype, ta, tb, tsa, tsb, a, di.sms, stream)
+               : launch_dt<256, false>(d_dtype, ta, tb, tsa, tsb, a, di.sms, stream);
   else
-    rc = tiled ? launch_dt<128, true>(d_dtype, ta, tb, a, di.sms, stream)
-               : launch_dt<128, false>(d_dtype, ta, tb, a, di.sms, stream);
+    rc = tiled ? launch_dt<128, true>(d_dtype, ta, tb, tsa, tsb, a, di.sms, stream)
+               : launch_dt<128, false>(d_dtype, ta, tb, tsa, tsb, a, di.sms, stream);
   if (pl.splits > 1 && !a.cluster_reduce) {
     if (rc == 0) {
       const int64_t total4 = M * N / 4;

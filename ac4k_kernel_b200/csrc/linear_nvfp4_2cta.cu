@@ -71,6 +71,7 @@ static constexpr int kThreadsPair = 512;
 template <bool SF_TILED, int OUT_DT, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreadsPair, 1)
 linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                         const __grid_constant__ CUtensorMap tma_sfa, const __grid_constant__ CUtensorMap tma_sfb,
                          const GemmArgs p) {
   using namespace pair;
   extern __shared__ uint8_t smem_raw[];
@@ -114,6 +115,10 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     fence_barrier_init();
     prefetch_tmap(&tma_a);
     prefetch_tmap(&tma_b);
+    if (!SF_TILED) {
+      prefetch_tmap(&tma_sfa);
+      prefetch_tmap(&tma_sfb);
+    }
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, kTmemCols);
@@ -249,7 +254,6 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         const int64_t mt = m0 / 128;
         const bool a_ok = SF_TILED ? (mt * 128 < p.rows_sfa) : (m0 < p.rows_sfa);
         const int nb_valid = min(2, (p.rows_sfb - n0) / 128);                       // tiled layout
-        const int ra = 4 * max(0, min(128, p.rows_sfa - m0)), rb = 4 * min(BN, p.rows_sfb - n0);   // row layout
         for (int kt = 0; kt < k_tiles; ++kt) {
           if (!mbar_wait(sffree_bar + 8 * s, ph ^ 1)) { atomicExch(p.status, kStatusTimeoutSf); ok = false; break; }
           const int nk = (kt + 1 < k_tiles) ? KS : last_nk;
@@ -262,12 +266,11 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
               bulk_load_1d_local(sSFB + s * SFB_BYTES + nb * (KS * 512),
                                  p.sfb + ((int64_t)(n0 / 128 + nb) * p.KT + k64) * 512, nk * 512, bar);
           } else {
-            mbar_arrive_expect_tx(bar, nk * (ra + rb));
-            for (int j = 0; j < nk; ++j) {
-              if (ra > 0)
-                bulk_load_1d_local(sSFA + s * SFA_BYTES + j * 512, p.sfa + ((k64 + j) * p.rows_sfa + m0) * 4, ra, bar);
-              bulk_load_1d_local(sSFB + s * SFB_BYTES + j * 1024, p.sfb + ((k64 + j) * p.rows_sfb + n0) * 4, rb, bar);
-            }
+            // row layout: one box of [8 K steps][128 or 256 rows] words per operand; rows and K steps
+            // outside the tensor arrive as zeros and count towards the transaction bytes
+            mbar_arrive_expect_tx(bar, SFA_BYTES + SFB_BYTES);
+            tma_load_2d_local(sSFA + s * SFA_BYTES, &tma_sfa, m0, (int)k64, bar);
+            tma_load_2d_local(sSFB + s * SFB_BYTES, &tma_sfb, n0, (int)k64, bar);
           }
           if (++s == SF_STAGES) { s = 0; ph ^= 1; }
         }
@@ -530,8 +533,8 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
 }
 
 template <bool SF_TILED, int OUT_DT, int EPI>
-static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const GemmArgs &args, int sms,
-                       cudaStream_t stream) {
+static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tsa, const CUtensorMap &tsb,
+                       const GemmArgs &args, int sms, cudaStream_t stream) {
   auto kern = linear_nvfp4_2cta_kernel<SF_TILED, OUT_DT, EPI>;
   static bool attr_set[64] = {};
   int dev = 0;
@@ -574,12 +577,12 @@ static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const GemmA
   attr.val.programmaticStreamSerializationAllowed = (args.dbg & 64) ? 0 : 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  AC4K_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, args));
+  AC4K_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, tsa, tsb, args));
   return 0;
 }
 
 int launch_linear_2cta(int d_dtype, bool sf_tiled, const CUtensorMap &ta, const CUtensorMap &tb,
-                       GemmArgs args, cudaStream_t stream) {
+                       const CUtensorMap &tsa, const CUtensorMap &tsb, GemmArgs args, cudaStream_t stream) {
   DeviceInfo di;
   if (int e = get_device_info(&di)) return e;
   args.tiles_m = (int)ceil_div(args.M, pair::BMP);
@@ -588,23 +591,23 @@ int launch_linear_2cta(int d_dtype, bool sf_tiled, const CUtensorMap &ta, const 
   // separate: their extra registers and code would otherwise slow the plain GEMM down
   if (args.q_out != nullptr) {
     if (d_dtype != AC4K_DT_BF16) return fail(AC4K_ERR_UNSUPPORTED, "the re-quantising epilogue rounds to bf16 first");
-    return sf_tiled ? launch_pair<true, AC4K_DT_BF16, EPI_REQUANT>(ta, tb, args, di.sms, stream)
-                    : launch_pair<false, AC4K_DT_BF16, EPI_REQUANT>(ta, tb, args, di.sms, stream);
+    return sf_tiled ? launch_pair<true, AC4K_DT_BF16, EPI_REQUANT>(ta, tb, tsa, tsb, args, di.sms, stream)
+                    : launch_pair<false, AC4K_DT_BF16, EPI_REQUANT>(ta, tb, tsa, tsb, args, di.sms, stream);
   }
   const bool gather = args.n_dst > 1;
   if (d_dtype == AC4K_DT_BF16) {
     if (gather)
-      return sf_tiled ? launch_pair<true, AC4K_DT_BF16, EPI_GATHER>(ta, tb, args, di.sms, stream)
-                      : launch_pair<false, AC4K_DT_BF16, EPI_GATHER>(ta, tb, args, di.sms, stream);
-    return sf_tiled ? launch_pair<true, AC4K_DT_BF16, EPI_PLAIN>(ta, tb, args, di.sms, stream)
-                    : launch_pair<false, AC4K_DT_BF16, EPI_PLAIN>(ta, tb, args, di.sms, stream);
+      return sf_tiled ? launch_pair<true, AC4K_DT_BF16, EPI_GATHER>(ta, tb, tsa, tsb, args, di.sms, stream)
+                      : launch_pair<false, AC4K_DT_BF16, EPI_GATHER>(ta, tb, tsa, tsb, args, di.sms, stream);
+    return sf_tiled ? launch_pair<true, AC4K_DT_BF16, EPI_PLAIN>(ta, tb, tsa, tsb, args, di.sms, stream)
+                    : launch_pair<false, AC4K_DT_BF16, EPI_PLAIN>(ta, tb, tsa, tsb, args, di.sms, stream);
   }
   if (d_dtype == AC4K_DT_FP16) {
     if (gather)
-      return sf_tiled ? launch_pair<true, AC4K_DT_FP16, EPI_GATHER>(ta, tb, args, di.sms, stream)
-                      : launch_pair<false, AC4K_DT_FP16, EPI_GATHER>(ta, tb, args, di.sms, stream);
-    return sf_tiled ? launch_pair<true, AC4K_DT_FP16, EPI_PLAIN>(ta, tb, args, di.sms, stream)
-                    : launch_pair<false, AC4K_DT_FP16, EPI_PLAIN>(ta, tb, args, di.sms, stream);
+      return sf_tiled ? launch_pair<true, AC4K_DT_FP16, EPI_GATHER>(ta, tb, tsa, tsb, args, di.sms, stream)
+                      : launch_pair<false, AC4K_DT_FP16, EPI_GATHER>(ta, tb, tsa, tsb, args, di.sms, stream);
+    return sf_tiled ? launch_pair<true, AC4K_DT_FP16, EPI_PLAIN>(ta, tb, tsa, tsb, args, di.sms, stream)
+                    : launch_pair<false, AC4K_DT_FP16, EPI_PLAIN>(ta, tb, tsa, tsb, args, di.sms, stream);
   }
   return fail(AC4K_ERR_UNSUPPORTED, "the CTA-pair kernel stores 16-bit outputs only");
 }

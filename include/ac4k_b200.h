@@ -103,13 +103,11 @@ int ac4k_linear_nvfp4(void *D, int d_dtype, const void *A, const void *A_sf,
  * memory while running (a plugin living inside someone else's fixed memory budget, a serving loop
  * that forbids allocator calls).  No counterpart in the reference, which never needs scratch.
  *
- * Where ac4k_linear_nvfp4 would take scratch from the stream-ordered allocator (split-K partial
- * sums of decode shapes; re-tiled scale factors of large AC4K_SF_AC4K problems), this entry point
- * uses a fixed 8 MiB array inside the library's device image (every GPU that loads the library
- * holds those 8 MiB until the process exits).  It calls no cudaMalloc / cudaFree of any kind.
- * Shapes whose split-K partial sums ([K slices, M, N] fp32) need more than 8 MiB are rejected with
- * AC4K_ERR_SHAPE and a message; scale factors that do not fit are simply not re-tiled (same
- * result, a slower kernel path); shapes that need no scratch run as usual.
+ * Where ac4k_linear_nvfp4 would take split-K scratch from the stream-ordered allocator, this entry
+ * point uses a fixed 8 MiB array inside the library's device image (every GPU that loads the
+ * library holds those 8 MiB until the process exits).  It calls no cudaMalloc / cudaFree of any
+ * kind.  Shapes whose split-K partial sums ([K slices, M, N] fp32) need more than 8 MiB are
+ * rejected with AC4K_ERR_SHAPE and a message; shapes that need no scratch run as usual.
  *
  *  - The first call on each device that needs scratch looks up the array's device address (device
  *    must be current); make such a call before starting any stream capture.

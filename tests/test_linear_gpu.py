@@ -206,10 +206,18 @@ def test_config3_decode_shapes(ops, m):
     (3, 4100, 2048, torch.bfloat16, None),              # N % 128 != 0, N % 4 == 0
 ])
 def test_split_k_decode_path(ops, m, n, k, odt, bdt):
-    """Few output tiles and a long K: the library slices K over more CTAs, sums fp32 partials from a
-    scratch buffer and applies alpha / bias / cast in a second kernel."""
-    run_case(ops, m, n, k, seed=21, layout="128x4", bias_dtype=bdt, out_dtype=odt, oracle_device="cuda")
-    run_case(ops, m, n, k, seed=22, layout="ac4k", bias_dtype=bdt, out_dtype=odt, oracle_device="cuda")
+    """Few output tiles and a long K: the library may slice K over more CTAs and add the fp32 partial
+    sums either inside a cluster (two slices) or from a scratch buffer in a second kernel that also
+    applies alpha / bias / cast.  The automatic plan and forced plans of 2, 3 and 4 slices (the library's
+    measurement switch) must all give the right answer."""
+    from ac4k_kernel_b200._lib import LIB
+    try:
+        for splits in (0, 2, 3, 4):
+            LIB.ac4k_debug_set_splits(splits)
+            run_case(ops, m, n, k, seed=21, layout="128x4", bias_dtype=bdt, out_dtype=odt, oracle_device="cuda")
+            run_case(ops, m, n, k, seed=22, layout="ac4k", bias_dtype=bdt, out_dtype=odt, oracle_device="cuda")
+    finally:
+        LIB.ac4k_debug_set_splits(0)
 
 
 def test_reference_8192_cube(ops):

@@ -39,8 +39,8 @@ def _operands(m, n, k, seed, layout):
 def test_noalloc_matches_regular_entry_point_twice(layout_name, layout):
     from ac4k_kernel_b200._lib import LIB, device_status, last_error
     # decode-shaped and split-K problems back to back
-    # (the first two now add their K slices inside the kernel and need no scratch at all; the fp32 one
-    # has two row tiles, which keeps it on the workspace path: 4 slices x 256 x 1024 fp32 = 4 MiB)
+    # (the first runs unsplit, the second adds its two K slices inside the kernel - neither needs scratch;
+    # the last one is cut into 8 slices whose partial sums, 8 x 200 x 1024 fp32 = 6.25 MiB, use the array)
     cases = [(16, 2048, 4096, torch.bfloat16, None), (64, 8192, 8192, torch.float16, torch.float32),
              (256, 1024, 4096, torch.float32, None), (200, 1024, 8192, torch.float32, torch.bfloat16)]
     for i, (m, n, k, odt, bdt) in enumerate(cases):
