@@ -284,6 +284,35 @@ def quantize_bandwidth(peaks):
     return res
 
 
+def decode_stream(peaks):
+    """BASELINE config 3: M in {1, 16, 64}, N = K = 8192, weights quantised once; 8 weight copies are
+    rotated (8 x 37.7 MB > 2 x L2) and 40 calls are replayed from one CUDA graph."""
+    from ac4k_kernel_b200 import _cuda_ops, ops
+    n = k = 8192
+    w = weights((n, k), 1, "cuda")
+    w4, wsf, wg = ops.quantize(w, 0, 1, sf_layout="128x4")
+    del w
+    sets = [(w4.clone(), wsf.clone()) for _ in range(8)]
+    stream_bytes = n * k // 2 + n * k // 16
+    res = {"workload": "decode GEMM M x 8192 x 8192 against resident NVFP4 weights, 8 weight copies rotated",
+           "algorithmic_bytes_per_call": stream_bytes}
+    for m in (1, 16, 64):
+        a = activations((m, k), 2, 0.0, 1.0, "cuda")
+        a4, asf, ag = ops.quantize(a, 0, 1, sf_layout="128x4")
+        out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+
+        def step(i):
+            _cuda_ops.linear_nvfp4(out, a4, asf, ag, sets[i][0], sets[i][1], wg, None)
+
+        secs, _, _ = time_graph(step, 8, 40, 3)
+        t = secs / 40
+        res[f"m{m}_us"] = t * 1e6
+        res[f"m{m}_weight_gbs"] = stream_bytes / t / 1e9
+    res["m16_frac_of_8tbs"] = res["m16_weight_gbs"] / NOMINAL_HBM_GBS
+    res["m16_frac_of_measured_copy"] = res["m16_weight_gbs"] / peaks["hbm_gbs"]
+    return res
+
+
 def run_single(args, peaks):
     from ac4k_kernel_b200 import _cuda_ops, ops
     torch.cuda.set_device(0)
@@ -377,6 +406,7 @@ def run_single(args, peaks):
     del sets, a_host
 
     quant = quantize_bandwidth(peaks)
+    decode = decode_stream(peaks)
     cpu_tflops, cores, sample, _, _ = cpu_emulation_c2()
 
     fp4_proxy_peak = 4.0 * peaks["bf16_tflops"]
@@ -399,6 +429,7 @@ def run_single(args, peaks):
                                   "measured on this pool; nominal dense FP4 is 9000 TFLOP/s",
                      "algorithmic_flops_per_launch": flops},
         "quantize": quant,
+        "decode": decode,
         "cpu_baseline": {"value": cpu_tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": e2e,
         "clocks": clocks,
