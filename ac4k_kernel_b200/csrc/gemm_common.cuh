@@ -18,7 +18,7 @@ static constexpr int kTmemCols = 512;
 static constexpr int kGroupM = 8;     // tile rasterisation: walk 8 M-tiles per N-tile
 
 enum : unsigned { kStatusTimeoutProducer = 0xA1, kStatusTimeoutMma = 0xA2, kStatusTimeoutSf = 0xA3,
-                  kStatusTimeoutEpilogue = 0xA4 };
+                  kStatusTimeoutEpilogue = 0xA4, kStatusSmemAlign = 0xB1 };
 
 template <int BN>
 struct Cfg {
@@ -41,6 +41,10 @@ struct Cfg {
 
 enum { EPI_PLAIN = 0, EPI_GATHER = 1, EPI_REQUANT = 2 };   // epilogue variants of the pair kernel
 static constexpr int kMaxDst = 8;     // output destinations of one launch (this GPU + up to 7 peers)
+
+// Tensor maps of the output destinations of the pair kernel's TMA-store epilogue: [0] this GPU's buffer,
+// [1 .. n_dst) the further destinations of the fused all-gather.
+struct DstMaps { CUtensorMap m[kMaxDst]; };
 
 struct GemmArgs {
   const uint8_t *sfa;
@@ -141,7 +145,10 @@ int get_tmap(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUt
 // 2-CTA kernel launcher (linear_nvfp4_2cta.cu); D must be bf16/fp16 with N % 8 == 0
 // tsa / tsb: tensor maps of row-layout scales (get_tmap_sf); ignored when sf_tiled
 int get_tmap_sf(const void *ptr, int64_t rows16, int64_t kt, int box_rows, int box_ksteps, CUtensorMap *out);
+int get_tmap_sf_tiled(const void *ptr, int64_t row_blocks, int64_t kt, int box_ksteps, CUtensorMap *out);
+// 16-bit output [rows, cols] with a row pitch of ld elements: boxes of 64 columns x 32 rows, 128-byte swizzle
+int get_tmap_out16(const void *ptr, int64_t rows, int64_t cols, int64_t ld, CUtensorMap *out);
 int launch_linear_2cta(int d_dtype, bool sf_tiled, const CUtensorMap &ta, const CUtensorMap &tb,
-                       const CUtensorMap &tsa, const CUtensorMap &tsb, GemmArgs args, cudaStream_t stream);
+                       const CUtensorMap &tsa, const CUtensorMap &tsb, const DstMaps &dm, GemmArgs args, cudaStream_t stream);
 
 }  // namespace ac4k

@@ -437,24 +437,29 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// Tensor maps depend only on (pointer, shape, box); encoding one costs a driver call, so the last few
+// are kept, per device, behind a mutex.  The reference re-encodes five per call (linear_nvfp4.cu:842-886).
 struct TmapKey {
   const void *ptr;
-  int64_t rows, row_bytes;
-  int box_rows, dev;
+  int64_t d0, d1, pitch;   // extents: innermost (elements), outer; row pitch in elements
+  int box0, box1, kind, dev;
   bool operator==(const TmapKey &o) const {
-    return ptr == o.ptr && rows == o.rows && row_bytes == o.row_bytes && box_rows == o.box_rows && dev == o.dev;
+    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && pitch == o.pitch && box0 == o.box0 && box1 == o.box1 &&
+           kind == o.kind && dev == o.dev;
   }
 };
 struct TmapEntry { TmapKey key; CUtensorMap map; };
+enum { kTmapOperand = 0, kTmapWords = 1, kTmapOut16 = 2 };
 
-// Tensor maps depend only on (pointer, shape, box); encoding costs a driver call, so the last
-// few are kept.  The reference re-encodes five per call (linear_nvfp4.cu:842-886).
-int get_tmap(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUtensorMap *out) {
+// kind kTmapOperand: bytes, 128-byte swizzle; kTmapWords: 32-bit words, not swizzled; kTmapOut16: 16-bit
+// elements, 128-byte swizzle.
+static int encode_cached(int kind, const void *ptr, int64_t d0, int64_t d1, int64_t pitch, int box0, int box1,
+                         CUtensorMap *out) {
   static std::mutex mu;
   static std::vector<TmapEntry> cache;
   int dev = 0;
   cudaGetDevice(&dev);
-  TmapKey key{ptr, rows, row_bytes, box_rows, dev};
+  TmapKey key{ptr, d0, d1, pitch, box0, box1, kind, dev};
   {
     std::lock_guard<std::mutex> lk(mu);
     for (auto &e : cache)
@@ -462,14 +467,18 @@ int get_tmap(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUt
   }
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return fail(AC4K_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
-  cuuint64_t gdim[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
-  cuuint64_t gstride[1] = {(cuuint64_t)row_bytes};
-  cuuint32_t box[2] = {(cuuint32_t)BKB, (cuuint32_t)box_rows};
+  const int esize = kind == kTmapOperand ? 1 : (kind == kTmapWords ? 4 : 2);
+  const CUtensorMapDataType dt = kind == kTmapOperand ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : (kind == kTmapWords ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16);
+  cuuint64_t gdim[2] = {(cuuint64_t)d0, (cuuint64_t)d1};
+  cuuint64_t gstride[1] = {(cuuint64_t)pitch * esize};
+  cuuint32_t box[2] = {(cuuint32_t)box0, (cuuint32_t)box1};
   cuuint32_t estr[2] = {1, 1};
   CUtensorMap m;
-  CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), gdim, gstride, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = enc(&m, dt, 2,
+                   const_cast<void *>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   kind == kTmapWords ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail((int)r > 0 ? (int)r : 999, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   {
     std::lock_guard<std::mutex> lk(mu);
@@ -480,21 +489,27 @@ int get_tmap(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUt
   return 0;
 }
 
+// packed operand [rows, row_bytes]: boxes of 128 bytes x box_rows rows, 128-byte swizzle
+int get_tmap(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUtensorMap *out) {
+  return encode_cached(kTmapOperand, ptr, row_bytes, rows, row_bytes, BKB, box_rows, out);
+}
+
 // Row-layout scale factors [K/64][rows16] as 32-bit words (the four scales of a row at one K step):
 // a box of `box_rows` words x `box_ksteps` K steps lands in shared memory as [K step][row], which is
-// what the kernels' scale warps read.  Not swizzled; out-of-range rows and K steps read as zero.
+// what the single-CTA kernel's scale warps read.  Out-of-range rows and K steps read as zero.
 int get_tmap_sf(const void *ptr, int64_t rows16, int64_t kt, int box_rows, int box_ksteps, CUtensorMap *out) {
-  EncodeTiledFn enc = get_encode_fn();
-  if (!enc) return fail(AC4K_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
-  cuuint64_t gdim[2] = {(cuuint64_t)rows16, (cuuint64_t)kt};
-  cuuint64_t gstride[1] = {(cuuint64_t)rows16 * 4};
-  cuuint32_t box[2] = {(cuuint32_t)box_rows, (cuuint32_t)box_ksteps};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(ptr), gdim, gstride, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail((int)r > 0 ? (int)r : 999, "cuTensorMapEncodeTiled (scales) failed with CUresult %d", (int)r);
-  return 0;
+  return encode_cached(kTmapWords, ptr, rows16, kt, rows16, box_rows, box_ksteps, out);
+}
+
+// Tiled scale factors [row blocks of 128][K/64][512 bytes] seen as a matrix of 512-byte rows: a box of
+// `box_ksteps` rows is the scale image of that many K steps of one row block, contiguous in shared
+// memory.  Rows past the end of the tensor read as zero.
+int get_tmap_sf_tiled(const void *ptr, int64_t row_blocks, int64_t kt, int box_ksteps, CUtensorMap *out) {
+  return encode_cached(kTmapWords, ptr, 128, row_blocks * kt, 128, 128, box_ksteps, out);
+}
+
+int get_tmap_out16(const void *ptr, int64_t rows, int64_t cols, int64_t ld, CUtensorMap *out) {
+  return encode_cached(kTmapOut16, ptr, cols, rows, ld, 64, 32, out);
 }
 
 int get_device_info(DeviceInfo *out) {
@@ -639,9 +654,9 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
   unsigned int *status = device_status_ptr();
   if (!status) return fail(AC4K_ERR_DEVICE, "cannot resolve the device status word");
 
-  // kernel choice: CTA pairs (256 x 256 tiles, TMA-store epilogue) when there are at least two row
-  // tiles to pair and the output can be stored by TMA; otherwise single CTAs with 128 x 256 or
-  // 128 x 128 tiles.  g_force_bn: 128 / 256 force the single-CTA kernel, 512 forces pairs.
+  // kernel choice: CTA pairs (256 x 256 tiles; the epilogue packs 16-bit outputs and stores 32-byte
+  // row pieces, which needs N % 8 == 0) when there are at least two row tiles to pair; otherwise single
+  // CTAs with 128 x 256 or 128 x 128 tiles.  g_force_bn: 128 / 256 force the single-CTA kernel, 512 forces pairs.
   const bool pair_ok = d_dtype != AC4K_DT_FP32 && (N % 8 == 0);
   bool use_pair = pair_ok && M > 128 && N > 128;
   if (out) {
@@ -713,12 +728,21 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
   const bool tiled = sf_layout == AC4K_SF_TILE128X4;
   if (use_pair) {
     // scales in the reference's row layout are fed by two more tensor maps (one box per operand and stage)
-    CUtensorMap tsa = ta, tsb = tb;      // placeholders when the scales are tiled (not used by the kernel then)
-    if (!tiled) {
-      if (int e = get_tmap_sf(A_sf, a.rows_sfa, a.KT, 128, 8, &tsa)) return e;
-      if (int e = get_tmap_sf(B_sf, a.rows_sfb, a.KT, 256, 8, &tsb)) return e;
+    CUtensorMap tsa = ta, tsb = tb;      // placeholders for scales in the row layout (read with plain loads)
+    if (tiled) {
+      if (int e = get_tmap_sf_tiled(A_sf, a.rows_sfa / 128, a.KT, 4, &tsa)) return e;
+      if (int e = get_tmap_sf_tiled(B_sf, a.rows_sfb / 128, a.KT, 4, &tsb)) return e;
     }
-    return launch_linear_2cta(d_dtype, tiled, ta, tb, tsa, tsb, a, stream);
+    // destinations of the epilogue's TMA stores: columns [0, col_off + N) of each [M, ldd] buffer, so that the
+    // stores are clipped at this launch's last column
+    DstMaps dm;
+    for (int i = 0; i < kMaxDst; ++i) dm.m[i] = ta;
+    if (!requant) {
+      if (int e = get_tmap_out16(D, M, a.col_off + N, a.ldd, &dm.m[0])) return e;
+      for (int i = 1; i < a.n_dst; ++i)
+        if (int e = get_tmap_out16(a.D_more[i - 1], M, a.col_off + N, a.ldd, &dm.m[i])) return e;
+    }
+    return launch_linear_2cta(d_dtype, tiled, ta, tb, tsa, tsb, dm, a, stream);
   }
   if (pl.splits > 1 && !a.cluster_reduce) {
     if (ws_mode == 1) {

@@ -7,21 +7,22 @@
 // FLOP this moves a third less operand data from L2 into shared memory than 128 x 256 tiles of
 // single CTAs.  No multicast loads are used.
 //
-// A pipeline stage is K = 512 elements (8 MMAs of K = 64): every role's per-stage bookkeeping
-// (mbarrier waits ~75-100 cycles each, tcgen05.commit ~110, a tcgen05.mma issue ~75-125, remote
-// arrives) was measured to be latency-bound, so fewer, larger stages keep each role's loop shorter
-// than the 1024 cycles the tensor pipe needs per stage.
+// A pipeline stage is K = 256 elements: one 128-row x 128-byte box of A, one of B, and the block
+// scales of the stage (2 KB for this CTA's A rows, 4 KB for all 256 B rows), 38 KB per CTA, five
+// stages.  The scales go from shared to tensor memory with tcgen05.cp, issued by the MMA warp right
+// in front of the MMAs that use them: the copies run in issue order with the MMAs and overlap them
+// (measured: 12 copies + 4 MMAs take 523 cycles, the 4 MMAs alone 520), so no other warp and no
+// barrier stands between a stage's arrival and its MMAs.
 //
-// Roles per CTA (512 threads):
-//   warp 0      TMA producer: A and B of this CTA, 4 boxes of 128 rows x 128 B per stage, 3 stages
-//   warp 1      MMA issuer (leader CTA only): 8 MMAs + 1 commit per stage; learns that a stage is
-//               ready from a counter in shared memory instead of waiting on mbarriers itself
-//   warps 2-5   scale warps: scale bytes shared memory -> registers -> tensor memory (tcgen05.st),
-//               one TMEM lane quarter each; 2-deep rings in shared and in tensor memory
-//   warp 10     scale feeder: bulk copies of scale bytes, as soon as the scale warps freed a slot
-//   warp 11     barrier watcher (leader CTA only): waits for each stage's operands + scales and
-//               publishes the count of ready stages
-//   warps 6-9, 12-15  epilogue: tcgen05.ld of 128 accumulator columns per warp into registers
+// Roles per CTA (448 threads); every role that issues TMA or tcgen05 instructions runs with its whole
+// warp converged and predicates those instructions on one elected lane (see elect_one()):
+//   warp 0      TMA producer: A, B and - for tiled scales - three scale boxes per stage, all
+//               completing on the leader CTA's barrier of the stage
+//   warp 1      MMA issuer (leader CTA only): per stage 12 scale copies, 4 MMAs, 1 commit
+//   warps 2-5   only for scales in the row layout [K/64][rows][4]: each warp takes every fourth
+//               stage, reads the stage's scale words from global memory and writes them to shared
+//               memory in the 32 x 16-byte order tcgen05.cp wants
+//   warps 6-13  epilogue: tcgen05.ld of 128 accumulator columns per warp into registers
 //               (* alpha, + bias, packed to 16 bit), hand the accumulator back, then store
 // Barriers that gate the MMA live in the leader CTA and are signalled by both CTAs; barriers that
 // release stages / publish the accumulator exist in both CTAs and are signalled by one
@@ -32,65 +33,109 @@ namespace ac4k {
 using namespace ptx;
 
 #ifdef AC4K_TRACE_ENABLED
-// region 0: MMA issuer, region 1: epilogue warp 6, region 2: scale warp 2 (all leader CTA, cluster 0)
+// region 0: MMA issuer, region 1: epilogue warp 6 (both leader CTA, cluster 0), region 3: kernel phases
 #define AC4K_TR(region, it, ev)                                                              \
   do {                                                                                      \
     if (p.trace != nullptr && cluster_id == 0 && rank == 0 && (it) < 128)                   \
       p.trace[((size_t)(region) * 128 + (it)) * 8 + (ev)] = clock64();                      \
   } while (0)
-// wall-clock (ns) stamps, comparable across the two CTAs of cluster 0
-#define AC4K_TRG(region, it, ev)                                                             \
+// region 5: one line per launch (index from a counter in the last slot of region 4): wall-clock ns and
+// clock64 at kernel start and end of cluster 0's leader, for the gaps between launches and the SM clock
+#define AC4K_TR_LAUNCH(begin)                                                                \
   do {                                                                                      \
-    if (p.trace != nullptr && cluster_id == 0 && (it) < 128)                                \
-      p.trace[((size_t)(region) * 128 + (it)) * 8 + (ev)] = globaltimer();                  \
+    if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {                        \
+      unsigned long long *ctr = p.trace + ((size_t)4 * 128 + 127) * 8;                      \
+      if (begin) launch_slot = (unsigned)atomicAdd(ctr, 1ull) & 127u;                       \
+      unsigned long long *line = p.trace + ((size_t)5 * 128 + launch_slot) * 8;             \
+      line[(begin) ? 0 : 2] = globaltimer();                                                \
+      line[(begin) ? 1 : 3] = clock64();                                                    \
+    }                                                                                       \
   } while (0)
 #else
 #define AC4K_TR(region, it, ev) do { } while (0)
-#define AC4K_TRG(region, it, ev) do { } while (0)
+#define AC4K_TR_LAUNCH(begin) do { } while (0)
 #endif
 
 namespace pair {
 static constexpr int BN = 256;                      // output columns of the pair tile
 static constexpr int BMP = 256;                     // output rows of the pair tile
-static constexpr int KS = 8;                        // K = 64 steps per stage
-static constexpr int HALF_BYTES = 128 * BKB;        // one 128-row x 128-byte box
-static constexpr int A_BYTES = 2 * HALF_BYTES;      // this CTA's 128 rows of A, K = 512
-static constexpr int B_BYTES = 2 * HALF_BYTES;      // this CTA's 128 rows of B, K = 512
-static constexpr int SFA_BYTES = KS * 512;
-static constexpr int SFB_BYTES = 2 * KS * 512;
-static constexpr int STAGES = 3;                    // operand ring
-static constexpr int SF_STAGES = 2;                 // scale rings (shared memory and tensor memory)
-static constexpr int BIAS_BYTES = 8 * 128 * 4;          // one tile's bias as fp32, 128 columns per epilogue warp
-static constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + SF_STAGES * (SFA_BYTES + SFB_BYTES) + 1024 + 512 + BIAS_BYTES;
-static constexpr int SFA_COL = 256, SFA_COLS = KS * 4, SFB_COL = SFA_COL + SF_STAGES * SFA_COLS, SFB_COLS = KS * 8;
-static_assert(SFB_COL + SF_STAGES * SFB_COLS <= kTmemCols, "tensor memory overflow");
+static constexpr int KS = 4;                        // K = 64 steps per stage
+static constexpr int A_BYTES = 128 * BKB;           // this CTA's 128 rows of A, K = 256
+static constexpr int B_BYTES = 128 * BKB;           // this CTA's 128 rows of B, K = 256
+static constexpr int SFA_BYTES = KS * 512;          // [K step][32 x 16 B]
+static constexpr int SFB_BYTES = 2 * KS * 512;      // [128-row block of B][K step][32 x 16 B]
+static constexpr int STAGE_TX = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;    // bytes one CTA's TMA loads of a stage bring
+static constexpr int STAGES = 5;
+// Tensor memory (512 columns): two accumulators of 256 columns that share 48 columns, and the scales
+// of one stage.  Tiles alternate between the accumulators; the shared columns are the last 48 of the
+// first accumulator's tile and the first 48 of the second one's, so between two tiles only those 48
+// columns have to be read out before the next tile's first MMA may write them - the other 208 are
+// drained while the next tile's MMAs already run.
+static constexpr int ACC1_COL = 208;                // accumulator 0: columns 0 - 255, accumulator 1: 208 - 463
+static constexpr int SHARED_COLS = BN - ACC1_COL;   // 48
+static constexpr int SF_COL = ACC1_COL + BN;        // 464: per K step 4 columns for A, then 8 per K step for B
+static constexpr int SF_COLS = KS * 12;
+static constexpr int BIAS_BYTES = 8 * 128 * 4;      // one tile's bias as fp32, 128 columns per epilogue warp
+static constexpr int OUT_STAGE_BYTES = 32 * 128;    // per epilogue warp: 32 rows x 64 columns of 16-bit outputs
+static constexpr int BAR_BYTES = 256;
+// no slack for aligning the base: the kernel declares the array 1024-byte aligned and checks it
+static constexpr int SMEM_BYTES = STAGES * STAGE_TX + 8 * OUT_STAGE_BYTES + BIAS_BYTES + BAR_BYTES;
+static_assert(SF_COL + SF_COLS <= kTmemCols, "tensor memory overflow");
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory overflow");
-static constexpr int kThreadsPair = 512;
+static constexpr int kThreadsPair = 448;           // 14 warps: 144 registers per thread for the epilogue
 }  // namespace pair
+
+// N accumulator columns starting at COL0 of this thread's 128-column segment: * alpha (+ bias from shared
+// memory), rounded to the 16-bit output type, two per word into w[COL0 / 2 ...].
+template <int OUT_DT, int COL0, int N>
+__device__ __forceinline__ void pack_cols(const uint32_t (&r)[N], uint32_t (&w)[64], float alpha, bool has_bias, uint32_t bias_s) {
+  static_assert(COL0 % 4 == 0 && N % 4 == 0, "whole 16-byte bias groups");
+  if (!has_bias) {
+#pragma unroll
+    for (int i = 0; i < N / 2; ++i)
+      w[COL0 / 2 + i] = (OUT_DT == AC4K_DT_BF16) ? scale_pack_bf16x2(r[2 * i], r[2 * i + 1], alpha)
+                                                 : scale_pack_f16x2(r[2 * i], r[2 * i + 1], alpha);
+  } else {
+#pragma unroll
+    for (int i = 0; i < N / 4; ++i) {
+      const float4 bb = ld_shared_v4f(bias_s + (COL0 + 4 * i) * 4);
+      if (OUT_DT == AC4K_DT_BF16) {
+        w[COL0 / 2 + 2 * i] = scale_bias_pack_bf16x2(r[4 * i], r[4 * i + 1], alpha, bb.x, bb.y);
+        w[COL0 / 2 + 2 * i + 1] = scale_bias_pack_bf16x2(r[4 * i + 2], r[4 * i + 3], alpha, bb.z, bb.w);
+      } else {
+        w[COL0 / 2 + 2 * i] = scale_bias_pack_f16x2(r[4 * i], r[4 * i + 1], alpha, bb.x, bb.y);
+        w[COL0 / 2 + 2 * i + 1] = scale_bias_pack_f16x2(r[4 * i + 2], r[4 * i + 3], alpha, bb.z, bb.w);
+      }
+    }
+  }
+}
 
 template <bool SF_TILED, int OUT_DT, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreadsPair, 1)
 linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                          const __grid_constant__ CUtensorMap tma_sfa, const __grid_constant__ CUtensorMap tma_sfb,
-                         const GemmArgs p) {
+                         const __grid_constant__ DstMaps dmaps, const GemmArgs p) {
   using namespace pair;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = smem_u32(smem_raw);
+  if (smem_base & 1023u) {      // the swizzled boxes need 1024-byte alignment; never seen, but not promised either
+    if (threadIdx.x == 0) atomicExch(p.status, kStatusSmemAlign);
+    return;
+  }
   const uint32_t sA = smem_base;
   const uint32_t sB = sA + STAGES * A_BYTES;
   const uint32_t sSFA = sB + STAGES * B_BYTES;
-  const uint32_t sSFB = sSFA + SF_STAGES * SFA_BYTES;
-  const uint32_t bars = sSFB + SF_STAGES * SFB_BYTES;
-  const uint32_t full_bar = bars;                     // [STAGES] leader: operands of both CTAs landed + all scales in TMEM
-  const uint32_t empty_bar = full_bar + 8 * STAGES;   // [STAGES] both: MMAs that used the stage are done
-  const uint32_t sffull_bar = empty_bar + 8 * STAGES; // [SF_STAGES] local: scale bytes landed
-  const uint32_t sffree_bar = sffull_bar + 8 * SF_STAGES;   // [SF_STAGES] local: 4 scale warps have read the slot
-  const uint32_t tfull_bar = sffree_bar + 8 * SF_STAGES;    // both: accumulator complete
-  const uint32_t tempty_bar = tfull_bar + 8;          // leader: 16 epilogue warps drained the accumulator
-  const uint32_t ready_word = tempty_bar + 8;         // leader: stages the watcher has seen complete
-  const uint32_t tmem_slot = ready_word + 8;
-  const uint32_t sBias = bars + 512;                  // [8 epilogue warps][128] fp32
-  uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sSFB = sSFA + STAGES * SFA_BYTES;
+  const uint32_t sOut = sSFB + STAGES * SFB_BYTES;     // [8 epilogue warps][32 rows x 128 B], swizzled like the TMA box
+  const uint32_t sBias = sOut + 8 * OUT_STAGE_BYTES;   // [8 epilogue warps][128] fp32
+  const uint32_t bars = sBias + BIAS_BYTES;
+  const uint32_t full_bar = bars;                     // [STAGES] leader: operands and scales of both CTAs are in shared memory
+  const uint32_t empty_bar = full_bar + 8 * STAGES;   // [STAGES] both: the MMAs that used the stage are done
+  const uint32_t tfull_bar = empty_bar + 8 * STAGES;  // [2] both: accumulator complete
+  const uint32_t tempty_bar = tfull_bar + 16;         // [2] leader: 16 epilogue warps drained the accumulator
+  const uint32_t shared_free_bar = tempty_bar + 16;   // leader: the 8 warps that own the shared columns have read them
+  const uint32_t tmem_slot = shared_free_bar + 8;
+  uint8_t *smem_gen = smem_raw;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -100,25 +145,28 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   const int last_nk = p.KT - (k_tiles - 1) * KS;      // K = 64 steps in the last stage of a tile
 
   if (threadIdx.x == 0) AC4K_TR(3, 0, 0);
+#ifdef AC4K_TRACE_ENABLED
+  unsigned launch_slot = 0;
+#endif
+  AC4K_TR_LAUNCH(true);
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar + 8 * s, 9);           // producer's expect_tx arrival + 8 scale warps
+      mbar_init(full_bar + 8 * s, SF_TILED ? 1 : 3);   // producer's expect_tx arrival (+ one scale warp per CTA)
       mbar_init(empty_bar + 8 * s, 1);
     }
-    for (int s = 0; s < SF_STAGES; ++s) {
-      mbar_init(sffull_bar + 8 * s, 1);
-      mbar_init(sffree_bar + 8 * s, 4);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar + 8 * a, 1);
+      mbar_init(tempty_bar + 8 * a, 16);        // 8 epilogue warps in each CTA
     }
-    mbar_init(tfull_bar, 1);
-    mbar_init(tempty_bar, 16);                  // 8 epilogue warps in each CTA
-    st_shared_release(ready_word, 0);
+    mbar_init(shared_free_bar, 8);              // 4 of them in each CTA
     fence_barrier_init();
     prefetch_tmap(&tma_a);
     prefetch_tmap(&tma_b);
-    if (!SF_TILED) {
+    if (SF_TILED) {
       prefetch_tmap(&tma_sfa);
       prefetch_tmap(&tma_sfb);
     }
+    if (EPI != EPI_REQUANT) prefetch_tmap(&dmaps.m[0]);
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, kTmemCols);
@@ -132,242 +180,200 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   // Everything above touched only this CTA's own resources, so it may overlap the tail of the kernel
   // before this one in the stream; from here on global memory is read and written.
   grid_launch_dependents();
+  if (warp == 2 && cluster_id < num_tiles && !(p.dbg & 128)) {
+    // While the kernel before this one may still be running: ask L2 for the operands of this CTA's first
+    // stages.  A prefetch returns no data, so the dependency wait below still orders every real read.
+    const uint32_t el = elect_one();
+    int tm, tn;
+    tile_coords(cluster_id, p.tiles_m, p.tiles_n, tm, tn);
+    const int m0 = tm * BMP + (int)rank * 128, nb0 = tn * BN + (int)rank * 128;
+    const int npre = k_tiles < STAGES ? k_tiles : STAGES;
+    for (int kt = 0; kt < npre; ++kt) {
+      tma_prefetch_2d_if(el, &tma_a, kt * BKB, m0);
+      tma_prefetch_2d_if(el, &tma_b, kt * BKB, nb0);
+    }
+  }
   grid_dependency_wait();
   if (threadIdx.x == 0) AC4K_TR(3, 0, 1);
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer (A and B)
-    if (lane == 0) {
-      uint32_t s = 0, ph = 0;
+    // ------------------------------------------------------------------ TMA producer
+    const uint32_t el = elect_one();
+    uint32_t s = 0, ph = 0;
+    const uint32_t leader_full0 = map_to_cta(full_bar, 0);
+    for (int t = cluster_id; t < num_tiles; t += num_clusters) {
+      int tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      const int m0 = tm * BMP + (int)rank * 128;        // this CTA's rows of A
+      const int nb0 = tn * BN + (int)rank * 128;        // this CTA's rows of B
+      const int sfa_row0 = (m0 / 128) * p.KT;           // tiled scales: row of [row block][K step] x 512 B
+      const int sfb_row0 = (tn * (BN / 128)) * p.KT;
       bool ok = true;
-      uint32_t leader_full[STAGES];
-#pragma unroll
-      for (int i = 0; i < STAGES; ++i) leader_full[i] = map_to_cta(full_bar + 8 * i, 0);
-      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
-        int tm, tn;
-        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
-        const int m0 = tm * BMP + (int)rank * 128;        // this CTA's rows of A
-        const int nb0 = tn * BN + (int)rank * 128;        // this CTA's rows of B
-        for (int kt = 0; kt < k_tiles; ++kt) {
-          if (!mbar_wait(empty_bar + 8 * s, ph ^ 1)) { atomicExch(p.status, kStatusTimeoutProducer); ok = false; break; }
-          const uint32_t lf = s == 0 ? leader_full[0] : (s == 1 ? leader_full[1] : leader_full[2]);
-          if (rank == 0) mbar_arrive_expect_tx(full_bar + 8 * s, 2 * (A_BYTES + B_BYTES));
-          const int kb = kt * (2 * BKB);
-          tma_load_2d_pair(sA + s * A_BYTES, &tma_a, kb, m0, lf);
-          tma_load_2d_pair(sB + s * B_BYTES, &tma_b, kb, nb0, lf);
-          tma_load_2d_pair(sA + s * A_BYTES + HALF_BYTES, &tma_a, kb + BKB, m0, lf);
-          tma_load_2d_pair(sB + s * B_BYTES + HALF_BYTES, &tma_b, kb + BKB, nb0, lf);
-          if (++s == STAGES) { s = 0; ph ^= 1; }
+      for (int kt = 0; kt < k_tiles; ++kt) {
+        ok = warp_all(mbar_wait(empty_bar + 8 * s, ph ^ 1));
+        if (!ok) break;
+        const uint32_t lf = leader_full0 + 8 * s;
+        // the leader announces the bytes of both CTAs; K steps past the end of K arrive as zeros
+        // (or as the next row block's scales, unused) and count all the same
+        if (rank == 0) mbar_arrive_expect_tx_if(el, full_bar + 8 * s, 2 * (SF_TILED ? STAGE_TX : A_BYTES + B_BYTES));
+        tma_load_2d_pair_if(el, sA + s * A_BYTES, &tma_a, kt * BKB, m0, lf);
+        tma_load_2d_pair_if(el, sB + s * B_BYTES, &tma_b, kt * BKB, nb0, lf);
+        if (SF_TILED) {
+          tma_load_2d_pair_if(el, sSFA + s * SFA_BYTES, &tma_sfa, 0, sfa_row0 + kt * KS, lf);
+          tma_load_2d_pair_if(el, sSFB + s * SFB_BYTES, &tma_sfb, 0, sfb_row0 + kt * KS, lf);
+          tma_load_2d_pair_if(el, sSFB + s * SFB_BYTES + KS * 512, &tma_sfb, 0, sfb_row0 + p.KT + kt * KS, lf);
         }
+        if (++s == STAGES) { s = 0; ph ^= 1; }
       }
+      if (!ok) { if (el) atomicExch(p.status, kStatusTimeoutProducer); break; }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA)
-    if (lane == 0 && rank == 0) {
+    if (rank == 0) {
+      const uint32_t el = elect_one();
       constexpr uint32_t idesc = make_idesc_mxf4nvf4(BMP, BN);
-      uint32_t s = 0, sf = 0, it = 0;
-      bool ok = true;
+      uint32_t s = 0, ph = 0, it = 0, ti = 0, acc_phs = 0, shared_ph = 0;
       const uint64_t adesc0 = make_smem_desc(sA, 16, 1024, kSwizzle128B);
       const uint64_t bdesc0 = make_smem_desc(sB, 16, 1024, kSwizzle128B);
-      uint32_t acc_ph = 0;
+      // scale chunks: 32 rows x 16 bytes, 8-row groups 128 bytes apart, not swizzled
+      const uint64_t sfadesc0 = make_smem_desc(sSFA, 0, 128, kSwizzleNone);
+      const uint64_t sfbdesc0 = make_smem_desc(sSFB, 0, 128, kSwizzleNone);
+      bool ok = true;
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
-        // the accumulator must have been drained by all 16 epilogue warps of the pair; waited for
-        // here and not through the watcher: it is the last link of the chain between two tiles
-        AC4K_TRG(0, it, 6);
-        if (!mbar_wait(tempty_bar, acc_ph ^ 1)) { ok = false; break; }
-        AC4K_TRG(0, it, 7);
-        acc_ph ^= 1;
+        // this tile's accumulator must have been drained (by the tile before the previous one), and the
+        // previous tile's epilogue must have read the columns both accumulators share
+        const uint32_t acc = ti & 1;
+        ok = warp_all(mbar_wait(tempty_bar + 8 * acc, ((acc_phs >> acc) & 1) ^ 1));
+        if (!ok) break;
+        acc_phs ^= 1u << acc;
+        ok = warp_all(mbar_wait(shared_free_bar, shared_ph ^ 1));
+        if (!ok) break;
+        shared_ph ^= 1;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * ACC1_COL;
         for (int kt = 0; kt < k_tiles; ++kt) {
-          AC4K_TR(0, it, 0);
-          uint32_t seen = ld_shared_volatile(ready_word);
-          if (seen <= it) {
-            const unsigned long long t0 = globaltimer();
-            while ((seen = ld_shared_volatile(ready_word)) <= it) {
-              // back off: a hot spin here takes issue slots from the epilogue and scale warps that
-              // share this scheduler, which is exactly what the issuer is waiting for
-              __nanosleep(40);
-              if (globaltimer() - t0 > kWaitTimeoutNs) { seen = 0xFFFFFFFFu; break; }
-            }
-          }
-          if (seen == 0xFFFFFFFFu) { ok = false; break; }
+          if (el) AC4K_TR(0, it, 0);
+          ok = warp_all(mbar_wait(full_bar + 8 * s, ph));
+          if (!ok) break;
           tc_fence_after();
-          AC4K_TR(0, it, 1);
-          if (it == 0) AC4K_TR(3, 0, 2);
-          const uint32_t t_sfa = tmem_base + SFA_COL + sf * SFA_COLS;
-          const uint32_t t_sfb = tmem_base + SFB_COL + sf * SFB_COLS;
+          if (el) AC4K_TR(0, it, 1);
+          const uint32_t t_sf = tmem_base + SF_COL;
           const uint64_t adesc = adesc0 + (uint64_t)(s * (A_BYTES >> 4));
           const uint64_t bdesc = bdesc0 + (uint64_t)(s * (B_BYTES >> 4));
+          const uint64_t sfadesc = sfadesc0 + (uint64_t)(s * (SFA_BYTES >> 4));
+          const uint64_t sfbdesc = sfbdesc0 + (uint64_t)(s * (SFB_BYTES >> 4));
           const int nk = (kt + 1 < k_tiles) ? KS : last_nk;
           if (nk == KS) {
 #pragma unroll
             for (int j = 0; j < KS; ++j) {
-              // K step j: box j / 4 of the stage, 32 bytes further inside the 128-byte swizzle atom per step
-              const uint32_t off = (j >> 2) * (HALF_BYTES >> 4) + 2 * (j & 3);
-              mma_mxf4nvf4_pair(tmem_base, adesc + off, bdesc + off, idesc, t_sfa + j * 4, t_sfb + j * 8,
-                                (kt > 0 || j > 0) ? 1u : 0u);
+              tmem_cp_32x128b_warpx4_pair_if(el, t_sf + j * 4, sfadesc + j * 32);
+              tmem_cp_32x128b_warpx4_pair_if(el, t_sf + KS * 4 + j * 8, sfbdesc + j * 32);
+              tmem_cp_32x128b_warpx4_pair_if(el, t_sf + KS * 4 + j * 8 + 4, sfbdesc + (KS + j) * 32);
             }
+#pragma unroll
+            for (int j = 0; j < KS; ++j)    // K step j: 32 bytes further inside the 128-byte swizzle atom
+              mma_mxf4nvf4_pair_if(el, d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, t_sf + j * 4, t_sf + KS * 4 + j * 8,
+                                   (kt > 0 || j > 0) ? 1u : 0u);
           } else {
             for (int j = 0; j < nk; ++j) {
-              const uint32_t off = (j >> 2) * (HALF_BYTES >> 4) + 2 * (j & 3);
-              mma_mxf4nvf4_pair(tmem_base, adesc + off, bdesc + off, idesc, t_sfa + j * 4, t_sfb + j * 8,
-                                (kt > 0 || j > 0) ? 1u : 0u);
+              tmem_cp_32x128b_warpx4_pair_if(el, t_sf + j * 4, sfadesc + j * 32);
+              tmem_cp_32x128b_warpx4_pair_if(el, t_sf + KS * 4 + j * 8, sfbdesc + j * 32);
+              tmem_cp_32x128b_warpx4_pair_if(el, t_sf + KS * 4 + j * 8 + 4, sfbdesc + (KS + j) * 32);
             }
+            for (int j = 0; j < nk; ++j)
+              mma_mxf4nvf4_pair_if(el, d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, t_sf + j * 4, t_sf + KS * 4 + j * 8,
+                                   (kt > 0 || j > 0) ? 1u : 0u);
           }
-          AC4K_TR(0, it, 3);
-          tc_commit_pair_both(empty_bar + 8 * s, 3);                 // stage free in both CTAs
-          if (kt == k_tiles - 1) tc_commit_pair_both(tfull_bar, 3);  // accumulator complete in both CTAs
-          AC4K_TR(0, it, 5);
+          tc_commit_pair_both_if(el, empty_bar + 8 * s, 3);                 // stage free in both CTAs
+          if (kt == k_tiles - 1) tc_commit_pair_both_if(el, tfull_bar + 8 * acc, 3);  // accumulator complete in both CTAs
+          if (el) AC4K_TR(0, it, 2);
           ++it;
-          sf ^= 1;
-          if (++s == STAGES) s = 0;
-        }
-      }
-      if (!ok) atomicExch(p.status, kStatusTimeoutMma);
-    }
-  } else if (warp == 11) {
-    // ------------------------------------------------------------------ barrier watcher (leader CTA)
-    if (lane == 0 && rank == 0) {
-      uint32_t s = 0, ph = 0, count = 0;
-      bool ok = true;
-      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
-        for (int kt = 0; kt < k_tiles && ok; ++kt) {
-          ok = mbar_wait(full_bar + 8 * s, ph);
-          if (!ok) break;
-          st_shared_release(ready_word, ++count);
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
+        ++ti;
       }
-      if (!ok) {
-        atomicExch(p.status, kStatusTimeoutMma);
-        st_shared_release(ready_word, 0xFFFFFFFFu);
-      }
+      if (!ok && el) atomicExch(p.status, kStatusTimeoutMma);
     }
-  } else if (warp == 10) {
-    // ------------------------------------------------------------------ scale feeder
-    if (lane == 0) {
-      uint32_t s = 0, ph = 0;
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ scale warps (row layout only)
+    // Scales stored as [K/64][rows][4 bytes]: the word of row r at K step k sits at word k * rows + r.
+    // tcgen05.cp wants, per K step and 128-row block, 32 rows of 16 bytes where row l holds the words
+    // of rows l, 32 + l, 64 + l, 96 + l.  Warp w takes the stages with (stage number % 4) == w - 2:
+    // its loads are in flight while the three stages before it are consumed.
+    if (!SF_TILED) {
+      const int w4 = warp - 2;
+      uint32_t s = 0, ph = 0, it = 0;
+      const uint32_t leader_full0 = map_to_cta(full_bar, 0);
+      const uint32_t *sfa_w = reinterpret_cast<const uint32_t *>(p.sfa);
+      const uint32_t *sfb_w = reinterpret_cast<const uint32_t *>(p.sfb);
       bool ok = true;
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
         const int m0 = tm * BMP + (int)rank * 128, n0 = tn * BN;
-        const int64_t mt = m0 / 128;
-        const bool a_ok = SF_TILED ? (mt * 128 < p.rows_sfa) : (m0 < p.rows_sfa);
-        const int nb_valid = min(2, (p.rows_sfb - n0) / 128);                       // tiled layout
         for (int kt = 0; kt < k_tiles; ++kt) {
-          if (!mbar_wait(sffree_bar + 8 * s, ph ^ 1)) { atomicExch(p.status, kStatusTimeoutSf); ok = false; break; }
-          const int nk = (kt + 1 < k_tiles) ? KS : last_nk;
-          const uint32_t bar = sffull_bar + 8 * s;
-          const int64_t k64 = (int64_t)kt * KS;
-          if (SF_TILED) {
-            mbar_arrive_expect_tx(bar, ((a_ok ? 1 : 0) + nb_valid) * nk * 512);
-            if (a_ok) bulk_load_1d_local(sSFA + s * SFA_BYTES, p.sfa + (mt * p.KT + k64) * 512, nk * 512, bar);
-            for (int nb = 0; nb < nb_valid; ++nb)
-              bulk_load_1d_local(sSFB + s * SFB_BYTES + nb * (KS * 512),
-                                 p.sfb + ((int64_t)(n0 / 128 + nb) * p.KT + k64) * 512, nk * 512, bar);
-          } else {
-            // row layout: one box of [8 K steps][128 or 256 rows] words per operand; rows and K steps
-            // outside the tensor arrive as zeros and count towards the transaction bytes
-            mbar_arrive_expect_tx(bar, SFA_BYTES + SFB_BYTES);
-            tma_load_2d_local(sSFA + s * SFA_BYTES, &tma_sfa, m0, (int)k64, bar);
-            tma_load_2d_local(sSFB + s * SFB_BYTES, &tma_sfb, n0, (int)k64, bar);
-          }
-          if (++s == SF_STAGES) { s = 0; ph ^= 1; }
-        }
-      }
-    }
-  } else if (warp < 6) {
-    // ------------------------------------------------------------------ scale warps
-    // Lane l of the warp owning TMEM lane quarter q writes, for K step j and row group g, the word
-    // of row 32 g + l into column (j * groups + g) of lane 32 q + l.  A tensor-memory slot is
-    // rewritten once the MMAs of the stage that used it two stages ago are done.
-    const int q = warp & 3;
-    uint32_t s = 0, ph = 0;          // scale rings (depth 2)
-    uint32_t os = 0, oph = 0;        // operand ring position of the current stage (depth 3)
-    uint32_t ps = 0, pph = 0;        // operand ring position of the stage two stages back
-    uint32_t it = 0;
-    bool ok = true;
-    const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
-    uint32_t leader_full[STAGES];
+          if ((int)(it & 3) == w4) {
+            uint32_t wa[KS][4], wb[KS][8];
 #pragma unroll
-    for (int i = 0; i < STAGES; ++i) leader_full[i] = map_to_cta(full_bar + 8 * i, 0);
-    for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
-      for (int kt = 0; kt < k_tiles; ++kt) {
-        if (warp == 2 && lane == 0) AC4K_TR(2, it, 0);
-        if (!mbar_wait(sffull_bar + 8 * s, ph)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutSf); ok = false; break; }
-        if (warp == 2 && lane == 0) AC4K_TR(2, it, 1);
-        const uint8_t *a_src = smem_gen + (sSFA + s * SFA_BYTES - smem_base);
-        const uint8_t *b_src = smem_gen + (sSFB + s * SFB_BYTES - smem_base);
-        uint32_t ra[32], rb[64];
-        if (SF_TILED) {
+            for (int j = 0; j < KS; ++j) {
+              const int k64 = kt * KS + j;
+              const bool k_ok = k64 < p.KT;
 #pragma unroll
-          for (int j = 0; j < KS; ++j) {
-            const uint4 v = *reinterpret_cast<const uint4 *>(a_src + j * 512 + lane * 16);
-            ra[j * 4 + 0] = v.x; ra[j * 4 + 1] = v.y; ra[j * 4 + 2] = v.z; ra[j * 4 + 3] = v.w;
+              for (int g = 0; g < 4; ++g) {
+                const int r = m0 + 32 * g + lane;
+                wa[j][g] = (k_ok && r < p.rows_sfa) ? __ldg(sfa_w + (int64_t)k64 * p.rows_sfa + r) : 0u;
+              }
 #pragma unroll
-            for (int nb = 0; nb < 2; ++nb) {
-              const uint4 w = *reinterpret_cast<const uint4 *>(b_src + (nb * KS + j) * 512 + lane * 16);
-              rb[j * 8 + nb * 4 + 0] = w.x; rb[j * 8 + nb * 4 + 1] = w.y;
-              rb[j * 8 + nb * 4 + 2] = w.z; rb[j * 8 + nb * 4 + 3] = w.w;
+              for (int g = 0; g < 8; ++g) {
+                const int r = n0 + 32 * g + lane;
+                wb[j][g] = (k_ok && r < p.rows_sfb) ? __ldg(sfb_w + (int64_t)k64 * p.rows_sfb + r) : 0u;
+              }
             }
+            ok = warp_all(mbar_wait(empty_bar + 8 * s, ph ^ 1));
+            if (!ok) break;
+#pragma unroll
+            for (int j = 0; j < KS; ++j) {
+              st_shared_v4u(sSFA + s * SFA_BYTES + j * 512 + lane * 16, wa[j][0], wa[j][1], wa[j][2], wa[j][3]);
+              st_shared_v4u(sSFB + s * SFB_BYTES + j * 512 + lane * 16, wb[j][0], wb[j][1], wb[j][2], wb[j][3]);
+              st_shared_v4u(sSFB + s * SFB_BYTES + (KS + j) * 512 + lane * 16, wb[j][4], wb[j][5], wb[j][6], wb[j][7]);
+            }
+            fence_proxy_async_smem();       // the tensor core reads these bytes through the async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_full0 + 8 * s);
           }
-        } else {
-#pragma unroll
-          for (int j = 0; j < KS; ++j) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g) ra[j * 4 + g] = reinterpret_cast<const uint32_t *>(a_src + j * 512)[g * 32 + lane];
-#pragma unroll
-            for (int g = 0; g < 8; ++g) rb[j * 8 + g] = reinterpret_cast<const uint32_t *>(b_src + j * 1024)[g * 32 + lane];
-          }
+          ++it;
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
-        if (warp == 2 && lane == 0) AC4K_TR(2, it, 2);
-        if (it >= SF_STAGES) {
-          if (!mbar_wait(empty_bar + 8 * ps, pph)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutSf); ok = false; break; }
-          if (++ps == STAGES) { ps = 0; pph ^= 1; }
-        }
-        if (warp == 2 && lane == 0) AC4K_TR(2, it, 3);
-        tc_fence_after();
-        tmem_st_32x32b_x32(lane_base + SFA_COL + s * SFA_COLS, ra);
-        tmem_st_32x32b_x64(lane_base + SFB_COL + s * SFB_COLS, rb);
-        tmem_st_wait();
-        if (warp == 2 && lane == 0) AC4K_TR(2, it, 5);
-        tc_fence_before();
-        __syncwarp();
-        // The shared-memory slot goes back to the feeder only now, after tcgen05.st has consumed the
-        // registers: an arrive issued right behind the loads can overtake them (they queue behind the
-        // tensor core's operand reads for hundreds of cycles), and the refill then landed under a
-        // warp that was still reading - seen as scales of two stages ahead in one lane quarter.
-        if (lane == 0) mbar_arrive(sffree_bar + 8 * s);
-        if (lane == 0) mbar_arrive_cluster(os == 0 ? leader_full[0] : (os == 1 ? leader_full[1] : leader_full[2]));
-        ++it;
-        if (++s == SF_STAGES) { s = 0; ph ^= 1; }
-        if (++os == STAGES) { os = 0; oph ^= 1; }
       }
+      if (!ok && lane == 0) atomicExch(p.status, kStatusTimeoutSf);
     }
-    (void)oph;
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 6-9, 12-15)
+    // ------------------------------------------------------------------ epilogue (warps 6-13)
     // Two warps per tensor-memory lane quarter, 128 accumulator columns each.  Phase 1: tcgen05.ld,
     // * alpha, + bias, pack to 16 bit, all into registers; then the accumulator goes back to the
     // MMA issuer.  Phase 2: each thread stores its 256-byte row segment; it overlaps the next
-    // tile's main loop.
+    // tile's main loop.  The warp whose 128 columns contain the 48 columns that both accumulators
+    // share reads those first and reports them free at once: that is all the next tile waits for.
     using T = typename OutT<OUT_DT>::type;
     const int q = warp & 3;
-    const int half = warp >= 12 ? 1 : 0;
-    uint32_t acc_ph = 0;
+    const int half = warp >= 10 ? 1 : 0;
+    uint32_t acc_phs = 0;
     int ti = 0;
     const float alpha = __fmul_rn(__ldg(p.a_gs), __ldg(p.b_gs));
-    const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + half * 128;
+    const bool has_bias = p.bias != nullptr;
     const uint32_t leader_tempty = map_to_cta(tempty_bar, 0);
+    const uint32_t leader_shared_free = map_to_cta(shared_free_bar, 0);
     for (int t = cluster_id; t < num_tiles; t += num_clusters) {
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
       const int row = tm * BMP + (int)rank * 128 + q * 32 + lane;
       const int col0 = tn * BN + half * 128;
       const uint32_t bias_s = sBias + (uint32_t)(half * 4 + q) * 512u;
-      if (p.bias != nullptr) {
+      const uint32_t acc = ti & 1;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * ACC1_COL + half * 128;
+      if (has_bias) {
         // this warp's 128 bias values go to shared memory while the tile's MMAs are still running, so
-        // that the drain below - which sits between two tiles - only adds broadcast shared-memory loads
+        // that the drain below only adds broadcast shared-memory loads
         float b4[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -377,46 +383,79 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         st_shared_v4f(bias_s + lane * 16, b4[0], b4[1], b4[2], b4[3]);
         __syncwarp();
       }
-      if (!mbar_wait(tfull_bar, acc_ph)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue); break; }
+      if (!mbar_wait(tfull_bar + 8 * acc, (acc_phs >> acc) & 1)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue); break; }
+      acc_phs ^= 1u << acc;
       tc_fence_after();
       if (warp == 6 && lane == 0) AC4K_TR(1, ti, 0);
-      if (lane == 0 && ti < 16) AC4K_TRG(4 + rank, ti * 8 + q + 4 * half, 0);
       uint32_t w[64];
-      if (p.bias == nullptr) {
-        // two 64-column loads: each load-and-wait costs a full tensor-memory round trip, and this
-        // drain is on the critical path between two tiles
+      if (half == (int)acc) {
+        // none of the shared columns: columns 0 - 127 of accumulator 0 or 128 - 255 of accumulator 1
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t r[64];
           tmem_ld_32x32b_x64_sync(t_row + c * 64, r);
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            w[c * 32 + i] = (OUT_DT == AC4K_DT_BF16) ? scale_pack_bf16x2(r[2 * i], r[2 * i + 1], alpha)
-                                                     : scale_pack_f16x2(r[2 * i], r[2 * i + 1], alpha);
+          if (c == 0) pack_cols<OUT_DT, 0, 64>(r, w, alpha, has_bias, bias_s);
+          else pack_cols<OUT_DT, 64, 64>(r, w, alpha, has_bias, bias_s);
+        }
+      } else if (half == 0) {
+        // accumulator 1, tile columns 0 - 127: the shared ones are this warp's first 48
+        {
+          uint32_t r0[32], r1[16];
+          tmem_ld_32x32b_x32(t_row, r0);
+          tmem_ld_32x32b_x16(t_row + 32, r1);
+          tmem_ld_wait();
+          tmem_pin(r0);
+          tmem_pin(r1);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(leader_shared_free);
+          pack_cols<OUT_DT, 0, 32>(r0, w, alpha, has_bias, bias_s);
+          pack_cols<OUT_DT, 32, 16>(r1, w, alpha, has_bias, bias_s);
+        }
+        {
+          uint32_t r[64];
+          tmem_ld_32x32b_x64_sync(t_row + 48, r);
+          pack_cols<OUT_DT, 48, 64>(r, w, alpha, has_bias, bias_s);
+        }
+        {
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(t_row + 112, r);
+          tmem_ld_wait();
+          tmem_pin(r);
+          pack_cols<OUT_DT, 112, 16>(r, w, alpha, has_bias, bias_s);
         }
       } else {
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        // accumulator 0, tile columns 128 - 255: the shared ones are this warp's last 48
+        {
+          uint32_t r0[16], r1[32];
+          tmem_ld_32x32b_x16(t_row + 80, r0);
+          tmem_ld_32x32b_x32(t_row + 96, r1);
+          tmem_ld_wait();
+          tmem_pin(r0);
+          tmem_pin(r1);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(leader_shared_free);
+          pack_cols<OUT_DT, 80, 16>(r0, w, alpha, has_bias, bias_s);
+          pack_cols<OUT_DT, 96, 32>(r1, w, alpha, has_bias, bias_s);
+        }
+        {
           uint32_t r[64];
-          tmem_ld_32x32b_x64_sync(t_row + c * 64, r);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float4 bb = ld_shared_v4f(bias_s + (c * 16 + i) * 16);
-            if (OUT_DT == AC4K_DT_BF16) {
-              w[c * 32 + 2 * i] = scale_bias_pack_bf16x2(r[4 * i], r[4 * i + 1], alpha, bb.x, bb.y);
-              w[c * 32 + 2 * i + 1] = scale_bias_pack_bf16x2(r[4 * i + 2], r[4 * i + 3], alpha, bb.z, bb.w);
-            } else {
-              w[c * 32 + 2 * i] = scale_bias_pack_f16x2(r[4 * i], r[4 * i + 1], alpha, bb.x, bb.y);
-              w[c * 32 + 2 * i + 1] = scale_bias_pack_f16x2(r[4 * i + 2], r[4 * i + 3], alpha, bb.z, bb.w);
-            }
-          }
+          tmem_ld_32x32b_x64_sync(t_row, r);
+          pack_cols<OUT_DT, 0, 64>(r, w, alpha, has_bias, bias_s);
+        }
+        {
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(t_row + 64, r);
+          tmem_ld_wait();
+          tmem_pin(r);
+          pack_cols<OUT_DT, 64, 16>(r, w, alpha, has_bias, bias_s);
         }
       }
       tc_fence_before();
       __syncwarp();
       if (warp == 6 && lane == 0) AC4K_TR(1, ti, 1);
-      if (lane == 0) mbar_arrive_cluster(leader_tempty);
-      if (lane == 0 && ti < 16) AC4K_TRG(4 + rank, ti * 8 + q + 4 * half, 1);
+      if (lane == 0) mbar_arrive_cluster(leader_tempty + 8 * acc);
       const int64_t col_base = p.col_off + col0;
       const bool last_tile = t + num_clusters >= num_tiles;
       if (EPI == EPI_REQUANT) {
@@ -460,65 +499,54 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
             *sfp = sfw[h2];
           }
         }
-      } else
-      if (row < p.M && !(p.dbg & 8)) {
-        // Each lane owns one row, so a store instruction touches 32 different rows however it is
-        // shaped; 32-byte stores make every one of those touches a full sector, and a short pause
-        // between them keeps the SM's memory pipe free for the barrier and shared-memory traffic of
-        // the warps that run the next tile's main loop (the stores have a whole tile time to finish).
-        T *dst = static_cast<T *>(p.D) + (int64_t)row * p.ldd + col_base;
-        const bool vec32 = col0 + 128 <= p.N && ((p.ldd | p.col_off) * (int64_t)sizeof(T)) % 32 == 0 &&
-                           (reinterpret_cast<uintptr_t>(p.D) & 31) == 0;
-        if (vec32) {
+      } else if (!(p.dbg & 8)) {
+        // The registers hold one row per lane; stored from there, every instruction would touch 32
+        // different rows, and that scatter was measured to slow the next tile's main loop down by
+        // 20 % while it lasted.  So each half (64 columns = 128 bytes per row) goes through this warp's
+        // 4 KB staging buffer in the 128-byte-swizzled order and leaves as one TMA store of 32 rows,
+        // clipped by the tensor map at the edges of the output.  With several destinations (the fused
+        // all-gather: this GPU's buffer and the peers', reached over NVLink) the same buffer is stored
+        // once per destination.
+        const uint32_t stage_buf = sOut + (uint32_t)(half * 4 + q) * OUT_STAGE_BYTES;
+        const int y0 = tm * BMP + (int)rank * 128 + q * 32;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            st_global_v8(reinterpret_cast<uint8_t *>(dst) + 32 * i, w[8 * i], w[8 * i + 1], w[8 * i + 2], w[8 * i + 3],
-                         w[8 * i + 4], w[8 * i + 5], w[8 * i + 6], w[8 * i + 7]);
-            if (!last_tile) __nanosleep(200);      // nothing left to make room for after the last tile
+        for (int h2 = 0; h2 < 2; ++h2) {
+          const int x0 = (int)col_base + 64 * h2;
+          if (col0 + 64 * h2 >= p.N || y0 >= p.M) break;     // warp-uniform: nothing of this box is inside the output
+#ifdef AC4K_TRACE_ENABLED
+          if (!last_tile && (p.dbg >> 8)) {                   // experiment: spread the 16 stores of a tile over time
+            const unsigned d = (unsigned)(p.dbg >> 8) * (unsigned)((h2 == 0 ? 0 : 8) + half * 4 + q) - (h2 == 0 ? 0u : (unsigned)(p.dbg >> 8) * (unsigned)(half * 4 + q));
+            if (d) __nanosleep(d);
           }
-        } else {
-          // ragged right edge or rows that are only 16-byte aligned: 16-byte groups
+#endif
+          if (lane == 0) bulk_wait_group_read0();            // the previous store has read the buffer
+          __syncwarp();
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            if (col0 + 8 * i < p.N)
-              __stcs(reinterpret_cast<uint4 *>(dst) + i, make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]));
-        }
-      }
-      if (EPI == EPI_GATHER && p.n_dst > 1 && !(p.dbg & 8)) {
-        // Fused all-gather: forward this warp's 32 rows x 256 bytes to the other destinations (peer
-        // GPUs' buffers, reached over NVLink).  The registers hold one row per lane, which would make
-        // every peer store a scatter of 32-byte pieces; NVLink wants long contiguous writes.  So the
-        // block is read back from this GPU's L2 in the other orientation - 16 lanes x 16 bytes cover a
-        // row's 256 bytes, two rows per instruction - and stored to each peer in that shape.
-        __syncwarp();                               // the warp's own stores above are ordered before its loads
-        const int row0 = tm * BMP + (int)rank * 128 + q * 32 + (lane >> 4);
-        const int cchunk = (lane & 15) * 8;         // first column of this lane's 16-byte piece
-        const bool col_ok = col0 + cchunk < p.N;
-        const T *src = static_cast<const T *>(p.D) + col_base + cchunk;
-        uint4 v[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int r = row0 + 2 * i;
-          if (col_ok && r < p.M) v[i] = ld_global_cg_v4(src + (int64_t)r * p.ldd);
-        }
-        // peer after peer (storing each piece to every peer in turn was measured slower at 8 GPUs: 594
-        // against 627 GB/s per direction)
-#pragma unroll
-        for (int d = 1; d < kMaxDst; ++d) {
-          if (d >= p.n_dst) break;
-          T *peer = static_cast<T *>(p.D_more[d - 1]) + col_base + cchunk;
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int r = row0 + 2 * i;
-            if (col_ok && r < p.M) st_global_v4(peer + (int64_t)r * p.ldd, v[i]);
+          for (int c = 0; c < 8; ++c)
+            st_shared_v4u(stage_buf + lane * 128 + ((c ^ (lane & 7)) << 4), w[32 * h2 + 4 * c], w[32 * h2 + 4 * c + 1],
+                          w[32 * h2 + 4 * c + 2], w[32 * h2 + 4 * c + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+#ifdef AC4K_TRACE_ENABLED
+            if (p.dbg & 16) tma_store_2d(&dmaps.m[0], 64 * h2 + half * 128, (int)rank * 128 + q * 32, stage_buf);   // experiment: every tile to one L2-resident corner
+            else if (p.dbg & 32) tma_store_2d_hint(&dmaps.m[0], x0, y0, stage_buf, make_policy_evict_first());
+            else
+#endif
+            tma_store_2d(&dmaps.m[0], x0, y0, stage_buf);
+            if (EPI == EPI_GATHER) {
+              // peers in turn, starting behind this rank, so that the ranks do not all write to the same GPU at once
+              for (int d = 1; d < p.n_dst; ++d) tma_store_2d(&dmaps.m[d], x0, y0, stage_buf);
+            }
+            bulk_commit_group();
           }
         }
       }
       if (warp == 6 && lane == 0) AC4K_TR(1, ti, 2);
       if (warp == 6 && lane == 0) AC4K_TR(3, 0, 3);
       ++ti;
-      acc_ph ^= 1;
     }
+    if (lane == 0) bulk_wait_group_read0(); // the staging buffer has been read by this warp's last stores before the CTA exits
   }
 
   if (threadIdx.x == 0) AC4K_TR(3, 0, 4);
@@ -530,11 +558,12 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     tmem_dealloc_pair(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0) AC4K_TR(3, 0, 5);
+  AC4K_TR_LAUNCH(false);
 }
 
 template <bool SF_TILED, int OUT_DT, int EPI>
 static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tsa, const CUtensorMap &tsb,
-                       const GemmArgs &args, int sms, cudaStream_t stream) {
+                       const DstMaps &dm, const GemmArgs &args, int sms, cudaStream_t stream) {
   auto kern = linear_nvfp4_2cta_kernel<SF_TILED, OUT_DT, EPI>;
   static bool attr_set[64] = {};
   int dev = 0;
@@ -577,12 +606,12 @@ static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUten
   attr.val.programmaticStreamSerializationAllowed = (args.dbg & 64) ? 0 : 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  AC4K_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, tsa, tsb, args));
+  AC4K_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, tsa, tsb, dm, args));
   return 0;
 }
 
 int launch_linear_2cta(int d_dtype, bool sf_tiled, const CUtensorMap &ta, const CUtensorMap &tb,
-                       const CUtensorMap &tsa, const CUtensorMap &tsb, GemmArgs args, cudaStream_t stream) {
+                       const CUtensorMap &tsa, const CUtensorMap &tsb, const DstMaps &dm, GemmArgs args, cudaStream_t stream) {
   DeviceInfo di;
   if (int e = get_device_info(&di)) return e;
   args.tiles_m = (int)ceil_div(args.M, pair::BMP);
@@ -591,23 +620,23 @@ int launch_linear_2cta(int d_dtype, bool sf_tiled, const CUtensorMap &ta, const 
   // separate: their extra registers and code would otherwise slow the plain GEMM down
   if (args.q_out != nullptr) {
     if (d_dtype != AC4K_DT_BF16) return fail(AC4K_ERR_UNSUPPORTED, "the re-quantising epilogue rounds to bf16 first");
-    return sf_tiled ? launch_pair<true, AC4K_DT_BF16, EPI_REQUANT>(ta, tb, tsa, tsb, args, di.sms, stream)
-                    : launch_pair<false, AC4K_DT_BF16, EPI_REQUANT>(ta, tb, tsa, tsb, args, di.sms, stream);
+    return sf_tiled ? launch_pair<true, AC4K_DT_BF16, EPI_REQUANT>(ta, tb, tsa, tsb, dm, args, di.sms, stream)
+                    : launch_pair<false, AC4K_DT_BF16, EPI_REQUANT>(ta, tb, tsa, tsb, dm, args, di.sms, stream);
   }
   const bool gather = args.n_dst > 1;
   if (d_dtype == AC4K_DT_BF16) {
     if (gather)
-      return sf_tiled ? launch_pair<true, AC4K_DT_BF16, EPI_GATHER>(ta, tb, tsa, tsb, args, di.sms, stream)
-                      : launch_pair<false, AC4K_DT_BF16, EPI_GATHER>(ta, tb, tsa, tsb, args, di.sms, stream);
-    return sf_tiled ? launch_pair<true, AC4K_DT_BF16, EPI_PLAIN>(ta, tb, tsa, tsb, args, di.sms, stream)
-                    : launch_pair<false, AC4K_DT_BF16, EPI_PLAIN>(ta, tb, tsa, tsb, args, di.sms, stream);
+      return sf_tiled ? launch_pair<true, AC4K_DT_BF16, EPI_GATHER>(ta, tb, tsa, tsb, dm, args, di.sms, stream)
+                      : launch_pair<false, AC4K_DT_BF16, EPI_GATHER>(ta, tb, tsa, tsb, dm, args, di.sms, stream);
+    return sf_tiled ? launch_pair<true, AC4K_DT_BF16, EPI_PLAIN>(ta, tb, tsa, tsb, dm, args, di.sms, stream)
+                    : launch_pair<false, AC4K_DT_BF16, EPI_PLAIN>(ta, tb, tsa, tsb, dm, args, di.sms, stream);
   }
   if (d_dtype == AC4K_DT_FP16) {
     if (gather)
-      return sf_tiled ? launch_pair<true, AC4K_DT_FP16, EPI_GATHER>(ta, tb, tsa, tsb, args, di.sms, stream)
-                      : launch_pair<false, AC4K_DT_FP16, EPI_GATHER>(ta, tb, tsa, tsb, args, di.sms, stream);
-    return sf_tiled ? launch_pair<true, AC4K_DT_FP16, EPI_PLAIN>(ta, tb, tsa, tsb, args, di.sms, stream)
-                    : launch_pair<false, AC4K_DT_FP16, EPI_PLAIN>(ta, tb, tsa, tsb, args, di.sms, stream);
+      return sf_tiled ? launch_pair<true, AC4K_DT_FP16, EPI_GATHER>(ta, tb, tsa, tsb, dm, args, di.sms, stream)
+                      : launch_pair<false, AC4K_DT_FP16, EPI_GATHER>(ta, tb, tsa, tsb, dm, args, di.sms, stream);
+    return sf_tiled ? launch_pair<true, AC4K_DT_FP16, EPI_PLAIN>(ta, tb, tsa, tsb, dm, args, di.sms, stream)
+                    : launch_pair<false, AC4K_DT_FP16, EPI_PLAIN>(ta, tb, tsa, tsb, dm, args, di.sms, stream);
   }
   return fail(AC4K_ERR_UNSUPPORTED, "the CTA-pair kernel stores 16-bit outputs only");
 }

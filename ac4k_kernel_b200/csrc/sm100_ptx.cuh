@@ -111,6 +111,13 @@ __device__ __forceinline__ void tma_load_2d_local(uint32_t dst, const void *tmap
       ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+// Hint: bring the box into L2.  Returns no data, so it may be issued before griddepcontrol.wait: lines
+// that an earlier kernel still writes are updated in L2, the point of coherence, like any others.
+__device__ __forceinline__ void tma_prefetch_2d_if(uint32_t pred, const void *tmap, int x, int y) {
+  asm volatile("{\n.reg .pred q;\nsetp.ne.b32 q, %3, 0;\n"
+               "@q cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];\n}"
+               ::"l"(tmap), "r"(x), "r"(y), "r"(pred) : "memory");
+}
 __device__ __forceinline__ void prefetch_tmap(const void *tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -241,6 +248,31 @@ __device__ __forceinline__ void tmem_ld_32x32b_x64_sync(uint32_t taddr, uint32_t
   for (int i = 0; i < 64; ++i) asm volatile("" : "+r"(v[i]) : : "memory");
 }
 
+// tcgen05.ld without the wait, for several loads in flight behind one tcgen05.wait::ld; the caller
+// pins the registers with tmem_pin() after the wait (see tmem_ld_32x32b_x32_sync).
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x64(uint32_t taddr, uint32_t (&v)[64]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31]), "=r"(v[32]), "=r"(v[33]), "=r"(v[34]), "=r"(v[35]), "=r"(v[36]), "=r"(v[37]), "=r"(v[38]), "=r"(v[39]), "=r"(v[40]), "=r"(v[41]), "=r"(v[42]), "=r"(v[43]), "=r"(v[44]), "=r"(v[45]), "=r"(v[46]), "=r"(v[47]), "=r"(v[48]), "=r"(v[49]), "=r"(v[50]), "=r"(v[51]), "=r"(v[52]), "=r"(v[53]), "=r"(v[54]), "=r"(v[55]), "=r"(v[56]), "=r"(v[57]), "=r"(v[58]), "=r"(v[59]), "=r"(v[60]), "=r"(v[61]), "=r"(v[62]), "=r"(v[63])
+      : "r"(taddr)
+      : "memory");
+}
+template <int N>
+__device__ __forceinline__ void tmem_pin(uint32_t (&v)[N]) {
+#pragma unroll
+  for (int i = 0; i < N; ++i) asm volatile("" : "+r"(v[i]) : : "memory");
+}
+
 __device__ __forceinline__ uint32_t ld_shared_volatile(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.volatile.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
@@ -357,6 +389,22 @@ __device__ __forceinline__ void tma_store_2d(const void *tmap, int x, int y, uin
                ::"l"(tmap), "r"(x), "r"(y), "r"(src)
                : "memory");
 }
+// same, with an L2 cache policy for the written lines (from make_policy_evict_first / _last)
+__device__ __forceinline__ void tma_store_2d_hint(const void *tmap, int x, int y, uint32_t src, uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group.L2::cache_hint [%0, {%1, %2}], [%3], %4;"
+               ::"l"(tmap), "r"(x), "r"(y), "r"(src), "l"(policy)
+               : "memory");
+}
+__device__ __forceinline__ uint64_t make_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t make_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 template <int N>
@@ -395,6 +443,92 @@ __device__ __forceinline__ void tc_commit_pair_both(uint32_t bar, uint16_t cta_m
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
                : "memory");
+}
+
+// ---- warp-wide issue ----------------------------------------------------------------------
+// A role that issues tcgen05 / TMA instructions runs with its whole warp converged and gives every
+// such instruction a predicate that is true in one elected lane.  Measured on a B200: issued from
+// inside an `if (lane == 0)` branch a tcgen05.mma / cp / commit costs the issuing thread 70 - 110
+// cycles each (a stage of 12 cp + 4 mma + 1 commit: 1 080 cycles); issued predicated from a converged
+// warp the same stage costs 330 cycles, because addresses and descriptors stay in uniform registers.
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t pred;
+  asm volatile("{\n.reg .pred P;\nelect.sync _|P, 0xffffffff;\nselp.u32 %0, 1, 0, P;\n}" : "=r"(pred));
+  return pred;
+}
+__device__ __forceinline__ bool warp_all(bool v) { return __all_sync(0xffffffffu, v); }
+
+__device__ __forceinline__ void mbar_arrive_expect_tx_if(uint32_t pred, uint32_t bar, uint32_t bytes) {
+  asm volatile("{\n.reg .pred q;\nsetp.ne.b32 q, %2, 0;\n@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n}"
+               ::"r"(bar), "r"(bytes), "r"(pred) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster_if(uint32_t pred, uint32_t bar_cluster_addr) {
+  asm volatile("{\n.reg .pred q;\nsetp.ne.b32 q, %1, 0;\n@q mbarrier.arrive.shared::cluster.b64 _, [%0];\n}"
+               ::"r"(bar_cluster_addr), "r"(pred) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_if(uint32_t pred, uint32_t dst, const void *tmap, int x, int y, uint32_t bar) {
+  asm volatile(
+      "{\n.reg .pred q;\nsetp.ne.b32 q, %5, 0;\n"
+      "@q cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n}"
+      ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar), "r"(pred)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair_if(uint32_t pred, uint32_t dst, const void *tmap, int x, int y,
+                                                    uint32_t bar_cluster_addr) {
+  asm volatile(
+      "{\n.reg .pred q;\nsetp.ne.b32 q, %5, 0;\n"
+      "@q cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n}"
+      ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar_cluster_addr), "r"(pred)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_load_1d_if(uint32_t pred, uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "{\n.reg .pred q;\nsetp.ne.b32 q, %4, 0;\n"
+      "@q cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n}"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "r"(pred)
+      : "memory");
+}
+__device__ __forceinline__ void mma_mxf4nvf4_if(uint32_t pred, uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p, q;\nsetp.ne.b32 p, %6, 0;\nsetp.ne.b32 q, %7, 0;\n"
+      "@q tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate), "r"(pred)
+      : "memory");
+}
+__device__ __forceinline__ void mma_mxf4nvf4_pair_if(uint32_t pred, uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                     uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p, q;\nsetp.ne.b32 p, %6, 0;\nsetp.ne.b32 q, %7, 0;\n"
+      "@q tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate), "r"(pred)
+      : "memory");
+}
+// 32 rows x 16 bytes of shared memory -> 4 columns of tensor memory, replicated to the four 32-lane
+// quarters.  The pair form copies in both CTAs, each from its own shared memory at the same offset
+// into its own tensor memory.  Executes in issue order with the MMAs of the same thread and overlaps
+// them: (12 cp + 4 MMA of 128 x 256 x 64) run in 523 cycles against 520 for the MMAs alone.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4_if(uint32_t pred, uint32_t taddr, uint64_t sdesc) {
+  asm volatile("{\n.reg .pred q;\nsetp.ne.b32 q, %2, 0;\n@q tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n}"
+               ::"r"(taddr), "l"(sdesc), "r"(pred) : "memory");
+}
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4_pair_if(uint32_t pred, uint32_t taddr, uint64_t sdesc) {
+  asm volatile("{\n.reg .pred q;\nsetp.ne.b32 q, %2, 0;\n@q tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;\n}"
+               ::"r"(taddr), "l"(sdesc), "r"(pred) : "memory");
+}
+__device__ __forceinline__ void tc_commit_if(uint32_t pred, uint32_t bar) {
+  asm volatile("{\n.reg .pred q;\nsetp.ne.b32 q, %1, 0;\n"
+               "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}"
+               ::"r"(bar), "r"(pred) : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair_both_if(uint32_t pred, uint32_t bar, uint16_t cta_mask) {
+  asm volatile("{\n.reg .pred q;\nsetp.ne.b32 q, %2, 0;\n"
+               "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n}"
+               ::"r"(bar), "h"(cta_mask), "r"(pred)
+               : "memory");
+}
+__device__ __forceinline__ void st_shared_v4u(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared::cta.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
 }  // namespace ptx
