@@ -149,6 +149,9 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   unsigned launch_slot = 0;
 #endif
   AC4K_TR_LAUNCH(true);
+#ifdef AC4K_TRACE_ENABLED
+  if (p.trace != nullptr && rank == 0 && threadIdx.x == 0 && cluster_id < 120) p.trace[((size_t)4 * 128 + cluster_id) * 8 + 0] = globaltimer();
+#endif
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar + 8 * s, SF_TILED ? 1 : 3);   // producer's expect_tx arrival (+ one scale warp per CTA)
@@ -195,6 +198,9 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   }
   grid_dependency_wait();
   if (threadIdx.x == 0) AC4K_TR(3, 0, 1);
+#ifdef AC4K_TRACE_ENABLED
+  if (p.trace != nullptr && rank == 0 && threadIdx.x == 0 && cluster_id < 120) p.trace[((size_t)4 * 128 + cluster_id) * 8 + 1] = globaltimer();
+#endif
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -558,6 +564,9 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     tmem_dealloc_pair(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0) AC4K_TR(3, 0, 5);
+#ifdef AC4K_TRACE_ENABLED
+  if (p.trace != nullptr && rank == 0 && threadIdx.x == 0 && cluster_id < 120) p.trace[((size_t)4 * 128 + cluster_id) * 8 + 2] = globaltimer();
+#endif
   AC4K_TR_LAUNCH(false);
 }
 
