@@ -30,12 +30,10 @@ struct Cfg {
   static constexpr int STAGES = (BN == 128) ? 6 : 4;
   static constexpr int ACC_STAGES = (BN == 128) ? 2 : 1;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 512 /*barriers*/;
-  // tensor-memory columns: accumulators, then one scale buffer per shared-memory stage
-  static constexpr int SFA_COL = ACC_STAGES * BN;
-  static constexpr int SFA_COLS = K64_PER_STAGE * 4;
-  static constexpr int SFB_COL = SFA_COL + STAGES * SFA_COLS;
-  static constexpr int SFB_COLS = K64_PER_STAGE * (BN / 32);
-  static_assert(SFB_COL + STAGES * SFB_COLS <= kTmemCols, "tensor memory overflow");
+  // tensor-memory columns: accumulators, then the scales of one stage (A: 4 columns per K step, then B)
+  static constexpr int SF_COL = ACC_STAGES * BN;
+  static constexpr int SF_COLS = K64_PER_STAGE * (4 + BN / 32);
+  static_assert(SF_COL + SF_COLS <= kTmemCols, "tensor memory overflow");
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory overflow");
 };
 
@@ -143,12 +141,16 @@ int get_device_info(DeviceInfo *out);
 // 2-D byte tensor map [rows, row_bytes] with a (128 B x box_rows) box and 128-byte swizzle
 int get_tmap(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUtensorMap *out);
 // 2-CTA kernel launcher (linear_nvfp4_2cta.cu); D must be bf16/fp16 with N % 8 == 0
-// tsa / tsb: tensor maps of row-layout scales (get_tmap_sf); ignored when sf_tiled
-int get_tmap_sf(const void *ptr, int64_t rows16, int64_t kt, int box_rows, int box_ksteps, CUtensorMap *out);
+// tsa / tsb: tensor maps of tiled scales (get_tmap_sf_tiled); scales in the row layout are read with plain loads
 int get_tmap_sf_tiled(const void *ptr, int64_t row_blocks, int64_t kt, int box_ksteps, CUtensorMap *out);
 // 16-bit output [rows, cols] with a row pitch of ld elements: boxes of 64 columns x 32 rows, 128-byte swizzle
 int get_tmap_out16(const void *ptr, int64_t rows, int64_t cols, int64_t ld, CUtensorMap *out);
 int launch_linear_2cta(int d_dtype, bool sf_tiled, const CUtensorMap &ta, const CUtensorMap &tb,
                        const CUtensorMap &tsa, const CUtensorMap &tsb, const DstMaps &dm, GemmArgs args, cudaStream_t stream);
+
+// decode-shape kernel (linear_nvfp4_skinny.cu): M <= nt activation rows, nt in {16, 32, 64}
+int skinny_max_splits(int nt);
+int launch_linear_skinny(int d_dtype, bool sf_tiled, int nt, const CUtensorMap &tx, const CUtensorMap &tw, const GemmArgs &args,
+                         cudaStream_t stream);
 
 }  // namespace ac4k

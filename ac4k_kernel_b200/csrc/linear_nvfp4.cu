@@ -6,15 +6,17 @@
 //   warp 0   TMA producer: per K-step of 256 elements, one 128-byte-swizzled box of A
 //            (128 rows x 128 B), one of B (BN rows x 128 B) and the scale bytes of both,
 //            into a multi-stage shared-memory ring guarded by full/empty mbarriers
-//   warp 1   MMA issuer (one lane): four K=64 tcgen05.mma kind::mxf4nvf4.block_scale per
-//            stage into a TMEM accumulator; releases the stage / publishes the accumulator
-//            with tcgen05.commit
-//   warps 2-5 scale warps: move the stage's scale bytes shared memory -> registers -> tensor
-//            memory with tcgen05.st, one TMEM lane quarter per warp.  (tcgen05.cp was measured
-//            at ~62 cycles per 512-byte copy, more than the MMAs it feeds; one tcgen05.st per
-//            operand and stage is far cheaper.)
+//   warp 1   MMA issuer: per stage the scales' tcgen05.cp copies (shared -> tensor memory), four
+//            K=64 tcgen05.mma kind::mxf4nvf4.block_scale into a TMEM accumulator, and the
+//            tcgen05.commit that releases the stage / publishes the accumulator
+//   warp 2   before the dependency wait: L2 prefetch of the weight bytes of the CTA's first work item
+//   warps 2-5 only for scales in the row layout [K/64][rows][4]: each warp takes every fourth stage,
+//            reads its scale words from global memory and writes them to shared memory in the
+//            32 x 16-byte order tcgen05.cp wants
 //   warps 6-9 epilogue: tcgen05.ld of the accumulator (one TMEM lane quarter per warp),
 //            * (gA*gB), + bias, convert, store
+// The roles that issue TMA or tcgen05 instructions run with their whole warp converged and predicate
+// those instructions on one elected lane (see elect_one()).
 //
 // Scale factors in tensor memory: the four e4m3 scales of row r for one K=64 step sit in lane
 // r % 32 (replicated in all four lane quarters), 32-bit column r / 32, so A (128 rows) takes 4
@@ -43,7 +45,6 @@ using namespace ptx;
 template <int BN, bool SF_TILED, int OUT_DT>
 __global__ void __launch_bounds__(kNumThreads, 1)
 linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                    const __grid_constant__ CUtensorMap tma_sfa, const __grid_constant__ CUtensorMap tma_sfb,
                     const GemmArgs p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -53,8 +54,8 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   const uint32_t sSFA = sB + C::STAGES * C::B_BYTES;
   const uint32_t sSFB = sSFA + C::STAGES * C::SFA_BYTES;
   const uint32_t bars = sSFB + C::STAGES * C::SFB_BYTES;
-  const uint32_t full_bar = bars, empty_bar = bars + 8 * C::STAGES, sf_bar = bars + 16 * C::STAGES;
-  const uint32_t tfull_bar = bars + 24 * C::STAGES, tempty_bar = tfull_bar + 8 * C::ACC_STAGES;
+  const uint32_t full_bar = bars, empty_bar = bars + 8 * C::STAGES;
+  const uint32_t tfull_bar = bars + 16 * C::STAGES, tempty_bar = tfull_bar + 8 * C::ACC_STAGES;
   const uint32_t tmem_slot = tempty_bar + 8 * C::ACC_STAGES;
   uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));   // generic pointer to smem_base
 
@@ -71,11 +72,16 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   };
 
   if (threadIdx.x == 0) AC4K_TR1(3, 0, 0);
+#ifdef AC4K_TRACE_ENABLED
+#define AC4K_TRW(ev) do { if (p.trace != nullptr && blockIdx.x < 127) p.trace[((size_t)4 * 128 + blockIdx.x) * 8 + (ev)] = globaltimer(); } while (0)
+#else
+#define AC4K_TRW(ev) do { } while (0)
+#endif
+  if (threadIdx.x == 0) AC4K_TRW(0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
-      mbar_init(full_bar + 8 * s, 1);
+      mbar_init(full_bar + 8 * s, SF_TILED ? 1 : 2);   // producer's expect_tx arrival (+ the stage's scale warp)
       mbar_init(empty_bar + 8 * s, 1);
-      mbar_init(sf_bar + 8 * s, 4);
     }
     for (int a = 0; a < C::ACC_STAGES; ++a) {
       mbar_init(tfull_bar + 8 * a, 1);
@@ -84,28 +90,164 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     fence_barrier_init();
     prefetch_tmap(&tma_a);
     prefetch_tmap(&tma_b);
-    if (!SF_TILED) {
-      prefetch_tmap(&tma_sfa);
-      prefetch_tmap(&tma_sfb);
-    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
+  if (warp == 2 && (int)blockIdx.x < num_work) {
+    // While the kernel before this one may still be running: ask L2 for the weight bytes of this CTA's
+    // first work item (a prefetch returns no data, so the dependency wait below still orders every real
+    // read).  On decode shapes that is the CTA's whole share of the weight stream, requested from HBM at
+    // once instead of one ring of stages at a time.
+    const uint32_t el = elect_one();
+    int t, split;
+    work_item(blockIdx.x, t, split);
+    const int kt0 = split * p.kt_per_split, kt1 = min(k_tiles_all, kt0 + p.kt_per_split);
+    int tm, tn;
+    tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+    const int npre = min(kt1 - kt0, 48);
+    for (int i = 0; i < npre; ++i) tma_prefetch_2d_if(el, &tma_b, (kt0 + i) * BKB, tn * BN);
+    if (SF_TILED) {
+      for (int nb = 0; nb < BN / 128; ++nb) {
+        const int64_t nt = (int64_t)tn * (BN / 128) + nb;
+        if (nt * 128 < p.rows_sfb)
+          bulk_prefetch_l2_if(el, p.sfb + (nt * p.KT + (int64_t)kt0 * K64_PER_STAGE) * 512,
+                              (uint32_t)min((int64_t)npre * K64_PER_STAGE, (int64_t)p.KT - (int64_t)kt0 * K64_PER_STAGE) * 512u);
+      }
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(smem_gen + (tmem_slot - smem_base));
-  // set-up done on this CTA's own resources only; global memory is touched from here on
+  // set-up done on this CTA's own resources only; global memory is read and written from here on
   grid_launch_dependents();
   grid_dependency_wait();
   if (threadIdx.x == 0) AC4K_TR1(3, 0, 1);
+  if (threadIdx.x == 0) AC4K_TRW(1);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      uint32_t s = 0, ph = 0;
+    const uint32_t el = elect_one();
+    uint32_t s = 0, ph = 0;
+    bool ok = true;
+    for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
+      int t, split;
+      work_item(wi, t, split);
+      const int kt0 = split * p.kt_per_split, kt1 = min(k_tiles_all, kt0 + p.kt_per_split);
+      int tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      const int m0 = tm * BM, n0 = tn * BN;
+      for (int kt = kt0; kt < kt1; ++kt) {
+        ok = warp_all(mbar_wait(empty_bar + 8 * s, ph ^ 1));
+        if (!ok) break;
+        const int nk = min(K64_PER_STAGE, p.KT - kt * K64_PER_STAGE);
+        uint32_t sf_bytes = 0;
+        if (SF_TILED) {
+          const int nb_valid = min(BN / 128, (p.rows_sfb - n0) / 128);
+          sf_bytes = (1 + nb_valid) * nk * 512;
+        }
+        const uint32_t fb = full_bar + 8 * s;
+        mbar_arrive_expect_tx_if(el, fb, C::A_BYTES + C::B_BYTES + sf_bytes);
+        tma_load_2d_if(el, sB + s * C::B_BYTES, &tma_b, kt * BKB, n0, fb);
+        tma_load_2d_if(el, sA + s * C::A_BYTES, &tma_a, kt * BKB, m0, fb);
+        if (SF_TILED) {
+          // [row tile of 128][K/64][512 B]: the nk chunks of one row tile are contiguous
+          const int64_t k64 = (int64_t)kt * K64_PER_STAGE;
+          bulk_load_1d_if(el, sSFA + s * C::SFA_BYTES, p.sfa + ((int64_t)tm * p.KT + k64) * 512, nk * 512, fb);
+          for (int nb = 0; nb < BN / 128; ++nb) {
+            const int64_t nt = n0 / 128 + nb;
+            if (nt * 128 < p.rows_sfb)
+              bulk_load_1d_if(el, sSFB + s * C::SFB_BYTES + nb * (K64_PER_STAGE * 512),
+                              p.sfb + (nt * p.KT + k64) * 512, nk * 512, fb);
+          }
+        }
+        if (++s == C::STAGES) { s = 0; ph ^= 1; }
+      }
+    }
+    if (!ok && el) atomicExch(p.status, kStatusTimeoutProducer);
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    const uint32_t el = elect_one();
+    constexpr uint32_t idesc = make_idesc_mxf4nvf4(BM, BN);
+    constexpr int NB = BN / 128;
+    uint32_t s = 0, ph = 0, acc = 0, acc_ph = 0;
+    bool ok = true;
+    int it = 0;
+    const uint64_t adesc0 = make_smem_desc(sA, 16, 1024, kSwizzle128B);
+    const uint64_t bdesc0 = make_smem_desc(sB, 16, 1024, kSwizzle128B);
+    // scale chunks: 32 rows x 16 bytes, 8-row groups 128 bytes apart, not swizzled
+    const uint64_t sfadesc0 = make_smem_desc(sSFA, 0, 128, kSwizzleNone);
+    const uint64_t sfbdesc0 = make_smem_desc(sSFB, 0, 128, kSwizzleNone);
+    const uint32_t t_sfa = tmem_base + C::SF_COL, t_sfb = t_sfa + K64_PER_STAGE * 4;
+    for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
+      int t_unused, split;
+      work_item(wi, t_unused, split);
+      const int kt0 = split * p.kt_per_split, kt1 = min(k_tiles_all, kt0 + p.kt_per_split);
+      ok = warp_all(mbar_wait(tempty_bar + 8 * acc, acc_ph ^ 1));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * BN;
+      for (int kt = kt0; kt < kt1; ++kt) {
+        if (el) AC4K_TR1(0, it, 0);
+        ok = warp_all(mbar_wait(full_bar + 8 * s, ph));
+        if (!ok) break;
+        tc_fence_after();
+        if (el) AC4K_TR1(0, it, 1);
+        if (el && it == 0) AC4K_TRW(3);
+        const int nk = min(K64_PER_STAGE, p.KT - kt * K64_PER_STAGE);
+        const uint64_t adesc = adesc0 + (uint64_t)(s * (C::A_BYTES >> 4));
+        const uint64_t bdesc = bdesc0 + (uint64_t)(s * (C::B_BYTES >> 4));
+        const uint64_t sfadesc = sfadesc0 + (uint64_t)(s * (C::SFA_BYTES >> 4));
+        const uint64_t sfbdesc = sfbdesc0 + (uint64_t)(s * (C::SFB_BYTES >> 4));
+        // The scales of the stage go to tensor memory with tcgen05.cp right in front of the MMAs that read
+        // them (same thread: executed in issue order, overlapping the MMAs).  K step j: +32 bytes inside the
+        // 128-byte swizzle atom = start-address field + 2.
+        if (nk == K64_PER_STAGE) {
+#pragma unroll
+          for (int j = 0; j < K64_PER_STAGE; ++j) {
+            tmem_cp_32x128b_warpx4_if(el, t_sfa + j * 4, sfadesc + j * 32);
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb)
+              tmem_cp_32x128b_warpx4_if(el, t_sfb + j * (BN / 32) + nb * 4, sfbdesc + (nb * K64_PER_STAGE + j) * 32);
+          }
+#pragma unroll
+          for (int j = 0; j < K64_PER_STAGE; ++j)
+            mma_mxf4nvf4_if(el, d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, t_sfa + j * 4, t_sfb + j * (BN / 32),
+                            (kt > kt0 || j > 0) ? 1u : 0u);
+        } else {
+          for (int j = 0; j < nk; ++j) {
+            tmem_cp_32x128b_warpx4_if(el, t_sfa + j * 4, sfadesc + j * 32);
+            for (int nb = 0; nb < NB; ++nb)
+              tmem_cp_32x128b_warpx4_if(el, t_sfb + j * (BN / 32) + nb * 4, sfbdesc + (nb * K64_PER_STAGE + j) * 32);
+          }
+          for (int j = 0; j < nk; ++j)
+            mma_mxf4nvf4_if(el, d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, t_sfa + j * 4, t_sfb + j * (BN / 32),
+                            (kt > kt0 || j > 0) ? 1u : 0u);
+        }
+        tc_commit_if(el, empty_bar + 8 * s);
+        if (el) AC4K_TR1(0, it, 3);
+        ++it;
+        if (++s == C::STAGES) { s = 0; ph ^= 1; }
+      }
+      if (ok) tc_commit_if(el, tfull_bar + 8 * acc);
+      if (el) AC4K_TRW(4);
+      if (++acc == C::ACC_STAGES) { acc = 0; acc_ph ^= 1; }
+    }
+    if (!ok && el) atomicExch(p.status, kStatusTimeoutMma);
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ scale warps (row layout only)
+    // Scales stored as [K/64][rows][4 bytes]: the word of row r at K step k sits at word k * rows + r.
+    // tcgen05.cp wants, per K step and 128-row block, 32 rows of 16 bytes where row l holds the words of
+    // rows l, 32 + l, 64 + l, 96 + l.  Warp w takes the stages whose running number is w - 2 modulo 4:
+    // its loads are in flight while the stages before it are consumed.
+    if (!SF_TILED) {
+      const int w4 = warp - 2;
+      constexpr int GB = BN / 32;
+      uint32_t s = 0, ph = 0, it = 0;
+      const uint32_t *sfa_w = reinterpret_cast<const uint32_t *>(p.sfa);
+      const uint32_t *sfb_w = reinterpret_cast<const uint32_t *>(p.sfb);
       bool ok = true;
       for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
         int t, split;
@@ -115,149 +257,43 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
         for (int kt = kt0; kt < kt1; ++kt) {
-          if (!mbar_wait(empty_bar + 8 * s, ph ^ 1)) { atomicExch(p.status, kStatusTimeoutProducer); ok = false; break; }
-          const int nk = min(K64_PER_STAGE, p.KT - kt * K64_PER_STAGE);
-          uint32_t sfa_bytes, sfb_bytes;
-          if (SF_TILED) {
-            sfa_bytes = nk * 512;
-            const int nb_valid = min(BN / 128, (p.rows_sfb - n0) / 128);
-            sfb_bytes = nb_valid * nk * 512;
-          } else {
-            // one box of [4 K steps][rows] words per operand; rows and K steps outside the tensor
-            // arrive as zeros and count towards the transaction bytes
-            sfa_bytes = K64_PER_STAGE * BM * 4;
-            sfb_bytes = K64_PER_STAGE * BN * 4;
-          }
-          const uint32_t fb = full_bar + 8 * s;
-          mbar_arrive_expect_tx(fb, C::A_BYTES + C::B_BYTES + sfa_bytes + sfb_bytes);
-          tma_load_2d(sA + s * C::A_BYTES, &tma_a, kt * BKB, m0, fb);
-          tma_load_2d(sB + s * C::B_BYTES, &tma_b, kt * BKB, n0, fb);
-          const int64_t k64 = (int64_t)kt * K64_PER_STAGE;
-          if (SF_TILED) {
-            // [row tile of 128][K/64][512 B]: the nk chunks of one row tile are contiguous
-            bulk_load_1d(sSFA + s * C::SFA_BYTES, p.sfa + ((int64_t)tm * p.KT + k64) * 512, nk * 512, fb);
-            for (int nb = 0; nb < BN / 128; ++nb) {
-              const int64_t nt = n0 / 128 + nb;
-              if (nt * 128 < p.rows_sfb)
-                bulk_load_1d(sSFB + s * C::SFB_BYTES + nb * (K64_PER_STAGE * 512),
-                             p.sfb + (nt * p.KT + k64) * 512, nk * 512, fb);
-            }
-          } else {
-            // [K/64][rows16] words: a box of 4 K steps x the tile's rows per operand
-            tma_load_2d(sSFA + s * C::SFA_BYTES, &tma_sfa, m0, (int)k64, fb);
-            tma_load_2d(sSFB + s * C::SFB_BYTES, &tma_sfb, n0, (int)k64, fb);
-          }
-          if (++s == C::STAGES) { s = 0; ph ^= 1; }
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_mxf4nvf4(BM, BN);
-      uint32_t s = 0, ph = 0, acc = 0, acc_ph = 0;
-      bool ok = true;
-      int it = 0;
-      const uint64_t adesc0 = make_smem_desc(sA, 16, 1024, kSwizzle128B);
-      const uint64_t bdesc0 = make_smem_desc(sB, 16, 1024, kSwizzle128B);
-      for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
-        int t_unused, split;
-        work_item(wi, t_unused, split);
-        const int kt0 = split * p.kt_per_split, kt1 = min(k_tiles_all, kt0 + p.kt_per_split);
-        if (!mbar_wait(tempty_bar + 8 * acc, acc_ph ^ 1)) { atomicExch(p.status, kStatusTimeoutMma); break; }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kt = kt0; kt < kt1; ++kt) {
-          AC4K_TR1(0, it, 0);
-          if (!mbar_wait(full_bar + 8 * s, ph)) { atomicExch(p.status, kStatusTimeoutMma); ok = false; break; }
-          AC4K_TR1(0, it, 1);
-          if (!mbar_wait(sf_bar + 8 * s, ph)) { atomicExch(p.status, kStatusTimeoutMma); ok = false; break; }
-          tc_fence_after();
-          AC4K_TR1(0, it, 2);
-          const int nk = min(K64_PER_STAGE, p.KT - kt * K64_PER_STAGE);
-          const uint32_t t_sfa = tmem_base + C::SFA_COL + s * C::SFA_COLS;
-          const uint32_t t_sfb = tmem_base + C::SFB_COL + s * C::SFB_COLS;
-          const uint64_t adesc = adesc0 + (uint64_t)(s * (C::A_BYTES >> 4));
-          const uint64_t bdesc = bdesc0 + (uint64_t)(s * (C::B_BYTES >> 4));
-          // +32 bytes of K per step inside the 128-byte swizzle atom: start-address field += 2.
-          // The full stage is unrolled: every cycle this thread spends between two issues shows up
-          // as time per stage on shapes that only stream weights.
-          if (nk == K64_PER_STAGE) {
+          static_assert(C::STAGES >= 4, "four scale warps: each may run at most one round of the ring ahead");
+          if ((int)(it & 3) == w4) {
+            uint32_t wa[K64_PER_STAGE][4], wb[K64_PER_STAGE][GB];
 #pragma unroll
-            for (int j = 0; j < K64_PER_STAGE; ++j)
-              mma_mxf4nvf4(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, t_sfa + j * 4, t_sfb + j * (BN / 32),
-                           (kt > kt0 || j > 0) ? 1u : 0u);
-          } else {
-            for (int j = 0; j < nk; ++j)
-              mma_mxf4nvf4(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, t_sfa + j * 4, t_sfb + j * (BN / 32),
-                           (kt > kt0 || j > 0) ? 1u : 0u);
+            for (int j = 0; j < K64_PER_STAGE; ++j) {
+              const int k64 = kt * K64_PER_STAGE + j;
+              const bool k_ok = k64 < p.KT;
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                const int r = m0 + 32 * g + lane;
+                wa[j][g] = (k_ok && r < p.rows_sfa) ? __ldg(sfa_w + (int64_t)k64 * p.rows_sfa + r) : 0u;
+              }
+#pragma unroll
+              for (int g = 0; g < GB; ++g) {
+                const int r = n0 + 32 * g + lane;
+                wb[j][g] = (k_ok && r < p.rows_sfb) ? __ldg(sfb_w + (int64_t)k64 * p.rows_sfb + r) : 0u;
+              }
+            }
+            ok = warp_all(mbar_wait(empty_bar + 8 * s, ph ^ 1));
+            if (!ok) break;
+#pragma unroll
+            for (int j = 0; j < K64_PER_STAGE; ++j) {
+              st_shared_v4u(sSFA + s * C::SFA_BYTES + j * 512 + lane * 16, wa[j][0], wa[j][1], wa[j][2], wa[j][3]);
+#pragma unroll
+              for (int nb = 0; nb < BN / 128; ++nb)
+                st_shared_v4u(sSFB + s * C::SFB_BYTES + (nb * K64_PER_STAGE + j) * 512 + lane * 16, wb[j][4 * nb],
+                              wb[j][4 * nb + 1], wb[j][4 * nb + 2], wb[j][4 * nb + 3]);
+            }
+            fence_proxy_async_smem();       // the tensor core reads these bytes through the async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full_bar + 8 * s);
           }
-          AC4K_TR1(0, it, 3);
-          tc_commit(empty_bar + 8 * s);
-          AC4K_TR1(0, it, 4);
           ++it;
           if (++s == C::STAGES) { s = 0; ph ^= 1; }
         }
-        if (ok) tc_commit(tfull_bar + 8 * acc);
-        if (++acc == C::ACC_STAGES) { acc = 0; acc_ph ^= 1; }
       }
-    }
-  } else if (warp < 6) {
-    // ------------------------------------------------------------------ scale warps
-    // Lane l of the warp owning TMEM lane quarter q writes, for K-step j and row group g, the
-    // 32-bit word of row 32 g + l into column (j * groups + g) of lane 32 q + l; all four
-    // quarters hold the same words.
-    const int q = warp & 3;
-    uint32_t s = 0, ph = 0;
-    bool ok = true;
-    for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
-      int t_unused, split;
-      work_item(wi, t_unused, split);
-      const int kt0 = split * p.kt_per_split, kt1 = min(k_tiles_all, kt0 + p.kt_per_split);
-      for (int kt = kt0; kt < kt1; ++kt) {
-        if (!mbar_wait(full_bar + 8 * s, ph)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutSf); ok = false; break; }
-        const uint8_t *a_src = smem_gen + (sSFA + s * C::SFA_BYTES - smem_base);
-        const uint8_t *b_src = smem_gen + (sSFB + s * C::SFB_BYTES - smem_base);
-        uint32_t ra[16];
-        uint32_t rb[C::SFB_COLS];
-        if (SF_TILED) {
-          // 512-byte tiles [32 lanes][4 groups] words: one 16-byte load per K-step
-#pragma unroll
-          for (int j = 0; j < K64_PER_STAGE; ++j) {
-            const uint4 v = *reinterpret_cast<const uint4 *>(a_src + j * 512 + lane * 16);
-            ra[j * 4 + 0] = v.x; ra[j * 4 + 1] = v.y; ra[j * 4 + 2] = v.z; ra[j * 4 + 3] = v.w;
-#pragma unroll
-            for (int nb = 0; nb < BN / 128; ++nb) {
-              const uint4 w = *reinterpret_cast<const uint4 *>(b_src + (nb * K64_PER_STAGE + j) * 512 + lane * 16);
-              rb[j * (BN / 32) + nb * 4 + 0] = w.x; rb[j * (BN / 32) + nb * 4 + 1] = w.y;
-              rb[j * (BN / 32) + nb * 4 + 2] = w.z; rb[j * (BN / 32) + nb * 4 + 3] = w.w;
-            }
-          }
-        } else {
-          // [K-step][row] words
-#pragma unroll
-          for (int j = 0; j < K64_PER_STAGE; ++j) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g)
-              ra[j * 4 + g] = reinterpret_cast<const uint32_t *>(a_src + j * 512)[g * 32 + lane];
-#pragma unroll
-            for (int g = 0; g < BN / 32; ++g)
-              rb[j * (BN / 32) + g] = reinterpret_cast<const uint32_t *>(b_src + j * (BN / 128) * 512)[g * 32 + lane];
-          }
-        }
-        const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
-        tmem_st_32x32b_x16(lane_base + C::SFA_COL + s * C::SFA_COLS, ra);
-        if constexpr (BN == 256) {
-          tmem_st_32x32b_x32(lane_base + C::SFB_COL + s * C::SFB_COLS, reinterpret_cast<uint32_t (&)[32]>(rb));
-        } else {
-          tmem_st_32x32b_x16(lane_base + C::SFB_COL + s * C::SFB_COLS, reinterpret_cast<uint32_t (&)[16]>(rb));
-        }
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(sf_bar + 8 * s);
-        if (++s == C::STAGES) { s = 0; ph ^= 1; }
-      }
+      if (!ok && lane == 0) atomicExch(p.status, kStatusTimeoutSf);
     }
   } else {
     // ------------------------------------------------------------------ epilogue
@@ -275,6 +311,7 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       if (!tfull_ok && !p.cluster_reduce) break;
       tc_fence_after();
       if (warp == 6 && lane == 0) AC4K_TR1(1, 0, 0);
+      if (warp == 6 && lane == 0) AC4K_TRW(5);
       const int row = tm * BM + q * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
       if constexpr (BN == 128) {
@@ -379,6 +416,7 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     tmem_dealloc(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0) AC4K_TR1(3, 0, 5);
+  if (threadIdx.x == 0) AC4K_TRW(2);
 }
 
 // out[m, n] = cast(alpha * sum_s ws[s, m, n] + bias[n]) for the split-K path; one thread per
@@ -494,13 +532,6 @@ int get_tmap(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUt
   return encode_cached(kTmapOperand, ptr, row_bytes, rows, row_bytes, BKB, box_rows, out);
 }
 
-// Row-layout scale factors [K/64][rows16] as 32-bit words (the four scales of a row at one K step):
-// a box of `box_rows` words x `box_ksteps` K steps lands in shared memory as [K step][row], which is
-// what the single-CTA kernel's scale warps read.  Out-of-range rows and K steps read as zero.
-int get_tmap_sf(const void *ptr, int64_t rows16, int64_t kt, int box_rows, int box_ksteps, CUtensorMap *out) {
-  return encode_cached(kTmapWords, ptr, rows16, kt, rows16, box_rows, box_ksteps, out);
-}
-
 // Tiled scale factors [row blocks of 128][K/64][512 bytes] seen as a matrix of 512-byte rows: a box of
 // `box_ksteps` rows is the scale image of that many K steps of one row block, contiguous in shared
 // memory.  Rows past the end of the tensor read as zero.
@@ -527,8 +558,7 @@ int get_device_info(DeviceInfo *out) {
 }
 
 template <int BN, bool SF_TILED, int OUT_DT>
-static int launch(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tsa, const CUtensorMap &tsb,
-                  const GemmArgs &args, int sms, cudaStream_t stream) {
+static int launch(const CUtensorMap &ta, const CUtensorMap &tb, const GemmArgs &args, int sms, cudaStream_t stream) {
   using C = Cfg<BN>;
   auto kern = linear_nvfp4_kernel<BN, SF_TILED, OUT_DT>;
   static bool attr_set[64] = {};
@@ -558,17 +588,17 @@ static int launch(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMa
     cfg.numAttrs = 2;
   }
   cfg.attrs = attr;
-  AC4K_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, tsa, tsb, args));
+  AC4K_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, args));
   return 0;
 }
 
 template <int BN, bool SF_TILED>
-static int launch_dt(int d_dtype, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tsa,
-                     const CUtensorMap &tsb, const GemmArgs &a, int sms, cudaStream_t st) {
+static int launch_dt(int d_dtype, const CUtensorMap &ta, const CUtensorMap &tb, const GemmArgs &a, int sms,
+                     cudaStream_t st) {
   switch (d_dtype) {
-    case AC4K_DT_BF16: return launch<BN, SF_TILED, AC4K_DT_BF16>(ta, tb, tsa, tsb, a, sms, st);
-    case AC4K_DT_FP16: return launch<BN, SF_TILED, AC4K_DT_FP16>(ta, tb, tsa, tsb, a, sms, st);
-    default: return launch<BN, SF_TILED, AC4K_DT_FP32>(ta, tb, tsa, tsb, a, sms, st);
+    case AC4K_DT_BF16: return launch<BN, SF_TILED, AC4K_DT_BF16>(ta, tb, a, sms, st);
+    case AC4K_DT_FP16: return launch<BN, SF_TILED, AC4K_DT_FP16>(ta, tb, a, sms, st);
+    default: return launch<BN, SF_TILED, AC4K_DT_FP32>(ta, tb, a, sms, st);
   }
 }
 
@@ -673,6 +703,39 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
     if (g_force_bn == 0 && ceil_div(M, BM) * ceil_div(N, 256) * 2 <= di.sms) bn = 128;
     pl = plan_split(M, N, K, bn, di.sms);
   }
+  // Decode shapes (a few activation rows): the kernel built around the weight stream.  K slices of a tile run
+  // as one cluster and add their partial sums through distributed shared memory: no scratch memory.
+  if (!out && M <= 64 && g_force_bn == 0) {
+    const int nt = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    const int64_t tiles_n = ceil_div(N, 128);
+    const int k_tiles = (int)ceil_div(K / 64, 4);
+    int splits = 1;
+    for (int cand = skinny_max_splits(nt); cand >= 2; --cand)      // as many slices as keep one wave of CTAs (two per SM)
+      if (tiles_n * cand <= 2 * di.sms && k_tiles / cand >= 4) { splits = cand; break; }
+    if (g_force_splits >= 1) splits = g_force_splits < skinny_max_splits(nt) ? g_force_splits : skinny_max_splits(nt);
+    if (splits > k_tiles) splits = k_tiles;
+    CUtensorMap tx, tw;
+    if (int e = get_tmap(A, M, K / 2, nt, &tx)) return e;
+    if (int e = get_tmap(B, N, K / 2, 128, &tw)) return e;
+    GemmArgs a = {};
+    a.sfa = static_cast<const uint8_t *>(A_sf);
+    a.sfb = static_cast<const uint8_t *>(B_sf);
+    a.D = D;
+    a.n_dst = 1;
+    a.ldd = N;
+    a.a_gs = A_gs; a.b_gs = B_gs;
+    a.bias = bias; a.bias_dt = bias_dtype;
+    a.status = status;
+    a.M = (int)M; a.N = (int)N; a.K = (int)K; a.KT = (int)(K / 64);
+    const int pad = sf_layout == AC4K_SF_AC4K ? 16 : 128;
+    a.rows_sfa = (int)align_up(M, pad);
+    a.rows_sfb = (int)align_up(N, pad);
+    a.tiles_m = 1;
+    a.tiles_n = (int)tiles_n;
+    a.kt_per_split = (int)ceil_div(k_tiles, splits);
+    a.splits = (int)ceil_div(k_tiles, a.kt_per_split);     // every slice has at least one stage
+    return launch_linear_skinny(d_dtype, sf_layout == AC4K_SF_TILE128X4, nt, tx, tw, a, stream);
+  }
   CUtensorMap ta, tb;
   if (int e = get_tmap(A, M, K / 2, BM, &ta)) return e;
   if (int e = get_tmap(B, N, K / 2, use_pair ? 128 : bn, &tb)) return e;
@@ -753,18 +816,13 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
       a.ws = static_cast<float *>(wsp);
     }
   }
-  CUtensorMap tsa = ta, tsb = tb;        // placeholders when the scales are tiled
-  if (!tiled) {
-    if (int e = get_tmap_sf(A_sf, a.rows_sfa, a.KT, BM, K64_PER_STAGE, &tsa)) return e;
-    if (int e = get_tmap_sf(B_sf, a.rows_sfb, a.KT, bn, K64_PER_STAGE, &tsb)) return e;
-  }
   int rc;
   if (bn == 256)
-    rc = tiled ? launch_dt<256, true>(d_dtype, ta, tb, tsa, tsb, a, di.sms, stream)
-               : launch_dt<256, false>(d_dtype, ta, tb, tsa, tsb, a, di.sms, stream);
+    rc = tiled ? launch_dt<256, true>(d_dtype, ta, tb, a, di.sms, stream)
+               : launch_dt<256, false>(d_dtype, ta, tb, a, di.sms, stream);
   else
-    rc = tiled ? launch_dt<128, true>(d_dtype, ta, tb, tsa, tsb, a, di.sms, stream)
-               : launch_dt<128, false>(d_dtype, ta, tb, tsa, tsb, a, di.sms, stream);
+    rc = tiled ? launch_dt<128, true>(d_dtype, ta, tb, a, di.sms, stream)
+               : launch_dt<128, false>(d_dtype, ta, tb, a, di.sms, stream);
   if (pl.splits > 1 && !a.cluster_reduce) {
     if (rc == 0) {
       const int64_t total4 = M * N / 4;

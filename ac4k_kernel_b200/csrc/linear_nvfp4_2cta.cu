@@ -318,6 +318,7 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
         const int m0 = tm * BMP + (int)rank * 128, n0 = tn * BN;
         for (int kt = 0; kt < k_tiles; ++kt) {
+          static_assert(STAGES >= 4, "four scale warps: each may run at most one round of the ring ahead");
           if ((int)(it & 3) == w4) {
             uint32_t wa[KS][4], wb[KS][8];
 #pragma unroll

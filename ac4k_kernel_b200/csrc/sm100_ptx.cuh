@@ -118,6 +118,11 @@ __device__ __forceinline__ void tma_prefetch_2d_if(uint32_t pred, const void *tm
                "@q cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];\n}"
                ::"l"(tmap), "r"(x), "r"(y), "r"(pred) : "memory");
 }
+// linear form of the same hint: `bytes` (multiple of 16) from a 16-byte aligned address
+__device__ __forceinline__ void bulk_prefetch_l2_if(uint32_t pred, const void *src, uint32_t bytes) {
+  asm volatile("{\n.reg .pred q;\nsetp.ne.b32 q, %2, 0;\n@q cp.async.bulk.prefetch.L2.global [%0], %1;\n}"
+               ::"l"(src), "r"(bytes), "r"(pred) : "memory");
+}
 __device__ __forceinline__ void prefetch_tmap(const void *tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
