@@ -149,7 +149,6 @@ int launch_linear_2cta(int d_dtype, bool sf_tiled, const CUtensorMap &ta, const 
                        const CUtensorMap &tsa, const CUtensorMap &tsb, const DstMaps &dm, GemmArgs args, cudaStream_t stream);
 
 // decode-shape kernel (linear_nvfp4_skinny.cu): M <= nt activation rows, nt in {16, 32, 64}
-int skinny_max_splits(int nt);
 int launch_linear_skinny(int d_dtype, bool sf_tiled, int nt, const CUtensorMap &tx, const CUtensorMap &tw, const GemmArgs &args,
                          cudaStream_t stream);
 

@@ -710,10 +710,10 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
     const int64_t tiles_n = ceil_div(N, 128);
     const int k_tiles = (int)ceil_div(K / 64, 4);
     int splits = 1;
-    for (int cand = skinny_max_splits(nt); cand >= 2; --cand)      // as many slices as keep one wave of CTAs (two per SM)
+    for (int cand = 4; cand >= 2; cand /= 2)      // 4, 2 or 1 slices: as many as keep one wave of CTAs (two per SM)
       if (tiles_n * cand <= 2 * di.sms && k_tiles / cand >= 4) { splits = cand; break; }
-    if (g_force_splits >= 1) splits = g_force_splits < skinny_max_splits(nt) ? g_force_splits : skinny_max_splits(nt);
-    if (splits > k_tiles) splits = k_tiles;
+    if (g_force_splits >= 1) splits = g_force_splits >= 4 ? 4 : (g_force_splits >= 2 ? 2 : 1);
+    while (splits > 1 && ceil_div(k_tiles, ceil_div(k_tiles, splits)) != splits) splits /= 2;   // every slice non-empty
     CUtensorMap tx, tw;
     if (int e = get_tmap(A, M, K / 2, nt, &tx)) return e;
     if (int e = get_tmap(B, N, K / 2, 128, &tw)) return e;
@@ -733,7 +733,8 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
     a.tiles_m = 1;
     a.tiles_n = (int)tiles_n;
     a.kt_per_split = (int)ceil_div(k_tiles, splits);
-    a.splits = (int)ceil_div(k_tiles, a.kt_per_split);     // every slice has at least one stage
+    a.splits = splits;
+    a.trace = g_trace;
     return launch_linear_skinny(d_dtype, sf_layout == AC4K_SF_TILE128X4, nt, tx, tw, a, stream);
   }
   CUtensorMap ta, tb;

@@ -6,13 +6,16 @@
 //   * The operands are swapped on the tensor core: 128 weight rows are the M side of the MMA, the
 //     activation rows (padded to NT = 16 / 32 / 64) the N side.  The accumulator is 128 lanes x NT columns,
 //     an activation box is NT x 128 bytes instead of 128 x 128, and a call with M = 1 costs what M = 16 costs.
-//   * One work item per CTA: a tile of 128 weight rows x one slice of K.  The `splits` slices of a tile are the
-//     CTAs of one cluster; the other slices write their fp32 partial sums into the leading CTA's shared memory
-//     (distributed shared memory) and the leader adds them in slice order.  No workspace, no second kernel.
-//   * A CTA needs < 100 KB of shared memory and 128 tensor-memory columns, so the CTAs of the next call of the
-//     stream (programmatic dependent launch) become resident while this call still runs; before they wait for
-//     it they ask L2 for their whole share of the weights (a prefetch returns no data, so the dependency is
-//     kept), and the weight stream of call i+1 runs under the tail of call i.
+//   * One work item per CTA: a tile of 128 weight rows x one slice of K.  The `splits` (1, 2 or 4) slices of a
+//     tile are the CTAs of one cluster.  The 128 rows of the tile are four quarters of 32 (one per epilogue
+//     warp); quarter q is finished by CTA q % splits: the other slices copy their fp32 partial sums of that
+//     quarter into a small region of its shared memory (one bulk copy through distributed shared memory,
+//     completing on the owner's mbarrier), it adds them in slice order, applies alpha and bias and stores.
+//     No workspace, no second kernel, no waiting for a leader.
+//   * A CTA needs 97 - 111 KB of shared memory and 128 tensor-memory columns, so two of them fit on an
+//     SM and the CTAs of the next call of the stream (programmatic dependent launch) become resident while this
+//     call still runs; before they wait for it they ask L2 for their whole share of the weights (a prefetch
+//     returns no data, so the dependency is kept), and the weight stream of call i+1 runs under the tail of call i.
 //
 // Roles (192 threads): warp 0 TMA producer, warp 1 MMA issuer (scales to tensor memory with tcgen05.cp, then
 // four MMAs per stage), warps 2-5 epilogue; for scales in the row layout [K/64][rows][4] the epilogue warps
@@ -35,35 +38,26 @@ static constexpr int SFW_COL = 64, SFX_COL = 80;
 template <int NT>
 struct Cfg {
   static constexpr int X_BYTES = NT * BKB;
-  static constexpr int STAGES = NT == 64 ? 3 : 4;      // two CTAs of this kernel fit on an SM in every configuration
+  static constexpr int STAGES = NT == 64 ? 3 : 4;       // two CTAs of this kernel fit on an SM in every configuration
   static constexpr int STAGE_BYTES = W_BYTES + X_BYTES + 2 * SF_BYTES;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
-  // partial sums of the other slices land in the leader's weight and activation buffers (contiguous):
-  // [slice - 1][NT][128] fp32
-  static constexpr int FIT = 1 + (STAGES * (W_BYTES + X_BYTES)) / (NT * 512);
-  static constexpr int MAX_SPLITS = FIT > 4 ? 4 : FIT;
+  // partial sums received from the other slices: up to 3 units of [NT][32] fp32 (4 slices: this CTA's one
+  // quarter from 3 slices; 2 slices: its two quarters from 1 slice each)
+  static constexpr int PART_UNIT = NT * 128;
+  static constexpr int PART_BYTES = 3 * PART_UNIT;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + PART_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+  static constexpr int MIN_CTAS = 2;                     // CTAs of this kernel that fit on an SM
+  static_assert(MIN_CTAS * (SMEM_BYTES + 1024) <= 228 * 1024, "shared memory per SM");
 };
 }  // namespace skinny
 
-// mbarrier operations that order data written by another CTA of the cluster
-__device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t bar_cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+__device__ __forceinline__ void st_shared_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cta.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
-__device__ __forceinline__ bool mbar_wait_acquire_cluster(uint32_t bar, uint32_t parity) {
-  const unsigned long long t0 = globaltimer();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 256; ++i) {
-      uint32_t ok;
-      asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-                   : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-      if (ok) return true;
-    }
-    if (globaltimer() - t0 > kWaitTimeoutNs) return false;
-  }
-}
-__device__ __forceinline__ void st_shared_cluster_f32(uint32_t addr, float v) {
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+// bulk copy from this CTA's shared memory into the shared memory of a CTA of the cluster, completing (bytes) on an
+// mbarrier of that CTA; 16-byte aligned addresses and size
+__device__ __forceinline__ void bulk_copy_to_cluster(uint32_t dst_cluster_addr, uint32_t src, uint32_t bytes, uint32_t bar_cluster_addr) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_cluster_addr), "r"(src), "r"(bytes), "r"(bar_cluster_addr) : "memory");
 }
 __device__ __forceinline__ float ld_shared_f32(uint32_t addr) {
   float v;
@@ -80,8 +74,54 @@ __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[NT]) 
   tmem_pin(r);
 }
 
+// The owner of a quarter of the rows: add the K slices in slice order (whichever of them this CTA computed
+// itself: `own`; the others from the partial-sum units, which skip the owner's own slice), apply alpha and
+// bias, round and store row by row.  Eight activation rows at a time so that their shared-memory loads are
+// independent of one another.
+template <int NT, int SPLITS, int OUT_DT>
+__device__ __forceinline__ void finish_rows(const uint32_t (&own)[NT], uint32_t part0, int slice, const GemmArgs &p, int n,
+                                            typename OutT<OUT_DT>::type *dst) {
+  using T = typename OutT<OUT_DT>::type;
+  constexpr int UNIT = NT * 128;
+  const float alpha = __fmul_rn(__ldg(p.a_gs), __ldg(p.b_gs));
+  const float b = p.bias != nullptr ? load_bias(p.bias, p.bias_dt, n) : 0.0f;
+#pragma unroll
+  for (int m0 = 0; m0 < NT; m0 += 8) {
+    if (m0 >= p.M) break;
+    float x[SPLITS > 1 ? SPLITS - 1 : 1][8];
+    if (SPLITS > 1) {
+#pragma unroll
+      for (int j = 0; j < SPLITS - 1; ++j)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[j][i] = ld_shared_f32(part0 + j * UNIT + (m0 + i) * 128);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int m = m0 + i;
+      float v = 0.0f;
+#pragma unroll
+      for (int sl = 0; sl < SPLITS; ++sl) {
+        float t = __uint_as_float(own[m]);
+        if (SPLITS > 1) {
+          // slice sl sits in unit sl if it comes before the owner's own slice, else in unit sl - 1
+          const float before = x[sl < SPLITS - 1 ? sl : SPLITS - 2][i], after = x[sl > 0 ? sl - 1 : 0][i];
+          t = sl == slice ? t : (sl < slice ? before : after);
+        }
+        v = sl == 0 ? t : __fadd_rn(v, t);
+      }
+      v = __fmul_rn(v, alpha);
+      if (p.bias != nullptr) v = __fadd_rn(v, b);
+      if (m < p.M) {
+        if (OUT_DT == AC4K_DT_BF16) dst[(int64_t)m * p.N] = (T)__float2bfloat16_rn(v);
+        else if (OUT_DT == AC4K_DT_FP16) dst[(int64_t)m * p.N] = (T)__float2half_rn(v);
+        else dst[(int64_t)m * p.N] = (T)v;
+      }
+    }
+  }
+}
+
 template <int NT, bool SF_TILED, int OUT_DT>
-__global__ void __launch_bounds__(skinny::kThreads, 2)
+__global__ void __launch_bounds__(skinny::kThreads, skinny::Cfg<NT>::MIN_CTAS)
 linear_nvfp4_skinny_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w,
                            const GemmArgs p) {
   using namespace skinny;
@@ -94,14 +134,22 @@ linear_nvfp4_skinny_kernel(const __grid_constant__ CUtensorMap tma_x, const __gr
   const uint32_t sX = sW + STAGES * W_BYTES;
   const uint32_t sSFW = sX + STAGES * C::X_BYTES;
   const uint32_t sSFX = sSFW + STAGES * SF_BYTES;
-  const uint32_t bars = sSFX + STAGES * SF_BYTES;
+  const uint32_t sPart = sSFX + STAGES * SF_BYTES;
+  const uint32_t bars = sPart + C::PART_BYTES;
   const uint32_t full_bar = bars, empty_bar = bars + 8 * STAGES;
   const uint32_t tfull_bar = bars + 16 * STAGES;
-  const uint32_t go_bar = tfull_bar + 8;        // other slices: the leader's MMAs are done, its weight buffers may be overwritten
-  const uint32_t part_bar = go_bar + 8;         // leader: the other slices' partial sums have landed
-  const uint32_t tmem_slot = part_bar + 8;
+  const uint32_t part_bar = tfull_bar + 8;      // [2] the other slices' partial sums of this CTA's first / second quarter have landed
+  const uint32_t tmem_slot = part_bar + 16;
   uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
+#ifdef AC4K_TRACE_ENABLED
+  // wall-clock stamps of every 4th CTA: [0] entry, [1] dependency wait passed, [2] exit, [3] first stage ready,
+  // [4] last MMA issued, [5] accumulator complete seen, [6] partial sums exchanged
+#define AC4K_TRS(ev) do { if (p.trace != nullptr && (blockIdx.x & 3) == 0 && (blockIdx.x >> 2) < 127) p.trace[((size_t)4 * 128 + (blockIdx.x >> 2)) * 8 + (ev)] = globaltimer(); } while (0)
+#else
+#define AC4K_TRS(ev) do { } while (0)
+#endif
+  if (threadIdx.x == 0) AC4K_TRS(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // work item of this CTA: the K slices of one tile are the consecutive CTAs of a cluster
   const int tn = blockIdx.x / p.splits;
@@ -116,8 +164,12 @@ linear_nvfp4_skinny_kernel(const __grid_constant__ CUtensorMap tma_x, const __gr
       mbar_init(empty_bar + 8 * s, 1);
     }
     mbar_init(tfull_bar, 1);
-    mbar_init(go_bar, 1);
-    mbar_init(part_bar, 4 * (p.splits - 1));
+    mbar_init(part_bar, 1);
+    mbar_init(part_bar + 8, 1);
+    if (p.splits > 1) {
+      // this CTA finishes 4 / splits quarters; each receives one copy of NT x 128 bytes from every other slice
+      for (int lq = 0; lq < 4 / p.splits; ++lq) mbar_arrive_expect_tx(part_bar + 8 * lq, (p.splits - 1) * C::PART_UNIT);
+    }
     fence_barrier_init();
     prefetch_tmap(&tma_x);
     prefetch_tmap(&tma_w);
@@ -142,6 +194,7 @@ linear_nvfp4_skinny_kernel(const __grid_constant__ CUtensorMap tma_x, const __gr
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(smem_gen + (tmem_slot - smem_base));
   grid_launch_dependents();
   grid_dependency_wait();
+  if (threadIdx.x == 0) AC4K_TRS(1);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -180,6 +233,7 @@ linear_nvfp4_skinny_kernel(const __grid_constant__ CUtensorMap tma_x, const __gr
       ok = warp_all(mbar_wait(full_bar + 8 * s, ph));
       if (!ok) break;
       tc_fence_after();
+      if (el && kt == kt0) AC4K_TRS(3);
       const int nk = min(KS, p.KT - kt * KS);
       const uint64_t wdesc = wdesc0 + (uint64_t)(s * (W_BYTES >> 4));
       const uint64_t xdesc = xdesc0 + (uint64_t)(s * (C::X_BYTES >> 4));
@@ -208,6 +262,7 @@ linear_nvfp4_skinny_kernel(const __grid_constant__ CUtensorMap tma_x, const __gr
       if (++s == STAGES) { s = 0; ph ^= 1; }
     }
     if (ok) tc_commit_if(el, tfull_bar);
+    if (el) AC4K_TRS(4);
     if (!ok && el) atomicExch(p.status, kStatusTimeoutMma);
   } else {
     // ------------------------------------------------------------------ scale re-ordering (row layout), then epilogue
@@ -260,45 +315,37 @@ linear_nvfp4_skinny_kernel(const __grid_constant__ CUtensorMap tma_x, const __gr
     const bool tfull_ok = mbar_wait(tfull_bar, 0);
     if (!tfull_ok && lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue);
     tc_fence_after();
+    if (warp == 2 && lane == 0) AC4K_TRS(5);
     uint32_t r[NT];
     tmem_ld_cols<NT>(tmem_base + ((uint32_t)(q * 32) << 16), r);
-    if (p.splits > 1) {
-      if (slice == 0) {
-        // the leader's MMAs are done: the other slices may write their partial sums over its operand buffers
-        if (warp == 2 && lane == 0)
-          for (int sl = 1; sl < p.splits; ++sl) mbar_arrive_cluster(map_to_cta(go_bar, sl));
-        const bool got = mbar_wait_acquire_cluster(part_bar, 0);
+    const int owner = q % p.splits;           // the slice (CTA of the cluster) that finishes this quarter of the rows
+    const int lq = q / p.splits;              // which of the owner's quarters it is
+    if (owner != slice) {
+      // This warp's partial sums go to the owner: unit [lq][source slice, skipping the owner's own][m][lane].
+      // They are laid out in this CTA's first weight buffer (free: all its MMAs are complete) and travel as one
+      // bulk copy; plain remote stores were measured at ~0.1 us per activation row.
+      const int unit = lq * (p.splits - 1) + (slice < owner ? slice : slice - 1);
+      const uint32_t scratch = sW + (uint32_t)(warp - 2) * C::PART_UNIT;
+#pragma unroll
+      for (int m = 0; m < NT; ++m) st_shared_f32(scratch + m * 128 + lane * 4, __uint_as_float(r[m]));
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0)
+        bulk_copy_to_cluster(map_to_cta(sPart + unit * C::PART_UNIT, owner), scratch, C::PART_UNIT,
+                             map_to_cta(part_bar + 8 * lq, owner));
+      if (warp == 2 && lane == 0) AC4K_TRS(6);
+    } else {
+      if (p.splits > 1) {
+        const bool got = mbar_wait(part_bar + 8 * lq, 0);
         if (!got && lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue);
-        for (int sl = 1; sl < p.splits; ++sl) {
-#pragma unroll
-          for (int m = 0; m < NT; ++m)
-            if (m < p.M)
-              r[m] = __float_as_uint(__fadd_rn(__uint_as_float(r[m]), ld_shared_f32(sW + ((sl - 1) * NT + m) * 512 + row_l * 4)));
-        }
-      } else {
-        const bool go = mbar_wait(go_bar, 0);
-        if (!go && lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue);
-        const uint32_t dst = map_to_cta(sW + (slice - 1) * NT * 512 + row_l * 4, 0);
-#pragma unroll
-        for (int m = 0; m < NT; ++m)
-          if (m < p.M) st_shared_cluster_f32(dst + m * 512, __uint_as_float(r[m]));
-        __syncwarp();
-        if (lane == 0) mbar_arrive_release_cluster(map_to_cta(part_bar, 0));
       }
-    }
-    if (slice == 0 && n < p.N && tfull_ok) {
-      const float alpha = __fmul_rn(__ldg(p.a_gs), __ldg(p.b_gs));
-      const float b = p.bias != nullptr ? load_bias(p.bias, p.bias_dt, n) : 0.0f;
-      T *dst = static_cast<T *>(p.D) + n;
-#pragma unroll
-      for (int m = 0; m < NT; ++m) {
-        if (m < p.M) {
-          float v = __fmul_rn(__uint_as_float(r[m]), alpha);
-          if (p.bias != nullptr) v = __fadd_rn(v, b);
-          if (OUT_DT == AC4K_DT_BF16) dst[(int64_t)m * p.N] = (T)__float2bfloat16_rn(v);
-          else if (OUT_DT == AC4K_DT_FP16) dst[(int64_t)m * p.N] = (T)__float2half_rn(v);
-          else dst[(int64_t)m * p.N] = (T)v;
-        }
+      if (warp == 2 && lane == 0) AC4K_TRS(6);
+      if (n < p.N && tfull_ok) {
+        const uint32_t part0 = sPart + lq * (p.splits - 1) * C::PART_UNIT + lane * 4;
+        T *dst = static_cast<T *>(p.D) + n;
+        if (p.splits == 4) finish_rows<NT, 4, OUT_DT>(r, part0, slice, p, n, dst);
+        else if (p.splits == 2) finish_rows<NT, 2, OUT_DT>(r, part0, slice, p, n, dst);
+        else finish_rows<NT, 1, OUT_DT>(r, part0, slice, p, n, dst);
       }
     }
   }
@@ -309,6 +356,12 @@ linear_nvfp4_skinny_kernel(const __grid_constant__ CUtensorMap tma_x, const __gr
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  // The bulk copies read this CTA's shared memory and complete on the owners' barriers only: every owner has
+  // seen its copies arrive before it reaches this barrier, so no CTA leaves while a copy still reads from it.
+  // (A relaxed arrive: nothing is handed over here, and the release form would also wait for this CTA's output
+  // stores - measured at 0.2 us per activation row.)
+  if (p.splits > 1) cluster_sync_relaxed();
+  if (threadIdx.x == 0) AC4K_TRS(2);
 }
 
 template <int NT, bool SF_TILED, int OUT_DT>
@@ -354,11 +407,7 @@ static int launch_skinny_dt(int d_dtype, const CUtensorMap &tx, const CUtensorMa
   }
 }
 
-int skinny_max_splits(int nt) {
-  return nt == 16 ? skinny::Cfg<16>::MAX_SPLITS : (nt == 32 ? skinny::Cfg<32>::MAX_SPLITS : skinny::Cfg<64>::MAX_SPLITS);
-}
-
-// args: M <= nt, tiles_n = ceil(N / 128), splits in 1 .. skinny_max_splits(nt), kt_per_split stages of K = 256 per slice
+// args: M <= nt, tiles_n = ceil(N / 128), splits in {1, 2, 4}, kt_per_split stages of K = 256 per slice
 int launch_linear_skinny(int d_dtype, bool sf_tiled, int nt, const CUtensorMap &tx, const CUtensorMap &tw, const GemmArgs &args,
                          cudaStream_t stream) {
   if (nt == 16)

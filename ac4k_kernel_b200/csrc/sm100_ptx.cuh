@@ -371,6 +371,11 @@ __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
 }
+// cluster barrier that only holds the CTAs back until all have arrived (no memory ordering of its own)
+__device__ __forceinline__ void cluster_sync_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+}
 // arrive on an mbarrier given by a shared::cluster address (own or peer CTA).  Default semantics
 // (release at CTA scope): the cluster-scope release form was measured at ~0.7 us per arrive,
 // and the data handed over here (tensor memory) is ordered by the tcgen05 fences instead.
