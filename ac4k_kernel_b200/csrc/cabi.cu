@@ -32,15 +32,16 @@ int cuda_fail(cudaError_t e, const char *what) {
 }
 
 unsigned int *device_status_ptr() {
-  static unsigned int *cache[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (!cache[dev]) {
+  static PerDevice<unsigned int *> cache;
+  unsigned int *ptr = nullptr;
+  const int rc = cache.get(&ptr, [](unsigned int *&v) {
     void *p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return nullptr;
-    cache[dev] = static_cast<unsigned int *>(p);
-  }
-  return cache[dev];
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_device_status);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_device_status)");
+    v = static_cast<unsigned int *>(p);
+    return 0;
+  });
+  return rc == 0 ? ptr : nullptr;
 }
 
 }  // namespace ac4k

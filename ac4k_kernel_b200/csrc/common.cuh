@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "ac4k_b200.h"
 
 namespace ac4k {
@@ -27,6 +29,31 @@ int cuda_fail(cudaError_t e, const char *what);
     cudaError_t _e = cudaGetLastError();                                        \
     if (_e != cudaSuccess) return ::ac4k::cuda_fail(_e, what);                  \
   } while (0)
+
+// A value that is computed once per CUDA device (devices 0 - 63), by whichever thread needs it first:
+// get() runs `init(value)` under std::call_once for the current device and hands the value out afterwards.
+// An init that fails is not retried; its return code is given to every later caller.
+template <typename T>
+struct PerDevice {
+  std::once_flag once[64];
+  T value[64] = {};
+  int status[64] = {};
+  template <typename F>
+  int get(T *out, F &&init) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64) return fail(AC4K_ERR_DEVICE, "device index %d out of range", dev);
+    std::call_once(once[dev], [&] { status[dev] = init(value[dev]); });
+    if (status[dev] != 0) return fail(status[dev], "per-device set-up failed earlier with code %d", status[dev]);
+    *out = value[dev];
+    return 0;
+  }
+};
+
+// SM count and compute capability of the current device (queried once per device)
+struct DeviceInfo { int sms = 0; int cc_major = 0; bool ok = false; };
+int get_device_info(DeviceInfo *out);
 
 // Address of the device status word of the current device (one per device, lives in this
 // library's module); kernels with bounded waits receive it as an argument.  NULL on error.

@@ -10,6 +10,16 @@
 namespace ac4k {
 using namespace ptx;
 
+#if defined(AC4K_TRACE_ENABLED) && !defined(AC4K_DEBUG_HOOKS)
+#define AC4K_DEBUG_HOOKS 1
+#endif
+// experiment switch `bit` of the kernel arguments / launch arguments `p`; constant 0 in the default build
+#ifdef AC4K_DEBUG_HOOKS
+#define AC4K_DBG(p, bit) ((p).dbg & (bit))
+#else
+#define AC4K_DBG(p, bit) 0
+#endif
+
 static constexpr int BM = 128;        // rows of A per tile (= TMEM lanes)
 static constexpr int BKB = 128;       // bytes of packed K per stage (= 256 elements = 4 MMA K-steps)
 static constexpr int K64_PER_STAGE = 4;
@@ -71,10 +81,8 @@ struct GemmArgs {
   int splits;           // split-K factor (1-CTA kernel only); > 1 writes fp32 partials to `ws`
   int kt_per_split;     // K stages (of 256 elements) per split
   float *ws;            // [splits, M, N] fp32 partial sums when splits > 1
-  int cluster_reduce;   // 1: the `splits` K slices of a tile run as one cluster and are added through
-                        // distributed shared memory (one work item per CTA); no workspace, no second kernel
-  int dbg;              // experiment switches, 0 in production
-  unsigned long long *trace;   // experiment: per-stage timestamps of cluster 0, NULL in production
+  int dbg;              // experiment switches (builds with -DAC4K_DEBUG_HOOKS), else 0
+  unsigned long long *trace;   // clock stamps (builds with -DAC4K_TRACE_ENABLED), else NULL
 };
 
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int &tm, int &tn) {
@@ -136,8 +144,6 @@ __device__ __forceinline__ void store_row32(void *D, int64_t off, const float (&
 
 
 // host helpers (linear_nvfp4.cu)
-struct DeviceInfo { int sms = 0; int cc_major = 0; bool ok = false; };
-int get_device_info(DeviceInfo *out);
 // 2-D byte tensor map [rows, row_bytes] with a (128 B x box_rows) box and 128-byte swizzle
 int get_tmap(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUtensorMap *out);
 // 2-CTA kernel launcher (linear_nvfp4_2cta.cu); D must be bf16/fp16 with N % 8 == 0

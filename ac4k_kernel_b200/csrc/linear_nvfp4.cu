@@ -65,11 +65,7 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int num_work = num_tiles * p.splits;
   const int k_tiles_all = (p.KT + K64_PER_STAGE - 1) / K64_PER_STAGE;
-  // with cluster_reduce the K slices of one tile are the consecutive CTAs of a cluster
-  auto work_item = [&](int wi, int &t, int &split) {
-    if (p.cluster_reduce) { t = wi / p.splits; split = wi % p.splits; }
-    else { t = wi % num_tiles; split = wi / num_tiles; }
-  };
+  auto work_item = [&](int wi, int &t, int &split) { t = wi % num_tiles; split = wi / num_tiles; };
 
   if (threadIdx.x == 0) AC4K_TR1(3, 0, 0);
 #ifdef AC4K_TRACE_ENABLED
@@ -308,67 +304,12 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
       const bool tfull_ok = mbar_wait(tfull_bar + 8 * acc, acc_ph);
       if (!tfull_ok && lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue);
-      if (!tfull_ok && !p.cluster_reduce) break;
+      if (!tfull_ok) break;
       tc_fence_after();
       if (warp == 6 && lane == 0) AC4K_TR1(1, 0, 0);
       if (warp == 6 && lane == 0) AC4K_TRW(5);
       const int row = tm * BM + q * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
-      if constexpr (BN == 128) {
-        if (p.cluster_reduce) {
-          // K slices of this tile sit in the CTAs of this cluster (slice = rank).  Every CTA reads its
-          // accumulator into registers; once all of them are past their MMAs (first cluster barrier)
-          // the operand buffers of the leader are free and the other slices write their partial sums
-          // there; after the second barrier the leader adds them in slice order - the same order of
-          // additions as the workspace path - and stores the result.
-          float v[BN];
-          if (tfull_ok) {
-#pragma unroll
-            for (int c = 0; c < BN; c += 32) {
-              uint32_t r[32];
-              tmem_ld_32x32b_x32_sync(t_row + c, r);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) v[c + i] = __uint_as_float(r[i]);
-            }
-          }
-          const int row_l = q * 32 + lane;
-          const uint32_t rank = cluster_ctarank();
-          cluster_sync();
-          if (rank != 0 && row < p.M) {
-            const uint32_t dst = map_to_cta(sA + ((rank - 1) * BM + row_l) * (BN * 4), 0);
-#pragma unroll
-            for (int c = 0; c < BN / 4; ++c)      // 16-byte pieces, rotated by the row to spread the banks
-              st_shared_cluster_v4(dst + (((c + row_l) & (BN / 4 - 1)) << 4), v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
-          }
-          cluster_sync();
-          if (rank == 0 && row < p.M && tfull_ok) {
-            for (int sl = 1; sl < p.splits; ++sl) {
-              const float4 *src = reinterpret_cast<const float4 *>(smem_gen + (sA - smem_base) + ((sl - 1) * BM + row_l) * (BN * 4));
-#pragma unroll
-              for (int c = 0; c < BN / 4; ++c) {
-                const float4 w = src[(c + row_l) & (BN / 4 - 1)];
-                v[4 * c] = __fadd_rn(v[4 * c], w.x); v[4 * c + 1] = __fadd_rn(v[4 * c + 1], w.y);
-                v[4 * c + 2] = __fadd_rn(v[4 * c + 2], w.z); v[4 * c + 3] = __fadd_rn(v[4 * c + 3], w.w);
-              }
-            }
-#pragma unroll
-            for (int c = 0; c < BN; c += 32) {
-              const int col = tn * BN + c;
-              const int ncols = min(32, p.N - col);
-              float o[32];
-#pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = __fmul_rn(v[c + i], alpha);
-              if (p.bias != nullptr) {
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                  if (i < ncols) o[i] = __fadd_rn(o[i], load_bias(p.bias, p.bias_dt, col + i));
-              }
-              if (ncols > 0) store_row32<OUT_DT>(p.D, (int64_t)row * p.N + col, o, ncols, vec_ok);
-            }
-          }
-          break;      // one work item per CTA in this mode
-        }
-      }
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
@@ -384,7 +325,7 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
             store_row32<AC4K_DT_FP32>(p.ws, ((int64_t)split * p.M + row) * p.N + col, v, ncols, p.N % 4 == 0);
           }
-        } else if (row < p.M && ncols > 0 && !(p.dbg & 8)) {
+        } else if (row < p.M && ncols > 0 && !AC4K_DBG(p, 8)) {
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __fmul_rn(__uint_as_float(r[i]), alpha);
@@ -405,10 +346,6 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   }
 
   if (threadIdx.x == 0) AC4K_TR1(3, 0, 4);
-  if (p.cluster_reduce && warp < 6) {      // the epilogue warps pass the same two barriers inside their role
-    cluster_sync();
-    cluster_sync();
-  }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -544,49 +481,41 @@ int get_tmap_out16(const void *ptr, int64_t rows, int64_t cols, int64_t ld, CUte
 }
 
 int get_device_info(DeviceInfo *out) {
-  static DeviceInfo info[64];
-  int dev = 0;
-  AC4K_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return fail(AC4K_ERR_DEVICE, "device index %d out of range", dev);
-  if (!info[dev].ok) {
-    AC4K_CUDA_TRY(cudaDeviceGetAttribute(&info[dev].sms, cudaDevAttrMultiProcessorCount, dev));
-    AC4K_CUDA_TRY(cudaDeviceGetAttribute(&info[dev].cc_major, cudaDevAttrComputeCapabilityMajor, dev));
-    info[dev].ok = true;
-  }
-  *out = info[dev];
-  return 0;
+  static PerDevice<DeviceInfo> info;
+  return info.get(out, [](DeviceInfo &v) {
+    int dev = 0;
+    AC4K_CUDA_TRY(cudaGetDevice(&dev));
+    AC4K_CUDA_TRY(cudaDeviceGetAttribute(&v.sms, cudaDevAttrMultiProcessorCount, dev));
+    AC4K_CUDA_TRY(cudaDeviceGetAttribute(&v.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+    v.ok = true;
+    return 0;
+  });
 }
 
 template <int BN, bool SF_TILED, int OUT_DT>
 static int launch(const CUtensorMap &ta, const CUtensorMap &tb, const GemmArgs &args, int sms, cudaStream_t stream) {
   using C = Cfg<BN>;
   auto kern = linear_nvfp4_kernel<BN, SF_TILED, OUT_DT>;
-  static bool attr_set[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!attr_set[dev]) {
-    AC4K_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-    attr_set[dev] = true;
-  }
+  static PerDevice<int> attr_set;
+  int unused = 0;
+  if (int e = attr_set.get(&unused, [&](int &v) {
+        AC4K_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        v = 1;
+        return 0;
+      }))
+    return e;
   const int num_work = args.tiles_m * args.tiles_n * args.splits;
   const int grid = num_work < sms ? num_work : sms;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(args.cluster_reduce ? num_work : grid);
+  cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kNumThreads);
   cfg.dynamicSmemBytes = C::SMEM_BYTES;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
+  cudaLaunchAttribute attr[1];
   // set-up may overlap the previous kernel's tail (see grid_dependency_wait)
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = (args.dbg & 64) ? 0 : 1;
+  attr[0].val.programmaticStreamSerializationAllowed = AC4K_DBG(args, 64) ? 0 : 1;
   cfg.numAttrs = 1;
-  if (args.cluster_reduce) {
-    attr[1].id = cudaLaunchAttributeClusterDimension;
-    attr[1].val.clusterDim.x = args.splits;
-    attr[1].val.clusterDim.y = 1;
-    attr[1].val.clusterDim.z = 1;
-    cfg.numAttrs = 2;
-  }
   cfg.attrs = attr;
   AC4K_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, args));
   return 0;
@@ -606,26 +535,34 @@ static int launch_dt(int d_dtype, const CUtensorMap &ta, const CUtensorMap &tb, 
 
 using namespace ac4k;
 
-// Measurement switches (process-wide, not part of the C ABI header, all 0 in production).  They let
-// one build time a kernel choice against its alternative:
+// Measurement switches.  They exist only in builds with -DAC4K_DEBUG_HOOKS (the trace build implies it); the
+// library built by default neither exports these symbols nor contains the branches they steer.  They are
+// process-wide and unsynchronised: for benchmarks and experiments, never for production use.
 //   ac4k_debug_set_tile_n(bn)   0 automatic; 128 / 256 force the single-CTA kernel with that tile
 //                               width; 512 forces the CTA-pair kernel
 //   ac4k_debug_set_splits(n)    0 automatic; 1 never cut K into slices; n > 1 force n slices
-//   ac4k_debug_set_flags(bits)  8 skip the epilogue's stores; 32 add K slices through the workspace
-//                               and the reduction kernel instead of inside a cluster; 64 launch without
-//                               the programmatic-stream-serialization attribute
+//   ac4k_debug_set_flags(bits)  8 skip the epilogue's stores; 64 launch without the
+//                               programmatic-stream-serialization attribute; 128 no L2 prefetch before the
+//                               dependency wait (pair kernel)
 //   ac4k_debug_set_trace(ptr)   device buffer for the clock stamps of builds with -DAC4K_TRACE_ENABLED
+#ifdef AC4K_DEBUG_HOOKS
 static int g_force_bn = 0;
-static int g_force_splits = 0;   // 0 = automatic, 1 = never split, n > 1 = force n K slices
-extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_splits(int n) { g_force_splits = n; }
+static int g_force_splits = 0;
 static int g_dbg = 0;
 static unsigned long long *g_trace = nullptr;
+extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_splits(int n) { g_force_splits = n; }
 extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_trace(void *p) { g_trace = static_cast<unsigned long long *>(p); }
 extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_flags(int f) { g_dbg = f; }
 extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_tile_n(int bn) { g_force_bn = bn; }
+#else
+static constexpr int g_force_bn = 0, g_force_splits = 0, g_dbg = 0;
+static constexpr unsigned long long *g_trace = nullptr;
+#endif
 
-// Split-K plan for shapes with too few output tiles to occupy the GPU (decode: M <= 128): how many
-// K slices, and the fp32 workspace [splits, M, N] they need.  splits == 1 means no workspace.
+// Split-K plan of the single-CTA kernel for shapes with too few output tiles to occupy the GPU (65 <= M <= 128,
+// or any M with an output the other kernels do not store): how many K slices, and the fp32 workspace
+// [splits, M, N] they need.  splits == 1 means no workspace.  (M <= 64 takes the decode-shape kernel, whose
+// slices are added inside a cluster.)
 struct SplitPlan { int splits; int kt_per_split; size_t ws_bytes; };
 
 static SplitPlan plan_split(int64_t M, int64_t N, int64_t K, int bn, int sms) {
@@ -777,16 +714,7 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
   a.splits = pl.splits;
   a.kt_per_split = pl.kt_per_split;
   a.ws = nullptr;
-  // Two K slices run as a cluster with an in-kernel reduction: every work item needs its own CTA and
-  // the other slice's partial sums ([128 rows, 128] fp32) must fit the leader's operand buffers.  More
-  // slices go through the workspace: one leader adding three or more partial tiles was measured slower
-  // than the reduction kernel (64 x 4096 x 4096 with 4 slices: 12.6 against 9.5 us)
-  a.cluster_reduce = 0;
-  if (!use_pair && pl.splits == 2 && bn == 128 && M <= BM && !(g_dbg & 32) &&
-      ceil_div(N, bn) * pl.splits <= di.sms &&
-      (size_t)(pl.splits - 1) * BM * 128 * 4 <= (size_t)Cfg<128>::STAGES * (Cfg<128>::A_BYTES + Cfg<128>::B_BYTES))
-    a.cluster_reduce = 1;
-  if (!use_pair && pl.splits > 1 && !a.cluster_reduce && ws_mode == 1 && pl.ws_bytes > ws_capacity)
+  if (!use_pair && pl.splits > 1 && ws_mode == 1 && pl.ws_bytes > ws_capacity)
     return fail(AC4K_ERR_SHAPE, "split-K workspace of %zu bytes exceeds the fixed scratch of %zu bytes",
                 pl.ws_bytes, ws_capacity);
   const bool tiled = sf_layout == AC4K_SF_TILE128X4;
@@ -808,7 +736,7 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
     }
     return launch_linear_2cta(d_dtype, tiled, ta, tb, tsa, tsb, dm, a, stream);
   }
-  if (pl.splits > 1 && !a.cluster_reduce) {
+  if (pl.splits > 1) {
     if (ws_mode == 1) {
       if (int e = ws_fixed(&a.ws)) return e;
     } else {
@@ -824,7 +752,7 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
   else
     rc = tiled ? launch_dt<128, true>(d_dtype, ta, tb, a, di.sms, stream)
                : launch_dt<128, false>(d_dtype, ta, tb, a, di.sms, stream);
-  if (pl.splits > 1 && !a.cluster_reduce) {
+  if (pl.splits > 1) {
     if (rc == 0) {
       const int64_t total4 = M * N / 4;
       const unsigned blocks = (unsigned)ceil_div(total4, 256);
@@ -872,18 +800,14 @@ static __device__ __align__(256) unsigned char g_fixed_scratch[kFixedScratchByte
 // In host code `g_fixed_scratch` is only a handle for the symbol, not a device address: the address
 // is looked up once per device, with that device current, and then handed to the kernels.
 static int fixed_scratch_ptr(float **out) {
-  static float *scratch[64] = {};
-  int dev = 0;
-  AC4K_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return fail(AC4K_ERR_DEVICE, "device index %d out of range", dev);
-  if (scratch[dev] == nullptr) {
+  static PerDevice<float *> scratch;
+  return scratch.get(out, [](float *&v) {
     void *ptr = nullptr;
-    cudaError_t e = cudaGetSymbolAddress(&ptr, g_fixed_scratch);
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_fixed_scratch);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_fixed_scratch)");
-    scratch[dev] = static_cast<float *>(ptr);
-  }
-  *out = scratch[dev];
-  return 0;
+    v = static_cast<float *>(ptr);
+    return 0;
+  });
 }
 
 extern "C" int ac4k_linear_nvfp4_noalloc(void *D, int d_dtype, const void *A, const void *A_sf,

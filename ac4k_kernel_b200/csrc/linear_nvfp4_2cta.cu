@@ -183,7 +183,7 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   // Everything above touched only this CTA's own resources, so it may overlap the tail of the kernel
   // before this one in the stream; from here on global memory is read and written.
   grid_launch_dependents();
-  if (warp == 2 && cluster_id < num_tiles && !(p.dbg & 128)) {
+  if (warp == 2 && cluster_id < num_tiles && !AC4K_DBG(p, 128)) {
     // While the kernel before this one may still be running: ask L2 for the operands of this CTA's first
     // stages.  A prefetch returns no data, so the dependency wait below still orders every real read.
     const uint32_t el = elect_one();
@@ -464,7 +464,6 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       if (warp == 6 && lane == 0) AC4K_TR(1, ti, 1);
       if (lane == 0) mbar_arrive_cluster(leader_tempty + 8 * acc);
       const int64_t col_base = p.col_off + col0;
-      const bool last_tile = t + num_clusters >= num_tiles;
       if (EPI == EPI_REQUANT) {
         // w[] holds this row's 128 outputs as packed bf16 - the quantiser's input format.  Quantise
         // them here (8 blocks of 16 along N, which is the next layer's K) instead of storing them.
@@ -506,7 +505,7 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
             *sfp = sfw[h2];
           }
         }
-      } else if (!(p.dbg & 8)) {
+      } else if (!AC4K_DBG(p, 8)) {
         // The registers hold one row per lane; stored from there, every instruction would touch 32
         // different rows, and that scatter was measured to slow the next tile's main loop down by
         // 20 % while it lasted.  So each half (64 columns = 128 bytes per row) goes through this warp's
@@ -520,12 +519,6 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         for (int h2 = 0; h2 < 2; ++h2) {
           const int x0 = (int)col_base + 64 * h2;
           if (col0 + 64 * h2 >= p.N || y0 >= p.M) break;     // warp-uniform: nothing of this box is inside the output
-#ifdef AC4K_TRACE_ENABLED
-          if (!last_tile && (p.dbg >> 8)) {                   // experiment: spread the 16 stores of a tile over time
-            const unsigned d = (unsigned)(p.dbg >> 8) * (unsigned)((h2 == 0 ? 0 : 8) + half * 4 + q) - (h2 == 0 ? 0u : (unsigned)(p.dbg >> 8) * (unsigned)(half * 4 + q));
-            if (d) __nanosleep(d);
-          }
-#endif
           if (lane == 0) bulk_wait_group_read0();            // the previous store has read the buffer
           __syncwarp();
 #pragma unroll
@@ -535,11 +528,6 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-#ifdef AC4K_TRACE_ENABLED
-            if (p.dbg & 16) tma_store_2d(&dmaps.m[0], 64 * h2 + half * 128, (int)rank * 128 + q * 32, stage_buf);   // experiment: every tile to one L2-resident corner
-            else if (p.dbg & 32) tma_store_2d_hint(&dmaps.m[0], x0, y0, stage_buf, make_policy_evict_first());
-            else
-#endif
             tma_store_2d(&dmaps.m[0], x0, y0, stage_buf);
             if (EPI == EPI_GATHER) {
               // peers in turn, starting behind this rank, so that the ranks do not all write to the same GPU at once
@@ -559,7 +547,7 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   if (threadIdx.x == 0) AC4K_TR(3, 0, 4);
   tc_fence_before();
   __syncthreads();
-  cluster_sync();          // neither CTA leaves while the other may still read its memory or barriers
+  cluster_sync_relaxed();  // neither CTA leaves while the other may still read its memory or barriers (nothing is handed over)
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, kTmemCols);
@@ -575,35 +563,33 @@ template <bool SF_TILED, int OUT_DT, int EPI>
 static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tsa, const CUtensorMap &tsb,
                        const DstMaps &dm, const GemmArgs &args, int sms, cudaStream_t stream) {
   auto kern = linear_nvfp4_2cta_kernel<SF_TILED, OUT_DT, EPI>;
-  static bool attr_set[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!attr_set[dev]) {
-    AC4K_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES));
-    attr_set[dev] = true;
-  }
-  // how many CTA pairs can be resident at once (not every SM can be paired on every part); the
-  // kernel is persistent, so launching more clusters than that would serialise whole waves
-  static int max_clusters[64] = {};
-  if (max_clusters[dev] == 0) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(sms & ~1);
-    cfg.blockDim = dim3(pair::kThreadsPair);
-    cfg.dynamicSmemBytes = pair::SMEM_BYTES;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    int n = 0;
-    AC4K_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
-    if (n < 1) return fail(AC4K_ERR_DEVICE, "no CTA pair of the GEMM kernel fits on this device");
-    max_clusters[dev] = n;
-  }
+  // Once per device: the shared-memory attribute, and how many CTA pairs can be resident at once (not every
+  // SM can be paired on every part); the kernel is persistent, so launching more clusters than that would
+  // serialise whole waves.
+  static PerDevice<int> max_clusters;
+  int clusters = 0;
+  if (int e = max_clusters.get(&clusters, [&](int &v) {
+        AC4K_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES));
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(sms & ~1);
+        cfg.blockDim = dim3(pair::kThreadsPair);
+        cfg.dynamicSmemBytes = pair::SMEM_BYTES;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        AC4K_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+        if (n < 1) return fail(AC4K_ERR_DEVICE, "no CTA pair of the GEMM kernel fits on this device");
+        v = n;
+        return 0;
+      }))
+    return e;
   const int num_tiles = args.tiles_m * args.tiles_n;
-  int clusters = max_clusters[dev];
+
   if (num_tiles < clusters) clusters = num_tiles;
   // launched so that its set-up may overlap the previous kernel's tail (see grid_dependency_wait)
   cudaLaunchConfig_t cfg = {};
@@ -613,7 +599,7 @@ static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUten
   cfg.stream = stream;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr.val.programmaticStreamSerializationAllowed = (args.dbg & 64) ? 0 : 1;
+  attr.val.programmaticStreamSerializationAllowed = AC4K_DBG(args, 64) ? 0 : 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
   AC4K_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, tsa, tsb, dm, args));

@@ -21,8 +21,6 @@
 // four MMAs per stage), warps 2-5 epilogue; for scales in the row layout [K/64][rows][4] the epilogue warps
 // also re-order each stage's scale words into the 32 x 16-byte chunks tcgen05.cp wants (every fourth stage
 // each).  Issuing roles run warp-wide with an elected lane (see elect_one()).
-#include <mutex>
-
 #include "gemm_common.cuh"
 
 namespace ac4k {
@@ -368,15 +366,14 @@ template <int NT, bool SF_TILED, int OUT_DT>
 static int launch_skinny(const CUtensorMap &tx, const CUtensorMap &tw, const GemmArgs &args, cudaStream_t stream) {
   using C = skinny::Cfg<NT>;
   auto kern = linear_nvfp4_skinny_kernel<NT, SF_TILED, OUT_DT>;
-  static std::once_flag once[64];
-  static cudaError_t attr_err[64];
-  int dev = 0;
-  AC4K_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return fail(AC4K_ERR_DEVICE, "device index %d out of range", dev);
-  std::call_once(once[dev], [&] {
-    attr_err[dev] = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-  });
-  if (attr_err[dev] != cudaSuccess) return cuda_fail(attr_err[dev], "cudaFuncSetAttribute(skinny GEMM)");
+  static PerDevice<int> attr_set;
+  int unused = 0;
+  if (int e = attr_set.get(&unused, [&](int &v) {
+        AC4K_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        v = 1;
+        return 0;
+      }))
+    return e;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(args.tiles_n * args.splits);
   cfg.blockDim = dim3(skinny::kThreads);

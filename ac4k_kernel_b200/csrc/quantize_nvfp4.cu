@@ -304,8 +304,10 @@ extern "C" int ac4k_global_scale_bf16(const void *x, int64_t numel, float max_sc
   AC4K_CUDA_TRY(cudaMemsetAsync(g_out, 0, sizeof(float), stream));
   if (numel == 0) return 0;
   const int threads = 512;
+  DeviceInfo di;
+  if (int e = get_device_info(&di)) return e;
   int64_t blocks = ceil_div(ceil_div(numel, 8), (int64_t)threads * 4);
-  if (blocks > 148 * 4) blocks = 148 * 4;
+  if (blocks > (int64_t)di.sms * 4) blocks = (int64_t)di.sms * 4;     // four resident CTAs of 512 threads per SM
   if (blocks < 1) blocks = 1;
   global_scale_kernel<<<(unsigned)blocks, threads, 0, stream>>>(static_cast<const uint16_t *>(x), numel,
                                                                max_scale, g_out);

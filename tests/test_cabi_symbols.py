@@ -25,6 +25,18 @@ def test_header_symbols_exported():
     assert set(_lib.SIGNATURES) == set(syms)
 
 
+def test_no_measurement_switches_in_the_default_build():
+    """The experiment switches (`ac4k_debug_set_*`) exist only in builds with -DAC4K_DEBUG_HOOKS; the library
+    that ships must not export them."""
+    import subprocess
+    from ac4k_kernel_b200 import _lib
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for name in ("ac4k_debug_set_flags", "ac4k_debug_set_splits", "ac4k_debug_set_tile_n", "ac4k_debug_set_trace"):
+        assert not hasattr(lib, name), f"{name} is exported by the default build"
+    exported = subprocess.run(["nm", "-D", "--defined-only", _lib.LIB_PATH], capture_output=True, text=True).stdout
+    assert "ac4k_debug" not in exported
+
+
 def test_module_mirrors_reference_names():
     import ac4k_kernel_b200 as pkg
     from ac4k_kernel_b200 import _cuda_ops
