@@ -131,24 +131,35 @@ class PeerOutput:
     per rank, every copy mapped into every rank's process so that a GEMM epilogue can store its
     tiles to all of them over NVLink.
 
+    `nbuf` copies are kept per rank (default 2) and used in turn, one per step.  With a single copy a
+    rank that is ahead could start storing step i+1 into a peer's buffer while that peer's kernels still
+    read step i from it: the one-element all-reduce that closes a step orders every rank's reads of step
+    i after every rank's stores of step i, but nothing orders the stores of step i+1 after those reads.
+    With two copies, step i+2 reuses the buffer of step i, and a rank can only reach step i+2 after the
+    all-reduce of step i+1, which every rank enqueues behind its own readers of step i.
+
     The memory comes from the library's `ac4k_peer_alloc` (plain cudaMalloc + CUDA IPC handle); the
-    handles travel through `all_gather_object` of the process group.  `tensor` is this rank's copy
-    as a torch tensor; `ptrs[i]` is the device address, in this process, of rank i's copy.
-    Call `close()` (collective) before the process group is destroyed.
+    handles travel through `all_gather_object` of the process group.  `tensor` is this rank's copy of
+    the step last computed, as a torch tensor; `ptrs[i]` is the device address, in this process, of rank
+    i's first copy.  Call `close()` (collective) before the process group is destroyed.
     """
 
-    def __init__(self, m: int, n: int, dtype=torch.bfloat16, group=None):
+    def __init__(self, m: int, n: int, dtype=torch.bfloat16, group=None, nbuf: int = 2):
         import ctypes
         from ._lib import LIB, check
         if not dist.is_initialized():
             raise RuntimeError("PeerOutput needs an initialised process group")
+        if nbuf < 1:
+            raise ValueError("nbuf must be at least 1")
         self.group = group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
-        self.m, self.n, self.dtype = m, n, dtype
-        nbytes = m * n * torch.empty((), dtype=dtype).element_size()
+        self.m, self.n, self.dtype, self.nbuf = m, n, dtype, nbuf
+        self.buf_bytes = m * n * torch.empty((), dtype=dtype).element_size()
+        self.buf_bytes = -(-self.buf_bytes // 256) * 256
+        self.step = 0
         ptr = ctypes.c_void_p()
         handle = ctypes.create_string_buffer(64)
-        check(LIB.ac4k_peer_alloc(nbytes, ctypes.byref(ptr), handle), "ac4k_peer_alloc")
+        check(LIB.ac4k_peer_alloc(self.buf_bytes * nbuf, ctypes.byref(ptr), handle), "ac4k_peer_alloc")
         self._own = ptr.value
         handles = [None] * self.world
         dist.all_gather_object(handles, handle.raw, group=group)
@@ -160,19 +171,27 @@ class PeerOutput:
             q = ctypes.c_void_p()
             check(LIB.ac4k_peer_open(h, ctypes.byref(q)), f"ac4k_peer_open(rank {r})")
             self.ptrs.append(q.value)
-        # this rank's copy as a tensor (CUDA array interface: no copy, this object keeps it alive)
+        # this rank's copies as tensors (CUDA array interface: no copy, this object keeps them alive)
         typestr = {torch.bfloat16: "<i2", torch.float16: "<f2"}[dtype]
-        holder = type("_Mem", (), {})()
-        holder.__cuda_array_interface__ = {"shape": (m, n), "typestr": typestr, "data": (self._own, False),
-                                           "version": 3, "strides": None}
-        t = torch.as_tensor(holder, device=torch.device("cuda", torch.cuda.current_device()))
-        self.tensor = t.view(dtype) if t.dtype != dtype else t
-        self._holder = holder
+        self._holders, self.tensors = [], []
+        for b in range(nbuf):
+            holder = type("_Mem", (), {})()
+            holder.__cuda_array_interface__ = {"shape": (m, n), "typestr": typestr,
+                                               "data": (self._own + b * self.buf_bytes, False),
+                                               "version": 3, "strides": None}
+            t = torch.as_tensor(holder, device=torch.device("cuda", torch.cuda.current_device()))
+            self.tensors.append(t.view(dtype) if t.dtype != dtype else t)
+            self._holders.append(holder)
 
-    def destinations(self):
-        """Device addresses ordered for this rank: own copy first, then the peers starting with the
-        next rank, so that at any moment different ranks are storing to different peers."""
-        return [self.ptrs[(self.rank + i) % self.world] for i in range(self.world)]
+    @property
+    def tensor(self):
+        """This rank's copy of the step computed last (the first copy before any step)."""
+        return self.tensors[(self.step - 1) % self.nbuf if self.step else 0]
+
+    def destinations(self, buf: int = 0):
+        """Device addresses of copy `buf`, ordered for this rank: own copy first, then the peers starting
+        with the next rank, so that at any moment different ranks are storing to different peers."""
+        return [self.ptrs[(self.rank + i) % self.world] + buf * self.buf_bytes for i in range(self.world)]
 
     def close(self):
         from ._lib import LIB, check
@@ -183,7 +202,7 @@ class PeerOutput:
                 check(LIB.ac4k_peer_close(p), "ac4k_peer_close")
         self.ptrs = []
         dist.barrier(group=self.group)              # every mapping is closed before the owners free
-        self.tensor = None
+        self.tensors = []
         if self._own is not None:
             check(LIB.ac4k_peer_free(self._own), "ac4k_peer_free")
             self._own = None
@@ -192,15 +211,20 @@ class PeerOutput:
 def column_parallel_linear_fused(x, x_scale, x_global_scale, w_shard, w_shard_scale, w_global_scale,
                                  peer_out: PeerOutput, bias_shard=None, sync: torch.Tensor | None = None):
     """Column-parallel step with the all-gather fused into the GEMM epilogue: this rank's kernel
-    stores each finished tile of its [M, N/w] columns into every rank's [M, N] buffer.  A one-element
-    all-reduce on the same stream then orders every rank's reads after every rank's stores.
-    Returns this rank's full [M, N] output (valid on the current stream after the call)."""
+    stores each finished tile of its [M, N/w] columns into every rank's [M, N] buffer (TMA stores; the
+    peers' buffers are reached over NVLink).  A one-element all-reduce on the same stream then orders
+    every rank's reads after every rank's stores.  Consecutive steps use the copies of `peer_out` in
+    turn (see PeerOutput).  Returns this rank's full [M, N] output of this step, valid on the current
+    stream after the call and until `nbuf` further steps have been issued."""
     from . import _cuda_ops
     lo, _ = shard_bounds(peer_out.n, peer_out.rank, peer_out.world, align=8)
-    _cuda_ops.linear_nvfp4_gather(peer_out.destinations(), peer_out.n, lo, peer_out.tensor, x, x_scale,
+    buf = peer_out.step % peer_out.nbuf
+    out = peer_out.tensors[buf]
+    _cuda_ops.linear_nvfp4_gather(peer_out.destinations(buf), peer_out.n, lo, out, x, x_scale,
                                   x_global_scale, w_shard, w_shard_scale, w_global_scale, bias_shard)
+    peer_out.step += 1
     if peer_out.world > 1:
         if sync is None:
             sync = torch.zeros(1, dtype=torch.float32, device=x.device)
         dist.all_reduce(sync, group=peer_out.group)
-    return peer_out.tensor
+    return out

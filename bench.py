@@ -156,7 +156,37 @@ def time_graph(fn_step, n_sets, steps, warmup, barrier=None):
     e1.record()
     torch.cuda.synchronize()
     t1 = time.perf_counter()
+    time_graph.last_graph = graph
     return e0.elapsed_time(e1) * 1e-3, t0, t1
+
+
+def sustained_run(graph, steps_per_replay, flops_per_step, device_index, seconds=2.5):
+    """Replay `graph` back to back for `seconds`, CUDA events around the whole run, NVML clock samples
+    inside it: what the kernel does once the power cap has set the clock."""
+    torch.cuda.synchronize()
+    one = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    one[0].record()
+    graph.replay()
+    one[1].record()
+    torch.cuda.synchronize()
+    replays = max(10, int(seconds / max(one[0].elapsed_time(one[1]) * 1e-3, 1e-6)))
+    with ClockSampler(device_index) as clk:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(replays):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+    secs = e0.elapsed_time(e1) * 1e-3
+    c = clk.summary(t0, t1)
+    tflops = flops_per_step * steps_per_replay * replays / secs / 1e12
+    ghz = (c["sm_mhz"] or 0) / 1e3
+    return {"value": tflops, "unit": "TFLOP/s", "seconds": secs, "launches": steps_per_replay * replays,
+            "us_per_step": secs / (steps_per_replay * replays) * 1e6, "clock_samples": c["samples"],
+            "sm_mhz_median": c["sm_mhz"], "sm_max_mhz": c["sm_max_mhz"], "reasons": c["reasons"],
+            "tflops_per_ghz": tflops / ghz if ghz else None}
 
 
 def time_eager(fn, reps, warmup=3):
@@ -176,8 +206,8 @@ def time_eager(fn, reps, warmup=3):
 # CPU emulation (the reference's CPU-runnable form of the path)
 # ------------------------------------------------------------------------------------------
 def cpu_emulation_c2(budget_s=15.0, reps=None):
-    """dequantise -> fp32 matmul -> bf16 on a row sample of the 4096^3 workload, all host threads.
-    Returns (TFLOP/s, cores, sample description, seconds per rep, reps)."""
+    """dequantise -> fp32 matmul -> bf16 on the whole 4096^3 workload, all host threads, as many repetitions
+    as fit the budget.  Returns (TFLOP/s, cores, sample description, seconds per rep, reps)."""
     from oracle import emulation as emu
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
@@ -185,7 +215,7 @@ def cpu_emulation_c2(budget_s=15.0, reps=None):
     g = torch.Generator().manual_seed(0)
     w = (torch.randn((n, k), generator=g) * 0.02).bfloat16()
     w4, wsf, wg = emu.quantize_nvfp4_ref(w)
-    rows = 256
+    rows = 4096
     a = torch.randn((rows, k), generator=g).bfloat16()
     a4, asf, ag = emu.quantize_nvfp4_ref(a)
     t = time.perf_counter()
@@ -198,51 +228,78 @@ def cpu_emulation_c2(budget_s=15.0, reps=None):
         emu.linear_nvfp4_ref(a4, asf, ag, w4, wsf, wg)
     dt = (time.perf_counter() - t) / reps
     tflops = 2.0 * rows * n * k / dt / 1e12
-    sample = f"{rows} of 4096 activation rows x full 4096x4096 weight, dequantise + fp32 matmul + cast, {reps} reps"
+    sample = f"the whole 4096^3 configuration, dequantise + fp32 matmul + cast, {reps} repetitions"
     return tflops, cores, sample, dt, reps
 
 
+C2_WORKLOAD = ("single-GPU square NVFP4 GEMM M=N=K=4096, activations N(0,1) + 0.5% x30 outliers, "
+               "weights N(0,0.02), 128x4 scale tiles, bf16 out, alpha = gA*gB")
+
+
+def c5_workload(world):
+    return (f"column-parallel NVFP4 GEMM M=8192 K=8192 N=28672 over {world} GPUs "
+            f"(N/{world} = {28672 // world} columns per rank) + all-gather of the bf16 output "
+            "(fused into the GEMM epilogue: TMA stores to every rank's buffer over NVLink)")
+
+
 def run_reference(args):
+    """The reference's CPU-runnable form of the path (its tests' torch emulation: dequantise -> fp32 matmul ->
+    cast, restated in oracle/emulation.py) on the host cores.  N = 1: the whole 4096^3 configuration, every
+    step.  N > 1: the column-parallel configuration is 28 times larger (3.85 TFLOP per step, about 10 s per
+    step on 16 cores), so a step is a sample: 512 of the 8192 activation rows against 4096 of the 28672 weight
+    rows, K in full, with the weight dequantised once outside the timed loop as a serving stack would."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     steps = max(1, args.steps)
+    warmup = max(args.warmup, 3)
     from oracle import emulation as emu
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    if args.gpus > 1:
-        # the N > 1 line of the other arm is the column-parallel config (M = K = 8192, N = 28672)
-        n, k, rows = 4096, 8192, 256
-        workload = (f"column-parallel NVFP4 GEMM M=8192 K=8192 N=28672 over {args.gpus} GPUs "
-                    "(row and column sample on CPU)")
-        what = f"{rows} of 8192 activation rows x {n} of 28672 weight rows (K = 8192 in full)"
-        scaling = "strong"
-    else:
-        n, k, rows = 4096, 4096, 256
-        workload = "single-GPU square NVFP4 GEMM M=N=K=4096 (row sample on CPU)"
-        what = f"{rows} of 4096 activation rows x full 4096x4096 weight"
-        scaling = "weak"
     g = torch.Generator().manual_seed(0)
-    w = (torch.randn((n, k), generator=g) * 0.02).bfloat16()
-    w4, wsf, wg = emu.quantize_nvfp4_ref(w)
-    a = torch.randn((rows, k), generator=g).bfloat16()
-    a4, asf, ag = emu.quantize_nvfp4_ref(a)
-    for _ in range(min(args.warmup, 2)):
-        emu.linear_nvfp4_ref(a4, asf, ag, w4, wsf, wg)
+    if args.gpus > 1:
+        n, k, rows = 4096, 8192, 512
+        workload = c5_workload(args.gpus)
+        what = (f"{rows} of 8192 activation rows x {n} of 28672 weight rows (K = 8192 in full), weight dequantised "
+                "outside the timed loop")
+        scaling = "strong"
+        w = (torch.randn((n, k), generator=g) * 0.02).bfloat16()
+        w4, wsf, wg = emu.quantize_nvfp4_ref(w, sf_layout="128x4")
+        wd = emu.dequantize_nvfp4_ref(w4, wsf, None)
+        a = torch.randn((rows, k), generator=g).bfloat16()
+        a4, asf, ag = emu.quantize_nvfp4_ref(a, sf_layout="128x4")
+
+        def step():
+            ad = emu.dequantize_nvfp4_ref(a4, asf, None)
+            return ((ad @ wd.t()) * (ag * wg)).to(torch.bfloat16)
+    else:
+        n = k = rows = 4096
+        workload = C2_WORKLOAD
+        what = "the whole configuration: 4096 activation rows x 4096 x 4096 weight, dequantise + fp32 matmul + cast"
+        scaling = "weak"
+        w = (torch.randn((n, k), generator=g) * 0.02).bfloat16()
+        w4, wsf, wg = emu.quantize_nvfp4_ref(w, sf_layout="128x4")
+        a = torch.randn((rows, k), generator=g)
+        a = torch.where(torch.rand((rows, k), generator=g) < 0.005, a * 30.0, a).bfloat16()
+        a4, asf, ag = emu.quantize_nvfp4_ref(a, sf_layout="128x4")
+
+        def step():
+            return emu.linear_nvfp4_ref(a4, asf, ag, w4, wsf, wg)
+    for _ in range(warmup):
+        step()
     t = time.perf_counter()
     done = 0
     for _ in range(steps):
-        emu.linear_nvfp4_ref(a4, asf, ag, w4, wsf, wg)
+        step()
         done += 1
         if time.perf_counter() - t > 150:
             break
     dt = (time.perf_counter() - t) / done
     tflops = 2.0 * rows * n * k / dt / 1e12
-    sample = (f"each step = {what} through the torch "
-              f"emulation (dequantise, fp32 matmul, bf16 cast); {done} steps timed")
+    sample = f"each step = {what}; {done} steps timed on {cores} host threads"
     line = {
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": done, "warmup": min(args.warmup, 2), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "steps": done, "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": scaling, "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3 block scales, fp32 accumulate)",
         "data": "synthetic",
         "config": {"workload": workload},
@@ -313,6 +370,29 @@ def decode_stream(peaks):
     return res
 
 
+def c5_single_gpu():
+    """BASELINE config 5 on one GPU (M = K = 8192, N = 28672): the same-workload base of the 1 -> N curve.
+    One operand set (600 MB, larger than L2), 5 steps in a graph."""
+    from ac4k_kernel_b200 import _cuda_ops, ops
+    m, k, n = 8192, 8192, 28672
+    a = activations((m, k), 0, 0.005, 30.0, "cuda")
+    w = weights((n, k), 1000, "cuda")
+    a4, asf, ag = ops.quantize(a, 0, 1, sf_layout="128x4")
+    w4, wsf, wg = ops.quantize(w, 0, 1, sf_layout="128x4")
+    del a, w
+    out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+
+    def step(i):
+        _cuda_ops.linear_nvfp4(out, a4, asf, ag, w4, wsf, wg, None)
+
+    steps = 5
+    secs, _, _ = time_graph(step, 1, steps, 3)
+    t = secs / steps
+    return {"workload": "NVFP4 GEMM M=8192 K=8192 N=28672 on one GPU (no exchange)", "ms_per_step": t * 1e3,
+            "value": 2.0 * m * n * k / t / 1e12, "unit": "TFLOP/s", "steps": steps,
+            "frac_of_nominal_fp4_peak": 2.0 * m * n * k / t / 1e12 / NOMINAL_FP4_TFLOPS}
+
+
 def run_single(args, peaks):
     from ac4k_kernel_b200 import _cuda_ops, ops
     torch.cuda.set_device(0)
@@ -338,6 +418,11 @@ def run_single(args, peaks):
     with ClockSampler(0) as clk:
         secs, t0, t1 = time_graph(step("128x4"), n_sets, args.steps, args.warmup)
     clocks = clk.summary(t0, t1)
+    # the same graph replayed back to back for seconds: throughput at the clock the power cap settles on
+    sustained = sustained_run(time_graph.last_graph, args.steps, flops, 0)
+    if peaks.get("bf16_tflops_sustained"):
+        sustained["frac_of_4x_measured_bf16_sustained"] = sustained["value"] / (4.0 * peaks["bf16_tflops_sustained"])
+    sustained["frac_of_nominal_fp4_peak"] = sustained["value"] / NOMINAL_FP4_TFLOPS
     secs_ac4k, _, _ = time_graph(step("ac4k"), n_sets, args.steps, args.warmup)
     ms_per_step = secs / args.steps * 1e3
     value = flops / (secs / args.steps) / 1e12
@@ -405,6 +490,7 @@ def run_single(args, peaks):
     del out_hosts, a_devs, out_devs
     del sets, a_host
 
+    c5 = c5_single_gpu()
     quant = quantize_bandwidth(peaks)
     decode = decode_stream(peaks)
     cpu_tflops, cores, sample, _, _ = cpu_emulation_c2()
@@ -414,17 +500,19 @@ def run_single(args, peaks):
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3 block scales, fp32 accumulate)", "data": "synthetic",
-        "config": {"workload": "single-GPU square NVFP4 GEMM M=N=K=4096, activations N(0,1) + 0.5% x30 outliers, "
-                               "weights N(0,0.02), 128x4 scale tiles, bf16 out, alpha = gA*gB",
+        "config": {"workload": C2_WORKLOAD,
                    "l2": f"{n_sets} operand/output sets rotated ({n_sets * set_bytes >> 20} MiB > 2 x L2)",
                    "timing": "K steps captured in one CUDA graph, CUDA events around the replay"},
         "frac_of_nominal_fp4_peak": value / NOMINAL_FP4_TFLOPS,
+        "tflops_per_ghz": value / (clocks["sm_mhz"] / 1e3) if clocks.get("sm_mhz") else None,
+        "sustained": sustained,
+        "c5_single_gpu": c5,
         "value_reference_scale_layout": flops / (secs_ac4k / args.steps) / 1e12,
         "roofline": {"bound": "tensor", "achieved": value, "peak": fp4_proxy_peak, "unit": "TFLOP/s",
                      "frac": value / fp4_proxy_peak,
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture
-                     # summarised in profiles/gemm_nvfp4_pair_4096cube.md
-                     "traffic": 19.09e6,
+                     # dram__bytes_read.sum + dram__bytes_write.sum per launch is not measured inside this run (it
+                     # needs ncu); the figure of the capture of one launch is in the file named here
+                     "traffic": None, "traffic_source": "profiles/gemm_nvfp4_pair_4096cube.md",
                      "peak_note": f"4 x {peaks['source']} bf16 burst ({peaks['bf16_tflops']} TFLOP/s): no FP4 figure is "
                                   "measured on this pool; nominal dense FP4 is 9000 TFLOP/s",
                      "algorithmic_flops_per_launch": flops},
@@ -519,11 +607,14 @@ def run_multi(args, peaks):
     peer = parallel.PeerOutput(m, n, torch.bfloat16)
     sync = torch.zeros(1, dtype=torch.float32, device="cuda")
 
+    last = {}
+
     def fused_step(i):
         wq, ws, _ = wsets[i]
-        parallel.column_parallel_linear_fused(a4, asf, ag, wq, ws, wg, peer, sync=sync)
+        last["out"] = parallel.column_parallel_linear_fused(a4, asf, ag, wq, ws, wg, peer, sync=sync)
 
-    peer.tensor.zero_()
+    for t_ in peer.tensors:
+        t_.zero_()
     torch.cuda.synchronize()
     dist.barrier()
     for i in range(max(args.warmup, 3)):
@@ -531,7 +622,7 @@ def run_multi(args, peaks):
     torch.cuda.synchronize()
     full_step(0)
     torch.cuda.synchronize()
-    fused_ok = all(torch.equal(peer.tensor[:, r * ns:(r + 1) * ns], gathered[r]) for r in range(world))
+    fused_ok = all(torch.equal(last["out"][:, r * ns:(r + 1) * ns], gathered[r]) for r in range(world))
     dist.barrier()
     torch.cuda.synchronize()
     with ClockSampler(local) as clk:
@@ -543,10 +634,31 @@ def run_multi(args, peaks):
         torch.cuda.synchronize()
         t1 = time.perf_counter()
     secs = e0.elapsed_time(e1) * 1e-3
-    t = torch.tensor([secs, secs_gemm, secs_serial, secs_pipe, 0.0 if fused_ok else 1.0], dtype=torch.float64,
+    # NVLink ceiling measured in this run: every rank sends 256 MiB to the next rank and receives as much from the
+    # previous one (NCCL send/recv, both directions of every GPU's links busy at once), CUDA events, 5 repetitions
+    ring_src = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    ring_dst = torch.empty_like(ring_src)
+
+    def ring():
+        ops_ = [dist.P2POp(dist.isend, ring_src, (rank + 1) % world), dist.P2POp(dist.irecv, ring_dst, (rank - 1) % world)]
+        for req in dist.batch_isend_irecv(ops_):
+            req.wait()
+
+    for _ in range(2):
+        ring()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0.record()
+    for _ in range(5):
+        ring()
+    e1.record()
+    torch.cuda.synchronize()
+    secs_ring = e0.elapsed_time(e1) * 1e-3 / 5
+    del ring_src, ring_dst
+    t = torch.tensor([secs, secs_gemm, secs_serial, secs_pipe, 0.0 if fused_ok else 1.0, secs_ring], dtype=torch.float64,
                      device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    secs, secs_gemm, secs_serial, secs_pipe, fused_bad = (float(v) for v in t)
+    secs, secs_gemm, secs_serial, secs_pipe, fused_bad, secs_ring = (float(v) for v in t)
     peer.close()
     dist.barrier()
     if rank == 0:
@@ -560,25 +672,30 @@ def run_multi(args, peaks):
             "warmup": max(args.warmup, 3), "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None,
             "dtype": "nvfp4 (e2m1 x ue4m3 block scales, fp32 accumulate)", "data": "synthetic",
-            "config": {"workload": f"column-parallel NVFP4 GEMM M=8192 K=8192 N=28672 over {world} GPUs "
-                                   f"(N/{world} = {ns} columns per rank) + all-gather of the bf16 output "
-                                   "(fused into the GEMM epilogue: peer stores over NVLink)",
+            "config": {"workload": c5_workload(world),
                        "l2": f"{n_sets} weight/output sets rotated per rank",
                        "timing": "CUDA events on each rank, max over ranks"},
             "gemm_only_tflops": gemm_tflops,
             "serial_gemm_then_all_gather_tflops": flops / (secs_serial / args.steps) / 1e12,
             "pipelined_send_recv_tflops": flops / (secs_pipe / args.steps) / 1e12,
-            "exchange": "all-gather fused into the GEMM epilogue: each tile is stored to every rank's [M, N] buffer "
-                        "(peer st.global over NVLink), closed by a one-element all-reduce; the serial NCCL "
-                        "all-gather and a 4-block send/recv pipeline are timed beside it",
+            "exchange": "all-gather fused into the GEMM epilogue: each tile is staged in shared memory once and stored "
+                        "to every rank's [M, N] buffer with TMA stores (the peers' over NVLink), closed by a "
+                        "one-element all-reduce; the serial NCCL all-gather and a 4-block send/recv pipeline are "
+                        "timed beside it",
             "fused_output_equals_nccl_all_gather": fused_bad == 0.0,
             "nvlink": {"sent_bytes_per_gpu": recv_bytes, "gbs_per_gpu_per_direction": recv_bytes / (secs / args.steps) / 1e9,
-                       "measured_peer_copy_gbs": 770.0},
+                       "measured_ring_send_recv_gbs_per_direction": (256 << 20) / secs_ring / 1e9,
+                       "frac_of_measured_ring": recv_bytes / (secs / args.steps) / ((256 << 20) / secs_ring),
+                       "floor_ms_at_measured_ring": recv_bytes / ((256 << 20) / secs_ring) * 1e3,
+                       "note": "the output is replicated on every rank, so each GPU sends and receives "
+                               "(w-1)/w x M x N x 2 bytes per step whatever the GEMM does"},
             "gemm_only_per_gpu_frac_of_nominal_fp4": gemm_tflops / world / NOMINAL_FP4_TFLOPS,
             "all_gather": {"recv_bytes_per_gpu": recv_bytes, "exposed_ms": gather_s * 1e3,
                            "recv_gbs_per_gpu": recv_bytes / gather_s / 1e9},
             "roofline": {"bound": "tensor", "achieved": gemm_tflops, "peak": fp4_proxy_peak, "unit": "TFLOP/s",
                          "frac": gemm_tflops / fp4_proxy_peak, "traffic": None,
+                         "traffic_note": "DRAM bytes need ncu, which never wraps a multi-rank run; NVLink bytes per GPU and "
+                                         "step are algorithmic, see nvlink.sent_bytes_per_gpu",
                          "peak_note": f"{world} x 4 x {peaks['source']} bf16 burst; GEMM-only"},
             "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                     "note": "activations and weights are layer-resident in this variant; see the 1-GPU line for host copies"},

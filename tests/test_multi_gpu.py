@@ -43,26 +43,41 @@ def _worker(rank, world, port, m, n, k, result_dir):
         parallel.column_parallel_linear_pipelined(x4, xsf, xg, w4, wsf, wg, g2, chunks=2)
         torch.cuda.synchronize()
         assert torch.equal(g2, gathered)
-        # (3) fused epilogue stores into every rank's [M, N] buffer
+        # (3) fused epilogue stores into every rank's [M, N] buffer.  The activations change every step and a
+        # consumer kernel reads this rank's copy between the steps (one rank is slowed down on purpose), so a
+        # step that overwrote a buffer another rank still reads would show up as a wrong checksum.
         peer = parallel.PeerOutput(m, n, torch.bfloat16)
-        peer.tensor.fill_(-3.0)
+        for t in peer.tensors:
+            t.fill_(-3.0)
         torch.cuda.synchronize()
         dist.barrier()
-        for _ in range(3):
-            full = parallel.column_parallel_linear_fused(x4, xsf, xg, w4, wsf, wg, peer)
+        steps = 6
+        xs = [gaussian((m, k), seed=100 + i).cuda() for i in range(steps)]
+        xq = [ops.quantize(v, 0, 1, sf_layout="128x4") for v in xs]
+        wholes = [ops.linear(q[0], q[1], q[2], f4, fsf, fg) for q in xq]
+        sums, fulls_ok = [], []
+        spin = torch.empty((4096, 4096), device="cuda")
+        for i in range(steps):
+            full = parallel.column_parallel_linear_fused(xq[i][0], xq[i][1], xq[i][2], w4, wsf, wg, peer)
+            if rank == i % world:
+                for _ in range(4):
+                    spin = spin @ spin * 0 + 1          # this rank's consumer starts late
+            sums.append(full.float().sum() + spin[0, 0] * 0)      # the consumer: reads the whole gathered output
+            fulls_ok.append(torch.equal(full, wholes[i]))
         torch.cuda.synchronize()
-        ok = torch.equal(full, whole)
+        ok = all(fulls_ok) and all(float(sums[i]) == float(wholes[i].float().sum()) for i in range(steps))
         peer.close()
-        assert ok, "fused all-gather output differs from the single-GPU GEMM"
+        assert ok, f"fused all-gather output differs from the single-GPU GEMM: {fulls_ok}"
         open(os.path.join(result_dir, f"ok{rank}"), "w").close()
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_column_parallel_two_gpus(tmp_path):
+@pytest.mark.parametrize("world", [2, 4])
+def test_column_parallel_gpus(tmp_path, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
-    world = 2
     port = _free_port()
     ctx = mp.get_context("spawn")
     procs = [ctx.Process(target=_worker, args=(r, world, port, 1024, 2048, 1024, str(tmp_path))) for r in range(world)]
