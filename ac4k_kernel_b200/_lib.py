@@ -72,6 +72,9 @@ def check(rc: int, what: str) -> None:
 
 
 def device_status(clear: bool = True) -> int:
+    """The device status word (0, or the code of an expired device-side wait); synchronises the device."""
     v = ctypes.c_uint32(0)
-    check(LIB.ac4k_device_status(ctypes.byref(v), int(clear)), "ac4k_device_status")
+    rc = LIB.ac4k_device_status(ctypes.byref(v), int(clear))
+    if rc != 0 and rc != -7:            # -7 (AC4K_ERR_TIMEOUT) comes with the code in v
+        check(rc, "ac4k_device_status")
     return v.value

@@ -1,0 +1,227 @@
+// The compiled `_cuda_ops` module over the C ABI: the translation unit a maintainer of ac4k_kernel would add
+// as lib/cuda/sm100/bindings_sm100.cc.  Same module name, function names, positional signatures and module
+// attributes as the reference's lib/cuda_bindings.cc:37-97 (prototypes: include/ac4k_kernel/ops.h:13-54);
+// the argument checks are the TORCH_CHECKs of the reference's host launchers, the launch is a call into
+// libac4k_b200.so with raw pointers and the current CUDA stream.
+//
+// Built by ac4k_kernel_b200/build.py (build_pybind) with the host compiler; no CUDA source is involved.
+#include <torch/extension.h>
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include <vector>
+
+#include "ac4k_b200.h"
+
+namespace ac4k {
+
+static int64_t align_up(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
+static int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+static void check_cuda(const torch::Tensor &t, at::ScalarType dt, const char *name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+  TORCH_CHECK(t.scalar_type() == dt, "Inconsistency of Tensor type: ", name);
+}
+
+// sizes and element strides ordered [outer0, outer1, cross, reduce], rank padded to 4 with leading 1s
+// (quantize_nvfp4.cu:226-241)
+static std::vector<int> view4(const torch::Tensor &in, uint32_t cross, uint32_t reduce, int64_t shape[4], int64_t stride[4]) {
+  std::vector<int> others;
+  for (int i = 0; i < in.dim(); ++i)
+    if (i != (int)cross && i != (int)reduce) others.push_back(i);
+  int o = 2 - (int)others.size();
+  for (int i = 0; i < o; ++i) { shape[i] = 1; stride[i] = 0; }
+  for (int i : others) { shape[o] = in.size(i); stride[o] = in.stride(i); ++o; }
+  shape[2] = in.size(cross);  stride[2] = in.stride(cross);
+  shape[3] = in.size(reduce); stride[3] = in.stride(reduce);
+  return others;
+}
+
+static std::vector<int> check_quant_common(const torch::Tensor &out, const torch::Tensor &in, uint32_t cross_dim,
+                                           uint32_t reduce_dim, int reduce_align, int reduce_div, int64_t shape[4],
+                                           int64_t stride[4]) {
+  TORCH_CHECK(in.dim() >= 2 && in.dim() <= 4, "in must be 2-4D");
+  TORCH_CHECK(cross_dim < (uint32_t)in.dim(), "cross_dim must be less than in.dim()");
+  TORCH_CHECK(reduce_dim < (uint32_t)in.dim(), "reduce_dim must be less than in.dim()");
+  TORCH_CHECK(cross_dim != reduce_dim, "cross_dim and reduce_dim must be different");
+  TORCH_CHECK(out.dim() == in.dim(), "out must be the same dim as in");
+  std::vector<int> others = view4(in, cross_dim, reduce_dim, shape, stride);
+  for (size_t c = 0; c < others.size(); ++c) TORCH_CHECK(out.size(c) == in.size(others[c]), "out must be the same shape as in");
+  TORCH_CHECK(out.size(-2) == shape[2], "meet invalid cross dim size");
+  TORCH_CHECK(out.size(-1) == align_up(shape[3], reduce_align) / reduce_div, "meet invalid reduce dim size");
+  return others;
+}
+
+// ops.h:27-29; checks of quantize_nvfp4.cu:171-224
+void quantize_nvfp4(torch::Tensor &out, torch::Tensor &sf, torch::Tensor const &in, torch::Tensor const &global_scale,
+                    uint32_t cross_dim, uint32_t reduce_dim, bool swizzle) {
+  check_cuda(in, at::kBFloat16, "in");
+  check_cuda(global_scale, at::kFloat, "global_scale");
+  TORCH_CHECK(global_scale.dim() == 0, "global_scale must be a scalar");
+  check_cuda(out, at::kByte, "out");
+  check_cuda(sf, at::kFloat8_e4m3fn, "sf");
+  int64_t shape[4], stride[4];
+  std::vector<int> others = check_quant_common(out, in, cross_dim, reduce_dim, 64, 2, shape, stride);
+  const int64_t kt = ceil_div(shape[3], 64);
+  std::vector<int64_t> want;
+  for (int i : others) want.push_back(in.size(i));
+  int layout;
+  if (sf.dim() == in.dim() + 1) {
+    layout = AC4K_SF_AC4K;
+    want.insert(want.end(), {kt, align_up(shape[2], 16), 4});
+  } else if (sf.dim() == in.dim() + 3) {
+    layout = AC4K_SF_TILE128X4;
+    want.insert(want.end(), {ceil_div(shape[2], 128), kt, 32, 4, 4});
+  } else {
+    TORCH_CHECK(false, "meet invalid sf rank");
+  }
+  TORCH_CHECK(sf.sizes().vec() == want, "meet invalid sf shape");
+  c10::cuda::CUDAGuard guard(in.device());
+  const int rc = ac4k_quantize_nvfp4(out.data_ptr(), sf.data_ptr(), in.data_ptr(), global_scale.data_ptr<float>(), shape,
+                                     stride, swizzle ? 1 : 0, layout, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "ac4k_quantize_nvfp4: ", ac4k_last_error());
+}
+
+// ops.h:31-33; checks of quantize_fp8.cu:196-247
+void quantize_fp8(torch::Tensor &out, torch::Tensor &sf, torch::Tensor const &in, torch::Tensor const &scale_max,
+                  uint32_t cross_dim, uint32_t reduce_dim, bool swizzle) {
+  check_cuda(in, at::kBFloat16, "in");
+  check_cuda(scale_max, at::kFloat, "scale_max");
+  TORCH_CHECK(scale_max.dim() == 0, "scale_max must be a scalar");
+  check_cuda(out, at::kFloat8_e4m3fn, "out");
+  check_cuda(sf, at::kFloat, "sf");
+  int64_t shape[4], stride[4];
+  std::vector<int> others = check_quant_common(out, in, cross_dim, reduce_dim, 16, 1, shape, stride);
+  TORCH_CHECK(sf.dim() == in.dim() - 1, "meet invalid sf rank");
+  std::vector<int64_t> want;
+  for (int i : others) want.push_back(in.size(i));
+  want.push_back(align_up(shape[2], 16));
+  TORCH_CHECK(sf.sizes().vec() == want, "meet invalid sf shape");
+  c10::cuda::CUDAGuard guard(in.device());
+  const int rc = ac4k_quantize_fp8(out.data_ptr(), sf.data_ptr<float>(), in.data_ptr(), scale_max.data_ptr<float>(), shape,
+                                   stride, swizzle ? 1 : 0, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "ac4k_quantize_fp8: ", ac4k_last_error());
+}
+
+// ops.h:35-37; checks of quantize_int8.cu:179-230
+void quantize_int8(torch::Tensor &out, torch::Tensor &sf, torch::Tensor const &in, torch::Tensor const &scale_max,
+                   uint32_t cross_dim, uint32_t reduce_dim) {
+  check_cuda(in, at::kBFloat16, "in");
+  check_cuda(scale_max, at::kInt, "scale_max");
+  TORCH_CHECK(scale_max.dim() == 0, "scale_max must be a scalar");
+  check_cuda(out, at::kChar, "out");
+  check_cuda(sf, at::kFloat, "sf");
+  int64_t shape[4], stride[4];
+  std::vector<int> others = check_quant_common(out, in, cross_dim, reduce_dim, 16, 1, shape, stride);
+  TORCH_CHECK(sf.dim() == in.dim() - 1, "meet invalid sf rank");
+  std::vector<int64_t> want;
+  for (int i : others) want.push_back(in.size(i));
+  want.push_back(align_up(shape[2], 16));
+  TORCH_CHECK(sf.sizes().vec() == want, "meet invalid sf shape");
+  c10::cuda::CUDAGuard guard(in.device());
+  const int rc = ac4k_quantize_int8(out.data_ptr(), sf.data_ptr<float>(), in.data_ptr(), scale_max.data_ptr<int32_t>(), shape,
+                                    stride, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "ac4k_quantize_int8: ", ac4k_last_error());
+}
+
+static int dtype_code(at::ScalarType t, const char *what) {
+  TORCH_CHECK(t == at::kBFloat16 || t == at::kHalf || t == at::kFloat, what, " must be bfloat16, half or float");
+  return t == at::kBFloat16 ? AC4K_DT_BF16 : (t == at::kHalf ? AC4K_DT_FP16 : AC4K_DT_FP32);
+}
+
+// ops.h:43-48; checks of linear_nvfp4.cu:759-805
+void linear_nvfp4(torch::Tensor &D, torch::Tensor const &A, torch::Tensor const &A_sf, torch::Tensor const &A_global_scale,
+                  torch::Tensor const &B, torch::Tensor const &B_sf, torch::Tensor const &B_global_scale,
+                  c10::optional<torch::Tensor> const &bias) {
+  TORCH_CHECK(D.dim() == 2, "d must be a 2d matrix");
+  const int64_t M = D.size(0), N = D.size(1);
+  const int d_dt = dtype_code(D.scalar_type(), "d");
+  TORCH_CHECK(D.is_cuda() && D.is_contiguous(), "d must be contiguous");
+  TORCH_CHECK(A.dim() == 2, "a must be a 2d matrix");
+  check_cuda(A, at::kByte, "a");
+  TORCH_CHECK(A.size(0) == M, "A size(0) must be ", M, " but see ", A.size(0));
+  const int64_t K = A.size(1) * 2;
+  TORCH_CHECK(K % 16 == 0, "A size(1)*2 must be multiple of 16 but see ", K);
+  TORCH_CHECK(B.dim() == 2, "b must be a 2d matrix");
+  check_cuda(B, at::kByte, "b");
+  TORCH_CHECK(B.size(0) == N, "B size(0) must be ", N, " but see ", B.size(0));
+  TORCH_CHECK(B.size(1) == A.size(1), "B size(1) must equal A size(1)");
+  const int64_t kt = ceil_div(K, 64);
+  check_cuda(A_sf, at::kFloat8_e4m3fn, "scale_a");
+  check_cuda(B_sf, at::kFloat8_e4m3fn, "scale_b");
+  int layout;
+  if (A_sf.dim() == 3) {
+    layout = AC4K_SF_AC4K;
+    TORCH_CHECK(A_sf.sizes().vec() == std::vector<int64_t>({kt, align_up(M, 16), 4}), "scale_a has an invalid shape");
+    TORCH_CHECK(B_sf.sizes().vec() == std::vector<int64_t>({kt, align_up(N, 16), 4}), "scale_b has an invalid shape");
+  } else {
+    TORCH_CHECK(A_sf.dim() == 5, "scale_a must be a 3d matrix");
+    layout = AC4K_SF_TILE128X4;
+    TORCH_CHECK(A_sf.sizes().vec() == std::vector<int64_t>({ceil_div(M, 128), kt, 32, 4, 4}), "scale_a has an invalid shape");
+    TORCH_CHECK(B_sf.sizes().vec() == std::vector<int64_t>({ceil_div(N, 128), kt, 32, 4, 4}), "scale_b has an invalid shape");
+  }
+  check_cuda(A_global_scale, at::kFloat, "global_scale_a");
+  TORCH_CHECK(A_global_scale.dim() == 0, "A_global_scale must be a scalar");
+  check_cuda(B_global_scale, at::kFloat, "global_scale_b");
+  TORCH_CHECK(B_global_scale.dim() == 0, "B_global_scale must be a scalar");
+  const void *bias_ptr = nullptr;
+  int bias_dt = 0;
+  if (bias.has_value()) {
+    bias_dt = dtype_code(bias->scalar_type(), "bias");
+    TORCH_CHECK(bias->is_cuda() && bias->is_contiguous(), "bias must be contiguous");
+    TORCH_CHECK(bias->dim() == 2, "bias must be a 2d matrix");
+    TORCH_CHECK(bias->size(0) == 1, "bias shape[0] must be 1");
+    TORCH_CHECK(bias->size(1) == N, "bias shape[1] must be ", N);
+    bias_ptr = bias->data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(D.device());
+  const int rc = ac4k_linear_nvfp4(D.data_ptr(), d_dt, A.data_ptr(), A_sf.data_ptr(), A_global_scale.data_ptr<float>(),
+                                   B.data_ptr(), B_sf.data_ptr(), B_global_scale.data_ptr<float>(), bias_ptr, bias_dt, M, N, K,
+                                   layout, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "ac4k_linear_nvfp4: ", ac4k_last_error());
+}
+
+// replaces the Triton kernel behind python/ac4k_kernel/ops/quant.py:21-59 (not in the reference's module)
+void global_scale_bf16(torch::Tensor &out, torch::Tensor const &x, double max_scale) {
+  check_cuda(x, at::kBFloat16, "x");
+  check_cuda(out, at::kFloat, "out");
+  TORCH_CHECK(out.numel() == 1, "out must hold one float");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int rc = ac4k_global_scale_bf16(x.data_ptr(), x.numel(), (float)max_scale, out.data_ptr<float>(),
+                                        at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "ac4k_global_scale_bf16: ", ac4k_last_error());
+}
+
+// The attention and RoPE operators of the reference module are different operators from the linear path this
+// library covers; the names exist so that `import` and introspection behave like the reference's module.
+void mha_nvfp4_fwd(torch::Tensor &, torch::Tensor &, torch::Tensor &, torch::Tensor &, torch::Tensor &, torch::Tensor &,
+                   torch::Tensor &, torch::Tensor &, torch::Tensor &, torch::Tensor &, float) {
+  TORCH_CHECK(false, "mha_nvfp4_fwd is not part of the sm100 linear-path library");
+}
+void mha_int8_x_fp8_fwd(torch::Tensor &, torch::Tensor &, torch::Tensor &, int, torch::Tensor &, torch::Tensor &, int,
+                        torch::Tensor &, torch::Tensor &, float) {
+  TORCH_CHECK(false, "mha_int8_x_fp8_fwd is not part of the sm100 linear-path library");
+}
+void rope3d(const torch::Tensor &, const torch::Tensor &, const torch::Tensor &, torch::Tensor &) {
+  TORCH_CHECK(false, "rope3d is not part of the sm100 linear-path library");
+}
+
+}  // namespace ac4k
+
+PYBIND11_MODULE(_cuda_ops, m) {
+  m.doc() = "ac4k_kernel operators for B200 (sm_100a) over libac4k_b200.so";
+  m.attr("__arch__") = ac4k_arch();
+  m.attr("__arch_description__") = ac4k_arch_description();
+  m.attr("__backend__") = ac4k_backend();
+  m.attr("__version__") = ac4k_version();
+  m.def("mha_nvfp4_fwd", &ac4k::mha_nvfp4_fwd, "Multi-Head Attention Forward (NVFP4): not built for sm100");
+  m.def("mha_int8_x_fp8_fwd", &ac4k::mha_int8_x_fp8_fwd, "Multi-Head Attention Forward (QK=INT8, PV=FP8): not built for sm100");
+  m.def("quantize_nvfp4", &ac4k::quantize_nvfp4, "Quantize bfloat16 tensor to NVFP4 format");
+  m.def("quantize_fp8", &ac4k::quantize_fp8, "Quantize bfloat16 tensor to FP8 format");
+  m.def("quantize_int8", &ac4k::quantize_int8, "Quantize bfloat16 tensor to INT8 format");
+  m.def("linear_nvfp4", &ac4k::linear_nvfp4, "NVFP4 Linear (fully-connected layer): y = x @ weight.T + bias");
+  m.def("rope3d", &ac4k::rope3d, "3D Rotary Position Embedding: not built for sm100");
+  m.def("global_scale_bf16", &ac4k::global_scale_bf16, "out[0] = max|x| / max_scale");
+}

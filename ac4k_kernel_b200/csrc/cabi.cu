@@ -62,5 +62,10 @@ extern "C" int ac4k_device_status(uint32_t *status_out, int clear) {
     unsigned int z = 0;
     AC4K_CUDA_TRY(cudaMemcpyToSymbol(ac4k::g_device_status, &z, sizeof(z)));
   }
+  if (v >= 0xA1 && v <= 0xA4) {
+    static const char *role[] = {"TMA producer", "MMA issuer", "scale warps", "epilogue"};
+    return ac4k::fail(AC4K_ERR_TIMEOUT, "a bounded device-side wait expired in a GEMM launched earlier (%s, status 0x%X); "
+                                        "the outputs of that launch are undefined", role[v - 0xA1], v);
+  }
   return 0;
 }

@@ -81,6 +81,7 @@ struct GemmArgs {
   int splits;           // split-K factor (1-CTA kernel only); > 1 writes fp32 partials to `ws`
   int kt_per_split;     // K stages (of 256 elements) per split
   float *ws;            // [splits, M, N] fp32 partial sums when splits > 1
+  unsigned long long wait_ns;   // limit of every device-side wait of the launch (kWaitTimeoutNs; shorter in the wait-expiry test)
   int dbg;              // experiment switches (builds with -DAC4K_DEBUG_HOOKS), else 0
   unsigned long long *trace;   // clock stamps (builds with -DAC4K_TRACE_ENABLED), else NULL
 };

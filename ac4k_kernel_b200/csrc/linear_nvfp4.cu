@@ -136,7 +136,7 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
       const int m0 = tm * BM, n0 = tn * BN;
       for (int kt = kt0; kt < kt1; ++kt) {
-        ok = warp_all(mbar_wait(empty_bar + 8 * s, ph ^ 1));
+        ok = warp_all(mbar_wait(empty_bar + 8 * s, ph ^ 1, p.wait_ns));
         if (!ok) break;
         const int nk = min(K64_PER_STAGE, p.KT - kt * K64_PER_STAGE);
         uint32_t sf_bytes = 0;
@@ -181,13 +181,13 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       int t_unused, split;
       work_item(wi, t_unused, split);
       const int kt0 = split * p.kt_per_split, kt1 = min(k_tiles_all, kt0 + p.kt_per_split);
-      ok = warp_all(mbar_wait(tempty_bar + 8 * acc, acc_ph ^ 1));
+      ok = warp_all(mbar_wait(tempty_bar + 8 * acc, acc_ph ^ 1, p.wait_ns));
       if (!ok) break;
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * BN;
       for (int kt = kt0; kt < kt1; ++kt) {
         if (el) AC4K_TR1(0, it, 0);
-        ok = warp_all(mbar_wait(full_bar + 8 * s, ph));
+        ok = warp_all(mbar_wait(full_bar + 8 * s, ph, p.wait_ns));
         if (!ok) break;
         tc_fence_after();
         if (el) AC4K_TR1(0, it, 1);
@@ -271,7 +271,7 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                 wb[j][g] = (k_ok && r < p.rows_sfb) ? __ldg(sfb_w + (int64_t)k64 * p.rows_sfb + r) : 0u;
               }
             }
-            ok = warp_all(mbar_wait(empty_bar + 8 * s, ph ^ 1));
+            ok = warp_all(mbar_wait(empty_bar + 8 * s, ph ^ 1, p.wait_ns));
             if (!ok) break;
 #pragma unroll
             for (int j = 0; j < K64_PER_STAGE; ++j) {
@@ -302,7 +302,7 @@ linear_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       work_item(wi, t, split);
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
-      const bool tfull_ok = mbar_wait(tfull_bar + 8 * acc, acc_ph);
+      const bool tfull_ok = mbar_wait(tfull_bar + 8 * acc, acc_ph, p.wait_ns);
       if (!tfull_ok && lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue);
       if (!tfull_ok) break;
       tc_fence_after();
@@ -544,12 +544,17 @@ using namespace ac4k;
 //   ac4k_debug_set_flags(bits)  8 skip the epilogue's stores; 64 launch without the
 //                               programmatic-stream-serialization attribute; 128 no L2 prefetch before the
 //                               dependency wait (pair kernel)
+//                               256 the pair kernel's producer leaves out the loads of its very first stage, so that
+//                               the waits for it expire (the wait-expiry test)
+//   ac4k_debug_set_wait_ns(ns)  limit of the device-side waits of later launches (0 = the default 2 s)
 //   ac4k_debug_set_trace(ptr)   device buffer for the clock stamps of builds with -DAC4K_TRACE_ENABLED
 #ifdef AC4K_DEBUG_HOOKS
 static int g_force_bn = 0;
 static int g_force_splits = 0;
 static int g_dbg = 0;
 static unsigned long long *g_trace = nullptr;
+static unsigned long long g_wait_ns = 0;
+extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_wait_ns(unsigned long long ns) { g_wait_ns = ns; }
 extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_splits(int n) { g_force_splits = n; }
 extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_trace(void *p) { g_trace = static_cast<unsigned long long *>(p); }
 extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_flags(int f) { g_dbg = f; }
@@ -557,6 +562,7 @@ extern "C" __attribute__((visibility("default"))) void ac4k_debug_set_tile_n(int
 #else
 static constexpr int g_force_bn = 0, g_force_splits = 0, g_dbg = 0;
 static constexpr unsigned long long *g_trace = nullptr;
+static constexpr unsigned long long g_wait_ns = 0;
 #endif
 
 // Split-K plan of the single-CTA kernel for shapes with too few output tiles to occupy the GPU (65 <= M <= 128,
@@ -672,6 +678,7 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
     a.kt_per_split = (int)ceil_div(k_tiles, splits);
     a.splits = splits;
     a.trace = g_trace;
+    a.wait_ns = g_wait_ns ? g_wait_ns : kWaitTimeoutNs;
     return launch_linear_skinny(d_dtype, sf_layout == AC4K_SF_TILE128X4, nt, tx, tw, a, stream);
   }
   CUtensorMap ta, tb;
@@ -711,6 +718,7 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
   a.tiles_n = (int)ceil_div(N, bn);
   a.dbg = g_dbg;
   a.trace = g_trace;
+  a.wait_ns = g_wait_ns ? g_wait_ns : kWaitTimeoutNs;
   a.splits = pl.splits;
   a.kt_per_split = pl.kt_per_split;
   a.ws = nullptr;

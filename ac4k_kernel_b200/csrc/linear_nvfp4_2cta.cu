@@ -216,9 +216,15 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       const int sfb_row0 = (tn * (BN / 128)) * p.KT;
       bool ok = true;
       for (int kt = 0; kt < k_tiles; ++kt) {
-        ok = warp_all(mbar_wait(empty_bar + 8 * s, ph ^ 1));
+        ok = warp_all(mbar_wait(empty_bar + 8 * s, ph ^ 1, p.wait_ns));
         if (!ok) break;
         const uint32_t lf = leader_full0 + 8 * s;
+        if (AC4K_DBG(p, 256) && kt == 0 && t == cluster_id) {
+          // wait-expiry test (debug-hook builds): this stage is never loaded, nothing arrives on its barrier, and
+          // every role of the pair must find its way out through its bounded waits
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+          continue;
+        }
         // the leader announces the bytes of both CTAs; K steps past the end of K arrive as zeros
         // (or as the next row block's scales, unused) and count all the same
         if (rank == 0) mbar_arrive_expect_tx_if(el, full_bar + 8 * s, 2 * (SF_TILED ? STAGE_TX : A_BYTES + B_BYTES));
@@ -249,17 +255,17 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         // this tile's accumulator must have been drained (by the tile before the previous one), and the
         // previous tile's epilogue must have read the columns both accumulators share
         const uint32_t acc = ti & 1;
-        ok = warp_all(mbar_wait(tempty_bar + 8 * acc, ((acc_phs >> acc) & 1) ^ 1));
+        ok = warp_all(mbar_wait(tempty_bar + 8 * acc, ((acc_phs >> acc) & 1) ^ 1, p.wait_ns));
         if (!ok) break;
         acc_phs ^= 1u << acc;
-        ok = warp_all(mbar_wait(shared_free_bar, shared_ph ^ 1));
+        ok = warp_all(mbar_wait(shared_free_bar, shared_ph ^ 1, p.wait_ns));
         if (!ok) break;
         shared_ph ^= 1;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * ACC1_COL;
         for (int kt = 0; kt < k_tiles; ++kt) {
           if (el) AC4K_TR(0, it, 0);
-          ok = warp_all(mbar_wait(full_bar + 8 * s, ph));
+          ok = warp_all(mbar_wait(full_bar + 8 * s, ph, p.wait_ns));
           if (!ok) break;
           tc_fence_after();
           if (el) AC4K_TR(0, it, 1);
@@ -336,7 +342,7 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
                 wb[j][g] = (k_ok && r < p.rows_sfb) ? __ldg(sfb_w + (int64_t)k64 * p.rows_sfb + r) : 0u;
               }
             }
-            ok = warp_all(mbar_wait(empty_bar + 8 * s, ph ^ 1));
+            ok = warp_all(mbar_wait(empty_bar + 8 * s, ph ^ 1, p.wait_ns));
             if (!ok) break;
 #pragma unroll
             for (int j = 0; j < KS; ++j) {
@@ -390,7 +396,7 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         st_shared_v4f(bias_s + lane * 16, b4[0], b4[1], b4[2], b4[3]);
         __syncwarp();
       }
-      if (!mbar_wait(tfull_bar + 8 * acc, (acc_phs >> acc) & 1)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue); break; }
+      if (!mbar_wait(tfull_bar + 8 * acc, (acc_phs >> acc) & 1, p.wait_ns)) { if (lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue); break; }
       acc_phs ^= 1u << acc;
       tc_fence_after();
       if (warp == 6 && lane == 0) AC4K_TR(1, ti, 0);

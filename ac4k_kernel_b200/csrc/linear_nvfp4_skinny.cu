@@ -200,7 +200,7 @@ linear_nvfp4_skinny_kernel(const __grid_constant__ CUtensorMap tma_x, const __gr
     uint32_t s = 0, ph = 0;
     bool ok = true;
     for (int kt = kt0; kt < kt1; ++kt) {
-      ok = warp_all(mbar_wait(empty_bar + 8 * s, ph ^ 1));
+      ok = warp_all(mbar_wait(empty_bar + 8 * s, ph ^ 1, p.wait_ns));
       if (!ok) break;
       const int nk = min(KS, p.KT - kt * KS);
       const uint32_t fb = full_bar + 8 * s;
@@ -228,7 +228,7 @@ linear_nvfp4_skinny_kernel(const __grid_constant__ CUtensorMap tma_x, const __gr
     const uint64_t sfxdesc0 = make_smem_desc(sSFX, 0, 128, kSwizzleNone);
     const uint32_t t_sfw = tmem_base + SFW_COL, t_sfx = tmem_base + SFX_COL;
     for (int kt = kt0; kt < kt1; ++kt) {
-      ok = warp_all(mbar_wait(full_bar + 8 * s, ph));
+      ok = warp_all(mbar_wait(full_bar + 8 * s, ph, p.wait_ns));
       if (!ok) break;
       tc_fence_after();
       if (el && kt == kt0) AC4K_TRS(3);
@@ -290,7 +290,7 @@ linear_nvfp4_skinny_kernel(const __grid_constant__ CUtensorMap tma_x, const __gr
               wx[j][g] = (k_ok && rx < p.rows_sfa) ? __ldg(sfx_w + (int64_t)k64 * p.rows_sfa + rx) : 0u;
             }
           }
-          ok = warp_all(mbar_wait(empty_bar + 8 * s, ph ^ 1));
+          ok = warp_all(mbar_wait(empty_bar + 8 * s, ph ^ 1, p.wait_ns));
           if (!ok) break;
 #pragma unroll
           for (int j = 0; j < KS; ++j) {
@@ -310,7 +310,7 @@ linear_nvfp4_skinny_kernel(const __grid_constant__ CUtensorMap tma_x, const __gr
     // columns are the activation rows
     const int row_l = q * 32 + lane;
     const int n = n0 + row_l;
-    const bool tfull_ok = mbar_wait(tfull_bar, 0);
+    const bool tfull_ok = mbar_wait(tfull_bar, 0, p.wait_ns);
     if (!tfull_ok && lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue);
     tc_fence_after();
     if (warp == 2 && lane == 0) AC4K_TRS(5);
@@ -334,7 +334,7 @@ linear_nvfp4_skinny_kernel(const __grid_constant__ CUtensorMap tma_x, const __gr
       if (warp == 2 && lane == 0) AC4K_TRS(6);
     } else {
       if (p.splits > 1) {
-        const bool got = mbar_wait(part_bar + 8 * lq, 0);
+        const bool got = mbar_wait(part_bar + 8 * lq, 0, p.wait_ns);
         if (!got && lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue);
       }
       if (warp == 2 && lane == 0) AC4K_TRS(6);

@@ -55,26 +55,16 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false if the phase did not complete within kWaitTimeoutNs.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-#ifdef AC4K_SPIN_TEST_WAIT
-  {
-    const unsigned long long t0 = globaltimer();
-    for (;;) {
-#pragma unroll 1
-      for (int i = 0; i < 1024; ++i)
-        if (mbar_test_wait(bar, parity)) return true;
-      if (globaltimer() - t0 > kWaitTimeoutNs) return false;
-    }
-  }
-#endif
+// Bounded wait: false if the phase did not complete within `limit_ns` (the kernels pass the limit they were
+// launched with: kWaitTimeoutNs unless a test build shortened it).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned long long limit_ns = kWaitTimeoutNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (globaltimer() - t0 > kWaitTimeoutNs) return false;
+    if (globaltimer() - t0 > limit_ns) return false;
   }
 }
 

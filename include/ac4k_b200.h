@@ -43,7 +43,8 @@ enum {
   AC4K_ERR_ENUM = -4,        /* unknown dtype / layout code                    */
   AC4K_ERR_UNSUPPORTED = -5, /* valid in the reference, not built here         */
   AC4K_ERR_DEVICE = -6,      /* current device is not an sm_100 part           */
-  AC4K_ERR_TIMEOUT = -7      /* a bounded device-side wait gave up (see status) */
+  AC4K_ERR_TIMEOUT = -7      /* returned by ac4k_device_status only: a bounded device-side
+                                wait of an earlier launch gave up                          */
 };
 
 enum { AC4K_SF_AC4K = 0, AC4K_SF_TILE128X4 = 1 };
@@ -57,7 +58,12 @@ const char *ac4k_version(void);          /* "0.1.0" */
 const char *ac4k_last_error(void);
 
 /* Device-side status word of the current device: 0, or the code left by a kernel whose
- * bounded wait expired.  Synchronises the device.  `clear` != 0 resets it. */
+ * bounded wait expired (0xA1 TMA producer, 0xA2 MMA issuer, 0xA3 scale warps, 0xA4 epilogue).
+ * Synchronises the device.  `clear` != 0 resets the word.  Returns AC4K_ERR_TIMEOUT when such a code is
+ * found, 0 when the word is 0.  Launches are asynchronous, so an entry point that enqueued the kernel has
+ * long returned 0 by then: this call is the only place where an expired wait is reported, and the outputs of
+ * the launch that left the code are undefined.  Every device-side wait (mbarrier, flag) is bounded (2 s) and
+ * the kernel leaves through its normal exit, releasing tensor memory, so the context stays usable. */
 int ac4k_device_status(uint32_t *status_out, int clear);
 
 /* g_out[0] = max|x| / max_scale over `numel` contiguous bf16 values (0 for numel == 0).
