@@ -685,7 +685,7 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
   if (int e = get_tmap(A, M, K / 2, BM, &ta)) return e;
   if (int e = get_tmap(B, N, K / 2, use_pair ? 128 : bn, &tb)) return e;
 
-  GemmArgs a;
+  GemmArgs a = {};
   a.sfa = static_cast<const uint8_t *>(A_sf);
   a.sfb = static_cast<const uint8_t *>(B_sf);
   a.D = D;
