@@ -294,7 +294,56 @@ def _out_of_scope(name):
     return fn
 
 
+def mha_nvfp4_fwd(o, q, q_sf, q_global_scale, k, k_sf, k_global_scale, v, v_sf, v_global_scale, sm_scale):
+    """o = softmax(sm_scale * q k^T) v on NVFP4 operands (ops.h:13-17; checks of
+    lib/cuda/sm120/mha_nvfp4.cu:897-1010).  q: [B, H, Nq, Dqk/2], k: [B, H, Nkv, Dqk/2],
+    v: [B, H, Dv, align64(Nkv)/2] (quantised along the keys, swizzle=True), o: bf16 [B, H, Nq, Dv] in any
+    strides (the reference passes a permuted [B, N, H, D] buffer).  Block scales in the tiled layout
+    [B, H, ceil(rows/128), K/64, 32, 4, 4]."""
+    _check_tensor(q, torch.uint8, "Q")
+    _require(q.dim() == 4, "Q must be a 4D tensor")
+    B, H, Nq = q.size(0), q.size(1), q.size(2)
+    Dqk = q.size(3) * 2
+    _require(Dqk % 16 == 0, "Dqk must be multiple of 16")
+    _require(Dqk <= 128, "Dqk must be less than 128")
+    _check_tensor(k, torch.uint8, "K")
+    _require(k.dim() == 4, "K must be a 4D tensor")
+    _require(k.size(0) == B, "K must have the same batch size as Q")
+    _require(k.size(1) == H, "K must have the same head number as Q")
+    Nkv = k.size(2)
+    _require(k.size(3) == q.size(3), "K must have the same dim as Q")
+    _check_tensor(v, torch.uint8, "V")
+    _require(v.dim() == 4, "V must be a 4D tensor")
+    _require(v.size(0) == B, "V must have the same batch size as Q")
+    _require(v.size(1) == H, "V must have the same head number as Q")
+    Dv = v.size(2)
+    _require(v.size(3) * 2 == _align_up(Nkv, 64), "V must have the same sequence length as K")
+    _require(Dv <= 128, "Dv must be less than 128")
+    for name, sf, rows, red in (("q_sf", q_sf, Nq, Dqk), ("k_sf", k_sf, Nkv, Dqk), ("v_sf", v_sf, Dv, Nkv)):
+        _check_tensor(sf, torch.float8_e4m3fn, name)
+        _require(sf.dim() in (5, 7), f"{name} must be a 5D tensor, or 7D in the tiled layout")
+        if sf.dim() == 5:
+            raise RuntimeError(f"{name}: the sm100 attention kernel reads block scales in the tiled layout "
+                               "(quantize(..., sf_layout=\"128x4\")); the [.., K/64, rows, 4] layout is not built")
+        _require(list(sf.shape) == [B, H, _ceil_div(rows, 128), _ceil_div(red, 64), 32, 4, 4],
+                 f"Meet invalid {name} shape {list(sf.shape)}")
+    for name, g in (("q_global_scale", q_global_scale), ("k_global_scale", k_global_scale),
+                    ("v_global_scale", v_global_scale)):
+        _check_tensor(g, torch.float32, name)
+        _require(g.dim() == 0, f"{name} must be a scalar")
+    _require(isinstance(o, torch.Tensor) and o.is_cuda, "O must be a CUDA tensor")
+    _require(o.dtype == torch.bfloat16, "O must be a bfloat16 tensor")
+    _require(o.dim() == 4, "O must be a 4D tensor")
+    _require(list(o.shape) == [B, H, Nq, Dv], f"O must have shape {[B, H, Nq, Dv]} but see {list(o.shape)}")
+    with torch.cuda.device(o.device):
+        check(LIB.ac4k_mha_nvfp4_fwd(o.data_ptr(), _I64x4(*o.stride()), q.data_ptr(), q_sf.data_ptr(),
+                                     q_global_scale.data_ptr(), k.data_ptr(), k_sf.data_ptr(),
+                                     k_global_scale.data_ptr(), v.data_ptr(), v_sf.data_ptr(),
+                                     v_global_scale.data_ptr(), B, H, Nq, Nkv, Dqk, Dv, float(sm_scale),
+                                     SF_TILE128X4, _stream(o)),
+              "mha_nvfp4_fwd")
+
+
 # Names that ac4k_kernel/__init__.py:19-34 imports eagerly; present so the import succeeds.
-mha_nvfp4_fwd = _out_of_scope("mha_nvfp4_fwd")
 mha_int8_x_fp8_fwd = _out_of_scope("mha_int8_x_fp8_fwd")
 rope3d = _out_of_scope("rope3d")

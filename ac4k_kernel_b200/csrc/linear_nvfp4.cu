@@ -424,10 +424,10 @@ struct TmapKey {
   }
 };
 struct TmapEntry { TmapKey key; CUtensorMap map; };
-enum { kTmapOperand = 0, kTmapWords = 1, kTmapOut16 = 2 };
+enum { kTmapOperand = 0, kTmapWords = 1, kTmapOut16 = 2, kTmapOut16Wide = 3, kTmapOperand64 = 4 };
 
-// kind kTmapOperand: bytes, 128-byte swizzle; kTmapWords: 32-bit words, not swizzled; kTmapOut16: 16-bit
-// elements, 128-byte swizzle.
+// kind kTmapOperand: bytes, 128-byte swizzle; kTmapWords: 32-bit words, not swizzled; kTmapOut16 / Wide: 16-bit
+// elements, 128-byte swizzle / not swizzled.
 static int encode_cached(int kind, const void *ptr, int64_t d0, int64_t d1, int64_t pitch, int box0, int box1,
                          CUtensorMap *out) {
   static std::mutex mu;
@@ -442,8 +442,11 @@ static int encode_cached(int kind, const void *ptr, int64_t d0, int64_t d1, int6
   }
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return fail(AC4K_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
-  const int esize = kind == kTmapOperand ? 1 : (kind == kTmapWords ? 4 : 2);
-  const CUtensorMapDataType dt = kind == kTmapOperand ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+  const bool bytes = kind == kTmapOperand || kind == kTmapOperand64;
+  const int esize = bytes ? 1 : (kind == kTmapWords ? 4 : 2);
+  const CUtensorMapSwizzle swz = (kind == kTmapOperand || kind == kTmapOut16) ? CU_TENSOR_MAP_SWIZZLE_128B
+                                 : (kind == kTmapOperand64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE);
+  const CUtensorMapDataType dt = bytes ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                  : (kind == kTmapWords ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16);
   cuuint64_t gdim[2] = {(cuuint64_t)d0, (cuuint64_t)d1};
   cuuint64_t gstride[1] = {(cuuint64_t)pitch * esize};
@@ -452,7 +455,7 @@ static int encode_cached(int kind, const void *ptr, int64_t d0, int64_t d1, int6
   CUtensorMap m;
   CUresult r = enc(&m, dt, 2,
                    const_cast<void *>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   kind == kTmapWords ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                   swz,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail((int)r > 0 ? (int)r : 999, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   {
@@ -478,6 +481,16 @@ int get_tmap_sf_tiled(const void *ptr, int64_t row_blocks, int64_t kt, int box_k
 
 int get_tmap_out16(const void *ptr, int64_t rows, int64_t cols, int64_t ld, CUtensorMap *out) {
   return encode_cached(kTmapOut16, ptr, cols, rows, ld, 64, 32, out);
+}
+
+// packed operand [rows, row_bytes] whose contraction rows are 64 bytes: boxes of 64 bytes x box_rows rows, 64-byte swizzle
+int get_tmap64(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUtensorMap *out) {
+  return encode_cached(kTmapOperand64, ptr, row_bytes, rows, row_bytes, 64, box_rows, out);
+}
+
+// the same output in boxes of 128 columns x 16 rows, not swizzled (the fused all-gather's 256-byte row pieces)
+int get_tmap_out16_wide(const void *ptr, int64_t rows, int64_t cols, int64_t ld, CUtensorMap *out) {
+  return encode_cached(kTmapOut16Wide, ptr, cols, rows, ld, 128, 16, out);
 }
 
 int get_device_info(DeviceInfo *out) {
@@ -737,10 +750,12 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
     // stores are clipped at this launch's last column
     DstMaps dm;
     for (int i = 0; i < kMaxDst; ++i) dm.m[i] = ta;
-    if (!requant) {
+    if (!requant && a.n_dst == 1) {
       if (int e = get_tmap_out16(D, M, a.col_off + N, a.ldd, &dm.m[0])) return e;
+    } else if (!requant) {
+      if (int e = get_tmap_out16_wide(D, M, a.col_off + N, a.ldd, &dm.m[0])) return e;
       for (int i = 1; i < a.n_dst; ++i)
-        if (int e = get_tmap_out16(a.D_more[i - 1], M, a.col_off + N, a.ldd, &dm.m[i])) return e;
+        if (int e = get_tmap_out16_wide(a.D_more[i - 1], M, a.col_off + N, a.ldd, &dm.m[i])) return e;
     }
     return launch_linear_2cta(d_dtype, tiled, ta, tb, tsa, tsb, dm, a, stream);
   }

@@ -1,6 +1,7 @@
-"""Operators of the NVFP4 linear path (mirrors python/ac4k_kernel/ops/__init__.py for the
-names this build covers)."""
+"""Operators of the NVFP4 linear path and NVFP4 attention (mirrors python/ac4k_kernel/ops/__init__.py
+for the names this build covers)."""
+from .attention import attention
 from .linear import linear, linear_nvfp4, linear_requant
 from .quant import quantize, quantize_nvfp4, quantize_fp8, quantize_int8
 
-__all__ = ["quantize", "linear", "quantize_nvfp4", "quantize_fp8", "quantize_int8", "linear_nvfp4", "linear_requant"]
+__all__ = ["quantize", "linear", "attention", "quantize_nvfp4", "quantize_fp8", "quantize_int8", "linear_nvfp4", "linear_requant"]

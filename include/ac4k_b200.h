@@ -133,9 +133,13 @@ int ac4k_linear_nvfp4_noalloc(void *D, int d_dtype, const void *A, const void *A
  *              entry 0 is normally this GPU's own buffer, the others are peers' buffers mapped into
  *              this process (see ac4k_peer_open).  The launch writes columns
  *              [col_off, col_off + N) of every destination; ldd and col_off are multiples of 8.
- * Peer stores travel over NVLink as plain st.global (no TMA, no multicast).  They are complete
- * when the kernel has finished; a peer may read its buffer after it has synchronised with this
- * GPU's stream past the launch (e.g. a stream-ordered barrier among the ranks). */
+ * Every piece of a tile is staged once in shared memory and stored to each destination with one TMA
+ * store (bulk tensor store, no multicast; the peers' buffers are reached over NVLink).  The stores are
+ * complete when the kernel has finished; a peer may read its buffer after it has synchronised with this
+ * GPU's stream past the launch (e.g. a stream-ordered barrier among the ranks).  That barrier orders the
+ * reads of step i after the stores of step i - not the stores of step i+1 after a slower rank's reads of
+ * step i: callers that launch step after step use two destination sets in turn, or synchronise the ranks
+ * once more between the readers of a buffer and the next launch that writes it. */
 int ac4k_linear_nvfp4_gather(void *const *D_dsts, int n_dst, int64_t ldd, int64_t col_off, int d_dtype,
                              const void *A, const void *A_sf, const float *A_gs, const void *B,
                              const void *B_sf, const float *B_gs, const void *bias, int bias_dtype,
@@ -155,6 +159,21 @@ int ac4k_linear_nvfp4_requant(void *out_fp4, void *out_sf, const float *out_gs, 
                               const void *A, const void *A_sf, const float *A_gs, const void *B,
                               const void *B_sf, const float *B_gs, const void *bias, int bias_dtype,
                               int64_t M, int64_t N, int64_t K, int sf_layout, ac4k_stream_t stream);
+
+/* O = softmax(sm_scale * Q K^T) V with Q, K, V and the probabilities in NVFP4, bf16 output.
+ * Replaces ac4k::mha_nvfp4_fwd, include/ac4k_kernel/ops.h:13-17, lib/cuda_bindings.cc:49-56,
+ * lib/cuda/sm120/mha_nvfp4.cu:897-1077 (checks) and :322-893 (kernel).
+ *   Q: [B, H, Nq, align64(Dqk)/2] bytes, K: [B, H, Nkv, align64(Dqk)/2] bytes (quantised along the head dimension);
+ *   V: [B, H, Dv, align64(Nkv)/2] bytes, quantised along the keys with the K permutation (swizzle = 1);
+ *   Q_sf, K_sf, V_sf: block scales of those quantiser calls in the tiled layout (AC4K_SF_TILE128X4);
+ *   *_gs: device fp32 scalars; O: bf16, element (b, h, n, d) at O + b*o_stride[0] + h*o_stride[1] + n*o_stride[2] +
+ *   d*o_stride[3] (elements), so both the [B, H, N, D] and the permuted [B, N, H, D] outputs of the reference work.
+ * Built for 64 < Dqk <= 128 and 64 < Dv <= 128 (the reference allows up to 128); other head dimensions and the
+ * reference's scale layout return AC4K_ERR_UNSUPPORTED. */
+int ac4k_mha_nvfp4_fwd(void *O, const int64_t o_stride[4], const void *Q, const void *Q_sf, const float *Q_gs,
+                       const void *K, const void *K_sf, const float *K_gs, const void *V, const void *V_sf,
+                       const float *V_gs, int64_t B, int64_t H, int64_t Nq, int64_t Nkv, int64_t Dqk, int64_t Dv,
+                       float sm_scale, int sf_layout, ac4k_stream_t stream);
 
 /* Device buffers that the other processes of the node can map (CUDA IPC), for the destinations of
  * ac4k_linear_nvfp4_gather.  No counterpart in the reference.

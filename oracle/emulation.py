@@ -314,3 +314,87 @@ def quantize_int8_ref(x, cross_dim=0, reduce_dim=1, scale_max: int = 127):
     q = torch.round(y).clamp(-128, 127)
     q = torch.where(torch.isnan(y), torch.zeros_like(q), q)
     return q.to(torch.int8).reshape(*lead, m, kp), sf
+
+
+# ----------------------------------------------------------------------------------------
+# NVFP4 attention
+# ----------------------------------------------------------------------------------------
+P_GLOBAL_RCP = 2688.0     # 6 * 448: reciprocal of the fixed global scale of P (mha_nvfp4.cu:253)
+LOG2E = 1.4426950408889634
+
+
+def _quantize_p_tile(p: torch.Tensor):
+    """[rows, 128] fp32 probabilities (already in the stored key order) -> their NVFP4 values as fp32,
+    still divided by the global scale: e2m1 * e4m3 per block of 16 (mha_nvfp4.cu:246-319: block scale
+    e4m3(2688 * (max / 6)), elements scaled by 2688 / scale)."""
+    rows = p.shape[0]
+    blk = p.reshape(rows, -1, BLOCK)
+    one_sixth = torch.tensor(ONE_SIXTH, dtype=torch.float32, device=p.device)
+    g = torch.tensor(P_GLOBAL_RCP, dtype=torch.float32, device=p.device)
+    sfb = e4m3_rne_sat_bits(g * (blk.amax(dim=-1) * one_sixth))
+    sff = e4m3_bits_to_float(sfb)
+    scale = torch.where(sff == 0, torch.zeros_like(sff), g / sff)
+    codes = e2m1_rne_sat_codes(blk * scale.unsqueeze(-1))
+    return (e2m1_codes_to_float(codes) * sff.unsqueeze(-1)).reshape(rows, -1)
+
+
+def mha_nvfp4_ref(q, q_sf, q_g, k, k_sf, k_g, v, v_sf, v_g, sm_scale: float, nkv: int,
+                  tile: int = 128, out_dtype=torch.bfloat16):
+    """softmax(sm_scale * Q K^T) V on quantised operands, walking the keys in tiles of `tile` with a running
+    maximum and sum the way the attention kernels do (lib/cuda/sm120/mha_nvfp4.cu:640-760 per key tile:
+    S, row max, P = exp(S - max) in fp32, l += sum(P), P re-quantised to NVFP4, O = O * exp(max_old - max)
+    + P V; :860-893: O * v_g / (2688 * l)).
+      q: [B, H, Nq, Dp/2], k: [B, H, Nkv, Dp/2], v: [B, H, Dv, align64(Nkv)/2] packed, V's keys in the
+      permuted order of `quantize(v, 3, N_dim, swizzle=True)`; scales in either layout; nkv = true key count.
+    Returns [B, H, Nq, Dv]."""
+    B, H, nq = q.shape[0], q.shape[1], q.shape[2]
+    dv = v.shape[2]
+    kvp = v.shape[3] * 2
+    dev = q.device
+    c1 = (q_g.to(torch.float32) * k_g.to(torch.float32) * torch.tensor(sm_scale, dtype=torch.float32, device=dev)
+          * torch.tensor(LOG2E, dtype=torch.float32, device=dev))
+    # stored position -> key index inside every group of 32 (inverse view of permute_k_nvfp4)
+    pos = torch.arange(kvp, device=dev)
+    key_of_pos = permute_k_nvfp4(pos.to(torch.float32)).to(torch.long)
+    out = torch.empty((B, H, nq, dv), dtype=out_dtype, device=dev)
+    layout = "ac4k" if q_sf.dim() == 5 else "128x4"
+    for b in range(B):
+        for h in range(H):
+            qd = dequantize_nvfp4_ref(q[b, h], q_sf[b, h], None, layout)
+            kd = dequantize_nvfp4_ref(k[b, h], k_sf[b, h], None, layout)
+            vd = dequantize_nvfp4_ref(v[b, h], v_sf[b, h], None, layout)          # [Dv, kvp], permuted keys
+            s_all = qd @ kd.t()                                                    # [Nq, Nkv] before the scales
+            m = torch.full((nq,), float("-inf"), dtype=torch.float32, device=dev)
+            l = torch.zeros((nq,), dtype=torch.float32, device=dev)
+            o = torch.zeros((nq, dv), dtype=torch.float32, device=dev)
+            for j0 in range(0, nkv, tile):
+                j1 = min(j0 + tile, nkv)
+                s = s_all[:, j0:j1]
+                m_new = torch.maximum(m, s.amax(dim=1) * c1)
+                p = torch.exp2(s * c1 - m_new.unsqueeze(1))
+                a = torch.exp2(m - m_new)
+                l = l * a + p.sum(dim=1)
+                # P in the stored key order of this tile, zero where the key does not exist
+                width = min(tile, kvp - j0)
+                pf = torch.zeros((nq, width), dtype=torch.float32, device=dev)
+                keys = key_of_pos[j0:j0 + width]
+                valid = keys < nkv
+                pf[:, valid] = p[:, keys[valid] - j0]
+                pq = _quantize_p_tile(pf)
+                o = o * a.unsqueeze(1) + pq @ vd[:, j0:j0 + width].t()
+                m = m_new
+            res = o * (v_g.to(torch.float32) / (torch.tensor(P_GLOBAL_RCP, device=dev) * l)).unsqueeze(1)
+            out[b, h] = res.to(out_dtype)
+    return out
+
+
+def attention_nvfp4_ref(q, k, v, layout: str = "BNHD", sf_layout: str = "128x4"):
+    """The reference's `attention(..., precision="nvfp4")` (python/ac4k_kernel/ops/attention.py:102-138) on this
+    module's quantiser: q, k quantised along the head dimension, v along the keys with the K permutation."""
+    n_dim = 1 if layout == "BNHD" else 2
+    nkv = k.shape[n_dim]
+    qq, qs, qg = quantize_nvfp4_ref(q, n_dim, 3, sf_layout=sf_layout)
+    kq, ks, kg = quantize_nvfp4_ref(k, n_dim, 3, sf_layout=sf_layout)
+    vq, vs, vg = quantize_nvfp4_ref(v, 3, n_dim, swizzle=True, sf_layout=sf_layout)
+    o = mha_nvfp4_ref(qq, qs, qg, kq, ks, kg, vq, vs, vg, 1.0 / (q.shape[-1] ** 0.5), nkv)
+    return o.permute(0, 2, 1, 3).contiguous() if layout == "BNHD" else o
