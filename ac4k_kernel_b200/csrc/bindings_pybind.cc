@@ -194,18 +194,63 @@ void global_scale_bf16(torch::Tensor &out, torch::Tensor const &x, double max_sc
   TORCH_CHECK(rc == 0, "ac4k_global_scale_bf16: ", ac4k_last_error());
 }
 
-// The attention and RoPE operators of the reference module are different operators from the linear path this
-// library covers; the names exist so that `import` and introspection behave like the reference's module.
-void mha_nvfp4_fwd(torch::Tensor &, torch::Tensor &, torch::Tensor &, torch::Tensor &, torch::Tensor &, torch::Tensor &,
-                   torch::Tensor &, torch::Tensor &, torch::Tensor &, torch::Tensor &, float) {
-  TORCH_CHECK(false, "mha_nvfp4_fwd is not part of the sm100 linear-path library");
+// ops.h:13-17; checks of mha_nvfp4.cu:897-1010.  O may be a permuted view ([B, N, H, D] storage): the kernel addresses it
+// by strides.  Block scales in the tiled layout [B, H, ceil(rows/128), K/64, 32, 4, 4].
+void mha_nvfp4_fwd(torch::Tensor &o, torch::Tensor &q, torch::Tensor &q_sf, torch::Tensor &q_global_scale, torch::Tensor &k,
+                   torch::Tensor &k_sf, torch::Tensor &k_global_scale, torch::Tensor &v, torch::Tensor &v_sf,
+                   torch::Tensor &v_global_scale, float sm_scale) {
+  check_cuda(q, at::kByte, "Q");
+  TORCH_CHECK(q.dim() == 4, "Q must be a 4D tensor");
+  const int64_t B = q.size(0), H = q.size(1), Nq = q.size(2), Dqk = q.size(3) * 2;
+  TORCH_CHECK(Dqk % 16 == 0, "Dqk must be multiple of 16");
+  TORCH_CHECK(Dqk <= 128, "Dqk must be less than 128");
+  check_cuda(k, at::kByte, "K");
+  TORCH_CHECK(k.dim() == 4, "K must be a 4D tensor");
+  TORCH_CHECK(k.size(0) == B, "K must have the same batch size as Q");
+  TORCH_CHECK(k.size(1) == H, "K must have the same head number as Q");
+  const int64_t Nkv = k.size(2);
+  TORCH_CHECK(k.size(3) == q.size(3), "K must have the same dim as Q");
+  check_cuda(v, at::kByte, "V");
+  TORCH_CHECK(v.dim() == 4, "V must be a 4D tensor");
+  TORCH_CHECK(v.size(0) == B, "V must have the same batch size as Q");
+  TORCH_CHECK(v.size(1) == H, "V must have the same head number as Q");
+  const int64_t Dv = v.size(2);
+  TORCH_CHECK(v.size(3) * 2 == align_up(Nkv, 64), "V must have the same sequence length as K");
+  TORCH_CHECK(Dv <= 128, "Dv must be less than 128");
+  struct Sf { const char *name; torch::Tensor *t; int64_t rows, red; };
+  const Sf sfs[3] = {{"q_sf", &q_sf, Nq, Dqk}, {"k_sf", &k_sf, Nkv, Dqk}, {"v_sf", &v_sf, Dv, Nkv}};
+  for (const Sf &s : sfs) {
+    check_cuda(*s.t, at::kFloat8_e4m3fn, s.name);
+    TORCH_CHECK(s.t->dim() == 7, s.name, ": the sm100 attention kernel reads block scales in the tiled layout "
+                "[B, H, ceil(rows/128), K/64, 32, 4, 4]; the [.., K/64, rows, 4] layout is not built");
+    const std::vector<int64_t> want = {B, H, ceil_div(s.rows, 128), ceil_div(s.red, 64), 32, 4, 4};
+    TORCH_CHECK(s.t->sizes().vec() == want, "Meet invalid ", s.name, " shape");
+  }
+  for (torch::Tensor *g : {&q_global_scale, &k_global_scale, &v_global_scale}) {
+    check_cuda(*g, at::kFloat, "global_scale");
+    TORCH_CHECK(g->dim() == 0, "global_scale must be a scalar");
+  }
+  TORCH_CHECK(o.is_cuda(), "O must be a CUDA tensor");
+  TORCH_CHECK(o.scalar_type() == at::kBFloat16, "O must be a bfloat16 tensor");
+  TORCH_CHECK(o.dim() == 4 && o.size(0) == B && o.size(1) == H && o.size(2) == Nq && o.size(3) == Dv,
+              "O must have shape [B, H, Nq, Dv]");
+  const c10::cuda::CUDAGuard guard(o.device());
+  const int64_t os[4] = {o.stride(0), o.stride(1), o.stride(2), o.stride(3)};
+  const int rc = ac4k_mha_nvfp4_fwd(o.data_ptr(), os, q.data_ptr(), q_sf.data_ptr(), q_global_scale.data_ptr<float>(),
+                                    k.data_ptr(), k_sf.data_ptr(), k_global_scale.data_ptr<float>(), v.data_ptr(),
+                                    v_sf.data_ptr(), v_global_scale.data_ptr<float>(), B, H, Nq, Nkv, Dqk, Dv, sm_scale,
+                                    AC4K_SF_TILE128X4, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "ac4k_mha_nvfp4_fwd: ", ac4k_last_error());
 }
+
+// The int8 x fp8 attention and RoPE operators of the reference module are different operators from the NVFP4 path this
+// library covers; the names exist so that `import` and introspection behave like the reference's module.
 void mha_int8_x_fp8_fwd(torch::Tensor &, torch::Tensor &, torch::Tensor &, int, torch::Tensor &, torch::Tensor &, int,
                         torch::Tensor &, torch::Tensor &, float) {
-  TORCH_CHECK(false, "mha_int8_x_fp8_fwd is not part of the sm100 linear-path library");
+  TORCH_CHECK(false, "mha_int8_x_fp8_fwd is not part of the sm100 NVFP4 library");
 }
 void rope3d(const torch::Tensor &, const torch::Tensor &, const torch::Tensor &, torch::Tensor &) {
-  TORCH_CHECK(false, "rope3d is not part of the sm100 linear-path library");
+  TORCH_CHECK(false, "rope3d is not part of the sm100 NVFP4 library");
 }
 
 }  // namespace ac4k
@@ -216,7 +261,7 @@ PYBIND11_MODULE(_cuda_ops, m) {
   m.attr("__arch_description__") = ac4k_arch_description();
   m.attr("__backend__") = ac4k_backend();
   m.attr("__version__") = ac4k_version();
-  m.def("mha_nvfp4_fwd", &ac4k::mha_nvfp4_fwd, "Multi-Head Attention Forward (NVFP4): not built for sm100");
+  m.def("mha_nvfp4_fwd", &ac4k::mha_nvfp4_fwd, "Multi-Head Attention Forward (NVFP4)");
   m.def("mha_int8_x_fp8_fwd", &ac4k::mha_int8_x_fp8_fwd, "Multi-Head Attention Forward (QK=INT8, PV=FP8): not built for sm100");
   m.def("quantize_nvfp4", &ac4k::quantize_nvfp4, "Quantize bfloat16 tensor to NVFP4 format");
   m.def("quantize_fp8", &ac4k::quantize_fp8, "Quantize bfloat16 tensor to FP8 format");

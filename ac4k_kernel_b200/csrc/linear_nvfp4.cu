@@ -424,10 +424,10 @@ struct TmapKey {
   }
 };
 struct TmapEntry { TmapKey key; CUtensorMap map; };
-enum { kTmapOperand = 0, kTmapWords = 1, kTmapOut16 = 2, kTmapOut16Wide = 3, kTmapOperand64 = 4 };
+enum { kTmapOperand = 0, kTmapWords = 1, kTmapOut16 = 2, kTmapOperand64 = 3 };
 
-// kind kTmapOperand: bytes, 128-byte swizzle; kTmapWords: 32-bit words, not swizzled; kTmapOut16 / Wide: 16-bit
-// elements, 128-byte swizzle / not swizzled.
+// kind kTmapOperand / kTmapOperand64: bytes, 128- / 64-byte swizzle; kTmapWords: 32-bit words, not swizzled;
+// kTmapOut16: 16-bit elements, 128-byte swizzle.
 static int encode_cached(int kind, const void *ptr, int64_t d0, int64_t d1, int64_t pitch, int box0, int box1,
                          CUtensorMap *out) {
   static std::mutex mu;
@@ -486,11 +486,6 @@ int get_tmap_out16(const void *ptr, int64_t rows, int64_t cols, int64_t ld, CUte
 // packed operand [rows, row_bytes] whose contraction rows are 64 bytes: boxes of 64 bytes x box_rows rows, 64-byte swizzle
 int get_tmap64(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUtensorMap *out) {
   return encode_cached(kTmapOperand64, ptr, row_bytes, rows, row_bytes, 64, box_rows, out);
-}
-
-// the same output in boxes of 128 columns x 16 rows, not swizzled (the fused all-gather's 256-byte row pieces)
-int get_tmap_out16_wide(const void *ptr, int64_t rows, int64_t cols, int64_t ld, CUtensorMap *out) {
-  return encode_cached(kTmapOut16Wide, ptr, cols, rows, ld, 128, 16, out);
 }
 
 int get_device_info(DeviceInfo *out) {
@@ -753,9 +748,9 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
     if (!requant && a.n_dst == 1) {
       if (int e = get_tmap_out16(D, M, a.col_off + N, a.ldd, &dm.m[0])) return e;
     } else if (!requant) {
-      if (int e = get_tmap_out16_wide(D, M, a.col_off + N, a.ldd, &dm.m[0])) return e;
+      if (int e = get_tmap_out16(D, M, a.col_off + N, a.ldd, &dm.m[0])) return e;
       for (int i = 1; i < a.n_dst; ++i)
-        if (int e = get_tmap_out16_wide(a.D_more[i - 1], M, a.col_off + N, a.ldd, &dm.m[i])) return e;
+        if (int e = get_tmap_out16(a.D_more[i - 1], M, a.col_off + N, a.ldd, &dm.m[i])) return e;
     }
     return launch_linear_2cta(d_dtype, tiled, ta, tb, tsa, tsb, dm, a, stream);
   }

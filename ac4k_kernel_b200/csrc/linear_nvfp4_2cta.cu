@@ -516,49 +516,30 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         // different rows, and that scatter was measured to slow the next tile's main loop down by
         // 20 % while it lasted.  So each half (64 columns = 128 bytes per row) goes through this warp's
         // 4 KB staging buffer in the 128-byte-swizzled order and leaves as one TMA store of 32 rows,
-        // clipped by the tensor map at the edges of the output.
+        // clipped by the tensor map at the edges of the output.  With several destinations (the fused
+        // all-gather: this GPU's buffer and the peers', reached over NVLink) the same buffer is stored
+        // once per destination.
         const uint32_t stage_buf = sOut + (uint32_t)(half * 4 + q) * OUT_STAGE_BYTES;
         const int y0 = tm * BMP + (int)rank * 128 + q * 32;
-        if (EPI == EPI_GATHER) {
-          // Fused all-gather: the step is bound by NVLink, and NVLink moves 256-byte pieces with less overhead
-          // than 128-byte ones.  So the staging buffer holds 16 whole 256-byte row segments (this warp's 128
-          // columns, not swizzled; the bank conflicts of writing one row per lane do not matter here) and
-          // leaves as one TMA store of 16 rows x 256 bytes per destination: this GPU's buffer first, then the
-          // peers in turn, starting behind this rank so that the ranks do not all write to the same GPU at once.
 #pragma unroll
-          for (int pass = 0; pass < 2; ++pass) {
-            if (col0 >= p.N || y0 + 16 * pass >= p.M) break;   // warp-uniform
-            if (lane == 0) bulk_wait_group_read0();            // the previous stores have read the buffer
-            __syncwarp();
-            if ((lane >> 4) == pass) {
+        for (int h2 = 0; h2 < 2; ++h2) {
+          const int x0 = (int)col_base + 64 * h2;
+          if (col0 + 64 * h2 >= p.N || y0 >= p.M) break;     // warp-uniform: nothing of this box is inside the output
+          if (lane == 0) bulk_wait_group_read0();            // the previous store has read the buffer
+          __syncwarp();
 #pragma unroll
-              for (int c = 0; c < 16; ++c)
-                st_shared_v4u(stage_buf + (lane & 15) * 256 + c * 16, w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+          for (int c = 0; c < 8; ++c)
+            st_shared_v4u(stage_buf + lane * 128 + ((c ^ (lane & 7)) << 4), w[32 * h2 + 4 * c], w[32 * h2 + 4 * c + 1],
+                          w[32 * h2 + 4 * c + 2], w[32 * h2 + 4 * c + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&dmaps.m[0], x0, y0, stage_buf);
+            if (EPI == EPI_GATHER) {
+              // peers in turn, starting behind this rank, so that the ranks do not all write to the same GPU at once
+              for (int d = 1; d < p.n_dst; ++d) tma_store_2d(&dmaps.m[d], x0, y0, stage_buf);
             }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              for (int d = 0; d < p.n_dst; ++d) tma_store_2d(&dmaps.m[d], (int)col_base, y0 + 16 * pass, stage_buf);
-              bulk_commit_group();
-            }
-          }
-        } else {
-#pragma unroll
-          for (int h2 = 0; h2 < 2; ++h2) {
-            const int x0 = (int)col_base + 64 * h2;
-            if (col0 + 64 * h2 >= p.N || y0 >= p.M) break;     // warp-uniform: nothing of this box is inside the output
-            if (lane == 0) bulk_wait_group_read0();            // the previous store has read the buffer
-            __syncwarp();
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-              st_shared_v4u(stage_buf + lane * 128 + ((c ^ (lane & 7)) << 4), w[32 * h2 + 4 * c], w[32 * h2 + 4 * c + 1],
-                            w[32 * h2 + 4 * c + 2], w[32 * h2 + 4 * c + 3]);
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_2d(&dmaps.m[0], x0, y0, stage_buf);
-              bulk_commit_group();
-            }
+            bulk_commit_group();
           }
         }
       }

@@ -86,3 +86,23 @@ def test_same_bytes_as_the_ctypes_path(mod):
             res.append((out, sf))
         assert torch.equal(res[0][0].view(torch.uint8), res[1][0].view(torch.uint8)) and torch.equal(res[0][1], res[1][1])
     torch.cuda.synchronize()
+
+
+@pytest.mark.gpu
+def test_attention_same_bytes_as_the_ctypes_path(mod):
+    from ac4k_kernel_b200 import _cuda_ops as ct
+    from ac4k_kernel_b200.ops import quantize
+    g = torch.Generator(device="cuda").manual_seed(4)
+    B, N, H, D = 2, 200, 3, 128
+    q, k, v = (torch.randn((B, N, H, D), generator=g, device="cuda").bfloat16() for _ in range(3))
+    qq, qs, qg = quantize(q, 1, 3, sf_layout="128x4")
+    kq, ks, kg = quantize(k, 1, 3, sf_layout="128x4")
+    vq, vs, vg = quantize(v, 3, 1, swizzle=True, sf_layout="128x4")
+    outs = []
+    for fn in (mod, ct):
+        o = torch.empty((B, N, H, D), dtype=torch.bfloat16, device="cuda")
+        fn.mha_nvfp4_fwd(o.permute(0, 2, 1, 3), qq, qs, qg, kq, ks, kg, vq, vs, vg, D ** -0.5)
+        outs.append(o)
+    assert torch.equal(outs[0], outs[1])
+    with pytest.raises(RuntimeError, match="tiled layout"):
+        mod.mha_nvfp4_fwd(outs[0].permute(0, 2, 1, 3), qq, quantize(q, 1, 3)[1], qg, kq, ks, kg, vq, vs, vg, 0.1)
