@@ -6,19 +6,22 @@
 // P = exp(S - max) re-quantised per 16 keys with the fixed global scale 1 / (6 * 448)
 // (mha_nvfp4.cu:246-319), O accumulated in fp32 and divided by the row sum at the end.
 //
-// One CTA per (batch, head, 128 query rows); it walks the keys in tiles of 128:
-//   warp 0     TMA producer: Q once; per key tile K [128 keys x D] and V^T [D x 128 keys] with their scale
-//              chunks, two stages
-//   warp 1     MMA issuer: S = Q K^T (tcgen05.mma kind::mxf4nvf4, M = 128 queries, N = 128 keys, K = D) into
-//              tensor memory; after the softmax warps have written P: O (+)= P V (M = 128, N = D, K = 128 keys).
-//              Block scales go from shared to tensor memory with tcgen05.cp in front of the MMAs.
-//   warps 2-5  softmax: thread = query row.  Read S from tensor memory, update the running maximum, rescale O
-//              in tensor memory when it moved, exponentiate, quantise P to e2m1 + e4m3 block scales and write
-//              both into shared memory in the layouts the tensor core reads (64-byte-swizzled K-major operand,
-//              32 x 16-byte scale chunks); at the end scale O by gV / (6 * 448 * row sum) and store bf16.
-// All contraction rows are 64 bytes (128 e2m1), hence the 64-byte swizzle everywhere.
+// One CTA per (batch, head, 128 query rows), two CTAs per SM; a CTA walks the keys in tiles of 64:
+//   warp 0     TMA producer: Q once; per key tile K [64 keys x D], V^T [D x 64 keys] and their scale chunks, four stages
+//   warp 1     MMA issuer: S = Q K^T (tcgen05.mma kind::mxf4nvf4, M = 128 queries, N = 64 keys, K = D) into tensor
+//              memory; once the softmax warps have written P: O (+)= P V (M = 128, N = D, K = 64 keys).  Block scales
+//              go from shared to tensor memory with tcgen05.cp in front of the MMAs.  S of the next key tile is
+//              issued as soon as the softmax warps hold the current S in registers, before the current P V.
+//   warps 2-5  softmax: thread = query row.  One pass over the 64 scores in registers: running maximum, O rescaled
+//              in tensor memory when a maximum of the warp moved, ex2.approx, row sum, P quantised to e2m1 + e4m3
+//              block scales (fixed global scale 1 / 2688) and written into shared memory in the layouts the tensor
+//              core reads (32-byte-swizzled K-major operand, 32 x 16-byte scale chunk); at the end
+//              O * gV / (2688 * row sum) is stored as bf16.
+// The softmax is what bounds this kernel (16 ex2 per clock per SM: 1024 cycles for 128 x 128 scores against 330 for
+// the four-bit MMAs), hence two CTAs per SM: eight softmax warps, and one CTA's MMAs, waits and TMEM traffic run under
+// the other's arithmetic.  Tensor memory per CTA: S 64 + O 128 + scales 24 columns of the 256 allocated.
 //
-// Supported: head dimension 128 for Q/K and V (padded by the quantiser), scales in the tiled layout
+// Supported: head dimensions in (64, 128] (padded to 128 by the quantiser), scales in the tiled layout
 // [.., 128-row block, K/64, 32 x 16 B]; V quantised along the keys (cross dimension = head dimension) with the
 // reference's K permutation (quantize(v, 3, N_dim, swizzle=True), python/ac4k_kernel/ops/attention.py:113-118):
 // P is written in the same key order, so scale blocks of P and V cover the same 16 keys as in the reference.
@@ -28,16 +31,24 @@ namespace ac4k {
 using namespace ptx;
 
 namespace mha {
-static constexpr int BQ = 128, BKV = 128, D = 128;
+static constexpr int BQ = 128, BKV = 64, D = 128;
 static constexpr int kThreads = 192;
-static constexpr int TILE_BYTES = 128 * 64;       // 128 rows x 128 e2m1
-static constexpr int SF_BYTES = 2 * 512;          // the two K = 64 steps of a 128-wide contraction
-static constexpr int KV_STAGES = 2;
-static constexpr int SMEM_BYTES = (2 + 2 * KV_STAGES) * TILE_BYTES + (2 + 2 * KV_STAGES) * SF_BYTES + 1024 + 256;
-// tensor memory: S (128 keys) | O (128 = D) | scales of Q, K, P, V (8 columns each: 4 per K = 64 step)
-static constexpr int S_COL = 0, O_COL = 128, SFQ_COL = 256, SFK_COL = 264, SFP_COL = 272, SFV_COL = 280;
-static constexpr int TMEM_COLS = 512;
+static constexpr int Q_BYTES = BQ * 64;           // 128 rows x 128 e2m1, 64-byte rows
+static constexpr int K_BYTES = BKV * 64;          // 64 keys x 128 e2m1
+static constexpr int V_BYTES = D * 32;            // 128 head-dimension rows x 64 keys, 32-byte rows
+static constexpr int P_BYTES = BQ * 32;           // 128 query rows x 64 keys
+static constexpr int SFQ_BYTES = 2 * 512;         // two K = 64 steps of D = 128, 128 rows
+static constexpr int SFK_BYTES = 2 * 512;         // the 128-key block the tile lies in (its half is picked by column)
+static constexpr int SFV_BYTES = 512;             // one K = 64 step, 128 head-dimension rows
+static constexpr int SFP_BYTES = 512;
+static constexpr int KV_STAGES = 4;
+static constexpr int STAGE_BYTES = K_BYTES + V_BYTES + SFK_BYTES + SFV_BYTES;       // 9 728
+static constexpr int SMEM_BYTES = Q_BYTES + P_BYTES + KV_STAGES * STAGE_BYTES + SFQ_BYTES + SFP_BYTES + 1024 + 256;
+// tensor memory columns
+static constexpr int S_COL = 0, O_COL = 64, SFQ_COL = 192, SFK_COL = 200, SFP_COL = 208, SFV_COL = 212;
+static constexpr int TMEM_COLS = 256;
 static constexpr float kPGlobal = 2688.0f;        // 6 * 448: reciprocal of P's fixed global scale
+static_assert(STAGE_BYTES % 512 == 0 && K_BYTES % 1024 == 0 && V_BYTES % 1024 == 0, "tile alignment");
 }  // namespace mha
 
 struct MhaArgs {
@@ -46,21 +57,33 @@ struct MhaArgs {
   void *O;
   int64_t o_b, o_h, o_n, o_d;           // strides of O in elements
   int B, H, Nq, Nkv, Dv;
-  int q_blocks, kv_blocks;              // ceil(Nq / 128), ceil(Nkv / 128)
-  int v_k64;                            // align64(Nkv) / 64: K = 64 steps of V^T that exist
+  int q_blocks, k_blocks;               // ceil(Nq / 128), ceil(Nkv / 128): 128-row blocks of the Q and K scales
+  int kv_tiles;                         // ceil(Nkv / 64): key tiles = K = 64 steps of V^T
   float sm_scale;
   unsigned int *status;
   unsigned long long wait_ns;
 };
 
-__device__ __forceinline__ uint32_t e4m3_byte(float s) {
-  uint16_t pk;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pk) : "f"(0.0f), "f"(s));
-  return pk & 0xFFu;
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
-__device__ __forceinline__ float e4m3_to_float(uint32_t b) {
-  const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
-  return __half2float(__half(h));
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// two non-negative fp32 -> two e4m3 bytes (a in the low byte) and their values back as fp32
+__device__ __forceinline__ uint32_t e4m3x2_round_trip(float a, float b, float &fa, float &fb) {
+  uint16_t pk;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pk) : "f"(b), "f"(a));
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(pk));
+  const __half2 hh = *reinterpret_cast<const __half2 *>(&h2);
+  fa = __low2float(hh);
+  fb = __high2float(hh);
+  return pk;
 }
 __device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
   asm volatile("st.shared::cta.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
@@ -72,41 +95,40 @@ __device__ __forceinline__ void tmem_st_32x32b_x32_f(uint32_t taddr, const float
   tmem_st_32x32b_x32(taddr, u);
 }
 
-__global__ void __launch_bounds__(mha::kThreads, 1)
+__global__ void __launch_bounds__(mha::kThreads, 2)
 mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                      const __grid_constant__ CUtensorMap tma_v, const MhaArgs p) {
   using namespace mha;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sQ = smem_base;
-  const uint32_t sK = sQ + TILE_BYTES;
-  const uint32_t sV = sK + KV_STAGES * TILE_BYTES;
-  const uint32_t sP = sV + KV_STAGES * TILE_BYTES;
-  const uint32_t sSFQ = sP + TILE_BYTES;
-  const uint32_t sSFK = sSFQ + SF_BYTES;
-  const uint32_t sSFV = sSFK + KV_STAGES * SF_BYTES;
-  const uint32_t sSFP = sSFV + KV_STAGES * SF_BYTES;
-  const uint32_t bars = sSFP + SF_BYTES;
-  const uint32_t q_full = bars, k_full = bars + 8, v_full = k_full + 8 * KV_STAGES, kv_empty = v_full + 8 * KV_STAGES;
-  const uint32_t s_full = kv_empty + 8 * KV_STAGES, p_full = s_full + 8, o_done = p_full + 8, tmem_slot = o_done + 8;
+  const uint32_t sP = sQ + Q_BYTES;
+  const uint32_t sKV = sP + P_BYTES;                 // per stage: K | V^T | SFK | SFV
+  const uint32_t sSFQ = sKV + KV_STAGES * STAGE_BYTES;
+  const uint32_t sSFP = sSFQ + SFQ_BYTES;
+  const uint32_t bars = sSFP + SFP_BYTES;
+  const uint32_t q_full = bars, kv_full = bars + 8, kv_empty = kv_full + 8 * KV_STAGES;
+  const uint32_t s_full = kv_empty + 8 * KV_STAGES, s_free = s_full + 8, p_full = s_free + 8, o_done = p_full + 8;
+  const uint32_t tmem_slot = o_done + 8;
   uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int64_t bh = (int64_t)b * p.H + h;
-  const int q_row0 = (int)(bh * p.Nq) + qt * BQ;          // row of Q in the [B*H*Nq, D/2] byte matrix
+  const int q_row0 = (int)(bh * p.Nq) + qt * BQ;    // row of Q in the [B*H*Nq, 64-byte] matrix
   const int k_row0 = (int)(bh * p.Nkv);
   const int v_row0 = (int)(bh * p.Dv);              // V^T rows of this head; rows past Dv belong to the next head and are not stored
+  const int n_tiles = p.kv_tiles;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < KV_STAGES; ++s) {
-      mbar_init(k_full + 8 * s, 1);
-      mbar_init(v_full + 8 * s, 1);
+      mbar_init(kv_full + 8 * s, 1);
       mbar_init(kv_empty + 8 * s, 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(p_full, 4);         // the four softmax warps
+    mbar_init(s_free, 4);         // the four softmax warps hold S in registers
+    mbar_init(p_full, 4);         // ... have written P and its scales
     mbar_init(o_done, 1);
     fence_barrier_init();
     prefetch_tmap(&tma_q);
@@ -127,45 +149,40 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     const uint32_t el = elect_one();
-    mbar_arrive_expect_tx_if(el, q_full, TILE_BYTES + SF_BYTES);
+    mbar_arrive_expect_tx_if(el, q_full, Q_BYTES + SFQ_BYTES);
     tma_load_2d_if(el, sQ, &tma_q, 0, q_row0, q_full);
-    bulk_load_1d_if(el, sSFQ, p.sfq + ((bh * p.q_blocks + qt) * 2) * 512, SF_BYTES, q_full);
+    bulk_load_1d_if(el, sSFQ, p.sfq + ((bh * p.q_blocks + qt) * 2) * 512, SFQ_BYTES, q_full);
     bool ok = true;
-    for (int j = 0; j < p.kv_blocks; ++j) {
-      const int s = j & 1;
-      ok = warp_all(mbar_wait(kv_empty + 8 * s, ((j >> 1) & 1) ^ 1, p.wait_ns));
+    for (int j = 0; j < n_tiles; ++j) {
+      const int s = j % KV_STAGES;
+      ok = warp_all(mbar_wait(kv_empty + 8 * s, ((j / KV_STAGES) & 1) ^ 1, p.wait_ns));
       if (!ok) break;
-      mbar_arrive_expect_tx_if(el, k_full + 8 * s, TILE_BYTES + SF_BYTES);
-      tma_load_2d_if(el, sK + s * TILE_BYTES, &tma_k, 0, k_row0 + j * BKV, k_full + 8 * s);
-      bulk_load_1d_if(el, sSFK + s * SF_BYTES, p.sfk + ((bh * p.kv_blocks + j) * 2) * 512, SF_BYTES, k_full + 8 * s);
-      // V^T: D rows x 128 keys; of the tile's two K = 64 steps only those below align64(Nkv) exist
-      const int nk = min(2, p.v_k64 - 2 * j);
-      mbar_arrive_expect_tx_if(el, v_full + 8 * s, TILE_BYTES + nk * 512);
-      tma_load_2d_if(el, sV + s * TILE_BYTES, &tma_v, j * 64, v_row0, v_full + 8 * s);
-      bulk_load_1d_if(el, sSFV + s * SF_BYTES, p.sfv + (bh * p.v_k64 + 2 * j) * 512, nk * 512, v_full + 8 * s);
+      const uint32_t st = sKV + s * STAGE_BYTES, fb = kv_full + 8 * s;
+      mbar_arrive_expect_tx_if(el, fb, STAGE_BYTES);
+      tma_load_2d_if(el, st, &tma_k, 0, k_row0 + j * BKV, fb);
+      tma_load_2d_if(el, st + K_BYTES, &tma_v, j * 32, v_row0, fb);
+      bulk_load_1d_if(el, st + K_BYTES + V_BYTES, p.sfk + ((bh * p.k_blocks + (j >> 1)) * 2) * 512, SFK_BYTES, fb);
+      bulk_load_1d_if(el, st + K_BYTES + V_BYTES + SFK_BYTES, p.sfv + (bh * p.kv_tiles + j) * 512, SFV_BYTES, fb);
     }
     if (!ok && el) atomicExch(p.status, kStatusTimeoutProducer);
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     const uint32_t el = elect_one();
-    constexpr uint32_t idesc = make_idesc_mxf4nvf4(128, 128);
+    constexpr uint32_t idesc_s = make_idesc_mxf4nvf4(128, BKV);
+    constexpr uint32_t idesc_o = make_idesc_mxf4nvf4(128, D);
     const uint64_t qdesc = make_smem_desc(sQ, 16, 512, kSwizzle64B);
-    const uint64_t pdesc = make_smem_desc(sP, 16, 512, kSwizzle64B);
+    const uint64_t pdesc = make_smem_desc(sP, 16, 256, kSwizzle32B);
     const uint64_t sfqdesc = make_smem_desc(sSFQ, 0, 128, kSwizzleNone);
     const uint64_t sfpdesc = make_smem_desc(sSFP, 0, 128, kSwizzleNone);
     const uint32_t t_s = tmem_base + S_COL, t_o = tmem_base + O_COL;
     bool ok = warp_all(mbar_wait(q_full, 0, p.wait_ns));
-    for (int j = 0; j < p.kv_blocks && ok; ++j) {
-      const int s = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      const uint64_t kdesc = make_smem_desc(sK + s * TILE_BYTES, 16, 512, kSwizzle64B);
-      const uint64_t vdesc = make_smem_desc(sV + s * TILE_BYTES, 16, 512, kSwizzle64B);
-      const uint64_t sfkdesc = make_smem_desc(sSFK + s * SF_BYTES, 0, 128, kSwizzleNone);
-      const uint64_t sfvdesc = make_smem_desc(sSFV + s * SF_BYTES, 0, 128, kSwizzleNone);
-      ok = warp_all(mbar_wait(k_full + 8 * s, ph, p.wait_ns));
-      if (!ok) break;
-      tc_fence_after();
-      // S = Q K^T over D = 128: two K = 64 steps, 32 bytes apart inside the 64-byte rows
+    // S of key tile j: two K = 64 steps over D, 32 bytes apart inside the 64-byte rows of Q and K.  The K scales of
+    // the tile's 64 keys are columns 2 * (j & 1) and the next of the 128-key block's four.
+    auto issue_s = [&](int j) {
+      const int s = j % KV_STAGES;
+      const uint32_t st = sKV + s * STAGE_BYTES;
+      const uint64_t kdesc = make_smem_desc(st, 16, 512, kSwizzle64B);
+      const uint64_t sfkdesc = make_smem_desc(st + K_BYTES + V_BYTES, 0, 128, kSwizzleNone);
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
         if (j == 0) tmem_cp_32x128b_warpx4_if(el, tmem_base + SFQ_COL + 4 * i, sfqdesc + 32 * i);
@@ -173,23 +190,37 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       }
 #pragma unroll
       for (int i = 0; i < 2; ++i)
-        mma_mxf4nvf4_if(el, t_s, qdesc + 2 * i, kdesc + 2 * i, idesc, tmem_base + SFQ_COL + 4 * i, tmem_base + SFK_COL + 4 * i,
-                        i > 0 ? 1u : 0u);
+        mma_mxf4nvf4_if(el, t_s, qdesc + 2 * i, kdesc + 2 * i, idesc_s, tmem_base + SFQ_COL + 4 * i,
+                        tmem_base + SFK_COL + 4 * i + 2 * (j & 1), i > 0 ? 1u : 0u);
       tc_commit_if(el, s_full);
+    };
+    if (ok) {
+      ok = warp_all(mbar_wait(kv_full, 0, p.wait_ns));
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+      }
+    }
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int s = j % KV_STAGES;
+      if (j + 1 < n_tiles) {
+        ok = warp_all(mbar_wait(kv_full + 8 * ((j + 1) % KV_STAGES), ((j + 1) / KV_STAGES) & 1, p.wait_ns));
+        if (!ok) break;
+        ok = warp_all(mbar_wait(s_free, j & 1, p.wait_ns));       // S of tile j is in the softmax warps' registers
+        if (!ok) break;
+        tc_fence_after();
+        issue_s(j + 1);
+      }
       // O (+)= P V once the softmax warps have written P (they have also rescaled O by then)
       ok = warp_all(mbar_wait(p_full, j & 1, p.wait_ns));
       if (!ok) break;
-      ok = warp_all(mbar_wait(v_full + 8 * s, ph, p.wait_ns));
-      if (!ok) break;
       tc_fence_after();
-      const int nk = min(2, p.v_k64 - 2 * j);
-      for (int i = 0; i < nk; ++i) {
-        tmem_cp_32x128b_warpx4_if(el, tmem_base + SFP_COL + 4 * i, sfpdesc + 32 * i);
-        tmem_cp_32x128b_warpx4_if(el, tmem_base + SFV_COL + 4 * i, sfvdesc + 32 * i);
-      }
-      for (int i = 0; i < nk; ++i)
-        mma_mxf4nvf4_if(el, t_o, pdesc + 2 * i, vdesc + 2 * i, idesc, tmem_base + SFP_COL + 4 * i, tmem_base + SFV_COL + 4 * i,
-                        (j > 0 || i > 0) ? 1u : 0u);
+      const uint32_t st = sKV + s * STAGE_BYTES;
+      const uint64_t vdesc = make_smem_desc(st + K_BYTES, 16, 256, kSwizzle32B);
+      const uint64_t sfvdesc = make_smem_desc(st + K_BYTES + V_BYTES + SFK_BYTES, 0, 128, kSwizzleNone);
+      tmem_cp_32x128b_warpx4_if(el, tmem_base + SFP_COL, sfpdesc);
+      tmem_cp_32x128b_warpx4_if(el, tmem_base + SFV_COL, sfvdesc);
+      mma_mxf4nvf4_if(el, t_o, pdesc, vdesc, idesc_o, tmem_base + SFP_COL, tmem_base + SFV_COL, j > 0 ? 1u : 0u);
       tc_commit_if(el, kv_empty + 8 * s);
       tc_commit_if(el, o_done);
     }
@@ -201,39 +232,49 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     const uint32_t t_s = tmem_base + lane_addr + S_COL, t_o = tmem_base + lane_addr + O_COL;
     // scores in units of log2: p = exp2(s * c1 - m)
-    const float c1 = __ldg(p.q_gs) * __ldg(p.k_gs) * p.sm_scale * 1.4426950408889634f;
+    // (c1 >= 0: the host rejects a negative sm_scale; the floor keeps -inf * c1 = -inf for masked keys when a global
+    // scale is 0)
+    const float c1 = fmaxf(__ldg(p.q_gs) * __ldg(p.k_gs) * p.sm_scale * 1.4426950408889634f, 1.17549435e-38f);
+    const uint32_t p_row = sP + row_l * 32;
+    const uint32_t p_xor = (uint32_t)((row_l >> 2) & 1) << 4;       // 32-byte swizzle: 16-byte chunk ^ ((row / 4) % 2)
     float m = -INFINITY, l = 0.0f;
     bool ok = true;
-    for (int j = 0; j < p.kv_blocks; ++j) {
-      ok = mbar_wait(s_full, j & 1, p.wait_ns);
+    for (int j = 0; j < n_tiles; ++j) {
+      ok = warp_all(mbar_wait(s_full, j & 1, p.wait_ns));
       if (!ok) break;
       tc_fence_after();
-      const int ncols = min(BKV, p.Nkv - j * BKV);       // keys of this tile that exist
-      // pass 1: row maximum
-      float mx = -INFINITY;
+      uint32_t r[64];
+      tmem_ld_32x32b_x64_sync(t_s, r);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free);
+      const int ncols = p.Nkv - j * BKV;                 // keys of this tile that exist (>= 64 except in the last tile)
+      if (ncols < BKV) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32_sync(t_s + 32 * c, r);
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (32 * c + i < ncols) mx = fmaxf(mx, __uint_as_float(r[i]));
+        for (int i = 0; i < BKV; ++i)
+          if (i >= ncols) r[i] = 0xff800000u;            // -inf: out of the maximum, probability 0
       }
-      const float m_new = fmaxf(m, mx * c1);
+      float mx0 = __uint_as_float(r[0]), mx1 = __uint_as_float(r[1]);
+#pragma unroll
+      for (int i = 2; i < BKV; i += 2) {
+        mx0 = fmaxf(mx0, __uint_as_float(r[i]));
+        mx1 = fmaxf(mx1, __uint_as_float(r[i + 1]));
+      }
+      const float m_new = fmaxf(m, fmaxf(mx0, mx1) * c1);
       if (j > 0) {
-        // the previous tile's P V must be complete before O is touched
-        ok = mbar_wait(o_done, (j - 1) & 1, p.wait_ns);
+        // the previous tile's P V must be complete before O or the P buffer is touched
+        ok = warp_all(mbar_wait(o_done, (j - 1) & 1, p.wait_ns));
         if (!ok) break;
-        tc_fence_after();
-        const float a = exp2f(m - m_new);
-        if (__any_sync(0xffffffffu, a != 1.0f)) {
+        const float a = ex2_approx(m - m_new);
+        if (__any_sync(0xffffffffu, m_new != m)) {
+          tc_fence_after();
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32_sync(t_o + 32 * c, r);
+            uint32_t ro[32];
+            tmem_ld_32x32b_x32_sync(t_o + 32 * c, ro);
             float v[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * a;
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(ro[i]) * a;
             tmem_st_32x32b_x32_f(t_o + 32 * c, v);
           }
           tmem_st_wait();
@@ -241,51 +282,57 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         l *= a;
       }
       m = m_new;
-      // pass 2: probabilities, row sum, NVFP4 quantisation of P (per 16 keys, global scale 1 / 2688)
-      uint32_t sfw[2] = {0u, 0u};
+      // probabilities, row sum, NVFP4 quantisation of P: four blocks of 16 keys, stored in the order of the reference's V
+      // quantiser ("swizzle": every 32 keys viewed as [4, 4, 2] and transposed to [4(b), 4(a), 2]), so that position n
+      // of P meets position n of V^T
+      float l0 = 0.0f, l1 = 0.0f;
+      uint32_t sfw = 0;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32_sync(t_s + 32 * c, r);
-        // keys are stored in the order the reference's V quantiser uses ("swizzle": every 32 keys viewed as
-        // [4, 4, 2] and transposed to [4(b), 4(a), 2]), so that position n of P meets position n of V^T
+      for (int g = 0; g < 2; ++g) {
         float pr[32];
 #pragma unroll
-        for (int n = 0; n < 32; ++n) {
-          const int i = (((n >> 1) & 3) * 4 + (n >> 3)) * 2 + (n & 1);     // key of this tile chunk held at position n
-          pr[n] = (32 * c + i < ncols) ? exp2f(__uint_as_float(r[i]) * c1 - m) : 0.0f;
-          l += pr[n];
+        for (int n = 0; n < 32; n += 2) {
+          const int i = 32 * g + (((n >> 1) & 3) * 4 + (n >> 3)) * 2;     // key held at positions n, n + 1
+          pr[n] = ex2_approx(fmaf(__uint_as_float(r[i]), c1, -m));
+          pr[n + 1] = ex2_approx(fmaf(__uint_as_float(r[i + 1]), c1, -m));
+          l0 += pr[n];
+          l1 += pr[n + 1];
         }
-        uint32_t codes[4];
+        float bm[2];
 #pragma unroll
         for (int blk = 0; blk < 2; ++blk) {
-          float bmax = pr[16 * blk];
+          float b0 = fmaxf(pr[16 * blk], pr[16 * blk + 1]), b1 = fmaxf(pr[16 * blk + 2], pr[16 * blk + 3]);
 #pragma unroll
-          for (int i = 1; i < 16; ++i) bmax = fmaxf(bmax, pr[16 * blk + i]);
-          const uint32_t sb = e4m3_byte(__fmul_rn(kPGlobal, __fmul_rn(bmax, kOneSixth)));
-          const float sd = e4m3_to_float(sb);
-          const float scale = sd != 0.0f ? __fdiv_rn(kPGlobal, sd) : 0.0f;
+          for (int i = 4; i < 16; i += 4) {
+            b0 = fmaxf(b0, fmaxf(pr[16 * blk + i], pr[16 * blk + i + 1]));
+            b1 = fmaxf(b1, fmaxf(pr[16 * blk + i + 2], pr[16 * blk + i + 3]));
+          }
+          bm[blk] = fmaxf(b0, b1);
+        }
+        float sd0, sd1;
+        const uint32_t sb2 = e4m3x2_round_trip(__fmul_rn(kPGlobal, __fmul_rn(bm[0], kOneSixth)),
+                                               __fmul_rn(kPGlobal, __fmul_rn(bm[1], kOneSixth)), sd0, sd1);
+        sfw |= sb2 << (16 * g);
+        const float sc[2] = {sd0 != 0.0f ? kPGlobal * rcp_approx(sd0) : 0.0f, sd1 != 0.0f ? kPGlobal * rcp_approx(sd1) : 0.0f};
+        uint32_t codes[4];
+#pragma unroll
+        for (int hh = 0; hh < 4; ++hh) {
           float x[8];
 #pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) x[i] = __fmul_rn(pr[16 * blk + 8 * hh + i], scale);
-            codes[2 * blk + hh] = f32x8_to_e2m1x8(x);
-          }
-          sfw[c >> 1] |= sb << (8 * (2 * (c & 1) + blk));
+          for (int i = 0; i < 8; ++i) x[i] = pr[8 * hh + i] * sc[hh >> 1];
+          codes[hh] = f32x8_to_e2m1x8(x);
         }
-        // 16-byte chunk c of this row's 64 bytes, 64-byte swizzle: chunk index ^ ((row / 2) % 4)
-        st_shared_v4u(sP + row_l * 64 + ((c ^ ((row_l >> 1) & 3)) << 4), codes[0], codes[1], codes[2], codes[3]);
+        st_shared_v4u(p_row + (((uint32_t)g << 4) ^ p_xor), codes[0], codes[1], codes[2], codes[3]);
       }
-      // scale chunk of K = 64 step i: 32 rows of 16 bytes, row l holding the words of rows l, 32 + l, 64 + l, 96 + l
-      st_shared_u32(sSFP + lane * 16 + q * 4, sfw[0]);
-      st_shared_u32(sSFP + 512 + lane * 16 + q * 4, sfw[1]);
+      l += l0 + l1;
+      // scale chunk: 32 rows of 16 bytes, row `lane` holding the words of query rows lane, 32 + lane, 64 + lane, 96 + lane
+      st_shared_u32(sSFP + lane * 16 + q * 4, sfw);
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
     }
-    if (ok) ok = mbar_wait(o_done, (p.kv_blocks - 1) & 1, p.wait_ns);
+    if (ok) ok = warp_all(mbar_wait(o_done, (n_tiles - 1) & 1, p.wait_ns));
     if (!ok) {
       if (lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue);
     } else {
@@ -295,8 +342,8 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(p.O) + (int64_t)b * p.o_b + (int64_t)h * p.o_h + (int64_t)n * p.o_n;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32_sync(t_o + 32 * c, r);
+        uint32_t ro[32];
+        tmem_ld_32x32b_x32_sync(t_o + 32 * c, ro);
         if (n < p.Nq) {
           if (p.o_d == 1 && p.Dv == D && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
@@ -304,8 +351,8 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
               uint32_t w[4];
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
-                const __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[8 * i + 2 * k]) * out_scale,
-                                                                __uint_as_float(r[8 * i + 2 * k + 1]) * out_scale);
+                const __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(ro[8 * i + 2 * k]) * out_scale,
+                                                                __uint_as_float(ro[8 * i + 2 * k + 1]) * out_scale);
                 w[k] = *reinterpret_cast<const uint32_t *>(&h2);
               }
               reinterpret_cast<uint4 *>(dst + 32 * c)[i] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -313,7 +360,7 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-              if (32 * c + i < p.Dv) dst[(int64_t)(32 * c + i) * p.o_d] = __float2bfloat16_rn(__uint_as_float(r[i]) * out_scale);
+              if (32 * c + i < p.Dv) dst[(int64_t)(32 * c + i) * p.o_d] = __float2bfloat16_rn(__uint_as_float(ro[i]) * out_scale);
           }
         }
       }
@@ -342,6 +389,7 @@ extern "C" int ac4k_mha_nvfp4_fwd(void *O, const int64_t o_stride[4], const void
   if (B < 0 || H < 0 || Nq < 0 || Nkv < 0) return fail(AC4K_ERR_SHAPE, "negative dimension");
   if (B == 0 || H == 0 || Nq == 0) return 0;
   if (Nkv == 0) return fail(AC4K_ERR_SHAPE, "attention over zero keys");
+  if (!(sm_scale >= 0.0f)) return fail(AC4K_ERR_UNSUPPORTED, "sm_scale must be >= 0 (the row maximum is taken before scaling)");
   if (Dqk <= 64 || Dqk > 128 || Dv <= 64 || Dv > 128)
     return fail(AC4K_ERR_UNSUPPORTED, "head dimensions in (64, 128] are built (Dqk = %lld, Dv = %lld)", (long long)Dqk, (long long)Dv);
   if (sf_layout != AC4K_SF_TILE128X4)
@@ -355,12 +403,12 @@ extern "C" int ac4k_mha_nvfp4_fwd(void *O, const int64_t o_stride[4], const void
   if (di.cc_major != 10) return fail(AC4K_ERR_DEVICE, "mha_nvfp4_fwd needs an sm_100 device (found sm_%d0)", di.cc_major);
   unsigned int *status = device_status_ptr();
   if (!status) return fail(AC4K_ERR_DEVICE, "cannot resolve the device status word");
-  const int64_t v_k64 = ceil_div(Nkv, 64);
+  const int64_t kv_tiles = ceil_div(Nkv, 64);
   CUtensorMap tq, tk, tv;
   // Q, K: [B*H*N, 64 bytes] (head dimension padded to 128 by the quantiser); V^T: [B*H*Dv, align64(Nkv)/2 bytes]
-  if (int e = get_tmap64(Q, B * H * Nq, 64, 128, &tq)) return e;
-  if (int e = get_tmap64(K, B * H * Nkv, 64, 128, &tk)) return e;
-  if (int e = get_tmap64(V, B * H * Dv, v_k64 * 32, 128, &tv)) return e;
+  if (int e = get_tmap64(Q, B * H * Nq, 64, mha::BQ, &tq)) return e;
+  if (int e = get_tmap64(K, B * H * Nkv, 64, mha::BKV, &tk)) return e;
+  if (int e = get_tmap32(V, B * H * Dv, kv_tiles * 32, 128, &tv)) return e;
   MhaArgs a = {};
   a.sfq = static_cast<const uint8_t *>(Q_sf);
   a.sfk = static_cast<const uint8_t *>(K_sf);
@@ -370,8 +418,8 @@ extern "C" int ac4k_mha_nvfp4_fwd(void *O, const int64_t o_stride[4], const void
   a.o_b = o_stride[0]; a.o_h = o_stride[1]; a.o_n = o_stride[2]; a.o_d = o_stride[3];
   a.B = (int)B; a.H = (int)H; a.Nq = (int)Nq; a.Nkv = (int)Nkv; a.Dv = (int)Dv;
   a.q_blocks = (int)ceil_div(Nq, 128);
-  a.kv_blocks = (int)ceil_div(Nkv, 128);
-  a.v_k64 = (int)v_k64;
+  a.k_blocks = (int)ceil_div(Nkv, 128);
+  a.kv_tiles = (int)kv_tiles;
   a.sm_scale = sm_scale;
   a.status = status;
   a.wait_ns = kWaitTimeoutNs;

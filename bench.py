@@ -370,6 +370,35 @@ def decode_stream(peaks):
     return res
 
 
+def attention_nvfp4(peaks):
+    """NVFP4 attention at the shapes of the reference's test/test_attention_tflops.py:36-39 ([1, 75600, 40, 128]; its
+    flop count 4 B H N^2 D, :32), a shorter one, and the same through `attention()` with the three quantiser
+    launches; torch's bf16 scaled_dot_product_attention on the same tensors beside it as a library yardstick."""
+    import math
+    import torch.nn.functional as F
+    from ac4k_kernel_b200 import _cuda_ops, ops
+    res = {"unit": "TFLOP/s", "flops": "4 * B * H * N^2 * D", "cases": []}
+    for (b, n, h, d, reps) in ((1, 16384, 16, 128, 10), (1, 75600, 40, 128, 3)):
+        g = torch.Generator(device="cuda").manual_seed(9567)
+        q, k, v = (torch.randn((b, n, h, d), dtype=torch.bfloat16, device="cuda", generator=g) for _ in range(3))
+        qq, qs, qg = ops.quantize(q, 1, 3, sf_layout="128x4")
+        kq, ks, kg = ops.quantize(k, 1, 3, sf_layout="128x4")
+        vq, vs, vg = ops.quantize(v, 3, 1, swizzle=True, sf_layout="128x4")
+        out = torch.empty_like(q)
+        view = out.permute(0, 2, 1, 3)
+        flops = 4.0 * b * h * n * n * d
+        t_k = time_eager(lambda: _cuda_ops.mha_nvfp4_fwd(view, qq, qs, qg, kq, ks, kg, vq, vs, vg, 1 / math.sqrt(d)), reps)
+        t_a = time_eager(lambda: ops.attention(q, k, v, layout="BNHD", precision="nvfp4", out=out), reps)
+        t_s = time_eager(lambda: F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)), reps)
+        res["cases"].append({"shape_BNHD": [b, n, h, d], "kernel_ms": t_k * 1e3, "kernel_tflops": flops / t_k / 1e12,
+                             "attention_call_ms": t_a * 1e3, "attention_call_tflops": flops / t_a / 1e12,
+                             "torch_sdpa_bf16_ms": t_s * 1e3, "torch_sdpa_bf16_tflops": flops / t_s / 1e12})
+        del q, k, v, qq, kq, vq, out
+    res["note"] = ("bounded by the softmax (16 ex2 per clock per SM = 1024 cycles per 128 x 128 scores), not by the "
+                   "four-bit MMAs; inputs are larger than L2 at both shapes")
+    return res
+
+
 def c5_single_gpu():
     """BASELINE config 5 on one GPU (M = K = 8192, N = 28672): the same-workload base of the 1 -> N curve.
     One operand set (600 MB, larger than L2), 5 steps in a graph."""
@@ -493,6 +522,7 @@ def run_single(args, peaks):
     c5 = c5_single_gpu()
     quant = quantize_bandwidth(peaks)
     decode = decode_stream(peaks)
+    attn = attention_nvfp4(peaks)
     cpu_tflops, cores, sample, _, _ = cpu_emulation_c2()
 
     fp4_proxy_peak = 4.0 * peaks["bf16_tflops"]
@@ -518,6 +548,7 @@ def run_single(args, peaks):
                      "algorithmic_flops_per_launch": flops},
         "quantize": quant,
         "decode": decode,
+        "attention_nvfp4": attn,
         "cpu_baseline": {"value": cpu_tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": e2e,
         "clocks": clocks,
@@ -726,6 +757,16 @@ def run_profile_case(case):
         out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
         for _ in range(3):
             _cuda_ops.linear_nvfp4(out, a4, asf, ag, w4, wsf, wg, None)
+    elif case == "mha":
+        import math
+        g = torch.Generator(device="cuda").manual_seed(9567)
+        q, k, v = (torch.randn((1, 8192, 16, 128), dtype=torch.bfloat16, device="cuda", generator=g) for _ in range(3))
+        qq, qs, qg = ops.quantize(q, 1, 3, sf_layout="128x4")
+        kq, ks, kg = ops.quantize(k, 1, 3, sf_layout="128x4")
+        vq, vs, vg = ops.quantize(v, 3, 1, swizzle=True, sf_layout="128x4")
+        out = torch.empty_like(q)
+        for _ in range(3):
+            _cuda_ops.mha_nvfp4_fwd(out.permute(0, 2, 1, 3), qq, qs, qg, kq, ks, kg, vq, vs, vg, 1 / math.sqrt(128))
     else:
         m, k = 32768, 8192
         x = activations((m, k), 0, 0.01, 50.0, "cuda")
@@ -747,7 +788,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--profile-case", default=None,
-                    choices=["gemm-c2", "gemm-8k", "gemm-decode", "quant-c4", "quant-c4-fp8", "quant-c4-int8"],
+                    choices=["gemm-c2", "gemm-8k", "gemm-decode", "mha", "quant-c4", "quant-c4-fp8", "quant-c4-int8"],
                     help="run one small workload three times and exit (for ncu)")
     args = ap.parse_args()
     if args.profile_case:
