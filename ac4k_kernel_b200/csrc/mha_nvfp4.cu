@@ -74,6 +74,33 @@ __device__ __forceinline__ float rcp_approx(float x) {
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// max of three (one FMNMX3), and two fp32 operations in one instruction on an aligned register pair
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n.reg .b64 ra, rb, rc, rd;\nmov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\nmov.b64 rc, {%6, %7};\n"
+      "fma.rn.f32x2 rd, ra, rb, rc;\nmov.b64 {%0, %1}, rd;\n}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n.reg .b64 ra, rb, rd;\nmov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\n"
+      "mul.rn.f32x2 rd, ra, rb;\nmov.b64 {%0, %1}, rd;\n}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n.reg .b64 ra, rb, rd;\nmov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\n"
+      "add.rn.f32x2 rd, ra, rb;\nmov.b64 {%0, %1}, rd;\n}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
 // two non-negative fp32 -> two e4m3 bytes (a in the low byte) and their values back as fp32
 __device__ __forceinline__ uint32_t e4m3x2_round_trip(float a, float b, float &fa, float &fb) {
   uint16_t pk;
@@ -254,13 +281,26 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         for (int i = 0; i < BKV; ++i)
           if (i >= ncols) r[i] = 0xff800000u;            // -inf: out of the maximum, probability 0
       }
-      float mx0 = __uint_as_float(r[0]), mx1 = __uint_as_float(r[1]);
+      // Maxima of the scores per block of 16 in the stored key order (the reference's V quantiser's "swizzle": every 32
+      // keys viewed as [4, 4, 2] and transposed to [4(b), 4(a), 2]; positions n, n + 1 hold keys key0(n), key0(n) + 1),
+      // and the row maximum from them.  ex2 is monotonic, so a block's largest probability is ex2 of its largest score.
+      float bs[4];
 #pragma unroll
-      for (int i = 2; i < BKV; i += 2) {
-        mx0 = fmaxf(mx0, __uint_as_float(r[i]));
-        mx1 = fmaxf(mx1, __uint_as_float(r[i + 1]));
+      for (int bk = 0; bk < 4; ++bk) {
+        float v[16];
+#pragma unroll
+        for (int n = 0; n < 16; n += 2) {
+          const int nn = 16 * (bk & 1) + n;
+          const int i = 32 * (bk >> 1) + (((nn >> 1) & 3) * 4 + (nn >> 3)) * 2;
+          v[n] = __uint_as_float(r[i]);
+          v[n + 1] = __uint_as_float(r[i + 1]);
+        }
+        float t = max3(v[0], v[1], v[2]);
+#pragma unroll
+        for (int n = 3; n < 15; n += 2) t = max3(t, v[n], v[n + 1]);
+        bs[bk] = fmaxf(t, v[15]);
       }
-      const float m_new = fmaxf(m, fmaxf(mx0, mx1) * c1);
+      const float m_new = fmaxf(m, fmaxf(max3(bs[0], bs[1], bs[2]), bs[3]) * c1);
       if (j > 0) {
         // the previous tile's P V must be complete before O or the P buffer is touched
         ok = warp_all(mbar_wait(o_done, (j - 1) & 1, p.wait_ns));
@@ -282,49 +322,44 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         l *= a;
       }
       m = m_new;
-      // probabilities, row sum, NVFP4 quantisation of P: four blocks of 16 keys, stored in the order of the reference's V
-      // quantiser ("swizzle": every 32 keys viewed as [4, 4, 2] and transposed to [4(b), 4(a), 2]), so that position n
-      // of P meets position n of V^T
-      float l0 = 0.0f, l1 = 0.0f;
+      // probabilities, row sum, NVFP4 quantisation of P: four blocks of 16 keys, so that position n of P meets position n
+      // of V^T
+      float2 lsum = make_float2(0.0f, 0.0f);
+      const float2 c1_2 = make_float2(c1, c1), negm2 = make_float2(-m, -m);
       uint32_t sfw = 0;
 #pragma unroll
       for (int g = 0; g < 2; ++g) {
-        float pr[32];
+        float2 pr[16];
 #pragma unroll
         for (int n = 0; n < 32; n += 2) {
-          const int i = 32 * g + (((n >> 1) & 3) * 4 + (n >> 3)) * 2;     // key held at positions n, n + 1
-          pr[n] = ex2_approx(fmaf(__uint_as_float(r[i]), c1, -m));
-          pr[n + 1] = ex2_approx(fmaf(__uint_as_float(r[i + 1]), c1, -m));
-          l0 += pr[n];
-          l1 += pr[n + 1];
+          const int i = 32 * g + (((n >> 1) & 3) * 4 + (n >> 3)) * 2;     // keys held at positions n, n + 1
+          const float2 e = ffma2(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), c1_2, negm2);
+          pr[n >> 1] = make_float2(ex2_approx(e.x), ex2_approx(e.y));
+          lsum = fadd2(lsum, pr[n >> 1]);
         }
-        float bm[2];
-#pragma unroll
-        for (int blk = 0; blk < 2; ++blk) {
-          float b0 = fmaxf(pr[16 * blk], pr[16 * blk + 1]), b1 = fmaxf(pr[16 * blk + 2], pr[16 * blk + 3]);
-#pragma unroll
-          for (int i = 4; i < 16; i += 4) {
-            b0 = fmaxf(b0, fmaxf(pr[16 * blk + i], pr[16 * blk + i + 1]));
-            b1 = fmaxf(b1, fmaxf(pr[16 * blk + i + 2], pr[16 * blk + i + 3]));
-          }
-          bm[blk] = fmaxf(b0, b1);
-        }
+        const float bm0 = ex2_approx(fmaf(bs[2 * g], c1, -m)), bm1 = ex2_approx(fmaf(bs[2 * g + 1], c1, -m));
         float sd0, sd1;
-        const uint32_t sb2 = e4m3x2_round_trip(__fmul_rn(kPGlobal, __fmul_rn(bm[0], kOneSixth)),
-                                               __fmul_rn(kPGlobal, __fmul_rn(bm[1], kOneSixth)), sd0, sd1);
+        const uint32_t sb2 = e4m3x2_round_trip(__fmul_rn(kPGlobal, __fmul_rn(bm0, kOneSixth)),
+                                               __fmul_rn(kPGlobal, __fmul_rn(bm1, kOneSixth)), sd0, sd1);
         sfw |= sb2 << (16 * g);
-        const float sc[2] = {sd0 != 0.0f ? kPGlobal * rcp_approx(sd0) : 0.0f, sd1 != 0.0f ? kPGlobal * rcp_approx(sd1) : 0.0f};
+        const float sc0 = sd0 != 0.0f ? kPGlobal * rcp_approx(sd0) : 0.0f, sc1 = sd1 != 0.0f ? kPGlobal * rcp_approx(sd1) : 0.0f;
         uint32_t codes[4];
 #pragma unroll
         for (int hh = 0; hh < 4; ++hh) {
+          const float sc = hh < 2 ? sc0 : sc1;
+          const float2 sc2 = make_float2(sc, sc);
           float x[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) x[i] = pr[8 * hh + i] * sc[hh >> 1];
+          for (int i = 0; i < 4; ++i) {
+            const float2 y = fmul2(pr[4 * hh + i], sc2);
+            x[2 * i] = y.x;
+            x[2 * i + 1] = y.y;
+          }
           codes[hh] = f32x8_to_e2m1x8(x);
         }
         st_shared_v4u(p_row + (((uint32_t)g << 4) ^ p_xor), codes[0], codes[1], codes[2], codes[3]);
       }
-      l += l0 + l1;
+      l += lsum.x + lsum.y;
       // scale chunk: 32 rows of 16 bytes, row `lane` holding the words of query rows lane, 32 + lane, 64 + lane, 96 + lane
       st_shared_u32(sSFP + lane * 16 + q * 4, sfw);
       fence_proxy_async_smem();
