@@ -577,6 +577,8 @@ static constexpr int g_force_bn = 0, g_force_splits = 0, g_dbg = 0;
 static constexpr unsigned long long *g_trace = nullptr;
 static constexpr unsigned long long g_wait_ns = 0;
 #endif
+// the clock-stamp buffer of trace builds for the other kernels of the library (NULL otherwise)
+unsigned long long *ac4k::debug_trace_ptr() { return g_trace; }
 
 // Split-K plan of the single-CTA kernel for shapes with too few output tiles to occupy the GPU (65 <= M <= 128,
 // or any M with an output the other kernels do not store): how many K slices, and the fp32 workspace

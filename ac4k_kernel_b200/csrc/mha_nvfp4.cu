@@ -43,7 +43,7 @@ static constexpr int SFV_BYTES = 512;             // one K = 64 step, 128 head-d
 static constexpr int SFP_BYTES = 512;
 static constexpr int KV_STAGES = 4;
 static constexpr int STAGE_BYTES = K_BYTES + V_BYTES + SFK_BYTES + SFV_BYTES;       // 9 728
-static constexpr int SMEM_BYTES = Q_BYTES + P_BYTES + KV_STAGES * STAGE_BYTES + SFQ_BYTES + SFP_BYTES + 1024 + 256;
+static constexpr int SMEM_BYTES = Q_BYTES + 2 * P_BYTES + KV_STAGES * STAGE_BYTES + SFQ_BYTES + 2 * SFP_BYTES + 1024 + 256;
 // tensor memory columns
 static constexpr int S_COL = 0, O_COL = 64, SFQ_COL = 192, SFK_COL = 200, SFP_COL = 208, SFV_COL = 212;
 static constexpr int TMEM_COLS = 256;
@@ -62,7 +62,20 @@ struct MhaArgs {
   float sm_scale;
   unsigned int *status;
   unsigned long long wait_ns;
+  unsigned long long *trace;            // clock stamps (builds with -DAC4K_TRACE_ENABLED), else NULL
 };
+
+// Trace builds: CTA (0, 0, 0) stamps clock64 into trace[(region * 128 + key tile) * 8 + event]; region 0 = softmax warp
+// of lane quarter 0, region 1 = MMA issuer.
+#ifdef AC4K_TRACE_ENABLED
+#define AC4K_TRM(region, it, ev)                                                                     \
+  do {                                                                                               \
+    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 128)   \
+      p.trace[((size_t)(region) * 128 + (it)) * 8 + (ev)] = clock64();                               \
+  } while (0)
+#else
+#define AC4K_TRM(region, it, ev) do { } while (0)
+#endif
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -130,13 +143,13 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sQ = smem_base;
   const uint32_t sP = sQ + Q_BYTES;
-  const uint32_t sKV = sP + P_BYTES;                 // per stage: K | V^T | SFK | SFV
+  const uint32_t sKV = sP + 2 * P_BYTES;             // per stage: K | V^T | SFK | SFV   (P and its scales: two buffers)
   const uint32_t sSFQ = sKV + KV_STAGES * STAGE_BYTES;
   const uint32_t sSFP = sSFQ + SFQ_BYTES;
-  const uint32_t bars = sSFP + SFP_BYTES;
+  const uint32_t bars = sSFP + 2 * SFP_BYTES;
   const uint32_t q_full = bars, kv_full = bars + 8, kv_empty = kv_full + 8 * KV_STAGES;
   const uint32_t s_full = kv_empty + 8 * KV_STAGES, s_free = s_full + 8, p_full = s_free + 8, o_done = p_full + 8;
-  const uint32_t tmem_slot = o_done + 8;
+  const uint32_t tmem_slot = o_done + 16;            // o_done: one barrier per P buffer (key tiles of equal parity)
   uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -157,6 +170,7 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     mbar_init(s_free, 4);         // the four softmax warps hold S in registers
     mbar_init(p_full, 4);         // ... have written P and its scales
     mbar_init(o_done, 1);
+    mbar_init(o_done + 8, 1);
     fence_barrier_init();
     prefetch_tmap(&tma_q);
     prefetch_tmap(&tma_k);
@@ -198,9 +212,7 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     constexpr uint32_t idesc_s = make_idesc_mxf4nvf4(128, BKV);
     constexpr uint32_t idesc_o = make_idesc_mxf4nvf4(128, D);
     const uint64_t qdesc = make_smem_desc(sQ, 16, 512, kSwizzle64B);
-    const uint64_t pdesc = make_smem_desc(sP, 16, 256, kSwizzle32B);
     const uint64_t sfqdesc = make_smem_desc(sSFQ, 0, 128, kSwizzleNone);
-    const uint64_t sfpdesc = make_smem_desc(sSFP, 0, 128, kSwizzleNone);
     const uint32_t t_s = tmem_base + S_COL, t_o = tmem_base + O_COL;
     bool ok = warp_all(mbar_wait(q_full, 0, p.wait_ns));
     // S of key tile j: two K = 64 steps over D, 32 bytes apart inside the 64-byte rows of Q and K.  The K scales of
@@ -230,26 +242,33 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     }
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int s = j % KV_STAGES;
+      if (el) AC4K_TRM(1, j, 0);
       if (j + 1 < n_tiles) {
         ok = warp_all(mbar_wait(kv_full + 8 * ((j + 1) % KV_STAGES), ((j + 1) / KV_STAGES) & 1, p.wait_ns));
         if (!ok) break;
         ok = warp_all(mbar_wait(s_free, j & 1, p.wait_ns));       // S of tile j is in the softmax warps' registers
         if (!ok) break;
         tc_fence_after();
+        if (el) AC4K_TRM(1, j, 1);
         issue_s(j + 1);
+        if (el) AC4K_TRM(1, j, 2);
       }
       // O (+)= P V once the softmax warps have written P (they have also rescaled O by then)
       ok = warp_all(mbar_wait(p_full, j & 1, p.wait_ns));
       if (!ok) break;
       tc_fence_after();
+      if (el) AC4K_TRM(1, j, 3);
       const uint32_t st = sKV + s * STAGE_BYTES;
       const uint64_t vdesc = make_smem_desc(st + K_BYTES, 16, 256, kSwizzle32B);
       const uint64_t sfvdesc = make_smem_desc(st + K_BYTES + V_BYTES + SFK_BYTES, 0, 128, kSwizzleNone);
+      const uint64_t pdesc = make_smem_desc(sP + (j & 1) * P_BYTES, 16, 256, kSwizzle32B);
+      const uint64_t sfpdesc = make_smem_desc(sSFP + (j & 1) * SFP_BYTES, 0, 128, kSwizzleNone);
       tmem_cp_32x128b_warpx4_if(el, tmem_base + SFP_COL, sfpdesc);
       tmem_cp_32x128b_warpx4_if(el, tmem_base + SFV_COL, sfvdesc);
       mma_mxf4nvf4_if(el, t_o, pdesc, vdesc, idesc_o, tmem_base + SFP_COL, tmem_base + SFV_COL, j > 0 ? 1u : 0u);
       tc_commit_if(el, kv_empty + 8 * s);
-      tc_commit_if(el, o_done);
+      tc_commit_if(el, o_done + 8 * (j & 1));
+      if (el) AC4K_TRM(1, j, 4);
     }
     if (!ok && el) atomicExch(p.status, kStatusTimeoutMma);
   } else {
@@ -262,16 +281,19 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     // (c1 >= 0: the host rejects a negative sm_scale; the floor keeps -inf * c1 = -inf for masked keys when a global
     // scale is 0)
     const float c1 = fmaxf(__ldg(p.q_gs) * __ldg(p.k_gs) * p.sm_scale * 1.4426950408889634f, 1.17549435e-38f);
-    const uint32_t p_row = sP + row_l * 32;
+    const uint32_t p_row0 = sP + row_l * 32;
     const uint32_t p_xor = (uint32_t)((row_l >> 2) & 1) << 4;       // 32-byte swizzle: 16-byte chunk ^ ((row / 4) % 2)
     float m = -INFINITY, l = 0.0f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
+      if (q == 0 && lane == 0) AC4K_TRM(0, j, 0);
       ok = warp_all(mbar_wait(s_full, j & 1, p.wait_ns));
       if (!ok) break;
       tc_fence_after();
+      if (q == 0 && lane == 0) AC4K_TRM(0, j, 1);
       uint32_t r[64];
       tmem_ld_32x32b_x64_sync(t_s, r);
+      if (q == 0 && lane == 0) AC4K_TRM(0, j, 2);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_free);
@@ -301,29 +323,33 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         bs[bk] = fmaxf(t, v[15]);
       }
       const float m_new = fmaxf(m, fmaxf(max3(bs[0], bs[1], bs[2]), bs[3]) * c1);
-      if (j > 0) {
-        // the previous tile's P V must be complete before O or the P buffer is touched
-        ok = warp_all(mbar_wait(o_done, (j - 1) & 1, p.wait_ns));
+      if (j > 0 && __any_sync(0xffffffffu, m_new != m)) {
+        // a maximum of this warp's rows moved: O is rescaled, once the previous tile's P V is complete
+        ok = warp_all(mbar_wait(o_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, p.wait_ns));
         if (!ok) break;
+        tc_fence_after();
         const float a = ex2_approx(m - m_new);
-        if (__any_sync(0xffffffffu, m_new != m)) {
-          tc_fence_after();
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t ro[32];
-            tmem_ld_32x32b_x32_sync(t_o + 32 * c, ro);
-            float v[32];
+        for (int c = 0; c < 4; ++c) {
+          uint32_t ro[32];
+          tmem_ld_32x32b_x32_sync(t_o + 32 * c, ro);
+          float v[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(ro[i]) * a;
-            tmem_st_32x32b_x32_f(t_o + 32 * c, v);
-          }
-          tmem_st_wait();
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(ro[i]) * a;
+          tmem_st_32x32b_x32_f(t_o + 32 * c, v);
         }
+        tmem_st_wait();
         l *= a;
       }
+      if (q == 0 && lane == 0) AC4K_TRM(0, j, 3);
+      // This tile's P buffer was last read by the P V of two tiles ago.  That MMA was issued before this tile's S, and
+      // the tensor pipe completes MMAs (and the commits behind them) in issue order: s_full of this tile, seen above,
+      // implies it is complete, so no wait is needed here.
       m = m_new;
+      if (q == 0 && lane == 0) AC4K_TRM(0, j, 4);
       // probabilities, row sum, NVFP4 quantisation of P: four blocks of 16 keys, so that position n of P meets position n
       // of V^T
+      const uint32_t p_row = p_row0 + (j & 1) * P_BYTES;
       float2 lsum = make_float2(0.0f, 0.0f);
       const float2 c1_2 = make_float2(c1, c1), negm2 = make_float2(-m, -m);
       uint32_t sfw = 0;
@@ -361,13 +387,14 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       }
       l += lsum.x + lsum.y;
       // scale chunk: 32 rows of 16 bytes, row `lane` holding the words of query rows lane, 32 + lane, 64 + lane, 96 + lane
-      st_shared_u32(sSFP + lane * 16 + q * 4, sfw);
+      st_shared_u32(sSFP + (j & 1) * SFP_BYTES + lane * 16 + q * 4, sfw);
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
+      if (q == 0 && lane == 0) AC4K_TRM(0, j, 5);
       if (lane == 0) mbar_arrive(p_full);
     }
-    if (ok) ok = warp_all(mbar_wait(o_done, (n_tiles - 1) & 1, p.wait_ns));
+    if (ok) ok = warp_all(mbar_wait(o_done + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, p.wait_ns));
     if (!ok) {
       if (lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue);
     } else {
@@ -458,6 +485,7 @@ extern "C" int ac4k_mha_nvfp4_fwd(void *O, const int64_t o_stride[4], const void
   a.sm_scale = sm_scale;
   a.status = status;
   a.wait_ns = kWaitTimeoutNs;
+  a.trace = debug_trace_ptr();
   static PerDevice<int> attr_set;
   int unused = 0;
   if (int e = attr_set.get(&unused, [&](int &v) {
