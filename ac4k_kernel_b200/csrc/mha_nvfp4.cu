@@ -6,20 +6,26 @@
 // P = exp(S - max) re-quantised per 16 keys with the fixed global scale 1 / (6 * 448)
 // (mha_nvfp4.cu:246-319), O accumulated in fp32 and divided by the row sum at the end.
 //
-// One CTA per (batch, head, 128 query rows), two CTAs per SM; a CTA walks the keys in tiles of 64:
-//   warp 0     TMA producer: Q once; per key tile K [64 keys x D], V^T [D x 64 keys] and their scale chunks, four stages
-//   warp 1     MMA issuer: S = Q K^T (tcgen05.mma kind::mxf4nvf4, M = 128 queries, N = 64 keys, K = D) into tensor
-//              memory; once the softmax warps have written P: O (+)= P V (M = 128, N = D, K = 64 keys).  Block scales
-//              go from shared to tensor memory with tcgen05.cp in front of the MMAs.  S of the next key tile is
-//              issued as soon as the softmax warps hold the current S in registers, before the current P V.
-//   warps 2-5  softmax: thread = query row.  One pass over the 64 scores in registers: running maximum, O rescaled
-//              in tensor memory when a maximum of the warp moved, ex2.approx, row sum, P quantised to e2m1 + e4m3
-//              block scales (fixed global scale 1 / 2688) and written into shared memory in the layouts the tensor
-//              core reads (32-byte-swizzled K-major operand, 32 x 16-byte scale chunk); at the end
-//              O * gV / (2688 * row sum) is stored as bf16.
-// The softmax is what bounds this kernel (16 ex2 per clock per SM: 1024 cycles for 128 x 128 scores against 330 for
-// the four-bit MMAs), hence two CTAs per SM: eight softmax warps, and one CTA's MMAs, waits and TMEM traffic run under
-// the other's arithmetic.  Tensor memory per CTA: S 64 + O 128 + scales 24 columns of the 256 allocated.
+// One CTA per (batch, head, 256 query rows), one CTA per SM; the CTA holds two query tiles of 128 rows (groups A, B)
+// and walks the keys in tiles of 128:
+//   warp 0     TMA producer: both Q tiles once; per key tile K [128 keys x D], V^T [D x 128 keys] and their scale
+//              chunks, four stages, shared by the two groups
+//   warp 1     MMA issuer: S = Q K^T (tcgen05.mma kind::mxf4nvf4, M = 128 queries, N = 128 keys, K = D) into ONE
+//              128-column score buffer in tensor memory that the groups use in turn (a group copies its scores to
+//              registers at once, which frees the buffer for the other group's MMA); once a group has written P:
+//              O_g (+)= P V (M = 128, N = D, K = 128 keys).  Block scales go from shared to tensor memory with
+//              tcgen05.cp in front of the MMAs.
+//   warps 2-5  softmax of group A, warps 6-9 of group B: thread = query row.  One pass over the 128 scores in
+//              registers: running maximum, O rescaled in tensor memory when a maximum of the warp moved, ex2.approx,
+//              row sum, P quantised to e2m1 + e4m3 block scales (fixed global scale 1 / 2688) and written into shared
+//              memory in the layouts the tensor core reads (64-byte-swizzled K-major operand, 32 x 16-byte scale
+//              chunks); at the end O * gV / (2688 * row sum) is stored as bf16.
+// The softmax bounds this kernel: an SM retires 16 ex2 per clock, 1024 cycles for 128 x 128 scores against 330 for the
+// four-bit MMAs.  So the exponential phases of the two groups take turns (a token passed through two mbarriers): while
+// one group keeps the ex2 pipe busy, the other does everything that does not need it (wait for S, copy it out, maxima,
+// rescale, fences, barrier traffic: ~800 cycles per key tile).  Two independent CTAs per SM measured 1.34x slower:
+// they start together and stay in step, so both sit in those phases at the same time.
+// Tensor memory: S 128 + O_A 128 + O_B 128 + scales 40 columns of 512.
 //
 // Supported: head dimensions in (64, 128] (padded to 128 by the quantiser), scales in the tiled layout
 // [.., 128-row block, K/64, 32 x 16 B]; V quantised along the keys (cross dimension = head dimension) with the
@@ -31,24 +37,23 @@ namespace ac4k {
 using namespace ptx;
 
 namespace mha {
-static constexpr int BQ = 128, BKV = 64, D = 128;
-static constexpr int kThreads = 192;
+static constexpr int BQ = 128, BKV = 128, D = 128;
+static constexpr int kThreads = 320;              // producer, MMA issuer, 2 x 4 softmax warps
 static constexpr int Q_BYTES = BQ * 64;           // 128 rows x 128 e2m1, 64-byte rows
-static constexpr int K_BYTES = BKV * 64;          // 64 keys x 128 e2m1
-static constexpr int V_BYTES = D * 32;            // 128 head-dimension rows x 64 keys, 32-byte rows
-static constexpr int P_BYTES = BQ * 32;           // 128 query rows x 64 keys
-static constexpr int SFQ_BYTES = 2 * 512;         // two K = 64 steps of D = 128, 128 rows
-static constexpr int SFK_BYTES = 2 * 512;         // the 128-key block the tile lies in (its half is picked by column)
-static constexpr int SFV_BYTES = 512;             // one K = 64 step, 128 head-dimension rows
-static constexpr int SFP_BYTES = 512;
+static constexpr int K_BYTES = BKV * 64;          // 128 keys x 128 e2m1
+static constexpr int V_BYTES = D * 64;            // 128 head-dimension rows x 128 keys
+static constexpr int P_BYTES = BQ * 64;           // 128 query rows x 128 keys
+static constexpr int SF_BYTES = 2 * 512;          // two K = 64 steps of 128 rows
 static constexpr int KV_STAGES = 4;
-static constexpr int STAGE_BYTES = K_BYTES + V_BYTES + SFK_BYTES + SFV_BYTES;       // 9 728
-static constexpr int SMEM_BYTES = Q_BYTES + 2 * P_BYTES + KV_STAGES * STAGE_BYTES + SFQ_BYTES + 2 * SFP_BYTES + 1024 + 256;
+static constexpr int STAGE_BYTES = K_BYTES + V_BYTES + 2 * SF_BYTES;       // 18 432
+static constexpr int SMEM_BYTES = 2 * Q_BYTES + 4 * P_BYTES + KV_STAGES * STAGE_BYTES + 2 * SF_BYTES + 4 * SF_BYTES + 1024 + 256;
 // tensor memory columns
-static constexpr int S_COL = 0, O_COL = 64, SFQ_COL = 192, SFK_COL = 200, SFP_COL = 208, SFV_COL = 212;
-static constexpr int TMEM_COLS = 256;
+static constexpr int S_COL = 0, O_COL = 128 /* + 128 * group */, SFQ_COL = 384 /* + 8 * group */, SFK_COL = 400, SFP_COL = 408,
+                     SFV_COL = 416;
+static constexpr int TMEM_COLS = 512;
 static constexpr float kPGlobal = 2688.0f;        // 6 * 448: reciprocal of P's fixed global scale
-static_assert(STAGE_BYTES % 512 == 0 && K_BYTES % 1024 == 0 && V_BYTES % 1024 == 0, "tile alignment");
+static_assert(STAGE_BYTES % 1024 == 0, "tile alignment");
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory overflow");
 }  // namespace mha
 
 struct MhaArgs {
@@ -57,16 +62,16 @@ struct MhaArgs {
   void *O;
   int64_t o_b, o_h, o_n, o_d;           // strides of O in elements
   int B, H, Nq, Nkv, Dv;
-  int q_blocks, k_blocks;               // ceil(Nq / 128), ceil(Nkv / 128): 128-row blocks of the Q and K scales
-  int kv_tiles;                         // ceil(Nkv / 64): key tiles = K = 64 steps of V^T
+  int q_blocks, kv_tiles;               // ceil(Nq / 128), ceil(Nkv / 128): 128-row blocks of Q and of the keys
+  int v_k64;                            // align64(Nkv) / 64: K = 64 steps of V^T that exist
   float sm_scale;
   unsigned int *status;
   unsigned long long wait_ns;
   unsigned long long *trace;            // clock stamps (builds with -DAC4K_TRACE_ENABLED), else NULL
 };
 
-// Trace builds: CTA (0, 0, 0) stamps clock64 into trace[(region * 128 + key tile) * 8 + event]; region 0 = softmax warp
-// of lane quarter 0, region 1 = MMA issuer.
+// Trace builds: CTA (0, 0, 0) stamps clock64 into trace[(region * 128 + key tile) * 8 + event]; region 0 / 2 = softmax warp
+// of lane quarter 0 of group A / B, region 1 = MMA issuer.
 #ifdef AC4K_TRACE_ENABLED
 #define AC4K_TRM(region, it, ev)                                                                     \
   do {                                                                                               \
@@ -135,30 +140,35 @@ __device__ __forceinline__ void tmem_st_32x32b_x32_f(uint32_t taddr, const float
   tmem_st_32x32b_x32(taddr, u);
 }
 
-__global__ void __launch_bounds__(mha::kThreads, 2)
+__global__ void __launch_bounds__(mha::kThreads, 1)
 mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                      const __grid_constant__ CUtensorMap tma_v, const MhaArgs p) {
   using namespace mha;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sQ = smem_base;
-  const uint32_t sP = sQ + Q_BYTES;
-  const uint32_t sKV = sP + 2 * P_BYTES;             // per stage: K | V^T | SFK | SFV   (P and its scales: two buffers)
-  const uint32_t sSFQ = sKV + KV_STAGES * STAGE_BYTES;
-  const uint32_t sSFP = sSFQ + SFQ_BYTES;
-  const uint32_t bars = sSFP + 2 * SFP_BYTES;
+  const uint32_t sQ = smem_base;                     // [group]
+  const uint32_t sP = sQ + 2 * Q_BYTES;              // [group][buffer]
+  const uint32_t sKV = sP + 4 * P_BYTES;             // per stage: K | V^T | SFK | SFV
+  const uint32_t sSFQ = sKV + KV_STAGES * STAGE_BYTES;   // [group]
+  const uint32_t sSFP = sSFQ + 2 * SF_BYTES;         // [group][buffer]
+  const uint32_t bars = sSFP + 4 * SF_BYTES;
   const uint32_t q_full = bars, kv_full = bars + 8, kv_empty = kv_full + 8 * KV_STAGES;
-  const uint32_t s_full = kv_empty + 8 * KV_STAGES, s_free = s_full + 8, p_full = s_free + 8, o_done = p_full + 8;
-  const uint32_t tmem_slot = o_done + 16;            // o_done: one barrier per P buffer (key tiles of equal parity)
+  const uint32_t s_full = kv_empty + 8 * KV_STAGES;  // [group]
+  const uint32_t s_free = s_full + 16;
+  const uint32_t p_full = s_free + 8;                // [group]
+  const uint32_t o_done = p_full + 16;               // [group][P buffer]
+  const uint32_t tok = o_done + 32;                  // [group]: the group may start its exponentials
+  const uint32_t tmem_slot = tok + 16;
   uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int64_t bh = (int64_t)b * p.H + h;
-  const int q_row0 = (int)(bh * p.Nq) + qt * BQ;    // row of Q in the [B*H*Nq, 64-byte] matrix
+  const int q_row0 = (int)(bh * p.Nq) + qt * 2 * BQ; // row of Q in the [B*H*Nq, 64-byte] matrix
   const int k_row0 = (int)(bh * p.Nkv);
-  const int v_row0 = (int)(bh * p.Dv);              // V^T rows of this head; rows past Dv belong to the next head and are not stored
+  const int v_row0 = (int)(bh * p.Dv);               // V^T rows of this head; rows past Dv belong to the next head and are not stored
   const int n_tiles = p.kv_tiles;
+  const bool both = 2 * qt + 1 < p.q_blocks;         // group B has query rows
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -166,11 +176,14 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       mbar_init(kv_full + 8 * s, 1);
       mbar_init(kv_empty + 8 * s, 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(s_free, 4);         // the four softmax warps hold S in registers
-    mbar_init(p_full, 4);         // ... have written P and its scales
-    mbar_init(o_done, 1);
-    mbar_init(o_done + 8, 1);
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(s_full + 8 * g, 1);
+      mbar_init(p_full + 8 * g, 4);     // the group's four warps have written P and its scales
+      mbar_init(o_done + 16 * g, 1);
+      mbar_init(o_done + 16 * g + 8, 1);
+      mbar_init(tok + 8 * g, 4);
+    }
+    mbar_init(s_free, 4);               // the four warps of the group whose turn it is hold S in registers
     fence_barrier_init();
     prefetch_tmap(&tma_q);
     prefetch_tmap(&tma_k);
@@ -190,114 +203,163 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     const uint32_t el = elect_one();
-    mbar_arrive_expect_tx_if(el, q_full, Q_BYTES + SFQ_BYTES);
-    tma_load_2d_if(el, sQ, &tma_q, 0, q_row0, q_full);
-    bulk_load_1d_if(el, sSFQ, p.sfq + ((bh * p.q_blocks + qt) * 2) * 512, SFQ_BYTES, q_full);
+    const int ng = both ? 2 : 1;
+    mbar_arrive_expect_tx_if(el, q_full, ng * (Q_BYTES + SF_BYTES));
+    for (int g = 0; g < ng; ++g) {
+      tma_load_2d_if(el, sQ + g * Q_BYTES, &tma_q, 0, q_row0 + g * BQ, q_full);
+      bulk_load_1d_if(el, sSFQ + g * SF_BYTES, p.sfq + ((bh * p.q_blocks + 2 * qt + g) * 2) * 512, SF_BYTES, q_full);
+    }
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int s = j % KV_STAGES;
       ok = warp_all(mbar_wait(kv_empty + 8 * s, ((j / KV_STAGES) & 1) ^ 1, p.wait_ns));
       if (!ok) break;
       const uint32_t st = sKV + s * STAGE_BYTES, fb = kv_full + 8 * s;
-      mbar_arrive_expect_tx_if(el, fb, STAGE_BYTES);
+      // V^T: D rows x 128 keys; of the tile's two K = 64 steps only those below align64(Nkv) exist
+      const int nk = min(2, p.v_k64 - 2 * j);
+      mbar_arrive_expect_tx_if(el, fb, K_BYTES + V_BYTES + SF_BYTES + nk * 512);
       tma_load_2d_if(el, st, &tma_k, 0, k_row0 + j * BKV, fb);
-      tma_load_2d_if(el, st + K_BYTES, &tma_v, j * 32, v_row0, fb);
-      bulk_load_1d_if(el, st + K_BYTES + V_BYTES, p.sfk + ((bh * p.k_blocks + (j >> 1)) * 2) * 512, SFK_BYTES, fb);
-      bulk_load_1d_if(el, st + K_BYTES + V_BYTES + SFK_BYTES, p.sfv + (bh * p.kv_tiles + j) * 512, SFV_BYTES, fb);
+      tma_load_2d_if(el, st + K_BYTES, &tma_v, j * 64, v_row0, fb);
+      bulk_load_1d_if(el, st + K_BYTES + V_BYTES, p.sfk + ((bh * p.kv_tiles + j) * 2) * 512, SF_BYTES, fb);
+      bulk_load_1d_if(el, st + K_BYTES + V_BYTES + SF_BYTES, p.sfv + (bh * p.v_k64 + 2 * j) * 512, nk * 512, fb);
     }
     if (!ok && el) atomicExch(p.status, kStatusTimeoutProducer);
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     const uint32_t el = elect_one();
-    constexpr uint32_t idesc_s = make_idesc_mxf4nvf4(128, BKV);
-    constexpr uint32_t idesc_o = make_idesc_mxf4nvf4(128, D);
-    const uint64_t qdesc = make_smem_desc(sQ, 16, 512, kSwizzle64B);
-    const uint64_t sfqdesc = make_smem_desc(sSFQ, 0, 128, kSwizzleNone);
-    const uint32_t t_s = tmem_base + S_COL, t_o = tmem_base + O_COL;
+    constexpr uint32_t idesc = make_idesc_mxf4nvf4(128, 128);
+    const uint32_t t_s = tmem_base + S_COL;
     bool ok = warp_all(mbar_wait(q_full, 0, p.wait_ns));
-    // S of key tile j: two K = 64 steps over D, 32 bytes apart inside the 64-byte rows of Q and K.  The K scales of
-    // the tile's 64 keys are columns 2 * (j & 1) and the next of the 128-key block's four.
-    auto issue_s = [&](int j) {
-      const int s = j % KV_STAGES;
-      const uint32_t st = sKV + s * STAGE_BYTES;
+    // S of group g and key tile j into the shared score buffer: two K = 64 steps over D, 32 bytes apart inside the
+    // 64-byte rows of Q and K
+    auto issue_s = [&](int g, int j) {
+      const uint32_t st = sKV + (j % KV_STAGES) * STAGE_BYTES;
+      const uint64_t qdesc = make_smem_desc(sQ + g * Q_BYTES, 16, 512, kSwizzle64B);
       const uint64_t kdesc = make_smem_desc(st, 16, 512, kSwizzle64B);
+      const uint64_t sfqdesc = make_smem_desc(sSFQ + g * SF_BYTES, 0, 128, kSwizzleNone);
       const uint64_t sfkdesc = make_smem_desc(st + K_BYTES + V_BYTES, 0, 128, kSwizzleNone);
+      const uint32_t t_sfq = tmem_base + SFQ_COL + 8 * g;
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
-        if (j == 0) tmem_cp_32x128b_warpx4_if(el, tmem_base + SFQ_COL + 4 * i, sfqdesc + 32 * i);
+        if (j == 0) tmem_cp_32x128b_warpx4_if(el, t_sfq + 4 * i, sfqdesc + 32 * i);
         tmem_cp_32x128b_warpx4_if(el, tmem_base + SFK_COL + 4 * i, sfkdesc + 32 * i);
       }
 #pragma unroll
       for (int i = 0; i < 2; ++i)
-        mma_mxf4nvf4_if(el, t_s, qdesc + 2 * i, kdesc + 2 * i, idesc_s, tmem_base + SFQ_COL + 4 * i,
-                        tmem_base + SFK_COL + 4 * i + 2 * (j & 1), i > 0 ? 1u : 0u);
-      tc_commit_if(el, s_full);
+        mma_mxf4nvf4_if(el, t_s, qdesc + 2 * i, kdesc + 2 * i, idesc, t_sfq + 4 * i, tmem_base + SFK_COL + 4 * i, i > 0 ? 1u : 0u);
+      tc_commit_if(el, s_full + 8 * g);
     };
-    if (ok) {
-      ok = warp_all(mbar_wait(kv_full, 0, p.wait_ns));
-      if (ok) {
-        tc_fence_after();
-        issue_s(0);
+    // O_g (+)= P V: two K = 64 steps over the tile's keys (one when only the first exists)
+    auto issue_pv = [&](int g, int j) {
+      const uint32_t st = sKV + (j % KV_STAGES) * STAGE_BYTES;
+      const uint64_t pdesc = make_smem_desc(sP + (2 * g + (j & 1)) * P_BYTES, 16, 512, kSwizzle64B);
+      const uint64_t vdesc = make_smem_desc(st + K_BYTES, 16, 512, kSwizzle64B);
+      const uint64_t sfpdesc = make_smem_desc(sSFP + (2 * g + (j & 1)) * SF_BYTES, 0, 128, kSwizzleNone);
+      const uint64_t sfvdesc = make_smem_desc(st + K_BYTES + V_BYTES + SF_BYTES, 0, 128, kSwizzleNone);
+      const int nk = min(2, p.v_k64 - 2 * j);
+      for (int i = 0; i < nk; ++i) {
+        tmem_cp_32x128b_warpx4_if(el, tmem_base + SFP_COL + 4 * i, sfpdesc + 32 * i);
+        tmem_cp_32x128b_warpx4_if(el, tmem_base + SFV_COL + 4 * i, sfvdesc + 32 * i);
       }
+      for (int i = 0; i < nk; ++i)
+        mma_mxf4nvf4_if(el, tmem_base + O_COL + 128 * g, pdesc + 2 * i, vdesc + 2 * i, idesc, tmem_base + SFP_COL + 4 * i,
+                        tmem_base + SFV_COL + 4 * i, (j > 0 || i > 0) ? 1u : 0u);
+      tc_commit_if(el, o_done + 16 * g + 8 * (j & 1));
+    };
+    // The score buffer is used in the order A(0), B(0), A(1), B(1), ... (A(0), A(1), ... without group B); use n of the
+    // buffer may be issued when use n - 1 has been copied to registers (s_free phase n - 1).
+    int n_use = 0;
+    auto issue_s_when_free = [&](int g, int j) {
+      bool good = true;
+      if (n_use > 0) good = warp_all(mbar_wait(s_free, (n_use - 1) & 1, p.wait_ns));
+      if (good) {
+        tc_fence_after();
+        issue_s(g, j);
+        ++n_use;
+      }
+      return good;
+    };
+    auto wait_kv = [&](int j) { return warp_all(mbar_wait(kv_full + 8 * (j % KV_STAGES), (j / KV_STAGES) & 1, p.wait_ns)); };
+    if (ok) ok = wait_kv(0);
+    if (ok) ok = issue_s_when_free(0, 0);
+    if (ok && both) ok = issue_s_when_free(1, 0);
+    if (ok && n_tiles > 1) {
+      ok = wait_kv(1);
+      if (ok) ok = issue_s_when_free(0, 1);
     }
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int s = j % KV_STAGES;
       if (el) AC4K_TRM(1, j, 0);
-      if (j + 1 < n_tiles) {
-        ok = warp_all(mbar_wait(kv_full + 8 * ((j + 1) % KV_STAGES), ((j + 1) / KV_STAGES) & 1, p.wait_ns));
-        if (!ok) break;
-        ok = warp_all(mbar_wait(s_free, j & 1, p.wait_ns));       // S of tile j is in the softmax warps' registers
-        if (!ok) break;
-        tc_fence_after();
-        if (el) AC4K_TRM(1, j, 1);
-        issue_s(j + 1);
-        if (el) AC4K_TRM(1, j, 2);
-      }
-      // O (+)= P V once the softmax warps have written P (they have also rescaled O by then)
       ok = warp_all(mbar_wait(p_full, j & 1, p.wait_ns));
       if (!ok) break;
       tc_fence_after();
-      if (el) AC4K_TRM(1, j, 3);
-      const uint32_t st = sKV + s * STAGE_BYTES;
-      const uint64_t vdesc = make_smem_desc(st + K_BYTES, 16, 256, kSwizzle32B);
-      const uint64_t sfvdesc = make_smem_desc(st + K_BYTES + V_BYTES + SFK_BYTES, 0, 128, kSwizzleNone);
-      const uint64_t pdesc = make_smem_desc(sP + (j & 1) * P_BYTES, 16, 256, kSwizzle32B);
-      const uint64_t sfpdesc = make_smem_desc(sSFP + (j & 1) * SFP_BYTES, 0, 128, kSwizzleNone);
-      tmem_cp_32x128b_warpx4_if(el, tmem_base + SFP_COL, sfpdesc);
-      tmem_cp_32x128b_warpx4_if(el, tmem_base + SFV_COL, sfvdesc);
-      mma_mxf4nvf4_if(el, t_o, pdesc, vdesc, idesc_o, tmem_base + SFP_COL, tmem_base + SFV_COL, j > 0 ? 1u : 0u);
-      tc_commit_if(el, kv_empty + 8 * s);
-      tc_commit_if(el, o_done + 8 * (j & 1));
+      issue_pv(0, j);
+      if (el) AC4K_TRM(1, j, 1);
+      if (both) {
+        if (j + 1 < n_tiles) {
+          ok = issue_s_when_free(1, j + 1);
+          if (!ok) break;
+        }
+        if (el) AC4K_TRM(1, j, 2);
+        ok = warp_all(mbar_wait(p_full + 8, j & 1, p.wait_ns));
+        if (!ok) break;
+        tc_fence_after();
+        issue_pv(1, j);
+        if (el) AC4K_TRM(1, j, 3);
+      }
+      tc_commit_if(el, kv_empty + 8 * (j % KV_STAGES));
+      if (j + 2 < n_tiles) {
+        ok = wait_kv(j + 2);
+        if (!ok) break;
+        ok = issue_s_when_free(0, j + 2);
+        if (!ok) break;
+      }
       if (el) AC4K_TRM(1, j, 4);
     }
     if (!ok && el) atomicExch(p.status, kStatusTimeoutMma);
-  } else {
+  } else if (warp < 6 || both) {
     // ------------------------------------------------------------------ softmax, correction, epilogue
-    const int q = warp & 3;                   // tensor-memory lane quarter (warps 2-5 -> 2, 3, 0, 1)
+    const int g = (warp - 2) >> 2;            // group: query tile A or B
+    const int q = warp & 3;                   // tensor-memory lane quarter (warps 2-5 and 6-9 -> 2, 3, 0, 1)
     const int row_l = q * 32 + lane;          // query row inside the tile = tensor-memory lane
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    const uint32_t t_s = tmem_base + lane_addr + S_COL, t_o = tmem_base + lane_addr + O_COL;
+    const uint32_t t_s = tmem_base + lane_addr + S_COL, t_o = tmem_base + lane_addr + O_COL + 128 * g;
     // scores in units of log2: p = exp2(s * c1 - m)
     // (c1 >= 0: the host rejects a negative sm_scale; the floor keeps -inf * c1 = -inf for masked keys when a global
     // scale is 0)
     const float c1 = fmaxf(__ldg(p.q_gs) * __ldg(p.k_gs) * p.sm_scale * 1.4426950408889634f, 1.17549435e-38f);
-    const uint32_t p_row0 = sP + row_l * 32;
-    const uint32_t p_xor = (uint32_t)((row_l >> 2) & 1) << 4;       // 32-byte swizzle: 16-byte chunk ^ ((row / 4) % 2)
+    const uint32_t p_row0 = sP + 2 * g * P_BYTES + row_l * 64;
+    const uint32_t p_xor = (uint32_t)((row_l >> 1) & 3) << 4;       // 64-byte swizzle: 16-byte chunk ^ ((row / 2) % 4)
+    const uint32_t sfp0 = sSFP + 2 * g * SF_BYTES + lane * 16 + q * 4;
+    const uint32_t my_s_full = s_full + 8 * g, my_p_full = p_full + 8 * g, my_o_done = o_done + 16 * g;
+    const uint32_t my_tok = tok + 8 * g, other_tok = tok + 8 * (1 - g);
+    const bool tracer = (q == 0 && lane == 0);
     float m = -INFINITY, l = 0.0f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      if (q == 0 && lane == 0) AC4K_TRM(0, j, 0);
-      ok = warp_all(mbar_wait(s_full, j & 1, p.wait_ns));
+      if (tracer) AC4K_TRM(2 * g, j, 0);
+      ok = warp_all(mbar_wait(my_s_full, j & 1, p.wait_ns));
       if (!ok) break;
       tc_fence_after();
-      if (q == 0 && lane == 0) AC4K_TRM(0, j, 1);
-      uint32_t r[64];
-      tmem_ld_32x32b_x64_sync(t_s, r);
-      if (q == 0 && lane == 0) AC4K_TRM(0, j, 2);
+      if (tracer) AC4K_TRM(2 * g, j, 1);
+      uint32_t r[128];
+      {
+        uint32_t lo[64], hi[64];
+        tmem_ld_32x32b_x64(t_s, lo);
+        tmem_ld_32x32b_x64(t_s + 64, hi);
+        tmem_ld_wait();
+        tmem_pin(lo);
+        tmem_pin(hi);
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          r[i] = lo[i];
+          r[64 + i] = hi[i];
+        }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_free);
-      const int ncols = p.Nkv - j * BKV;                 // keys of this tile that exist (>= 64 except in the last tile)
+      if (tracer) AC4K_TRM(2 * g, j, 2);
+      const int ncols = p.Nkv - j * BKV;                 // keys of this tile that exist (>= 128 except in the last tile)
       if (ncols < BKV) {
 #pragma unroll
         for (int i = 0; i < BKV; ++i)
@@ -306,9 +368,9 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       // Maxima of the scores per block of 16 in the stored key order (the reference's V quantiser's "swizzle": every 32
       // keys viewed as [4, 4, 2] and transposed to [4(b), 4(a), 2]; positions n, n + 1 hold keys key0(n), key0(n) + 1),
       // and the row maximum from them.  ex2 is monotonic, so a block's largest probability is ex2 of its largest score.
-      float bs[4];
+      float bs[8];
 #pragma unroll
-      for (int bk = 0; bk < 4; ++bk) {
+      for (int bk = 0; bk < 8; ++bk) {
         float v[16];
 #pragma unroll
         for (int n = 0; n < 16; n += 2) {
@@ -317,57 +379,62 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
           v[n] = __uint_as_float(r[i]);
           v[n + 1] = __uint_as_float(r[i + 1]);
         }
-        float t = max3(v[0], v[1], v[2]);
-#pragma unroll
-        for (int n = 3; n < 15; n += 2) t = max3(t, v[n], v[n + 1]);
-        bs[bk] = fmaxf(t, v[15]);
+        const float t0 = max3(v[0], v[1], v[2]), t1 = max3(v[3], v[4], v[5]), t2 = max3(v[6], v[7], v[8]);
+        const float t3 = max3(v[9], v[10], v[11]), t4 = max3(v[12], v[13], v[14]);
+        bs[bk] = fmaxf(max3(t0, t1, t2), max3(t3, t4, v[15]));
       }
-      const float m_new = fmaxf(m, fmaxf(max3(bs[0], bs[1], bs[2]), bs[3]) * c1);
+      const float m_new = fmaxf(m, fmaxf(max3(bs[0], bs[1], bs[2]), max3(bs[3], bs[4], max3(bs[5], bs[6], bs[7]))) * c1);
       if (j > 0 && __any_sync(0xffffffffu, m_new != m)) {
         // a maximum of this warp's rows moved: O is rescaled, once the previous tile's P V is complete
-        ok = warp_all(mbar_wait(o_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, p.wait_ns));
+        ok = warp_all(mbar_wait(my_o_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, p.wait_ns));
         if (!ok) break;
         tc_fence_after();
         const float a = ex2_approx(m - m_new);
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          uint32_t ro[16];
+          tmem_ld_32x32b_x16(t_o + 16 * c, ro);
+          tmem_ld_wait();
+          tmem_pin(ro);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t ro[32];
-          tmem_ld_32x32b_x32_sync(t_o + 32 * c, ro);
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(ro[i]) * a;
-          tmem_st_32x32b_x32_f(t_o + 32 * c, v);
+          for (int i = 0; i < 16; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * a);
+          tmem_st_32x32b_x16(t_o + 16 * c, ro);
         }
         tmem_st_wait();
         l *= a;
       }
-      if (q == 0 && lane == 0) AC4K_TRM(0, j, 3);
+      m = m_new;
+      if (tracer) AC4K_TRM(2 * g, j, 3);
+      // the exponential phases of the two groups take turns
+      if (both) {
+        ok = warp_all(mbar_wait(my_tok, g == 0 ? ((j & 1) ^ 1) : (j & 1), p.wait_ns));
+        if (!ok) break;
+      }
+      if (tracer) AC4K_TRM(2 * g, j, 4);
       // This tile's P buffer was last read by the P V of two tiles ago.  That MMA was issued before this tile's S, and
       // the tensor pipe completes MMAs (and the commits behind them) in issue order: s_full of this tile, seen above,
       // implies it is complete, so no wait is needed here.
-      m = m_new;
-      if (q == 0 && lane == 0) AC4K_TRM(0, j, 4);
-      // probabilities, row sum, NVFP4 quantisation of P: four blocks of 16 keys, so that position n of P meets position n
-      // of V^T
+      // Probabilities, row sum, NVFP4 quantisation of P: eight blocks of 16 keys, so that position n of P meets position
+      // n of V^T.
       const uint32_t p_row = p_row0 + (j & 1) * P_BYTES;
       float2 lsum = make_float2(0.0f, 0.0f);
       const float2 c1_2 = make_float2(c1, c1), negm2 = make_float2(-m, -m);
-      uint32_t sfw = 0;
+      uint32_t sfw[2] = {0u, 0u};
 #pragma unroll
-      for (int g = 0; g < 2; ++g) {
+      for (int gg = 0; gg < 4; ++gg) {
         float2 pr[16];
 #pragma unroll
         for (int n = 0; n < 32; n += 2) {
-          const int i = 32 * g + (((n >> 1) & 3) * 4 + (n >> 3)) * 2;     // keys held at positions n, n + 1
+          const int i = 32 * gg + (((n >> 1) & 3) * 4 + (n >> 3)) * 2;     // keys held at positions n, n + 1
           const float2 e = ffma2(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), c1_2, negm2);
           pr[n >> 1] = make_float2(ex2_approx(e.x), ex2_approx(e.y));
           lsum = fadd2(lsum, pr[n >> 1]);
         }
-        const float bm0 = ex2_approx(fmaf(bs[2 * g], c1, -m)), bm1 = ex2_approx(fmaf(bs[2 * g + 1], c1, -m));
+        const float bm0 = ex2_approx(fmaf(bs[2 * gg], c1, -m)), bm1 = ex2_approx(fmaf(bs[2 * gg + 1], c1, -m));
         float sd0, sd1;
         const uint32_t sb2 = e4m3x2_round_trip(__fmul_rn(kPGlobal, __fmul_rn(bm0, kOneSixth)),
                                                __fmul_rn(kPGlobal, __fmul_rn(bm1, kOneSixth)), sd0, sd1);
-        sfw |= sb2 << (16 * g);
+        sfw[gg >> 1] |= sb2 << (16 * (gg & 1));
         const float sc0 = sd0 != 0.0f ? kPGlobal * rcp_approx(sd0) : 0.0f, sc1 = sd1 != 0.0f ? kPGlobal * rcp_approx(sd1) : 0.0f;
         uint32_t codes[4];
 #pragma unroll
@@ -383,23 +450,30 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
           }
           codes[hh] = f32x8_to_e2m1x8(x);
         }
-        st_shared_v4u(p_row + (((uint32_t)g << 4) ^ p_xor), codes[0], codes[1], codes[2], codes[3]);
+        st_shared_v4u(p_row + (((uint32_t)gg << 4) ^ p_xor), codes[0], codes[1], codes[2], codes[3]);
       }
       l += lsum.x + lsum.y;
-      // scale chunk: 32 rows of 16 bytes, row `lane` holding the words of query rows lane, 32 + lane, 64 + lane, 96 + lane
-      st_shared_u32(sSFP + (j & 1) * SFP_BYTES + lane * 16 + q * 4, sfw);
+      if (both) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(other_tok);
+      }
+      if (tracer) AC4K_TRM(2 * g, j, 5);
+      // scale chunks of the two K = 64 steps: 32 rows of 16 bytes, row `lane` holding the words of query rows lane,
+      // 32 + lane, 64 + lane, 96 + lane
+      st_shared_u32(sfp0 + (j & 1) * SF_BYTES, sfw[0]);
+      st_shared_u32(sfp0 + (j & 1) * SF_BYTES + 512, sfw[1]);
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (q == 0 && lane == 0) AC4K_TRM(0, j, 5);
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(my_p_full);
+      if (tracer) AC4K_TRM(2 * g, j, 6);
     }
-    if (ok) ok = warp_all(mbar_wait(o_done + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, p.wait_ns));
+    if (ok) ok = warp_all(mbar_wait(my_o_done + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, p.wait_ns));
     if (!ok) {
       if (lane == 0) atomicExch(p.status, kStatusTimeoutEpilogue);
     } else {
       tc_fence_after();
-      const int n = qt * BQ + row_l;
+      const int n = (2 * qt + g) * BQ + row_l;
       const float out_scale = __ldg(p.v_gs) / (kPGlobal * l);
       __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(p.O) + (int64_t)b * p.o_b + (int64_t)h * p.o_h + (int64_t)n * p.o_n;
 #pragma unroll
@@ -465,12 +539,12 @@ extern "C" int ac4k_mha_nvfp4_fwd(void *O, const int64_t o_stride[4], const void
   if (di.cc_major != 10) return fail(AC4K_ERR_DEVICE, "mha_nvfp4_fwd needs an sm_100 device (found sm_%d0)", di.cc_major);
   unsigned int *status = device_status_ptr();
   if (!status) return fail(AC4K_ERR_DEVICE, "cannot resolve the device status word");
-  const int64_t kv_tiles = ceil_div(Nkv, 64);
+  const int64_t v_k64 = ceil_div(Nkv, 64);
   CUtensorMap tq, tk, tv;
   // Q, K: [B*H*N, 64 bytes] (head dimension padded to 128 by the quantiser); V^T: [B*H*Dv, align64(Nkv)/2 bytes]
   if (int e = get_tmap64(Q, B * H * Nq, 64, mha::BQ, &tq)) return e;
   if (int e = get_tmap64(K, B * H * Nkv, 64, mha::BKV, &tk)) return e;
-  if (int e = get_tmap32(V, B * H * Dv, kv_tiles * 32, 128, &tv)) return e;
+  if (int e = get_tmap64(V, B * H * Dv, v_k64 * 32, 128, &tv)) return e;
   MhaArgs a = {};
   a.sfq = static_cast<const uint8_t *>(Q_sf);
   a.sfk = static_cast<const uint8_t *>(K_sf);
@@ -480,8 +554,8 @@ extern "C" int ac4k_mha_nvfp4_fwd(void *O, const int64_t o_stride[4], const void
   a.o_b = o_stride[0]; a.o_h = o_stride[1]; a.o_n = o_stride[2]; a.o_d = o_stride[3];
   a.B = (int)B; a.H = (int)H; a.Nq = (int)Nq; a.Nkv = (int)Nkv; a.Dv = (int)Dv;
   a.q_blocks = (int)ceil_div(Nq, 128);
-  a.k_blocks = (int)ceil_div(Nkv, 128);
-  a.kv_tiles = (int)kv_tiles;
+  a.kv_tiles = (int)ceil_div(Nkv, 128);
+  a.v_k64 = (int)v_k64;
   a.sm_scale = sm_scale;
   a.status = status;
   a.wait_ns = kWaitTimeoutNs;
@@ -495,7 +569,7 @@ extern "C" int ac4k_mha_nvfp4_fwd(void *O, const int64_t o_stride[4], const void
       }))
     return e;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)a.q_blocks, (unsigned)H, (unsigned)B);
+  cfg.gridDim = dim3((unsigned)((a.q_blocks + 1) / 2), (unsigned)H, (unsigned)B);
   cfg.blockDim = dim3(mha::kThreads);
   cfg.dynamicSmemBytes = mha::SMEM_BYTES;
   cfg.stream = stream;

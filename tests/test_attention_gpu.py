@@ -79,8 +79,8 @@ ORACLE_CASES = [
     (1, 1, 64, 64, 128, 128),
     (2, 3, 200, 200, 128, 128),
     (1, 2, 77, 515, 128, 128),       # Nq != Nkv, ragged last key tile (3 keys), ragged query tile
-    (1, 2, 300, 129, 128, 128),      # one key in the third key tile
-    (1, 1, 40, 64, 128, 128),        # a single key tile
+    (1, 2, 300, 129, 128, 128),      # one key in the second key tile; three query tiles (the last CTA has one)
+    (1, 1, 40, 64, 128, 128),        # a single key tile, half of it
     (1, 2, 130, 190, 96, 80),        # head dimensions below 128 (padded by the quantiser)
     (1, 1, 128, 2048, 128, 128),
 ]
@@ -106,9 +106,9 @@ def test_kernel_against_oracle_on_the_same_operands(B, H, Nq, Nkv, Dqk, Dv, layo
     torch.cuda.synchronize()
     from ac4k_kernel_b200 import _lib
     assert _lib.device_status() == 0
-    # the restatement walks the keys in the kernel's tiles of 64 (the reference's kernel: 128); the tile moves the running
-    # maximum P is rounded against and nothing else (tests/test_attention_oracle.py)
-    want = E.mha_nvfp4_ref(qq, qs, qg, kq, ks, kg, vq, vs, vg, sm, Nkv, tile=64)
+    # the restatement walks the keys in tiles of 128, as the kernel and the reference's kernel do (the tile decides which
+    # running maximum P is rounded against: tests/test_attention_oracle.py)
+    want = E.mha_nvfp4_ref(qq, qs, qg, kq, ks, kg, vq, vs, vg, sm, Nkv, tile=128)
     got = view.float()
     assert torch.isfinite(got).all()
     # Tolerance, stated: the kernel and the restatement differ in fp32 accumulation order, in ex2.approx
