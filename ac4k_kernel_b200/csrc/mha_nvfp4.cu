@@ -21,10 +21,10 @@
 //              memory in the layouts the tensor core reads (64-byte-swizzled K-major operand, 32 x 16-byte scale
 //              chunks); at the end O * gV / (2688 * row sum) is stored as bf16.
 // The softmax bounds this kernel: an SM retires 16 ex2 per clock, 1024 cycles for 128 x 128 scores against 330 for the
-// four-bit MMAs.  So the exponential phases of the two groups take turns (a token passed through two mbarriers): while
-// one group keeps the ex2 pipe busy, the other does everything that does not need it (wait for S, copy it out, maxima,
-// rescale, fences, barrier traffic: ~800 cycles per key tile).  Two independent CTAs per SM measured 1.34x slower:
-// they start together and stay in step, so both sit in those phases at the same time.
+// four-bit MMAs.  One warp per scheduler keeps the ex2 pipe ~65 % busy, two keep it full, but two groups that run in
+// step also sit together in the phases that do not use it (wait for S, copy it out, maxima, rescale, fences, barrier
+// traffic: ~800 cycles per key tile).  So the groups are kept out of step by a token passed through two mbarriers: a
+// group starts the exponentials of a tile only when the other group is at least half way through its own.
 // Tensor memory: S 128 + O_A 128 + O_B 128 + scales 40 columns of 512.
 //
 // Supported: head dimensions in (64, 128] (padded to 128 by the quantiser), scales in the tiled layout
@@ -46,7 +46,8 @@ static constexpr int P_BYTES = BQ * 64;           // 128 query rows x 128 keys
 static constexpr int SF_BYTES = 2 * 512;          // two K = 64 steps of 128 rows
 static constexpr int KV_STAGES = 4;
 static constexpr int STAGE_BYTES = K_BYTES + V_BYTES + 2 * SF_BYTES;       // 18 432
-static constexpr int SMEM_BYTES = 2 * Q_BYTES + 4 * P_BYTES + KV_STAGES * STAGE_BYTES + 2 * SF_BYTES + 4 * SF_BYTES + 1024 + 256;
+static constexpr int LUT_BYTES = 128 * 4;         // 2688 / e4m3 value for the 127 finite non-negative e4m3 bytes
+static constexpr int SMEM_BYTES = 2 * Q_BYTES + 4 * P_BYTES + KV_STAGES * STAGE_BYTES + 2 * SF_BYTES + 4 * SF_BYTES + LUT_BYTES + 1024 + 256;
 // tensor memory columns
 static constexpr int S_COL = 0, O_COL = 128 /* + 128 * group */, SFQ_COL = 384 /* + 8 * group */, SFK_COL = 400, SFP_COL = 408,
                      SFV_COL = 416;
@@ -151,7 +152,8 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   const uint32_t sKV = sP + 4 * P_BYTES;             // per stage: K | V^T | SFK | SFV
   const uint32_t sSFQ = sKV + KV_STAGES * STAGE_BYTES;   // [group]
   const uint32_t sSFP = sSFQ + 2 * SF_BYTES;         // [group][buffer]
-  const uint32_t bars = sSFP + 4 * SF_BYTES;
+  const uint32_t sLUT = sSFP + 4 * SF_BYTES;
+  const uint32_t bars = sLUT + LUT_BYTES;
   const uint32_t q_full = bars, kv_full = bars + 8, kv_empty = kv_full + 8 * KV_STAGES;
   const uint32_t s_full = kv_empty + 8 * KV_STAGES;  // [group]
   const uint32_t s_free = s_full + 16;
@@ -192,6 +194,14 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
+  }
+  if (threadIdx.x >= 64 && threadIdx.x < 192) {
+    // what a block's probabilities are multiplied with, by the block's e4m3 scale byte: 2688 / scale (0 for scale 0)
+    const uint32_t bte = threadIdx.x - 64;
+    const __half_raw hr = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)bte, __NV_E4M3);
+    const float sd = __half2float(__half(hr));
+    const float sc = (bte != 0 && bte != 127) ? __fdiv_rn(kPGlobal, sd) : 0.0f;
+    asm volatile("st.shared::cta.f32 [%0], %1;" ::"r"(sLUT + bte * 4), "f"(sc) : "memory");
   }
   tc_fence_before();
   __syncthreads();
@@ -341,20 +351,13 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       if (!ok) break;
       tc_fence_after();
       if (tracer) AC4K_TRM(2 * g, j, 1);
-      uint32_t r[128];
-      {
-        uint32_t lo[64], hi[64];
-        tmem_ld_32x32b_x64(t_s, lo);
-        tmem_ld_32x32b_x64(t_s + 64, hi);
-        tmem_ld_wait();
-        tmem_pin(lo);
-        tmem_pin(hi);
-#pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          r[i] = lo[i];
-          r[64 + i] = hi[i];
-        }
-      }
+      uint32_t lo[64], hi[64];               // scores of keys 0-63 and 64-127
+      tmem_ld_32x32b_x64(t_s, lo);
+      tmem_ld_32x32b_x64(t_s + 64, hi);
+      tmem_ld_wait();
+      tmem_pin(lo);
+      tmem_pin(hi);
+#define AC4K_S(i) ((i) < 64 ? lo[(i) & 63] : hi[(i) & 63])
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_free);
@@ -362,12 +365,15 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       const int ncols = p.Nkv - j * BKV;                 // keys of this tile that exist (>= 128 except in the last tile)
       if (ncols < BKV) {
 #pragma unroll
-        for (int i = 0; i < BKV; ++i)
-          if (i >= ncols) r[i] = 0xff800000u;            // -inf: out of the maximum, probability 0
+        for (int i = 0; i < 64; ++i) {
+          if (i >= ncols) lo[i] = 0xff800000u;           // -inf: out of the maximum, probability 0
+          if (64 + i >= ncols) hi[i] = 0xff800000u;
+        }
       }
       // Maxima of the scores per block of 16 in the stored key order (the reference's V quantiser's "swizzle": every 32
       // keys viewed as [4, 4, 2] and transposed to [4(b), 4(a), 2]; positions n, n + 1 hold keys key0(n), key0(n) + 1),
-      // and the row maximum from them.  ex2 is monotonic, so a block's largest probability is ex2 of its largest score.
+      // and the row maximum from them.  ex2 is monotonic, so a block's largest probability is ex2 of its largest score:
+      // it is known before the block's probabilities are, and their conversion does not have to wait for all of them.
       float bs[8];
 #pragma unroll
       for (int bk = 0; bk < 8; ++bk) {
@@ -376,8 +382,8 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         for (int n = 0; n < 16; n += 2) {
           const int nn = 16 * (bk & 1) + n;
           const int i = 32 * (bk >> 1) + (((nn >> 1) & 3) * 4 + (nn >> 3)) * 2;
-          v[n] = __uint_as_float(r[i]);
-          v[n + 1] = __uint_as_float(r[i + 1]);
+          v[n] = __uint_as_float(AC4K_S(i));
+          v[n + 1] = __uint_as_float(AC4K_S(i + 1));
         }
         const float t0 = max3(v[0], v[1], v[2]), t1 = max3(v[3], v[4], v[5]), t2 = max3(v[6], v[7], v[8]);
         const float t3 = max3(v[9], v[10], v[11]), t4 = max3(v[12], v[13], v[14]);
@@ -414,28 +420,35 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       // This tile's P buffer was last read by the P V of two tiles ago.  That MMA was issued before this tile's S, and
       // the tensor pipe completes MMAs (and the commits behind them) in issue order: s_full of this tile, seen above,
       // implies it is complete, so no wait is needed here.
-      // Probabilities, row sum, NVFP4 quantisation of P: eight blocks of 16 keys, so that position n of P meets position
-      // n of V^T.
+      // Probabilities, row sum, NVFP4 quantisation of P in eight blocks of 16 keys.  P is stored in the key order of the
+      // reference's V quantiser ("swizzle": every 32 keys viewed as [4, 4, 2] and transposed to [4(b), 4(a), 2]; positions
+      // n, n + 1 hold keys key0(n), key0(n) + 1), so that position n of P meets position n of V^T.
       const uint32_t p_row = p_row0 + (j & 1) * P_BYTES;
-      float2 lsum = make_float2(0.0f, 0.0f);
+      float2 lsum[4];
       const float2 c1_2 = make_float2(c1, c1), negm2 = make_float2(-m, -m);
       uint32_t sfw[2] = {0u, 0u};
 #pragma unroll
       for (int gg = 0; gg < 4; ++gg) {
         float2 pr[16];
+        lsum[gg] = make_float2(0.0f, 0.0f);
 #pragma unroll
         for (int n = 0; n < 32; n += 2) {
           const int i = 32 * gg + (((n >> 1) & 3) * 4 + (n >> 3)) * 2;     // keys held at positions n, n + 1
-          const float2 e = ffma2(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), c1_2, negm2);
+          const float2 e = ffma2(make_float2(__uint_as_float(AC4K_S(i)), __uint_as_float(AC4K_S(i + 1))), c1_2, negm2);
           pr[n >> 1] = make_float2(ex2_approx(e.x), ex2_approx(e.y));
-          lsum = fadd2(lsum, pr[n >> 1]);
+          lsum[gg] = fadd2(lsum[gg], pr[n >> 1]);
         }
-        const float bm0 = ex2_approx(fmaf(bs[2 * gg], c1, -m)), bm1 = ex2_approx(fmaf(bs[2 * gg + 1], c1, -m));
-        float sd0, sd1;
-        const uint32_t sb2 = e4m3x2_round_trip(__fmul_rn(kPGlobal, __fmul_rn(bm0, kOneSixth)),
-                                               __fmul_rn(kPGlobal, __fmul_rn(bm1, kOneSixth)), sd0, sd1);
-        sfw[gg >> 1] |= sb2 << (16 * (gg & 1));
-        const float sc0 = sd0 != 0.0f ? kPGlobal * rcp_approx(sd0) : 0.0f, sc1 = sd1 != 0.0f ? kPGlobal * rcp_approx(sd1) : 0.0f;
+        float bm[2];
+        bm[0] = ex2_approx(fmaf(bs[2 * gg], c1, -m));
+        bm[1] = ex2_approx(fmaf(bs[2 * gg + 1], c1, -m));
+        uint16_t sb2;
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(sb2) : "f"(__fmul_rn(kPGlobal, __fmul_rn(bm[1], kOneSixth))),
+            "f"(__fmul_rn(kPGlobal, __fmul_rn(bm[0], kOneSixth))));
+        sfw[gg >> 1] |= (uint32_t)sb2 << (16 * (gg & 1));
+        float sc0, sc1;
+        // (the table is written once before the first barrier: these loads may be scheduled freely)
+        asm("ld.shared::cta.f32 %0, [%1];" : "=f"(sc0) : "r"(sLUT + ((uint32_t)sb2 & 0xffu) * 4));
+        asm("ld.shared::cta.f32 %0, [%1];" : "=f"(sc1) : "r"(sLUT + ((uint32_t)sb2 >> 8) * 4));
         uint32_t codes[4];
 #pragma unroll
         for (int hh = 0; hh < 4; ++hh) {
@@ -451,12 +464,14 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
           codes[hh] = f32x8_to_e2m1x8(x);
         }
         st_shared_v4u(p_row + (((uint32_t)gg << 4) ^ p_xor), codes[0], codes[1], codes[2], codes[3]);
+        if (gg == 1 && both) {
+          // half of this tile's exponentials are issued: the other group may start its own
+          __syncwarp();
+          if (lane == 0) mbar_arrive(other_tok);
+        }
       }
-      l += lsum.x + lsum.y;
-      if (both) {
-        __syncwarp();
-        if (lane == 0) mbar_arrive(other_tok);
-      }
+#undef AC4K_S
+      l += (lsum[0].x + lsum[0].y) + (lsum[1].x + lsum[1].y) + ((lsum[2].x + lsum[2].y) + (lsum[3].x + lsum[3].y));
       if (tracer) AC4K_TRM(2 * g, j, 5);
       // scale chunks of the two K = 64 steps: 32 rows of 16 bytes, row `lane` holding the words of query rows lane,
       // 32 + lane, 64 + lane, 96 + lane
