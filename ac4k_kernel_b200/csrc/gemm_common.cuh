@@ -153,7 +153,6 @@ int get_tmap_sf_tiled(const void *ptr, int64_t row_blocks, int64_t kt, int box_k
 // 16-bit output [rows, cols] with a row pitch of ld elements: boxes of 64 columns x 32 rows, 128-byte swizzle
 int get_tmap64(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUtensorMap *out);
 unsigned long long *debug_trace_ptr();
-int get_tmap32(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUtensorMap *out);
 int get_tmap_out16(const void *ptr, int64_t rows, int64_t cols, int64_t ld, CUtensorMap *out);
 int launch_linear_2cta(int d_dtype, bool sf_tiled, const CUtensorMap &ta, const CUtensorMap &tb,
                        const CUtensorMap &tsa, const CUtensorMap &tsb, const DstMaps &dm, GemmArgs args, cudaStream_t stream);

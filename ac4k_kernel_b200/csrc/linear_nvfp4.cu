@@ -424,9 +424,9 @@ struct TmapKey {
   }
 };
 struct TmapEntry { TmapKey key; CUtensorMap map; };
-enum { kTmapOperand = 0, kTmapWords = 1, kTmapOut16 = 2, kTmapOperand64 = 3, kTmapOperand32 = 4 };
+enum { kTmapOperand = 0, kTmapWords = 1, kTmapOut16 = 2, kTmapOperand64 = 3 };
 
-// kind kTmapOperand / kTmapOperand64 / kTmapOperand32: bytes, 128- / 64- / 32-byte swizzle; kTmapWords: 32-bit words, not swizzled;
+// kind kTmapOperand / kTmapOperand64: bytes, 128- / 64-byte swizzle; kTmapWords: 32-bit words, not swizzled;
 // kTmapOut16: 16-bit elements, 128-byte swizzle.
 static int encode_cached(int kind, const void *ptr, int64_t d0, int64_t d1, int64_t pitch, int box0, int box1,
                          CUtensorMap *out) {
@@ -442,11 +442,10 @@ static int encode_cached(int kind, const void *ptr, int64_t d0, int64_t d1, int6
   }
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return fail(AC4K_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
-  const bool bytes = kind == kTmapOperand || kind == kTmapOperand64 || kind == kTmapOperand32;
+  const bool bytes = kind == kTmapOperand || kind == kTmapOperand64;
   const int esize = bytes ? 1 : (kind == kTmapWords ? 4 : 2);
   const CUtensorMapSwizzle swz = (kind == kTmapOperand || kind == kTmapOut16) ? CU_TENSOR_MAP_SWIZZLE_128B
-                                 : (kind == kTmapOperand64 ? CU_TENSOR_MAP_SWIZZLE_64B
-                                    : (kind == kTmapOperand32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE));
+                                 : (kind == kTmapOperand64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE);
   const CUtensorMapDataType dt = bytes ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                  : (kind == kTmapWords ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16);
   cuuint64_t gdim[2] = {(cuuint64_t)d0, (cuuint64_t)d1};
@@ -487,10 +486,6 @@ int get_tmap_out16(const void *ptr, int64_t rows, int64_t cols, int64_t ld, CUte
 // packed operand [rows, row_bytes] whose contraction rows are 64 bytes: boxes of 64 bytes x box_rows rows, 64-byte swizzle
 int get_tmap64(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUtensorMap *out) {
   return encode_cached(kTmapOperand64, ptr, row_bytes, rows, row_bytes, 64, box_rows, out);
-}
-// ... whose contraction rows are taken 32 bytes at a time: boxes of 32 bytes x box_rows rows, 32-byte swizzle
-int get_tmap32(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUtensorMap *out) {
-  return encode_cached(kTmapOperand32, ptr, row_bytes, rows, row_bytes, 32, box_rows, out);
 }
 
 int get_device_info(DeviceInfo *out) {

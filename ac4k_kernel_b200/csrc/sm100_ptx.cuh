@@ -136,8 +136,8 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 // Shared-memory matrix descriptor (K-major operand).  Fields: start address >> 4 in bits
 // [0,14), leading-dimension byte offset >> 4 in [16,30), stride-dimension byte offset >> 4 in
 // [32,46) (distance between 8-row groups), descriptor version 1 in [46,48), swizzle mode in
-// [61,64) (0 none, 2 = 128-byte, 4 = 64-byte, 6 = 32-byte).
-static constexpr uint32_t kSwizzleNone = 0, kSwizzle128B = 2, kSwizzle64B = 4, kSwizzle32B = 6;
+// [61,64) (0 none, 2 = 128-byte, 4 = 64-byte).
+static constexpr uint32_t kSwizzleNone = 0, kSwizzle128B = 2, kSwizzle64B = 4;
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
                                                    uint32_t swizzle) {
   uint64_t d = 0;
