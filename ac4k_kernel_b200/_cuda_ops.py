@@ -298,8 +298,8 @@ def mha_nvfp4_fwd(o, q, q_sf, q_global_scale, k, k_sf, k_global_scale, v, v_sf, 
     """o = softmax(sm_scale * q k^T) v on NVFP4 operands (ops.h:13-17; checks of
     lib/cuda/sm120/mha_nvfp4.cu:897-1010).  q: [B, H, Nq, Dqk/2], k: [B, H, Nkv, Dqk/2],
     v: [B, H, Dv, align64(Nkv)/2] (quantised along the keys, swizzle=True), o: bf16 [B, H, Nq, Dv] in any
-    strides (the reference passes a permuted [B, N, H, D] buffer).  Block scales in the tiled layout
-    [B, H, ceil(rows/128), K/64, 32, 4, 4]."""
+    strides (the reference passes a permuted [B, N, H, D] buffer).  Block scales either in the reference's layout
+    [B, H, K/64, align16(rows), 4] or tiled [B, H, ceil(rows/128), K/64, 32, 4, 4] (all three alike)."""
     _check_tensor(q, torch.uint8, "Q")
     _require(q.dim() == 4, "Q must be a 4D tensor")
     B, H, Nq = q.size(0), q.size(1), q.size(2)
@@ -319,14 +319,17 @@ def mha_nvfp4_fwd(o, q, q_sf, q_global_scale, k, k_sf, k_global_scale, v, v_sf, 
     Dv = v.size(2)
     _require(v.size(3) * 2 == _align_up(Nkv, 64), "V must have the same sequence length as K")
     _require(Dv <= 128, "Dv must be less than 128")
+    layout = SF_TILE128X4 if q_sf.dim() == 7 else SF_AC4K
     for name, sf, rows, red in (("q_sf", q_sf, Nq, Dqk), ("k_sf", k_sf, Nkv, Dqk), ("v_sf", v_sf, Dv, Nkv)):
         _check_tensor(sf, torch.float8_e4m3fn, name)
-        _require(sf.dim() in (5, 7), f"{name} must be a 5D tensor, or 7D in the tiled layout")
-        if sf.dim() == 5:
-            raise RuntimeError(f"{name}: the sm100 attention kernel reads block scales in the tiled layout "
-                               "(quantize(..., sf_layout=\"128x4\")); the [.., K/64, rows, 4] layout is not built")
-        _require(list(sf.shape) == [B, H, _ceil_div(rows, 128), _ceil_div(red, 64), 32, 4, 4],
-                 f"Meet invalid {name} shape {list(sf.shape)}")
+        if layout == SF_AC4K:       # the reference's layout and checks (mha_nvfp4.cu:915-1008)
+            _require(sf.dim() == 5, f"{name} must be a 5D tensor")
+            _require(list(sf.shape) == [B, H, _ceil_div(red, 64), _align_up(rows, 16), 4],
+                     f"Meet invalid {name} shape {list(sf.shape)}")
+        else:
+            _require(sf.dim() == 7, f"{name} must be a 7D tensor like q_sf (tiled layout)")
+            _require(list(sf.shape) == [B, H, _ceil_div(rows, 128), _ceil_div(red, 64), 32, 4, 4],
+                     f"Meet invalid {name} shape {list(sf.shape)}")
     for name, g in (("q_global_scale", q_global_scale), ("k_global_scale", k_global_scale),
                     ("v_global_scale", v_global_scale)):
         _check_tensor(g, torch.float32, name)
@@ -340,7 +343,7 @@ def mha_nvfp4_fwd(o, q, q_sf, q_global_scale, k, k_sf, k_global_scale, v, v_sf, 
                                      q_global_scale.data_ptr(), k.data_ptr(), k_sf.data_ptr(),
                                      k_global_scale.data_ptr(), v.data_ptr(), v_sf.data_ptr(),
                                      v_global_scale.data_ptr(), B, H, Nq, Nkv, Dqk, Dv, float(sm_scale),
-                                     SF_TILE128X4, _stream(o)),
+                                     layout, _stream(o)),
               "mha_nvfp4_fwd")
 
 

@@ -195,7 +195,8 @@ void global_scale_bf16(torch::Tensor &out, torch::Tensor const &x, double max_sc
 }
 
 // ops.h:13-17; checks of mha_nvfp4.cu:897-1010.  O may be a permuted view ([B, N, H, D] storage): the kernel addresses it
-// by strides.  Block scales in the tiled layout [B, H, ceil(rows/128), K/64, 32, 4, 4].
+// by strides.  Block scales in the reference's layout [B, H, K/64, align16(rows), 4] or tiled
+// [B, H, ceil(rows/128), K/64, 32, 4, 4].
 void mha_nvfp4_fwd(torch::Tensor &o, torch::Tensor &q, torch::Tensor &q_sf, torch::Tensor &q_global_scale, torch::Tensor &k,
                    torch::Tensor &k_sf, torch::Tensor &k_global_scale, torch::Tensor &v, torch::Tensor &v_sf,
                    torch::Tensor &v_global_scale, float sm_scale) {
@@ -219,12 +220,17 @@ void mha_nvfp4_fwd(torch::Tensor &o, torch::Tensor &q, torch::Tensor &q_sf, torc
   TORCH_CHECK(Dv <= 128, "Dv must be less than 128");
   struct Sf { const char *name; torch::Tensor *t; int64_t rows, red; };
   const Sf sfs[3] = {{"q_sf", &q_sf, Nq, Dqk}, {"k_sf", &k_sf, Nkv, Dqk}, {"v_sf", &v_sf, Dv, Nkv}};
+  const bool tiled = q_sf.dim() == 7;
   for (const Sf &s : sfs) {
     check_cuda(*s.t, at::kFloat8_e4m3fn, s.name);
-    TORCH_CHECK(s.t->dim() == 7, s.name, ": the sm100 attention kernel reads block scales in the tiled layout "
-                "[B, H, ceil(rows/128), K/64, 32, 4, 4]; the [.., K/64, rows, 4] layout is not built");
-    const std::vector<int64_t> want = {B, H, ceil_div(s.rows, 128), ceil_div(s.red, 64), 32, 4, 4};
-    TORCH_CHECK(s.t->sizes().vec() == want, "Meet invalid ", s.name, " shape");
+    if (tiled) {
+      const std::vector<int64_t> want = {B, H, ceil_div(s.rows, 128), ceil_div(s.red, 64), 32, 4, 4};
+      TORCH_CHECK(s.t->sizes().vec() == want, "Meet invalid ", s.name, " shape (tiled layout)");
+    } else {   // the reference's layout and checks (mha_nvfp4.cu:915-1008)
+      TORCH_CHECK(s.t->dim() == 5, s.name, " must be a 5D tensor");
+      const std::vector<int64_t> want = {B, H, ceil_div(s.red, 64), align_up(s.rows, 16), 4};
+      TORCH_CHECK(s.t->sizes().vec() == want, "Meet invalid ", s.name, " shape");
+    }
   }
   for (torch::Tensor *g : {&q_global_scale, &k_global_scale, &v_global_scale}) {
     check_cuda(*g, at::kFloat, "global_scale");
@@ -239,7 +245,7 @@ void mha_nvfp4_fwd(torch::Tensor &o, torch::Tensor &q, torch::Tensor &q_sf, torc
   const int rc = ac4k_mha_nvfp4_fwd(o.data_ptr(), os, q.data_ptr(), q_sf.data_ptr(), q_global_scale.data_ptr<float>(),
                                     k.data_ptr(), k_sf.data_ptr(), k_global_scale.data_ptr<float>(), v.data_ptr(),
                                     v_sf.data_ptr(), v_global_scale.data_ptr<float>(), B, H, Nq, Nkv, Dqk, Dv, sm_scale,
-                                    AC4K_SF_TILE128X4, at::cuda::getCurrentCUDAStream().stream());
+                                    tiled ? AC4K_SF_TILE128X4 : AC4K_SF_AC4K, at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(rc == 0, "ac4k_mha_nvfp4_fwd: ", ac4k_last_error());
 }
 

@@ -27,8 +27,8 @@
 // group starts the exponentials of a tile only when the other group is at least half way through its own.
 // Tensor memory: S 128 + O_A 128 + O_B 128 + scales 40 columns of 512.
 //
-// Supported: head dimensions in (64, 128] (padded to 128 by the quantiser), scales in the tiled layout
-// [.., 128-row block, K/64, 32 x 16 B]; V quantised along the keys (cross dimension = head dimension) with the
+// Supported: head dimensions in (64, 128] (padded to 128 by the quantiser); block scales in the tiled layout
+// [.., 128-row block, K/64, 32 x 16 B] or in the reference's [.., K/64, align16(rows), 4]; V quantised along the keys (cross dimension = head dimension) with the
 // reference's K permutation (quantize(v, 3, N_dim, swizzle=True), python/ac4k_kernel/ops/attention.py:113-118):
 // P is written in the same key order, so scale blocks of P and V cover the same 16 keys as in the reference.
 #include "gemm_common.cuh"
@@ -38,7 +38,7 @@ using namespace ptx;
 
 namespace mha {
 static constexpr int BQ = 128, BKV = 128, D = 128;
-static constexpr int kThreads = 320;              // producer, MMA issuer, 2 x 4 softmax warps
+static constexpr int kThreads = 352;              // producer, MMA issuer, 2 x 4 softmax warps, scale re-order warp
 static constexpr int Q_BYTES = BQ * 64;           // 128 rows x 128 e2m1, 64-byte rows
 static constexpr int K_BYTES = BKV * 64;          // 128 keys x 128 e2m1
 static constexpr int V_BYTES = D * 64;            // 128 head-dimension rows x 128 keys
@@ -58,13 +58,14 @@ static_assert(SMEM_BYTES <= 227 * 1024, "shared memory overflow");
 }  // namespace mha
 
 struct MhaArgs {
-  const uint8_t *sfq, *sfk, *sfv;       // tiled scales
+  const uint8_t *sfq, *sfk, *sfv;       // block scales: tiled layout, or the reference's [K/64, align16(rows), 4]
   const float *q_gs, *k_gs, *v_gs;
   void *O;
   int64_t o_b, o_h, o_n, o_d;           // strides of O in elements
   int B, H, Nq, Nkv, Dv;
   int q_blocks, kv_tiles;               // ceil(Nq / 128), ceil(Nkv / 128): 128-row blocks of Q and of the keys
   int v_k64;                            // align64(Nkv) / 64: K = 64 steps of V^T that exist
+  int q_pad, k_pad, v_pad;              // align16 of Nq, Nkv, Dv: scale rows per K step in the reference's layout
   float sm_scale;
   unsigned int *status;
   unsigned long long wait_ns;
@@ -160,6 +161,10 @@ __device__ __forceinline__ void tmem_st_32x32b_x32_f(uint32_t taddr, const float
   tmem_st_32x32b_x32(taddr, u);
 }
 
+// SF_TILED: block scales arrive as 512-byte chunks that tensor memory takes as they are (bulk copies).  Otherwise they
+// are in the reference's layout, one 32-bit word per row and K = 64 step, rows contiguous: warp 10 transposes each
+// chunk (128 words -> 32 rows of 4 words) into shared memory with plain loads.
+template <bool SF_TILED>
 __global__ void __launch_bounds__(mha::kThreads, 1)
 mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                      const __grid_constant__ CUtensorMap tma_v, const MhaArgs p) {
@@ -192,9 +197,9 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   const bool both = 2 * qt + 1 < p.q_blocks;         // group B has query rows
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
+    mbar_init(q_full, SF_TILED ? 1 : 2);
     for (int s = 0; s < KV_STAGES; ++s) {
-      mbar_init(kv_full + 8 * s, 1);
+      mbar_init(kv_full + 8 * s, SF_TILED ? 1 : 2);
       mbar_init(kv_empty + 8 * s, 1);
     }
     for (int g = 0; g < 2; ++g) {
@@ -233,10 +238,11 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     // ------------------------------------------------------------------ TMA producer
     const uint32_t el = elect_one();
     const int ng = both ? 2 : 1;
-    mbar_arrive_expect_tx_if(el, q_full, ng * (Q_BYTES + SF_BYTES));
+    mbar_arrive_expect_tx_if(el, q_full, ng * (Q_BYTES + (SF_TILED ? SF_BYTES : 0)));
     for (int g = 0; g < ng; ++g) {
       tma_load_2d_if(el, sQ + g * Q_BYTES, &tma_q, 0, q_row0 + g * BQ, q_full);
-      bulk_load_1d_if(el, sSFQ + g * SF_BYTES, p.sfq + ((bh * p.q_blocks + 2 * qt + g) * 2) * 512, SF_BYTES, q_full);
+      if (SF_TILED)
+        bulk_load_1d_if(el, sSFQ + g * SF_BYTES, p.sfq + ((bh * p.q_blocks + 2 * qt + g) * 2) * 512, SF_BYTES, q_full);
     }
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
@@ -246,11 +252,13 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       const uint32_t st = sKV + s * STAGE_BYTES, fb = kv_full + 8 * s;
       // V^T: D rows x 128 keys; of the tile's two K = 64 steps only those below align64(Nkv) exist
       const int nk = min(2, p.v_k64 - 2 * j);
-      mbar_arrive_expect_tx_if(el, fb, K_BYTES + V_BYTES + SF_BYTES + nk * 512);
+      mbar_arrive_expect_tx_if(el, fb, K_BYTES + V_BYTES + (SF_TILED ? SF_BYTES + nk * 512 : 0));
       tma_load_2d_if(el, st, &tma_k, 0, k_row0 + j * BKV, fb);
       tma_load_2d_if(el, st + K_BYTES, &tma_v, j * 64, v_row0, fb);
-      bulk_load_1d_if(el, st + K_BYTES + V_BYTES, p.sfk + ((bh * p.kv_tiles + j) * 2) * 512, SF_BYTES, fb);
-      bulk_load_1d_if(el, st + K_BYTES + V_BYTES + SF_BYTES, p.sfv + (bh * p.v_k64 + 2 * j) * 512, nk * 512, fb);
+      if (SF_TILED) {
+        bulk_load_1d_if(el, st + K_BYTES + V_BYTES, p.sfk + ((bh * p.kv_tiles + j) * 2) * 512, SF_BYTES, fb);
+        bulk_load_1d_if(el, st + K_BYTES + V_BYTES + SF_BYTES, p.sfv + (bh * p.v_k64 + 2 * j) * 512, nk * 512, fb);
+      }
     }
     if (!ok && el) atomicExch(p.status, kStatusTimeoutProducer);
   } else if (warp == 1) {
@@ -345,6 +353,44 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       if (el) AC4K_TRM(1, j, 4);
     }
     if (!ok && el) atomicExch(p.status, kStatusTimeoutMma);
+  } else if (warp == 10) {
+    // ------------------------------------------------------------------ scale re-order (reference layout only)
+    if (!SF_TILED) {
+      // chunk of K = 64 step k and rows [row0, row0 + 128) of a [K/64, pad, 4-byte] scale array: lane l takes the words
+      // of rows row0 + l, + 32, + 64, + 96 (coalesced over the lanes) and stores them as its 16-byte row of the chunk
+      auto put_chunk = [&](uint32_t dst, const uint8_t *base, int k, int pad, int row0) {
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(base) + (int64_t)k * pad;
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int r = row0 + 32 * i + lane;
+          w[i] = r < pad ? __ldg(src + r) : 0u;
+        }
+        st_shared_v4u(dst + lane * 16, w[0], w[1], w[2], w[3]);
+      };
+      const uint8_t *q_base = p.sfq + bh * 2 * (int64_t)p.q_pad * 4;
+      const uint8_t *k_base = p.sfk + bh * 2 * (int64_t)p.k_pad * 4;
+      const uint8_t *v_base = p.sfv + bh * (int64_t)p.v_k64 * p.v_pad * 4;
+      for (int g = 0; g < (both ? 2 : 1); ++g)
+        for (int i = 0; i < 2; ++i) put_chunk(sSFQ + g * SF_BYTES + i * 512, q_base, i, p.q_pad, (2 * qt + g) * BQ);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(q_full);
+      bool ok = true;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j % KV_STAGES;
+        ok = warp_all(mbar_wait(kv_empty + 8 * s, ((j / KV_STAGES) & 1) ^ 1, p.wait_ns));
+        if (!ok) break;
+        const uint32_t st = sKV + s * STAGE_BYTES + K_BYTES + V_BYTES;
+        const int nk = min(2, p.v_k64 - 2 * j);
+        for (int i = 0; i < 2; ++i) put_chunk(st + i * 512, k_base, i, p.k_pad, j * BKV);
+        for (int i = 0; i < nk; ++i) put_chunk(st + SF_BYTES + i * 512, v_base, 2 * j + i, p.v_pad, 0);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(kv_full + 8 * s);
+      }
+      if (!ok && lane == 0) atomicExch(p.status, kStatusTimeoutSf);
+    }
   } else if (warp < 6 || both) {
     // ------------------------------------------------------------------ softmax, correction, epilogue
     const int g = (warp - 2) >> 2;            // group: query tile A or B
@@ -563,8 +609,7 @@ extern "C" int ac4k_mha_nvfp4_fwd(void *O, const int64_t o_stride[4], const void
   if (!(sm_scale >= 0.0f)) return fail(AC4K_ERR_UNSUPPORTED, "sm_scale must be >= 0 (the row maximum is taken before scaling)");
   if (Dqk <= 64 || Dqk > 128 || Dv <= 64 || Dv > 128)
     return fail(AC4K_ERR_UNSUPPORTED, "head dimensions in (64, 128] are built (Dqk = %lld, Dv = %lld)", (long long)Dqk, (long long)Dv);
-  if (sf_layout != AC4K_SF_TILE128X4)
-    return fail(AC4K_ERR_UNSUPPORTED, "the attention kernel reads block scales in the tiled layout (AC4K_SF_TILE128X4)");
+  if (sf_layout != AC4K_SF_TILE128X4 && sf_layout != AC4K_SF_AC4K) return fail(AC4K_ERR_ENUM, "unknown scale layout %d", sf_layout);
   if (B > 65535 || H > 65535 || B * H * Nq > (1ll << 31) - 256 || B * H * Nkv > (1ll << 31) - 256)
     return fail(AC4K_ERR_SHAPE, "dimension too large");
   for (const void *ptr : {Q, Q_sf, K, K_sf, V, V_sf})
@@ -591,14 +636,19 @@ extern "C" int ac4k_mha_nvfp4_fwd(void *O, const int64_t o_stride[4], const void
   a.q_blocks = (int)ceil_div(Nq, 128);
   a.kv_tiles = (int)ceil_div(Nkv, 128);
   a.v_k64 = (int)v_k64;
+  a.q_pad = (int)align_up(Nq, 16);
+  a.k_pad = (int)align_up(Nkv, 16);
+  a.v_pad = (int)align_up(Dv, 16);
   a.sm_scale = sm_scale;
   a.status = status;
   a.wait_ns = kWaitTimeoutNs;
   a.trace = debug_trace_ptr();
+  const bool tiled = sf_layout == AC4K_SF_TILE128X4;
   static PerDevice<int> attr_set;
   int unused = 0;
   if (int e = attr_set.get(&unused, [&](int &v) {
-        AC4K_CUDA_TRY(cudaFuncSetAttribute(mha_nvfp4_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mha::SMEM_BYTES));
+        AC4K_CUDA_TRY(cudaFuncSetAttribute(mha_nvfp4_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, mha::SMEM_BYTES));
+        AC4K_CUDA_TRY(cudaFuncSetAttribute(mha_nvfp4_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, mha::SMEM_BYTES));
         v = 1;
         return 0;
       }))
@@ -613,6 +663,9 @@ extern "C" int ac4k_mha_nvfp4_fwd(void *O, const int64_t o_stride[4], const void
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  AC4K_CUDA_TRY(cudaLaunchKernelEx(&cfg, mha_nvfp4_fwd_kernel, tq, tk, tv, a));
+  if (tiled)
+    AC4K_CUDA_TRY(cudaLaunchKernelEx(&cfg, mha_nvfp4_fwd_kernel<true>, tq, tk, tv, a));
+  else
+    AC4K_CUDA_TRY(cudaLaunchKernelEx(&cfg, mha_nvfp4_fwd_kernel<false>, tq, tk, tv, a));
   return 0;
 }

@@ -165,11 +165,12 @@ int ac4k_linear_nvfp4_requant(void *out_fp4, void *out_sf, const float *out_gs, 
  * lib/cuda/sm120/mha_nvfp4.cu:897-1077 (checks) and :322-893 (kernel).
  *   Q: [B, H, Nq, align64(Dqk)/2] bytes, K: [B, H, Nkv, align64(Dqk)/2] bytes (quantised along the head dimension);
  *   V: [B, H, Dv, align64(Nkv)/2] bytes, quantised along the keys with the K permutation (swizzle = 1);
- *   Q_sf, K_sf, V_sf: block scales of those quantiser calls in the tiled layout (AC4K_SF_TILE128X4);
+ *   Q_sf, K_sf, V_sf: block scales of those quantiser calls, all three in `sf_layout` (the tiled layout is
+ *   copied as it is; the reference's is re-ordered by one more warp of the kernel);
  *   *_gs: device fp32 scalars; O: bf16, element (b, h, n, d) at O + b*o_stride[0] + h*o_stride[1] + n*o_stride[2] +
  *   d*o_stride[3] (elements), so both the [B, H, N, D] and the permuted [B, N, H, D] outputs of the reference work.
- * Built for 64 < Dqk <= 128 and 64 < Dv <= 128 (the reference allows up to 128); other head dimensions and the
- * reference's scale layout return AC4K_ERR_UNSUPPORTED. */
+ * Built for 64 < Dqk <= 128 and 64 < Dv <= 128 (the reference allows up to 128) and sm_scale >= 0; other head
+ * dimensions return AC4K_ERR_UNSUPPORTED. */
 int ac4k_mha_nvfp4_fwd(void *O, const int64_t o_stride[4], const void *Q, const void *Q_sf, const float *Q_gs,
                        const void *K, const void *K_sf, const float *K_gs, const void *V, const void *V_sf,
                        const float *V_gs, int64_t B, int64_t H, int64_t Nq, int64_t Nkv, int64_t Dqk, int64_t Dv,

@@ -88,13 +88,14 @@ ORACLE_CASES = [
 
 @pytest.mark.parametrize("B,H,Nq,Nkv,Dqk,Dv", ORACLE_CASES)
 @pytest.mark.parametrize("layout", ["BHND", "BNHD"])
-def test_kernel_against_oracle_on_the_same_operands(B, H, Nq, Nkv, Dqk, Dv, layout):
+@pytest.mark.parametrize("sf_layout", ["128x4", "ac4k"])
+def test_kernel_against_oracle_on_the_same_operands(B, H, Nq, Nkv, Dqk, Dv, layout, sf_layout):
     ops, _, quantize = _ops()
     q, k, v = _qkv(B, Nq, Nkv, H, Dqk, Dv, layout, seed=17 * Nq + Nkv)
     n_dim = 1 if layout == "BNHD" else 2
-    qq, qs, qg = quantize(q, n_dim, 3, sf_layout="128x4")
-    kq, ks, kg = quantize(k, n_dim, 3, sf_layout="128x4")
-    vq, vs, vg = quantize(v, 3, n_dim, swizzle=True, sf_layout="128x4")
+    qq, qs, qg = quantize(q, n_dim, 3, sf_layout=sf_layout)
+    kq, ks, kg = quantize(k, n_dim, 3, sf_layout=sf_layout)
+    vq, vs, vg = quantize(v, 3, n_dim, swizzle=True, sf_layout=sf_layout)
     sm = 1 / math.sqrt(Dqk)
     if layout == "BNHD":
         out = torch.full((B, Nq, H, Dv), float("nan"), dtype=torch.bfloat16, device="cuda")
@@ -117,6 +118,22 @@ def test_kernel_against_oracle_on_the_same_operands(B, H, Nq, Nkv, Dqk, Dv, layo
     rel = ((got - want.float()).norm() / want.float().norm()).item()
     assert rel < 2e-3, rel
     torch.testing.assert_close(got, want.float(), atol=2e-2, rtol=2e-2)
+
+
+def test_both_scale_layouts_give_the_same_bytes():
+    """The reference's call, verbatim (python/ac4k_kernel/ops/attention.py:113-128: default scale layout), against the
+    tiled layout that `attention()` here asks the quantiser for."""
+    ops, _, quantize = _ops()
+    q, k, v = _qkv(2, 333, 200, 3, 128, 128, "BNHD", seed=11)
+    outs = []
+    for sf_layout in ("ac4k", "128x4"):
+        qq, qs, qg = quantize(q, 1, 3, sf_layout=sf_layout)
+        kq, ks, kg = quantize(k, 1, 3, sf_layout=sf_layout)
+        vq, vs, vg = quantize(v, 3, 1, swizzle=True, sf_layout=sf_layout)
+        o = torch.empty((2, 333, 3, 128), dtype=torch.bfloat16, device="cuda")
+        ops.mha_nvfp4_fwd(o.permute(0, 2, 1, 3), qq, qs, qg, kq, ks, kg, vq, vs, vg, 128 ** -0.5)
+        outs.append(o)
+    assert torch.equal(outs[0], outs[1])
 
 
 def test_out_argument_and_repeatability():
@@ -142,7 +159,7 @@ def test_argument_checks():
         ops.mha_nvfp4_fwd(o, qq, qs, qg, kq[..., :32].contiguous(), ks, kg, vq, vs, vg, 0.1)
     with pytest.raises(RuntimeError):      # V over another number of keys
         ops.mha_nvfp4_fwd(o, qq, qs, qg, kq, ks, kg, torch.cat([vq, vq], dim=-1), vs, vg, 0.1)
-    with pytest.raises(RuntimeError):      # the reference's scale layout is not built for this kernel
+    with pytest.raises(RuntimeError):      # scale layouts must agree
         q5 = quantize(q, 2, 3)[1]
         ops.mha_nvfp4_fwd(o, qq, q5, qg, kq, ks, kg, vq, vs, vg, 0.1)
     with pytest.raises(RuntimeError):      # head dimension 64: a valid call in the reference, not built here

@@ -104,5 +104,5 @@ def test_attention_same_bytes_as_the_ctypes_path(mod):
         fn.mha_nvfp4_fwd(o.permute(0, 2, 1, 3), qq, qs, qg, kq, ks, kg, vq, vs, vg, D ** -0.5)
         outs.append(o)
     assert torch.equal(outs[0], outs[1])
-    with pytest.raises(RuntimeError, match="tiled layout"):
+    with pytest.raises(RuntimeError, match="5D tensor"):      # scale layouts must agree: q_sf decides
         mod.mha_nvfp4_fwd(outs[0].permute(0, 2, 1, 3), qq, quantize(q, 1, 3)[1], qg, kq, ks, kg, vq, vs, vg, 0.1)
