@@ -347,6 +347,28 @@ def mha_nvfp4_fwd(o, q, q_sf, q_global_scale, k, k_sf, k_global_scale, v, v_sf, 
               "mha_nvfp4_fwd")
 
 
+def rope3d(x, grid_sizes, freqs, output):
+    """3-D rotary position embedding (ops.h:50-54; checks of lib/cuda/sm120/rope3d.cu:133-165).
+    x, output: bf16 [B, S, N, D]; grid_sizes: int32 [B, 3]; freqs: complex128 [max_pos, D // 2]."""
+    _check_tensor(x, torch.bfloat16, "x")
+    _check_tensor(grid_sizes, torch.int32, "grid_sizes")
+    _check_tensor(freqs, torch.complex128, "freqs")
+    _check_tensor(output, torch.bfloat16, "output")
+    _require(x.dim() == 4, "x must be 4D tensor")
+    _require(grid_sizes.dim() == 2, "grid_sizes must be 2D tensor")
+    _require(freqs.dim() == 2, "freqs must be 2D tensor")
+    _require(output.dim() == 4, "output must be 4D tensor")
+    B, S, N, D = x.shape
+    _require(grid_sizes.size(0) == B, "grid_sizes batch size must match x")
+    _require(grid_sizes.size(1) == 3, "grid_sizes must have 3 dimensions (F, H, W)")
+    _require(list(output.shape) == [B, S, N, D], "output shape must match x")
+    _require(D % 2 == 0, "feature dimension must be even")
+    _require(freqs.size(1) == D // 2, "freqs must have D / 2 columns")
+    with torch.cuda.device(x.device):
+        check(LIB.ac4k_rope3d(output.data_ptr(), x.data_ptr(), grid_sizes.data_ptr(), freqs.data_ptr(), B, S, N, D,
+                              freqs.size(0), _stream(x)),
+              "rope3d")
+
+
 # Names that ac4k_kernel/__init__.py:19-34 imports eagerly; present so the import succeeds.
 mha_int8_x_fp8_fwd = _out_of_scope("mha_int8_x_fp8_fwd")
-rope3d = _out_of_scope("rope3d")

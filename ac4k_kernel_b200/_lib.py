@@ -42,6 +42,8 @@ SIGNATURES = {
     "ac4k_mha_nvfp4_fwd": (ctypes.c_int, [_vp, _c_i64p, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                           ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                           ctypes.c_int64, ctypes.c_int64, ctypes.c_float, ctypes.c_int, _vp]),
+    "ac4k_rope3d": (ctypes.c_int, [_vp, _vp, _vp, _vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                   ctypes.c_int64, _vp]),
     "ac4k_peer_alloc": (ctypes.c_int, [ctypes.c_int64, ctypes.POINTER(_vp), ctypes.c_char_p]),
     "ac4k_peer_open": (ctypes.c_int, [ctypes.c_char_p, ctypes.POINTER(_vp)]),
     "ac4k_peer_close": (ctypes.c_int, [_vp]),

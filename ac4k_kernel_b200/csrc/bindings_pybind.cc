@@ -249,14 +249,31 @@ void mha_nvfp4_fwd(torch::Tensor &o, torch::Tensor &q, torch::Tensor &q_sf, torc
   TORCH_CHECK(rc == 0, "ac4k_mha_nvfp4_fwd: ", ac4k_last_error());
 }
 
-// The int8 x fp8 attention and RoPE operators of the reference module are different operators from the NVFP4 path this
-// library covers; the names exist so that `import` and introspection behave like the reference's module.
+// The int8 x fp8 attention operator of the reference module is not built; the name exists so that `import` and
+// introspection behave like the reference's module.
 void mha_int8_x_fp8_fwd(torch::Tensor &, torch::Tensor &, torch::Tensor &, int, torch::Tensor &, torch::Tensor &, int,
                         torch::Tensor &, torch::Tensor &, float) {
   TORCH_CHECK(false, "mha_int8_x_fp8_fwd is not part of the sm100 NVFP4 library");
 }
-void rope3d(const torch::Tensor &, const torch::Tensor &, const torch::Tensor &, torch::Tensor &) {
-  TORCH_CHECK(false, "rope3d is not part of the sm100 NVFP4 library");
+// ops.h:50-54; checks of rope3d.cu:133-165
+void rope3d(const torch::Tensor &x, const torch::Tensor &grid_sizes, const torch::Tensor &freqs, torch::Tensor &output) {
+  check_cuda(x, at::kBFloat16, "x");
+  check_cuda(grid_sizes, at::kInt, "grid_sizes");
+  check_cuda(freqs, at::kComplexDouble, "freqs");
+  check_cuda(output, at::kBFloat16, "output");
+  TORCH_CHECK(x.dim() == 4, "x must be 4D tensor");
+  TORCH_CHECK(grid_sizes.dim() == 2, "grid_sizes must be 2D tensor");
+  TORCH_CHECK(freqs.dim() == 2, "freqs must be 2D tensor");
+  TORCH_CHECK(output.dim() == 4, "output must be 4D tensor");
+  const int64_t B = x.size(0), S = x.size(1), N = x.size(2), D = x.size(3);
+  TORCH_CHECK(grid_sizes.size(0) == B, "grid_sizes batch size must match x");
+  TORCH_CHECK(grid_sizes.size(1) == 3, "grid_sizes must have 3 dimensions (F, H, W)");
+  TORCH_CHECK(output.sizes() == x.sizes(), "output shape must match x");
+  TORCH_CHECK(D % 2 == 0 && freqs.size(1) == D / 2, "freqs must have D / 2 columns");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int rc = ac4k_rope3d(output.data_ptr(), x.data_ptr(), grid_sizes.data_ptr<int32_t>(), freqs.data_ptr(), B, S, N, D,
+                             freqs.size(0), at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "ac4k_rope3d: ", ac4k_last_error());
 }
 
 }  // namespace ac4k
@@ -273,6 +290,6 @@ PYBIND11_MODULE(_cuda_ops, m) {
   m.def("quantize_fp8", &ac4k::quantize_fp8, "Quantize bfloat16 tensor to FP8 format");
   m.def("quantize_int8", &ac4k::quantize_int8, "Quantize bfloat16 tensor to INT8 format");
   m.def("linear_nvfp4", &ac4k::linear_nvfp4, "NVFP4 Linear (fully-connected layer): y = x @ weight.T + bias");
-  m.def("rope3d", &ac4k::rope3d, "3D Rotary Position Embedding: not built for sm100");
+  m.def("rope3d", &ac4k::rope3d, "3D Rotary Position Embedding");
   m.def("global_scale_bf16", &ac4k::global_scale_bf16, "out[0] = max|x| / max_scale");
 }

@@ -2,6 +2,7 @@
 for the names this build covers)."""
 from .attention import attention
 from .linear import linear, linear_nvfp4, linear_requant
+from .rope_3d import rope3d
 from .quant import quantize, quantize_nvfp4, quantize_fp8, quantize_int8
 
-__all__ = ["quantize", "linear", "attention", "quantize_nvfp4", "quantize_fp8", "quantize_int8", "linear_nvfp4", "linear_requant"]
+__all__ = ["quantize", "linear", "attention", "rope3d", "quantize_nvfp4", "quantize_fp8", "quantize_int8", "linear_nvfp4", "linear_requant"]

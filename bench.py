@@ -399,6 +399,25 @@ def attention_nvfp4(peaks):
     return res
 
 
+def rope3d_stream(peaks):
+    """3-D rotary embedding at the shape of the reference's test (test/test_rope_3d_apply.py:49-56): [1, 21 * 45 * 80,
+    40, 128] bf16 with a 1024-row complex128 table; 2 bytes read + 2 written per element, 1.55 GB per launch."""
+    from ac4k_kernel_b200 import ops
+    f, h, w, n, d = 21, 45, 80, 40, 128
+    g = torch.Generator(device="cuda").manual_seed(9567)
+    x = torch.randn((1, f * h * w, n, d), dtype=torch.bfloat16, device="cuda", generator=g)
+    grid = torch.tensor([[f, h, w]], dtype=torch.int32, device="cuda")
+    ang = torch.outer(torch.arange(1024, dtype=torch.float64),
+                      1.0 / torch.pow(torch.tensor(10000.0, dtype=torch.float64), torch.arange(0, d, 2, dtype=torch.float64) / d))
+    freqs = torch.polar(torch.ones_like(ang), ang).cuda()
+    out = torch.empty_like(x)
+    t = time_eager(lambda: ops.rope3d(x, grid, freqs, out), 10)
+    gbs = x.numel() * 4 / t / 1e9
+    return {"workload": "rope3d bf16 [1, 75600, 40, 128], grid 21 x 45 x 80, complex128 table [1024, 64]",
+            "ms": t * 1e3, "gbs": gbs, "frac_of_8tbs": gbs / NOMINAL_HBM_GBS, "frac_of_measured_copy": gbs / peaks["hbm_gbs"],
+            "algorithmic_bytes_per_launch": x.numel() * 4}
+
+
 def c5_single_gpu():
     """BASELINE config 5 on one GPU (M = K = 8192, N = 28672): the same-workload base of the 1 -> N curve.
     One operand set (600 MB, larger than L2), 5 steps in a graph."""
@@ -525,6 +544,7 @@ def run_single(args, peaks):
     quant = quantize_bandwidth(peaks)
     decode = decode_stream(peaks)
     attn = attention_nvfp4(peaks)
+    rope = rope3d_stream(peaks)
     cpu_tflops, cores, sample, _, _ = cpu_emulation_c2()
 
     fp4_proxy_peak = 4.0 * peaks["bf16_tflops"]
@@ -551,6 +571,7 @@ def run_single(args, peaks):
         "quantize": quant,
         "decode": decode,
         "attention_nvfp4": attn,
+        "rope3d": rope,
         "cpu_baseline": {"value": cpu_tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": e2e,
         "clocks": clocks,
@@ -759,6 +780,17 @@ def run_profile_case(case):
         out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
         for _ in range(3):
             _cuda_ops.linear_nvfp4(out, a4, asf, ag, w4, wsf, wg, None)
+    elif case == "rope3d":
+        f, h, w = 21, 45, 80
+        x = torch.randn((1, f * h * w, 40, 128), dtype=torch.bfloat16, device="cuda",
+                        generator=torch.Generator(device="cuda").manual_seed(9567))
+        grid = torch.tensor([[f, h, w]], dtype=torch.int32, device="cuda")
+        ang = torch.outer(torch.arange(1024, dtype=torch.float64),
+                          1.0 / torch.pow(torch.tensor(10000.0, dtype=torch.float64), torch.arange(0, 128, 2, dtype=torch.float64) / 128))
+        freqs = torch.polar(torch.ones_like(ang), ang).cuda()
+        out = torch.empty_like(x)
+        for _ in range(3):
+            ops.rope3d(x, grid, freqs, out)
     elif case == "mha":
         import math
         g = torch.Generator(device="cuda").manual_seed(9567)
@@ -790,7 +822,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--profile-case", default=None,
-                    choices=["gemm-c2", "gemm-8k", "gemm-decode", "mha", "quant-c4", "quant-c4-fp8", "quant-c4-int8"],
+                    choices=["gemm-c2", "gemm-8k", "gemm-decode", "mha", "rope3d", "quant-c4", "quant-c4-fp8", "quant-c4-int8"],
                     help="run one small workload three times and exit (for ncu)")
     args = ap.parse_args()
     if args.profile_case:

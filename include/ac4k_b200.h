@@ -176,6 +176,17 @@ int ac4k_mha_nvfp4_fwd(void *O, const int64_t o_stride[4], const void *Q, const 
                        const float *V_gs, int64_t B, int64_t H, int64_t Nq, int64_t Nkv, int64_t Dqk, int64_t Dv,
                        float sm_scale, int sf_layout, ac4k_stream_t stream);
 
+/* 3-D rotary position embedding: out[b, s, n, 2c..2c+1] = x[b, s, n, 2c..2c+1] * freqs[row(s, c), c] as complex numbers,
+ * row = the position's frame, height or width index in the [F, H, W] grid of its batch entry, by thirds of the C = D / 2
+ * pairs (c1 = C - 2 (C / 3) frame pairs, then C / 3 height pairs, then C / 3 width pairs).
+ * Replaces ac4k::rope3d, include/ac4k_kernel/ops.h:50-54, lib/cuda_bindings.cc:91-97, lib/cuda/sm120/rope3d.cu:23-187.
+ *   x, out: bf16 [B, S, N, D] contiguous; grid_sizes: int32 [B, 3] on the device; freqs: complex128 [max_pos, D / 2].
+ * fp64 arithmetic as in the reference.  Positions s >= F * H * W are copied from x (the reference's kernel leaves them
+ * unwritten; its Python oracle, test/test_rope_3d_apply.py:14-42, copies them).  A grid index >= max_pos reads the last
+ * row of the table.  D even, D <= 2048. */
+int ac4k_rope3d(void *out, const void *x, const int32_t *grid_sizes, const void *freqs, int64_t B, int64_t S,
+                int64_t N, int64_t D, int64_t max_pos, ac4k_stream_t stream);
+
 /* Device buffers that the other processes of the node can map (CUDA IPC), for the destinations of
  * ac4k_linear_nvfp4_gather.  No counterpart in the reference.
  *   ac4k_peer_alloc: cudaMalloc on the current device + its 64-byte IPC handle.

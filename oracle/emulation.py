@@ -398,3 +398,44 @@ def attention_nvfp4_ref(q, k, v, layout: str = "BNHD", sf_layout: str = "128x4")
     vq, vs, vg = quantize_nvfp4_ref(v, 3, n_dim, swizzle=True, sf_layout=sf_layout)
     o = mha_nvfp4_ref(qq, qs, qg, kq, ks, kg, vq, vs, vg, 1.0 / (q.shape[-1] ** 0.5), nkv)
     return o.permute(0, 2, 1, 3).contiguous() if layout == "BNHD" else o
+
+
+# ----------------------------------------------------------------------------------------
+# 3-D rotary position embedding
+# ----------------------------------------------------------------------------------------
+def rope_params_ref(max_pos: int, dim: int, theta: float = 10000.0) -> torch.Tensor:
+    """complex128 [max_pos, dim // 2]: exp(i * p * theta^(-2c / dim)) (test/test_rope_3d_apply.py:5-12)."""
+    assert dim % 2 == 0
+    inv = 1.0 / torch.pow(torch.tensor(theta, dtype=torch.float64),
+                          torch.arange(0, dim, 2, dtype=torch.float64) / dim)
+    ang = torch.outer(torch.arange(max_pos, dtype=torch.float64), inv)
+    return torch.polar(torch.ones_like(ang), ang)
+
+
+def rope3d_ref(x: torch.Tensor, grid_sizes: torch.Tensor, freqs: torch.Tensor) -> torch.Tensor:
+    """x bf16 [B, S, N, D], grid_sizes int [B, 3] = (F, H, W), freqs complex128 [max_pos, D // 2] -> bf16 [B, S, N, D].
+
+    Position s < F * H * W sits at (f, h, w) = (s // (H W), (s % (H W)) // W, s % W); of the C = D // 2 complex pairs of
+    every head the first C - 2 (C // 3) are multiplied by freqs[f, c], the next C // 3 by freqs[h, c], the last C // 3 by
+    freqs[w, c]; products in complex128, result -> fp32 -> bf16.  Positions behind the grid are copied from x
+    (test/test_rope_3d_apply.py:14-42; the kernel, lib/cuda/sm120/rope3d.cu:44-129, does the same arithmetic per
+    element and leaves those positions unwritten)."""
+    B, S, N, D = x.shape
+    C = D // 2
+    c2 = C // 3
+    c1 = C - 2 * c2
+    out = x.clone()
+    col = torch.arange(C, device=x.device)
+    for b in range(B):
+        F_, H_, W_ = (int(v) for v in grid_sizes[b].tolist())
+        n = min(F_ * H_ * W_, S)
+        if n == 0:
+            continue
+        s = torch.arange(n, device=x.device)
+        f, h, w = s // (H_ * W_), (s % (H_ * W_)) // W_, s % W_
+        row = torch.where(col[None, :] < c1, f[:, None], torch.where(col[None, :] < c1 + c2, h[:, None], w[:, None]))
+        fac = freqs[row, col[None, :].expand(n, C)]                       # [n, C] complex128
+        xc = torch.view_as_complex(x[b, :n].to(torch.float64).reshape(n, N, C, 2))
+        y = torch.view_as_real(xc * fac[:, None, :]).reshape(n, N, D)
+        out[b, :n] = y.to(torch.float32).to(torch.bfloat16)
+    return out

@@ -10,6 +10,8 @@ B200 box.  Their *oracle* halves, however, are plain torch:
   * `test/test_quantize_bench.py::get_ref`       (NVFP4 quantiser, known-answer inputs)
   * `test/test_quantize_bench.py::qunatize_fp8`  (per-token FP8, exact equality)
   * `test/test_linear_bench.py::get_torch_results` (dequantise -> fp32 matmul -> cast)
+  * `test/test_rope_3d_apply.py::rope_params`, `::rope_apply_reference` (3-D rotary embedding;
+    `python tests/golden/make_golden.py <checkout> rope` writes only that fixture)
 
 This script imports those files with `ac4k_kernel.ops` replaced by a stub, redirects their
 hard-coded "cuda" allocations to the CPU, runs them on seeded inputs and stores inputs and
@@ -65,6 +67,7 @@ def _stub_ops():
     pkg = types.ModuleType("ac4k_kernel")
     ops = types.ModuleType("ac4k_kernel.ops")
     ops.quantize, ops.linear = quantize, linear
+    ops.rope3d = lambda x, grid_sizes, freqs, output=None: emu.rope3d_ref(x, grid_sizes, freqs)
     pkg.ops = ops
     sys.modules["ac4k_kernel"] = pkg
     sys.modules["ac4k_kernel.ops"] = ops
@@ -81,9 +84,37 @@ def bits16(t):
     return t.view(torch.int16).numpy().view(np.uint16)
 
 
-def main(ref_root):
+def rope_golden(ref_root):
+    """Outputs of the reference's rope_params / rope_apply_reference on seeded inputs."""
+    tr = _load(os.path.join(ref_root, "test", "test_rope_3d_apply.py"), "ref_test_rope")
+    g = torch.Generator().manual_seed(9567)
+    cases = [(2, 70, 3, 16, [(3, 4, 5), (2, 5, 7)], 16),       # one batch entry padded, one full
+             (1, 24, 2, 20, [(2, 3, 4)], 8),                   # C = 10: 4 + 3 + 3 pairs, D not a multiple of 8
+             (1, 40, 2, 128, [(2, 4, 5)], 32),
+             (2, 36, 1, 6, [(1, 1, 1), (3, 3, 4)], 4)]         # C = 3: one pair per axis; a grid of a single position
+    out = {}
+    for i, (b, s, n, d, grids, max_pos) in enumerate(cases):
+        x = torch.randn((b, s, n, d), generator=g).bfloat16()
+        gs = torch.tensor(grids, dtype=torch.int32)
+        fr = tr.rope_params(max_pos, d)
+        y = tr.rope_apply_reference(x, gs, fr)
+        assert torch.equal(y.view(torch.int16), emu.rope3d_ref(x, gs, fr).view(torch.int16))
+        out[f"r{i}_x"] = bits16(x)
+        out[f"r{i}_grid"] = gs.numpy()
+        out[f"r{i}_max_pos"] = np.array(max_pos)
+        out[f"r{i}_freqs"] = torch.view_as_real(fr).numpy()
+        out[f"r{i}_out"] = bits16(y)
+    out["n_cases"] = np.array(len(cases))
+    np.savez_compressed(os.path.join(HERE, "rope3d_reference_oracle.npz"), **out)
+    print("rope3d golden vectors written")
+
+
+def main(ref_root, only=None):
     _cpu_factories()
     _stub_ops()
+    if only == "rope":
+        rope_golden(ref_root)
+        return
     tq = _load(os.path.join(ref_root, "test", "test_quantize_bench.py"), "ref_test_quantize")
     tl = _load(os.path.join(ref_root, "test", "test_linear_bench.py"), "ref_test_linear")
 
@@ -170,10 +201,11 @@ def main(ref_root):
         out[f"f{i}_sf"] = sf_ref.numpy()
     out["n_cases"] = np.array(3)
     np.savez_compressed(os.path.join(HERE, "fp8_quantize_known_answer.npz"), **out)
+    rope_golden(ref_root)
     print("golden vectors written to", HERE)
 
 
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
-        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of ac4k_kernel>")
-    main(sys.argv[1])
+    if len(sys.argv) not in (2, 3):
+        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of ac4k_kernel> [rope]")
+    main(sys.argv[1], sys.argv[2] if len(sys.argv) == 3 else None)

@@ -46,7 +46,7 @@ def test_module_mirrors_reference_names():
         assert hasattr(_cuda_ops, name)
     assert pkg.get_arch() == "sm100" and pkg.get_backend() == "cuda"
     with pytest.raises(NotImplementedError):
-        _cuda_ops.rope3d()
+        _cuda_ops.mha_int8_x_fp8_fwd()
 
 
 def test_argument_errors_without_gpu():
@@ -58,6 +58,13 @@ def test_argument_errors_without_gpu():
     assert "NULL" in last_error()
     assert LIB.ac4k_quantize_nvfp4(8, 8, 16, 16, shape, stride, 0, 7, None) == -4
     assert LIB.ac4k_global_scale_bf16(None, -1, 1.0, 8, None) == -2
+    assert LIB.ac4k_rope3d(8, 8, 8, 16, 1, 4, 2, 7, 4, None) == -2          # odd feature dimension
+    assert LIB.ac4k_rope3d(None, 8, 8, 16, 1, 4, 2, 8, 4, None) == -1
+    assert LIB.ac4k_rope3d(8, 8, 8, 16, 1, 4, 2, 4096, 4, None) == -5       # feature dimension above what is built
+    o4 = (ctypes.c_int64 * 4)(1, 1, 1, 1)
+    assert LIB.ac4k_mha_nvfp4_fwd(16, o4, 16, 16, 16, 16, 16, 16, 16, 16, 16, 1, 1, 8, 8, 64, 128, 0.1, 1, None) == -5
+    assert LIB.ac4k_mha_nvfp4_fwd(16, o4, 16, 16, 16, 16, 16, 16, 16, 16, 16, 1, 1, 8, 0, 128, 128, 0.1, 1, None) == -2
+    assert LIB.ac4k_mha_nvfp4_fwd(16, o4, 16, 16, 16, 16, 16, 16, 16, 16, 16, 1, 1, 8, 8, 128, 128, -1.0, 1, None) == -5
     bad = (ctypes.c_int64 * 4)(1, 1, -3, 64)
     assert LIB.ac4k_quantize_fp8(8, 8, 16, 16, bad, stride, 0, None) == -2
 

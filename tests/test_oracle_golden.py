@@ -120,3 +120,17 @@ def test_layout_roundtrip(shape, cd, rd):
         r2 = emu.sf_tile128x4_to_rows(sf2f[b].view(torch.uint8), m, emu.align_up(k, 64) // 16)
         assert torch.equal(r1, r2)
     assert len(lead) == len(shape) - 2
+
+
+def test_rope3d_vs_reference_oracle(golden_dir):
+    """The restatement against outputs of the reference's own rope_params / rope_apply_reference
+    (test/test_rope_3d_apply.py:5-42), bit for bit."""
+    z = np.load(os.path.join(golden_dir, "rope3d_reference_oracle.npz"))
+    for i in range(int(z["n_cases"])):
+        x = bf16_from_bits(z[f"r{i}_x"])
+        grid = torch.from_numpy(z[f"r{i}_grid"])
+        freqs = torch.view_as_complex(torch.from_numpy(z[f"r{i}_freqs"]))
+        assert torch.equal(torch.view_as_real(emu.rope_params_ref(int(z[f"r{i}_max_pos"]), x.shape[-1])),
+                           torch.view_as_real(freqs))
+        out = emu.rope3d_ref(x, grid, freqs)
+        np.testing.assert_array_equal(out.view(torch.int16).numpy().view(np.uint16), z[f"r{i}_out"])
