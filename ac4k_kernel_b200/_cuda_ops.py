@@ -286,14 +286,6 @@ def global_scale_bf16(out, input, max_scale):
               "global_scale_bf16")
 
 
-def _out_of_scope(name):
-    def fn(*args, **kwargs):
-        raise NotImplementedError(
-            f"{name} is outside the NVFP4 linear path that this sm100 build covers")
-    fn.__name__ = name
-    return fn
-
-
 def mha_nvfp4_fwd(o, q, q_sf, q_global_scale, k, k_sf, k_global_scale, v, v_sf, v_global_scale, sm_scale):
     """o = softmax(sm_scale * q k^T) v on NVFP4 operands (ops.h:13-17; checks of
     lib/cuda/sm120/mha_nvfp4.cu:897-1010).  q: [B, H, Nq, Dqk/2], k: [B, H, Nkv, Dqk/2],
@@ -370,5 +362,64 @@ def rope3d(x, grid_sizes, freqs, output):
               "rope3d")
 
 
-# Names that ac4k_kernel/__init__.py:19-34 imports eagerly; present so the import succeeds.
-mha_int8_x_fp8_fwd = _out_of_scope("mha_int8_x_fp8_fwd")
+def mha_int8_x_fp8_fwd(o, q, q_sf, q_quantize_block_size, k, k_sf, k_quantize_block_size, v, v_sf, sm_scale):
+    """o = softmax(sm_scale * q k^T) v with INT8 q, k and FP8 p, v (ops.h:19-25; checks of
+    lib/cuda/sm120/mha_int8_x_fp8.cu:983-1060).  q: int8 [B, H, Nq, Dqk], q_sf: fp32 [B, H, ceil(Nq / q_block)];
+    k: int8 [B, H, Nkv, Dqk], k_sf: fp32 [B, H, ceil(Nkv / k_block)]; v: e4m3 [B, H, Dv, align16(Nkv)] (quantised along
+    the keys, swizzle=True, max_scale 2.25), v_sf: fp32 [B, H, align16(Dv)]; o: bf16 [B, H, Nq, Dv] in any strides."""
+    _check_tensor(q, torch.int8, "Q")
+    _require(q.dim() == 4, "Q must be a 4D tensor")
+    B, H, Nq, Dqk = q.shape
+    _require(Dqk % 16 == 0, "Dqk must be multiple of 16")
+    _require(Dqk <= 128, "Dqk must be less than 128")
+    qb, kb = int(q_quantize_block_size), int(k_quantize_block_size)
+    _check_tensor(q_sf, torch.float32, "Q_SF")
+    _require(q_sf.dim() == 3, "Q_SF must be a 3D tensor")
+    _require(list(q_sf.shape) == [B, H, _ceil_div(Nq, qb)], f"Meet invalid Q_SF shape {list(q_sf.shape)}")
+    _check_tensor(k, torch.int8, "K")
+    _require(k.dim() == 4, "K must be a 4D tensor")
+    _require(k.size(0) == B, "K must have the same batch size as Q")
+    _require(k.size(1) == H, "K must have the same head number as Q")
+    Nkv = k.size(2)
+    _require(k.size(3) == Dqk, "K must have the same dim as Q")
+    _check_tensor(k_sf, torch.float32, "K_SF")
+    _require(k_sf.dim() == 3, "K_SF must be a 3D tensor")
+    _require(list(k_sf.shape) == [B, H, _ceil_div(Nkv, kb)], f"Meet invalid K_SF shape {list(k_sf.shape)}")
+    _check_tensor(v, torch.float8_e4m3fn, "V")
+    _require(v.dim() == 4, "V must be a 4D tensor")
+    _require(v.size(0) == B, "V must have the same batch size as Q")
+    _require(v.size(1) == H, "V must have the same head number as Q")
+    Dv = v.size(2)
+    _require(v.size(3) == _align_up(Nkv, 16), "V must have the same sequence length as K")
+    _require(Dv <= 128, "Dv must be less than 128")
+    _check_tensor(v_sf, torch.float32, "V_SF")
+    _require(v_sf.dim() == 3, "V_SF must be a 3D tensor")
+    _require(list(v_sf.shape) == [B, H, _align_up(Dv, 16)], f"Meet invalid v_sf shape {list(v_sf.shape)}")
+    _require(isinstance(o, torch.Tensor) and o.is_cuda, "O must be a CUDA tensor")
+    _require(o.dtype == torch.bfloat16, "O must be a bfloat16 tensor")
+    _require(o.dim() == 4, "O must be a 4D tensor")
+    _require(list(o.shape) == [B, H, Nq, Dv], f"O must have shape {[B, H, Nq, Dv]} but see {list(o.shape)}")
+    with torch.cuda.device(o.device):
+        check(LIB.ac4k_mha_int8_x_fp8_fwd(o.data_ptr(), _I64x4(*o.stride()), q.data_ptr(), q_sf.data_ptr(), qb,
+                                          k.data_ptr(), k_sf.data_ptr(), kb, v.data_ptr(), v_sf.data_ptr(), B, H, Nq,
+                                          Nkv, Dqk, Dv, float(sm_scale), _stream(o)),
+              "mha_int8_x_fp8_fwd")
+
+
+def quantize_int8_block(out, scale, input, layout, block_size):
+    """INT8 quantisation in blocks of `block_size` tokens (all features of a head share the block's scale); stands in
+    for the reference's Triton kernel (python/ac4k_kernel/ops/attention.py:18-99).  input: bf16 [B, N, H, D] ("BNHD")
+    or [B, H, N, D] ("BHND"), any strides; out: int8 [B, H, N, align16(D)]; scale: fp32 [B, H, ceil(N / block_size)]."""
+    _require(layout in ("BNHD", "BHND"), f"Unsupported layout: {layout}")
+    _require(isinstance(input, torch.Tensor) and input.is_cuda and input.dtype == torch.bfloat16 and input.dim() == 4,
+             "in must be a 4D bfloat16 CUDA tensor")
+    x = input.permute(0, 2, 1, 3) if layout == "BNHD" else input
+    B, H, N, D = x.shape
+    _check_tensor(out, torch.int8, "out")
+    _check_tensor(scale, torch.float32, "scale")
+    _require(list(out.shape) == [B, H, N, _align_up(D, 16)], "out has an invalid shape")
+    _require(list(scale.shape) == [B, H, _ceil_div(N, int(block_size))], "scale has an invalid shape")
+    with torch.cuda.device(input.device):
+        check(LIB.ac4k_quantize_int8_block(out.data_ptr(), scale.data_ptr(), x.data_ptr(), _I64x4(B, H, N, D),
+                                           _I64x4(*x.stride()), int(block_size), _stream(input)),
+              "quantize_int8_block")

@@ -42,6 +42,10 @@ SIGNATURES = {
     "ac4k_mha_nvfp4_fwd": (ctypes.c_int, [_vp, _c_i64p, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                           ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                           ctypes.c_int64, ctypes.c_int64, ctypes.c_float, ctypes.c_int, _vp]),
+    "ac4k_quantize_int8_block": (ctypes.c_int, [_vp, _vp, _vp, _c_i64p, _c_i64p, ctypes.c_int64, _vp]),
+    "ac4k_mha_int8_x_fp8_fwd": (ctypes.c_int, [_vp, _c_i64p, _vp, _vp, ctypes.c_int64, _vp, _vp, ctypes.c_int64, _vp, _vp,
+                                               ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                               ctypes.c_int64, ctypes.c_int64, ctypes.c_float, _vp]),
     "ac4k_rope3d": (ctypes.c_int, [_vp, _vp, _vp, _vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                    ctypes.c_int64, _vp]),
     "ac4k_peer_alloc": (ctypes.c_int, [ctypes.c_int64, ctypes.POINTER(_vp), ctypes.c_char_p]),

@@ -25,7 +25,7 @@ OBJ_DIR = os.path.join(PKG_DIR, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libac4k_b200.so")
 
 SOURCES = ["cabi.cu", "quantize_nvfp4.cu", "quantize_rowwise.cu", "linear_nvfp4.cu",
-           "linear_nvfp4_2cta.cu", "linear_nvfp4_skinny.cu", "mha_nvfp4.cu", "rope3d.cu"]
+           "linear_nvfp4_2cta.cu", "linear_nvfp4_skinny.cu", "mha_nvfp4.cu", "rope3d.cu", "mha_int8_fp8.cu", "quantize_int8_block.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",

@@ -249,12 +249,46 @@ void mha_nvfp4_fwd(torch::Tensor &o, torch::Tensor &q, torch::Tensor &q_sf, torc
   TORCH_CHECK(rc == 0, "ac4k_mha_nvfp4_fwd: ", ac4k_last_error());
 }
 
-// The int8 x fp8 attention operator of the reference module is not built; the name exists so that `import` and
-// introspection behave like the reference's module.
-void mha_int8_x_fp8_fwd(torch::Tensor &, torch::Tensor &, torch::Tensor &, int, torch::Tensor &, torch::Tensor &, int,
-                        torch::Tensor &, torch::Tensor &, float) {
-  TORCH_CHECK(false, "mha_int8_x_fp8_fwd is not part of the sm100 NVFP4 library");
+// ops.h:19-25; checks of mha_int8_x_fp8.cu:983-1060
+void mha_int8_x_fp8_fwd(torch::Tensor &o, torch::Tensor &q, torch::Tensor &q_sf, int q_quantize_block_size, torch::Tensor &k,
+                        torch::Tensor &k_sf, int k_quantize_block_size, torch::Tensor &v, torch::Tensor &v_sf, float sm_scale) {
+  check_cuda(q, at::kChar, "Q");
+  TORCH_CHECK(q.dim() == 4, "Q must be a 4D tensor");
+  const int64_t B = q.size(0), H = q.size(1), Nq = q.size(2), Dqk = q.size(3);
+  TORCH_CHECK(Dqk % 16 == 0, "Dqk must be multiple of 16");
+  TORCH_CHECK(Dqk <= 128, "Dqk must be less than 128");
+  check_cuda(q_sf, at::kFloat, "Q_SF");
+  TORCH_CHECK(q_sf.dim() == 3 && q_sf.size(0) == B && q_sf.size(1) == H && q_sf.size(2) == ceil_div(Nq, q_quantize_block_size),
+              "Meet invalid Q_SF shape");
+  check_cuda(k, at::kChar, "K");
+  TORCH_CHECK(k.dim() == 4, "K must be a 4D tensor");
+  TORCH_CHECK(k.size(0) == B, "K must have the same batch size as Q");
+  TORCH_CHECK(k.size(1) == H, "K must have the same head number as Q");
+  const int64_t Nkv = k.size(2);
+  TORCH_CHECK(k.size(3) == Dqk, "K must have the same dim as Q");
+  check_cuda(k_sf, at::kFloat, "K_SF");
+  TORCH_CHECK(k_sf.dim() == 3 && k_sf.size(0) == B && k_sf.size(1) == H && k_sf.size(2) == ceil_div(Nkv, k_quantize_block_size),
+              "Meet invalid K_SF shape");
+  check_cuda(v, at::kFloat8_e4m3fn, "V");
+  TORCH_CHECK(v.dim() == 4, "V must be a 4D tensor");
+  TORCH_CHECK(v.size(0) == B, "V must have the same batch size as Q");
+  TORCH_CHECK(v.size(1) == H, "V must have the same head number as Q");
+  const int64_t Dv = v.size(2);
+  TORCH_CHECK(v.size(3) == align_up(Nkv, 16), "V must have the same sequence length as K");
+  TORCH_CHECK(Dv <= 128, "Dv must be less than 128");
+  check_cuda(v_sf, at::kFloat, "V_SF");
+  TORCH_CHECK(v_sf.dim() == 3 && v_sf.size(0) == B && v_sf.size(1) == H && v_sf.size(2) == align_up(Dv, 16), "Meet invalid v_sf shape");
+  TORCH_CHECK(o.is_cuda(), "O must be a CUDA tensor");
+  TORCH_CHECK(o.scalar_type() == at::kBFloat16, "O must be a bfloat16 tensor");
+  TORCH_CHECK(o.dim() == 4 && o.size(0) == B && o.size(1) == H && o.size(2) == Nq && o.size(3) == Dv, "O must have shape [B, H, Nq, Dv]");
+  const c10::cuda::CUDAGuard guard(o.device());
+  const int64_t os[4] = {o.stride(0), o.stride(1), o.stride(2), o.stride(3)};
+  const int rc = ac4k_mha_int8_x_fp8_fwd(o.data_ptr(), os, q.data_ptr(), q_sf.data_ptr<float>(), q_quantize_block_size, k.data_ptr(),
+                                         k_sf.data_ptr<float>(), k_quantize_block_size, v.data_ptr(), v_sf.data_ptr<float>(), B, H, Nq,
+                                         Nkv, Dqk, Dv, sm_scale, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "ac4k_mha_int8_x_fp8_fwd: ", ac4k_last_error());
 }
+
 // ops.h:50-54; checks of rope3d.cu:133-165
 void rope3d(const torch::Tensor &x, const torch::Tensor &grid_sizes, const torch::Tensor &freqs, torch::Tensor &output) {
   check_cuda(x, at::kBFloat16, "x");
@@ -285,7 +319,7 @@ PYBIND11_MODULE(_cuda_ops, m) {
   m.attr("__backend__") = ac4k_backend();
   m.attr("__version__") = ac4k_version();
   m.def("mha_nvfp4_fwd", &ac4k::mha_nvfp4_fwd, "Multi-Head Attention Forward (NVFP4)");
-  m.def("mha_int8_x_fp8_fwd", &ac4k::mha_int8_x_fp8_fwd, "Multi-Head Attention Forward (QK=INT8, PV=FP8): not built for sm100");
+  m.def("mha_int8_x_fp8_fwd", &ac4k::mha_int8_x_fp8_fwd, "Multi-Head Attention Forward (QK=INT8, PV=FP8)");
   m.def("quantize_nvfp4", &ac4k::quantize_nvfp4, "Quantize bfloat16 tensor to NVFP4 format");
   m.def("quantize_fp8", &ac4k::quantize_fp8, "Quantize bfloat16 tensor to FP8 format");
   m.def("quantize_int8", &ac4k::quantize_int8, "Quantize bfloat16 tensor to INT8 format");

@@ -1,0 +1,95 @@
+// Block-of-tokens INT8 quantiser of the INT8 x FP8 attention path: x[b, h, n, :] bf16 (any strides) ->
+// y[b, h, n, align16(D)] int8 and one fp32 scale per block of `block` consecutive tokens (all D features):
+//   scale = max|x| / 127 over the block,  y = trunc(x / scale)  (0 when the block is all zero), padding columns 0.
+// Stands in for the Triton kernel and its wrapper in ac4k_kernel's python/ac4k_kernel/ops/attention.py:18-48 and
+// :51-99 (`tl.cast(fp32 -> int8)` truncates toward zero; the division is a true fp32 division).
+//
+// One CTA per (token block, head, batch entry): the block (at most 128 x 256 bf16) is read once into registers,
+// reduced to its maximum through shared memory, and written back as bytes.  HBM traffic 2 + 1 bytes per element.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace ac4k {
+
+static constexpr int kQ8Threads = 256;
+static constexpr int kQ8MaxElemsPerThread = 128;     // 128 tokens x 256 features / 256 threads
+
+// EPT: elements per thread, >= block * align16(D) / 256
+template <int EPT>
+__global__ void __launch_bounds__(kQ8Threads) quantize_int8_block_kernel(
+    int8_t *__restrict__ y, float *__restrict__ scale, const uint16_t *__restrict__ x, int N, int D, int Dp, int block, int nblk,
+    int64_t sb, int64_t sh, int64_t sn, int64_t sd, int H) {
+  __shared__ float red[kQ8Threads / 32];
+  const int blk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int n0 = blk * block;
+  const int rows = min(block, N - n0);
+  const uint16_t *src = x + b * sb + h * sh;
+  const int total = block * Dp;                       // elements of the output tile, padding columns included
+  float v[EPT];
+  float amax = 0.0f;
+  grid_dependency_wait();
+#pragma unroll
+  for (int i = 0; i < EPT; ++i) {
+    const int e = i * kQ8Threads + threadIdx.x;       // consecutive threads take consecutive features
+    v[i] = 0.0f;
+    if (e < total) {
+      const int r = e / Dp, c = e - r * Dp;
+      if (r < rows && c < D) {
+        v[i] = __uint_as_float((uint32_t)__ldg(src + (int64_t)(n0 + r) * sn + (int64_t)c * sd) << 16);
+        amax = fmaxf(amax, fabsf(v[i]));
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int w = 1; w < kQ8Threads / 32; ++w) amax = fmaxf(amax, red[w]);
+  const float s = __fdiv_rn(amax, 127.0f);
+  if (threadIdx.x == 0) scale[((int64_t)b * H + h) * nblk + blk] = s;
+  int8_t *dst = y + (((int64_t)b * H + h) * N + n0) * Dp;
+#pragma unroll
+  for (int i = 0; i < EPT; ++i) {
+    const int e = i * kQ8Threads + threadIdx.x;
+    if (e < rows * Dp) dst[e] = s == 0.0f ? (int8_t)0 : (int8_t)__float2int_rz(__fdiv_rn(v[i], s));
+  }
+  grid_launch_dependents();
+}
+
+}  // namespace ac4k
+
+using namespace ac4k;
+
+extern "C" int ac4k_quantize_int8_block(void *out, float *scale, const void *in, const int64_t shape[4], const int64_t stride[4],
+                                        int64_t block, ac4k_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!shape || !stride) return fail(AC4K_ERR_NULL, "shape/stride is NULL");
+  const int64_t B = shape[0], H = shape[1], N = shape[2], D = shape[3];
+  if (B < 0 || H < 0 || N < 0 || D < 0) return fail(AC4K_ERR_SHAPE, "negative dimension");
+  if (block < 16 || block > 128 || (block & (block - 1))) return fail(AC4K_ERR_SHAPE, "the token block must be a power of two in [16, 128], got %lld", (long long)block);
+  if (B == 0 || H == 0 || N == 0 || D == 0) return 0;
+  if (!out || !scale || !in) return fail(AC4K_ERR_NULL, "out/scale/in is NULL");
+  const int64_t Dp = align_up(D, 16);
+  if (block * Dp > (int64_t)kQ8MaxElemsPerThread * kQ8Threads)
+    return fail(AC4K_ERR_UNSUPPORTED, "block x align16(D) up to %d elements is built, got %lld x %lld", kQ8MaxElemsPerThread * kQ8Threads,
+                (long long)block, (long long)Dp);
+  if (H > 65535 || B > 65535 || N > INT32_MAX) return fail(AC4K_ERR_SHAPE, "dimension too large");
+  if ((reinterpret_cast<uintptr_t>(in) & 1) || (reinterpret_cast<uintptr_t>(scale) & 3)) return fail(AC4K_ERR_ALIGN, "in must be 2-byte and scale 4-byte aligned");
+  const int64_t nblk = ceil_div(N, block);
+  dim3 grid((unsigned)nblk, (unsigned)H, (unsigned)B);
+  const int64_t ept = ceil_div(block * Dp, kQ8Threads);
+#define AC4K_Q8_LAUNCH(E)                                                                                                          \
+  quantize_int8_block_kernel<E><<<grid, kQ8Threads, 0, stream>>>(static_cast<int8_t *>(out), scale, static_cast<const uint16_t *>(in), \
+                                                                  (int)N, (int)D, (int)Dp, (int)block, (int)nblk, stride[0], stride[1],  \
+                                                                  stride[2], stride[3], (int)H)
+  if (ept <= 16) AC4K_Q8_LAUNCH(16);
+  else if (ept <= 32) AC4K_Q8_LAUNCH(32);
+  else if (ept <= 64) AC4K_Q8_LAUNCH(64);
+  else AC4K_Q8_LAUNCH(128);
+#undef AC4K_Q8_LAUNCH
+  AC4K_LAUNCH_CHECK("quantize_int8_block_kernel");
+  return 0;
+}

@@ -21,6 +21,7 @@
 namespace ac4k {
 
 static constexpr int kRopeThreads = 256;
+static constexpr int kRopeCtasPerSm = 5;     // 48 registers per thread; the grid is this many CTAs per SM
 static constexpr int kRopeMaxC = 1024;      // complex pairs per head staged in shared memory (D <= 2048)
 
 __device__ __forceinline__ uint32_t rope_pair(uint32_t xy, double2 f) {
@@ -39,7 +40,7 @@ __device__ __forceinline__ int rope_row(int c, int c1, int c2, int fi, int hi, i
 // MODE 1: 16-byte accesses, the position's C factors staged in shared memory (two CTA barriers per position).
 // MODE 2: one pair per access (D % 8 != 0 or tensors not 16-byte aligned), factors in shared memory.
 template <int MODE>
-__global__ void __launch_bounds__(kRopeThreads) rope3d_kernel(const uint16_t *__restrict__ x, const int32_t *__restrict__ grid_sizes,
+__global__ void __launch_bounds__(kRopeThreads, kRopeCtasPerSm) rope3d_kernel(const uint16_t *__restrict__ x, const int32_t *__restrict__ grid_sizes,
                                                                const double2 *__restrict__ freqs, uint16_t *__restrict__ out,
                                                                int64_t BS, int S, int N, int D, int C, int max_pos) {
   __shared__ double2 sf[MODE == 0 ? 1 : kRopeMaxC];
@@ -130,8 +131,7 @@ extern "C" int ac4k_rope3d(void *out, const void *x, const int32_t *grid_sizes, 
   DeviceInfo di;
   if (int e = get_device_info(&di)) return e;
   const int64_t BS = B * S;
-  // resident CTAs: 8 per SM (256 threads, 16 KB of shared memory each)
-  const unsigned blocks = (unsigned)std::min<int64_t>(BS, (int64_t)di.sms * 8);
+  const unsigned blocks = (unsigned)std::min<int64_t>(BS, (int64_t)di.sms * kRopeCtasPerSm);
   const bool vec = (D % 8 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
   const int mode = !vec ? 2 : ((kRopeThreads * 4) % (D / 2) == 0 ? 0 : 1);
   const uint16_t *xp = static_cast<const uint16_t *>(x);

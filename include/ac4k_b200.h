@@ -176,6 +176,30 @@ int ac4k_mha_nvfp4_fwd(void *O, const int64_t o_stride[4], const void *Q, const 
                        const float *V_gs, int64_t B, int64_t H, int64_t Nq, int64_t Nkv, int64_t Dqk, int64_t Dv,
                        float sm_scale, int sf_layout, ac4k_stream_t stream);
 
+/* Block-of-tokens INT8 quantiser of the INT8 x FP8 attention path: one fp32 scale = max|x| / 127 per `block`
+ * consecutive tokens of a head (all features), y = trunc(x / scale), feature padding to a multiple of 16 written as 0.
+ * Replaces the Triton kernel `_triton_block_token_quantize` and `_int8_quantize`,
+ * python/ac4k_kernel/ops/attention.py:18-48, :51-99.
+ *   in: bf16, logical [B, H, N, D] given by shape[4] = {B, H, N, D} and element strides stride[4] (so both tensor
+ *   layouts of the reference work); out: int8 [B, H, N, align16(D)] contiguous; scale: fp32 [B, H, ceil(N / block)].
+ *   block: power of two in [16, 128], block * align16(D) <= 32768. */
+int ac4k_quantize_int8_block(void *out, float *scale, const void *in, const int64_t shape[4], const int64_t stride[4],
+                             int64_t block, ac4k_stream_t stream);
+
+/* O = softmax(sm_scale * Q K^T) V with Q, K in INT8 (scales per block of tokens), P and V in FP8 e4m3 (V with one scale
+ * per channel), bf16 output.  Replaces ac4k::mha_int8_x_fp8_fwd, include/ac4k_kernel/ops.h:19-25,
+ * lib/cuda_bindings.cc:57-58, lib/cuda/sm120/mha_int8_x_fp8.cu:979-1137 (checks) and :403-975 (kernel).
+ *   Q: int8 [B, H, Nq, align16(Dqk)], Q_sf: fp32 [B, H, ceil(Nq / q_block)]; K: int8 [B, H, Nkv, align16(Dqk)],
+ *   K_sf: fp32 [B, H, ceil(Nkv / k_block)]; V: e4m3 [B, H, Dv, align16(Nkv)], quantised along the keys with the FP8 K
+ *   permutation (swizzle = 1) and max_scale 2.25, V_sf: fp32 [B, H, align16(Dv)]; O: bf16 by element strides as in
+ *   ac4k_mha_nvfp4_fwd.
+ * Built for Dqk, Dv <= 128, k_block = 128 (the reference's default), q_block in {16, 32, 64, 128}, sm_scale >= 0; the
+ * P V products accumulate in fp32 (the reference: fp16 within a key tile). */
+int ac4k_mha_int8_x_fp8_fwd(void *O, const int64_t o_stride[4], const void *Q, const float *Q_sf, int64_t q_block,
+                            const void *K, const float *K_sf, int64_t k_block, const void *V, const float *V_sf,
+                            int64_t B, int64_t H, int64_t Nq, int64_t Nkv, int64_t Dqk, int64_t Dv, float sm_scale,
+                            ac4k_stream_t stream);
+
 /* 3-D rotary position embedding: out[b, s, n, 2c..2c+1] = x[b, s, n, 2c..2c+1] * freqs[row(s, c), c] as complex numbers,
  * row = the position's frame, height or width index in the [F, H, W] grid of its batch entry, by thirds of the C = D / 2
  * pairs (c1 = C - 2 (C / 3) frame pairs, then C / 3 height pairs, then C / 3 width pairs).

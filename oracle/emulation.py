@@ -439,3 +439,87 @@ def rope3d_ref(x: torch.Tensor, grid_sizes: torch.Tensor, freqs: torch.Tensor) -
         y = torch.view_as_real(xc * fac[:, None, :]).reshape(n, N, D)
         out[b, :n] = y.to(torch.float32).to(torch.bfloat16)
     return out
+
+
+# ----------------------------------------------------------------------------------------
+# INT8 x FP8 attention
+# ----------------------------------------------------------------------------------------
+EXP_OFFSET = 7.5          # log2 units taken off the row maximum so that P uses e4m3's range (mha_int8_x_fp8.cu:119-121)
+V_SCALE_MAX = 2.25        # largest |V| after its per-channel FP8 quantisation (mha_int8_x_fp8.cu:119; attention.py:171-176)
+
+
+def quantize_int8_block_ref(x: torch.Tensor, layout: str, block: int):
+    """bf16 [B, N, H, D] ("BNHD") or [B, H, N, D] ("BHND") -> (int8 [B, H, N, align16(D)], fp32 [B, H, ceil(N / block)]).
+    One scale per `block` consecutive tokens of a head: max|x| / 127; values trunc(x / scale), 0 for an all-zero block
+    (python/ac4k_kernel/ops/attention.py:18-48: `tl.cast` to int8 truncates toward zero; :51-99 shapes).  The division
+    is a true fp32 division here and in the CUDA kernel; Triton's may differ in the last bit."""
+    assert x.dtype == torch.bfloat16 and x.dim() == 4
+    xb = x.permute(0, 2, 1, 3) if layout == "BNHD" else x
+    B, H, N, D = xb.shape
+    nblk = ceil_div(N, block)
+    xf = torch.zeros((B, H, nblk * block, D), dtype=torch.float32, device=x.device)
+    xf[:, :, :N] = xb.to(torch.float32)
+    blk = xf.reshape(B, H, nblk, block * D)
+    scale = blk.abs().amax(dim=-1) / torch.tensor(127.0, dtype=torch.float32, device=x.device)
+    q = torch.where(scale.unsqueeze(-1) == 0, torch.zeros_like(blk), torch.trunc(blk / scale.unsqueeze(-1)))
+    y = torch.zeros((B, H, N, align_up(D, 16)), dtype=torch.int8, device=x.device)
+    y[..., :D] = q.reshape(B, H, nblk * block, D)[:, :, :N].to(torch.int8)
+    return y, scale
+
+
+def mha_int8_x_fp8_ref(q, q_sf, q_block: int, k, k_sf, k_block: int, v, v_sf, sm_scale: float, tile: int = 128,
+                       fp16_tile_accumulate: bool = False, out_dtype=torch.bfloat16):
+    """softmax(sm_scale * Q K^T) V on INT8 q, k and FP8 p, v, walking the keys in tiles of `tile` the way the kernels do
+    (lib/cuda/sm120/mha_int8_x_fp8.cu:640-700 scores, :700-715 maximum with the 7.5 offset, :717-790 P and the row sum,
+    :795-880 P V, :893-910 the final scaling).
+      q: int8 [B, H, Nq, Dp], q_sf: fp32 [B, H, ceil(Nq / q_block)]; k: int8 [B, H, Nkv, Dp], k_sf likewise with k_block;
+      v: e4m3 [B, H, Dv, align16(Nkv)] with the keys in the order of `quantize(v, 3, N_dim, swizzle=True,
+      precision="fp8e4m3")`, v_sf: fp32 [B, H, align16(Dv)].
+    `fp16_tile_accumulate` rounds every tile's P V to fp16 before it is added to O, as the reference's MMA does; the
+    tcgen05 kernel accumulates in fp32.  Returns [B, H, Nq, Dv]."""
+    B, H, nq, _ = q.shape
+    nkv, dv, kvp = k.shape[2], v.shape[2], v.shape[3]
+    dev = q.device
+    f32 = lambda t: torch.tensor(t, dtype=torch.float32, device=dev)
+    c0 = f32(sm_scale) * f32(LOG2E)
+    key_of_pos = permute_k_fp8(torch.arange(kvp, device=dev).to(torch.float32)).to(torch.long)
+    out = torch.empty((B, H, nq, dv), dtype=out_dtype, device=dev)
+    rows = torch.arange(nq, device=dev)
+    for b in range(B):
+        for h in range(H):
+            s_int = (q[b, h].to(torch.float64) @ k[b, h].to(torch.float64).t()).to(torch.float32)   # exact: |S| < 2^24
+            c_row = c0 * q_sf[b, h][rows // q_block]                                                # [Nq]
+            vnat = torch.zeros((dv, kvp), dtype=torch.float32, device=dev)
+            vnat[:, key_of_pos] = v[b, h].to(torch.float32)                                         # natural key order
+            m = torch.full((nq,), float("-inf"), dtype=torch.float32, device=dev)
+            l = torch.zeros((nq,), dtype=torch.float32, device=dev)
+            o = torch.zeros((nq, dv), dtype=torch.float32, device=dev)
+            for j0 in range(0, nkv, tile):
+                j1 = min(j0 + tile, nkv)
+                cols = torch.arange(j0, j1, device=dev)
+                c = c_row[:, None] * k_sf[b, h][cols // k_block][None, :]
+                s = s_int[:, j0:j1] * c
+                m_new = torch.maximum(m, s.amax(dim=1) - EXP_OFFSET)
+                p = torch.exp2(s - m_new[:, None])
+                a = torch.exp2(m - m_new)
+                l = l * a + p.sum(dim=1)
+                p8 = e4m3_bits_to_float(e4m3_rne_sat_bits(p))
+                pv = p8 @ vnat[:, j0:j1].t()
+                if fp16_tile_accumulate:
+                    pv = pv.to(torch.float16).to(torch.float32)
+                o = o * a[:, None] + pv
+                m = m_new
+            out[b, h] = (o * (v_sf[b, h][:dv][None, :] / l[:, None])).to(out_dtype)
+    return out
+
+
+def attention_int8_x_fp8_ref(q, k, v, layout: str = "BNHD", q_block: int = 64, k_block: int = 128):
+    """The reference's `attention(..., precision="int8+fp8e4m3")` (python/ac4k_kernel/ops/attention.py:141-193) on this
+    module's quantisers."""
+    n_dim = 1 if layout == "BNHD" else 2
+    k = k - k.mean(dim=n_dim, keepdim=True)
+    qq, qs = quantize_int8_block_ref(q, layout, q_block)
+    kq, ks = quantize_int8_block_ref(k, layout, k_block)
+    vq, vs = quantize_fp8_ref(v, 3, n_dim, V_SCALE_MAX, swizzle=True)
+    o = mha_int8_x_fp8_ref(qq, qs, q_block, kq, ks, k_block, vq, vs, 1.0 / (q.shape[-1] ** 0.5))
+    return o.permute(0, 2, 1, 3).contiguous() if layout == "BNHD" else o

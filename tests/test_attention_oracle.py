@@ -39,3 +39,27 @@ def test_tile_size_only_changes_rounding():
     a = E.mha_nvfp4_ref(qq, qs, qg, kq, ks, kg, vq, vs, vg, 128 ** -0.5, 200, tile=128, out_dtype=torch.float32)
     b = E.mha_nvfp4_ref(qq, qs, qg, kq, ks, kg, vq, vs, vg, 128 ** -0.5, 200, tile=64, out_dtype=torch.float32)
     assert ((a - b).norm() / a.norm()).item() < 5e-2
+
+
+@pytest.mark.parametrize("B,N,H,D,layout", [(1, 256, 1, 128, "BNHD"), (1, 100, 1, 128, "BNHD"), (3, 100, 2, 12, "BNHD"),
+                                             (2, 111, 2, 100, "BHND")])
+def test_int8_x_fp8_restatement_meets_the_reference_bar(B, N, H, D, layout):
+    """test/test_attention_bench.py:67-176: cosine > 0.99, assert_close atol 2e-1 / rtol 1e-2 against SDPA."""
+    g = torch.Generator().manual_seed(9567)
+    shape = (B, N, H, D) if layout == "BNHD" else (B, H, N, D)
+    q, k, v = (torch.randn(shape, generator=g).bfloat16() for _ in range(3))
+    o = E.attention_int8_x_fp8_ref(q, k, v, layout)
+    ref = _sdp(q, k, v, layout)
+    cos = F.cosine_similarity(o.float().flatten()[None], ref.flatten()[None]).item()
+    assert cos > 0.99
+    torch.testing.assert_close(o.float(), ref, atol=2e-1, rtol=1e-2)
+
+
+def test_int8_block_quantiser_restatement():
+    x = torch.tensor([[1.0, -2.0, 0.5, 127.0], [3.0, 0.0, -127.0, 63.4]]).bfloat16().reshape(1, 1, 2, 4)
+    y, s = E.quantize_int8_block_ref(x, "BHND", 16)
+    assert y.shape == (1, 1, 2, 16) and s.shape == (1, 1, 1) and s.item() == 1.0
+    assert y[0, 0, :, :4].tolist() == [[1, -2, 0, 127], [3, 0, -127, 63]]      # truncation toward zero
+    assert (y[..., 4:] == 0).all()
+    z, sz = E.quantize_int8_block_ref(torch.zeros((1, 20, 2, 8), dtype=torch.bfloat16), "BNHD", 16)
+    assert (z == 0).all() and (sz == 0).all() and sz.shape == (1, 2, 2)

@@ -30,7 +30,7 @@ def test_checks_raise_like_torch_check(mod):
         mod.linear_nvfp4(torch.zeros(4), x, x, x, x, x, x, None)
     with pytest.raises(RuntimeError, match="CUDA tensor"):
         mod.rope3d(x, x, x, x)
-    with pytest.raises(RuntimeError, match="not part of"):
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
         mod.mha_int8_x_fp8_fwd(x, x, x, 64, x, x, 128, x, x, 0.1)
 
 
