@@ -6,6 +6,7 @@
 //
 // One CTA per (token block, head, batch entry): the block (at most 128 x 256 bf16) is read once into registers,
 // reduced to its maximum through shared memory, and written back as bytes.  HBM traffic 2 + 1 bytes per element.
+// Two kernels: 16-byte vectors when the features are contiguous and aligned, single elements otherwise.
 #include <algorithm>
 
 #include "common.cuh"
@@ -59,6 +60,67 @@ __global__ void __launch_bounds__(kQ8Threads) quantize_int8_block_kernel(
   grid_launch_dependents();
 }
 
+// The usual case: features contiguous, D a multiple of 8, rows 16-byte aligned.  A thread takes 16-byte vectors of eight
+// features (consecutive threads = consecutive vectors of a row, then the next row), keeps them packed in registers,
+// and writes eight bytes per vector.  VPT: vectors per thread, >= block * D / 8 / 256.
+template <int VPT>
+__global__ void __launch_bounds__(kQ8Threads) quantize_int8_block_vec_kernel(
+    int8_t *__restrict__ y, float *__restrict__ scale, const uint16_t *__restrict__ x, int N, int D, int Dp, int block, int nblk,
+    int64_t sb, int64_t sh, int64_t sn, int H) {
+  __shared__ float red[kQ8Threads / 32];
+  const int blk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int n0 = blk * block;
+  const int rows = min(block, N - n0);
+  const uint16_t *src = x + b * sb + h * sh + (int64_t)n0 * sn;
+  const int vpr = D / 8, vpr_out = Dp / 8;            // vectors per input row / per output row (padding included)
+  const int nvec = rows * vpr_out;
+  uint4 v[VPT];
+  __nv_bfloat162 am2 = __floats2bfloat162_rn(0.0f, 0.0f);
+  grid_dependency_wait();
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int e = i * kQ8Threads + threadIdx.x;
+    v[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (e < nvec) {
+      const int r = e / vpr_out, c = e - r * vpr_out;
+      if (c < vpr) {
+        v[i] = __ldcs(reinterpret_cast<const uint4 *>(src + (int64_t)r * sn) + c);
+        const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&v[i]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) am2 = __hmax2(am2, __habs2(h2[k]));
+      }
+    }
+  }
+  float amax = fmaxf(__low2float(am2), __high2float(am2));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int w = 1; w < kQ8Threads / 32; ++w) amax = fmaxf(amax, red[w]);
+  const float s = __fdiv_rn(amax, 127.0f);
+  if (threadIdx.x == 0) scale[((int64_t)b * H + h) * nblk + blk] = s;
+  uint2 *dst = reinterpret_cast<uint2 *>(y + (((int64_t)b * H + h) * N + n0) * Dp);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int e = i * kQ8Threads + threadIdx.x;
+    if (e < nvec) {
+      const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+      uint32_t o[2] = {0u, 0u};
+      if (s != 0.0f) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float f = __uint_as_float((k & 1) ? (w[k >> 1] & 0xffff0000u) : (w[k >> 1] << 16));
+          o[k >> 2] |= ((uint32_t)__float2int_rz(__fdiv_rn(f, s)) & 0xffu) << (8 * (k & 3));
+        }
+      }
+      __stcs(dst + e, make_uint2(o[0], o[1]));
+    }
+  }
+  grid_launch_dependents();
+}
+
 }  // namespace ac4k
 
 using namespace ac4k;
@@ -80,6 +142,22 @@ extern "C" int ac4k_quantize_int8_block(void *out, float *scale, const void *in,
   if ((reinterpret_cast<uintptr_t>(in) & 1) || (reinterpret_cast<uintptr_t>(scale) & 3)) return fail(AC4K_ERR_ALIGN, "in must be 2-byte and scale 4-byte aligned");
   const int64_t nblk = ceil_div(N, block);
   dim3 grid((unsigned)nblk, (unsigned)H, (unsigned)B);
+  const bool vec = stride[3] == 1 && D % 8 == 0 && stride[0] % 8 == 0 && stride[1] % 8 == 0 && stride[2] % 8 == 0 &&
+                   (reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 7) == 0;
+  if (vec) {
+    const int64_t vpt = ceil_div(block * (Dp / 8), kQ8Threads);
+#define AC4K_Q8V_LAUNCH(V)                                                                                                            \
+  quantize_int8_block_vec_kernel<V><<<grid, kQ8Threads, 0, stream>>>(static_cast<int8_t *>(out), scale, static_cast<const uint16_t *>(in), \
+                                                                      (int)N, (int)D, (int)Dp, (int)block, (int)nblk, stride[0], stride[1],  \
+                                                                      stride[2], (int)H)
+    if (vpt <= 2) AC4K_Q8V_LAUNCH(2);
+    else if (vpt <= 4) AC4K_Q8V_LAUNCH(4);
+    else if (vpt <= 8) AC4K_Q8V_LAUNCH(8);
+    else AC4K_Q8V_LAUNCH(16);
+#undef AC4K_Q8V_LAUNCH
+    AC4K_LAUNCH_CHECK("quantize_int8_block_vec_kernel");
+    return 0;
+  }
   const int64_t ept = ceil_div(block * Dp, kQ8Threads);
 #define AC4K_Q8_LAUNCH(E)                                                                                                          \
   quantize_int8_block_kernel<E><<<grid, kQ8Threads, 0, stream>>>(static_cast<int8_t *>(out), scale, static_cast<const uint16_t *>(in), \

@@ -158,6 +158,117 @@ rowwise_quantize_strided_kernel(uint8_t *__restrict__ out, float *__restrict__ s
   }
 }
 
+// ----------------------------------------------------------------------------------------
+// Rows strided, columns contiguous (stride_m == 1): the V operand of attention, quantised along the keys
+// with the head dimension as rows of the output.  The one-warp-per-row kernel above reads 2 bytes per
+// 32-byte sector here; these three kernels read the input in its own order instead:
+//   1. column maxima: CTAs walk chunks of 256 reduce-rows, a warp reads 128 contiguous bytes of a row,
+//      per-column maxima meet in shared memory and leave as one atomicMax per column and CTA (on the
+//      bit pattern: non-negative floats order like integers) into the scale array, zeroed before;
+//   2. quantise + transpose: tiles of 64 reduce-rows x 128 columns through shared memory, written out as
+//      16-byte pieces along the reduce dimension (with the K permutation if asked for);
+//   3. scale array: maxima -> maxima / scale_max, padding rows 0.
+// ----------------------------------------------------------------------------------------
+static constexpr int kTrCols = 128, kTrRows = 64, kTrChunk = 256;
+
+__global__ void __launch_bounds__(256)
+colmax_kernel(float *__restrict__ sf, const uint16_t *__restrict__ in, int64_t M, int64_t K, int64_t M16, int64_t d1,
+              int64_t stride0, int64_t stride1, int64_t stride_k) {
+  __shared__ uint32_t red[4][kTrCols];
+  const int64_t batch = blockIdx.z;
+  const int cx = threadIdx.x & 63, ry = threadIdx.x >> 6;
+  const int64_t col = (int64_t)blockIdx.y * kTrCols + 2 * cx;
+  const uint16_t *base = in + (batch / d1) * stride0 + (batch % d1) * stride1;
+  const int64_t k0 = (int64_t)blockIdx.x * kTrChunk, k1 = min(k0 + kTrChunk, K);
+  uint32_t m0 = 0, m1 = 0;
+  if (col < M)
+    for (int64_t k = k0 + ry; k < k1; k += 4) {
+      const uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(base + k * stride_k + col));
+      m0 = max(m0, w & 0x7FFFu);
+      m1 = max(m1, (w >> 16) & 0x7FFFu);
+    }
+  red[ry][2 * cx] = m0;
+  red[ry][2 * cx + 1] = m1;
+  __syncthreads();
+  if (threadIdx.x < kTrCols) {
+    const int64_t c = (int64_t)blockIdx.y * kTrCols + threadIdx.x;
+    if (c < M) {
+      const uint32_t m = max(max(red[0][threadIdx.x], red[1][threadIdx.x]), max(red[2][threadIdx.x], red[3][threadIdx.x]));
+      atomicMax(reinterpret_cast<unsigned int *>(sf + batch * M16 + c), m << 16);
+    }
+  }
+}
+
+template <int FMT, bool PERMUTE>
+__global__ void __launch_bounds__(256)
+transpose_quantize_kernel(uint8_t *__restrict__ out, const float *__restrict__ amax_bits, const uint16_t *__restrict__ in,
+                          const void *__restrict__ scale_max_p, int scale_max_is_int, int64_t M, int64_t K, int64_t M16, int64_t d1,
+                          int64_t stride0, int64_t stride1, int64_t stride_k) {
+  __shared__ uint32_t tile[kTrCols][kTrRows / 4 + 1];       // [column][4 reduce-rows per word], padded
+  __shared__ float rs[kTrCols];
+  const int64_t batch = blockIdx.z;
+  const int64_t Kp = align_up(K, 16);
+  const int64_t c0 = (int64_t)blockIdx.y * kTrCols, k0 = (int64_t)blockIdx.x * kTrRows;
+  const uint16_t *base = in + (batch / d1) * stride0 + (batch % d1) * stride1;
+  const float smax = load_scale_max(scale_max_p, scale_max_is_int);
+  if (threadIdx.x < kTrCols) {
+    const int64_t c = c0 + threadIdx.x;
+    rs[threadIdx.x] = c < M ? __fdiv_rn(smax, __ldg(amax_bits + batch * M16 + c)) : 0.0f;
+  }
+  __syncthreads();
+  const int cx = threadIdx.x & 63, ry = threadIdx.x >> 6;
+  const int64_t col = c0 + 2 * cx;
+  const float r0 = rs[2 * cx], r1 = rs[2 * cx + 1];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int kq = ry + 4 * i;                                  // word index: reduce-rows 4 kq .. 4 kq + 3 of the tile
+    float a[4], b[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t k = k0 + 4 * kq + j;
+      uint32_t w = 0;
+      if (col < M && k < K) w = __ldg(reinterpret_cast<const uint32_t *>(base + k * stride_k + col));
+      a[j] = __fmul_rn(__uint_as_float(w << 16), r0);
+      b[j] = __fmul_rn(__uint_as_float(w & 0xFFFF0000u), r1);
+      // (padding of the reduce dimension reads as 0 and is multiplied like the rest: 0 * inf = NaN for a zero row,
+      // as in the reference and the one-warp-per-row kernel)
+    }
+    if (FMT == kFmtE4M3) {
+      tile[2 * cx][kq] = f32x4_to_e4m3x4(a[0], a[1], a[2], a[3]);
+      tile[2 * cx + 1][kq] = f32x4_to_e4m3x4(b[0], b[1], b[2], b[3]);
+    } else {
+      tile[2 * cx][kq] = f32x4_to_s8x4(a[0], a[1], a[2], a[3]);
+      tile[2 * cx + 1][kq] = f32x4_to_s8x4(b[0], b[1], b[2], b[3]);
+    }
+  }
+  __syncthreads();
+  // 128 columns x 4 groups of 16 reduce-rows: one 16-byte store each
+  for (int v = threadIdx.x; v < kTrCols * (kTrRows / 16); v += 256) {
+    const int c = v >> 2, g = v & 3;
+    const int64_t k = k0 + 16 * g;
+    if (c0 + c >= M || k >= Kp) continue;
+    const uint32_t n0 = tile[c][4 * g], n1 = tile[c][4 * g + 1], n2 = tile[c][4 * g + 2], n3 = tile[c][4 * g + 3];
+    uint4 o;
+    if (PERMUTE) {          // every 16 viewed as [2][4][2], first two modes transposed: positions 0-3 = elements 0, 1, 8, 9, ...
+      o.x = __byte_perm(n0, n2, 0x5410);
+      o.y = __byte_perm(n0, n2, 0x7632);
+      o.z = __byte_perm(n1, n3, 0x5410);
+      o.w = __byte_perm(n1, n3, 0x7632);
+    } else {
+      o = make_uint4(n0, n1, n2, n3);
+    }
+    *reinterpret_cast<uint4 *>(out + (batch * M + c0 + c) * Kp + k) = o;
+  }
+}
+
+__global__ void colmax_to_scale_kernel(float *__restrict__ sf, const void *__restrict__ scale_max_p, int scale_max_is_int, int64_t M,
+                                       int64_t M16, int64_t total) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const float smax = load_scale_max(scale_max_p, scale_max_is_int);
+  sf[i] = (i % M16) < M ? __fdiv_rn(sf[i], smax) : 0.0f;
+}
+
 template <int FMT>
 static int launch_rowwise(void *out, float *sf, const void *in, const void *scale_max, int is_int,
                           const int64_t shape[4], const int64_t stride[4], int swizzle,
@@ -190,6 +301,28 @@ static int launch_rowwise(void *out, float *sf, const void *in, const void *scal
                                                                     d1, stride[0], stride[1], stride[2]);
     }
     AC4K_LAUNCH_CHECK("rowwise_quantize_kernel");
+    return 0;
+  }
+  // columns contiguous, rows strided: the transposing kernels
+  const bool tr_ok = stride[2] == 1 && K > 0 && M % 2 == 0 && stride[3] % 2 == 0 && stride[0] % 2 == 0 && stride[1] % 2 == 0 &&
+                     ((reinterpret_cast<uintptr_t>(in) & 3) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
+                     ceil_div(K, kTrRows) <= 0x7fffffff && ceil_div(M, kTrCols) <= 65535;
+  if (tr_ok) {
+    AC4K_CUDA_TRY(cudaMemsetAsync(sf, 0, (size_t)(nbatch * M16) * sizeof(float), stream));
+    dim3 g1((unsigned)ceil_div(K, kTrChunk), (unsigned)ceil_div(M, kTrCols), (unsigned)nbatch);
+    colmax_kernel<<<g1, 256, 0, stream>>>(sf, inp, M, K, M16, d1, stride[0], stride[1], stride[3]);
+    AC4K_LAUNCH_CHECK("colmax_kernel");
+    dim3 g2((unsigned)ceil_div(align_up(K, 16), kTrRows), (unsigned)ceil_div(M, kTrCols), (unsigned)nbatch);
+    if (swizzle)
+      transpose_quantize_kernel<FMT, true><<<g2, 256, 0, stream>>>(outp, sf, inp, scale_max, is_int, M, K, M16, d1, stride[0],
+                                                                   stride[1], stride[3]);
+    else
+      transpose_quantize_kernel<FMT, false><<<g2, 256, 0, stream>>>(outp, sf, inp, scale_max, is_int, M, K, M16, d1, stride[0],
+                                                                    stride[1], stride[3]);
+    AC4K_LAUNCH_CHECK("transpose_quantize_kernel");
+    const int64_t total = nbatch * M16;
+    colmax_to_scale_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, stream>>>(sf, scale_max, is_int, M, M16, total);
+    AC4K_LAUNCH_CHECK("colmax_to_scale_kernel");
     return 0;
   }
   dim3 grid((unsigned)ceil_div(M16, 8), (unsigned)nbatch);

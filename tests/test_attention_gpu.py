@@ -165,5 +165,5 @@ def test_argument_checks():
     with pytest.raises(RuntimeError):      # head dimension 64: a valid call in the reference, not built here
         q64, k64, v64 = _qkv(1, 64, 64, 1, 64, 64, "BHND", seed=2)
         attention(q64, k64, v64, layout="BHND", precision="nvfp4")
-    with pytest.raises(NotImplementedError):
-        attention(q, k, v, layout="BHND", precision="int8+fp8e4m3")
+    with pytest.raises(AssertionError):
+        attention(q, k, v, layout="BHND", precision="fp16")
