@@ -371,31 +371,44 @@ def decode_stream(peaks):
 
 
 def attention_nvfp4(peaks):
-    """NVFP4 attention at the shapes of the reference's test/test_attention_tflops.py:36-39 ([1, 75600, 40, 128]; its
-    flop count 4 B H N^2 D, :32), a shorter one, and the same through `attention()` with the three quantiser
-    launches; torch's bf16 scaled_dot_product_attention on the same tensors beside it as a library yardstick."""
+    """Both attention precisions at the shape of the reference's test/test_attention_tflops.py:36-39 ([1, 75600, 40, 128];
+    its flop count 4 B H N^2 D, :32; it times `attention(precision="int8+fp8e4m3")`, quantisers included) and a shorter
+    one: the kernels alone on resident quantised operands, the `attention()` calls with their quantiser launches, and
+    torch's bf16 scaled_dot_product_attention on the same tensors as a library yardstick."""
     import math
     import torch.nn.functional as F
     from ac4k_kernel_b200 import _cuda_ops, ops
+    from ac4k_kernel_b200.ops.attention import _int8_quantize
     res = {"unit": "TFLOP/s", "flops": "4 * B * H * N^2 * D", "cases": []}
     for (b, n, h, d, reps) in ((1, 16384, 16, 128, 10), (1, 75600, 40, 128, 3)):
         g = torch.Generator(device="cuda").manual_seed(9567)
         q, k, v = (torch.randn((b, n, h, d), dtype=torch.bfloat16, device="cuda", generator=g) for _ in range(3))
-        qq, qs, qg = ops.quantize(q, 1, 3, sf_layout="128x4")
-        kq, ks, kg = ops.quantize(k, 1, 3, sf_layout="128x4")
-        vq, vs, vg = ops.quantize(v, 3, 1, swizzle=True, sf_layout="128x4")
         out = torch.empty_like(q)
         view = out.permute(0, 2, 1, 3)
         flops = 4.0 * b * h * n * n * d
+        case = {"shape_BNHD": [b, n, h, d]}
+        qq, qs, qg = ops.quantize(q, 1, 3, sf_layout="128x4")
+        kq, ks, kg = ops.quantize(k, 1, 3, sf_layout="128x4")
+        vq, vs, vg = ops.quantize(v, 3, 1, swizzle=True, sf_layout="128x4")
         t_k = time_eager(lambda: _cuda_ops.mha_nvfp4_fwd(view, qq, qs, qg, kq, ks, kg, vq, vs, vg, 1 / math.sqrt(d)), reps)
         t_a = time_eager(lambda: ops.attention(q, k, v, layout="BNHD", precision="nvfp4", out=out), reps)
+        case.update({"kernel_ms": t_k * 1e3, "kernel_tflops": flops / t_k / 1e12,
+                     "attention_call_ms": t_a * 1e3, "attention_call_tflops": flops / t_a / 1e12})
+        del qq, kq, vq
+        q8, q8s = _int8_quantize(q, "BNHD", 1, BLOCK_SIZE=64)
+        k8, k8s = _int8_quantize(k, "BNHD", 1, BLOCK_SIZE=128)
+        v8, v8s = ops.quantize(v, 3, 1, swizzle=True, max_scale=2.25, precision="fp8e4m3")
+        t_k8 = time_eager(lambda: _cuda_ops.mha_int8_x_fp8_fwd(view, q8, q8s, 64, k8, k8s, 128, v8, v8s, 1 / math.sqrt(d)), reps)
+        t_a8 = time_eager(lambda: ops.attention(q, k, v, layout="BNHD", precision="int8+fp8e4m3", out=out), reps)
+        case.update({"int8_x_fp8_kernel_ms": t_k8 * 1e3, "int8_x_fp8_kernel_tflops": flops / t_k8 / 1e12,
+                     "int8_x_fp8_attention_call_ms": t_a8 * 1e3, "int8_x_fp8_attention_call_tflops": flops / t_a8 / 1e12})
+        del q8, k8, v8
         t_s = time_eager(lambda: F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)), reps)
-        res["cases"].append({"shape_BNHD": [b, n, h, d], "kernel_ms": t_k * 1e3, "kernel_tflops": flops / t_k / 1e12,
-                             "attention_call_ms": t_a * 1e3, "attention_call_tflops": flops / t_a / 1e12,
-                             "torch_sdpa_bf16_ms": t_s * 1e3, "torch_sdpa_bf16_tflops": flops / t_s / 1e12})
-        del q, k, v, qq, kq, vq, out
-    res["note"] = ("bounded by the softmax (16 ex2 per clock per SM = 1024 cycles per 128 x 128 scores), not by the "
-                   "four-bit MMAs; inputs are larger than L2 at both shapes")
+        case.update({"torch_sdpa_bf16_ms": t_s * 1e3, "torch_sdpa_bf16_tflops": flops / t_s / 1e12})
+        res["cases"].append(case)
+        del q, k, v, out
+    res["note"] = ("both kernels are bounded by the softmax (16 ex2 per clock per SM = 1024 cycles per 128 x 128 scores), not by "
+                   "the four- or eight-bit MMAs; inputs are larger than L2 at both shapes")
     return res
 
 
