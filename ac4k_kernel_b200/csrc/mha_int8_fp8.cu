@@ -18,7 +18,7 @@
 // FMA pipe.  Because of the 7.5 offset a row's maximum rarely moves after the first tiles, so O is rarely rescaled.
 //
 // Supported: head dimensions up to 128 for Q/K (rows padded to a multiple of 16 bytes by the quantiser) and up to 128
-// for V; K quantised in blocks of 128 tokens (the reference's default; the key tile), Q in blocks of 16 to 128.
+// for V; Q and K quantised in blocks of 16, 32, 64 or 128 tokens (the reference's defaults: 64 and 128).
 #include "gemm_common.cuh"
 #include "mha_common.cuh"
 
@@ -39,12 +39,13 @@ static_assert(SMEM_BYTES <= 227 * 1024, "shared memory overflow");
 }  // namespace mha8
 
 struct Mha8Args {
-  const float *q_sf, *k_sf, *v_sf;      // [B, H, ceil(Nq / q_block)], [B, H, ceil(Nkv / 128)], [B, H, align16(Dv)]
+  const float *q_sf, *k_sf, *v_sf;      // [B, H, ceil(Nq / q_block)], [B, H, ceil(Nkv / k_block)], [B, H, align16(Dv)]
   void *O;
   int64_t o_b, o_h, o_n, o_d;           // strides of O in elements
   int B, H, Nq, Nkv, Dv;
   int q_blocks, kv_tiles;               // ceil(Nq / 128), ceil(Nkv / 128)
   int q_block, q_nblk, v_pad;           // tokens per Q scale, Q scales per head, align16(Dv)
+  int k_shift, k_nblk;                  // log2 of the tokens per K scale (4 .. 7), K scales per head
   float sm_scale_log2;                  // sm_scale * log2(e)
   unsigned int *status;
   unsigned long long wait_ns;
@@ -80,6 +81,8 @@ __device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
   return r;
 }
 
+// K128: K is quantised in blocks of 128 tokens (the reference's default): one scale per key tile instead of one per 16 keys.
+template <bool K128>
 __global__ void __launch_bounds__(mha8::kThreads, 1)
 mha_int8_fp8_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                         const __grid_constant__ CUtensorMap tma_v, const Mha8Args p) {
@@ -237,7 +240,7 @@ mha_int8_fp8_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_
     const int n_row = (2 * qt + g) * BQ + row_l;                 // query row in the head
     // scores in units of log2: s = int32 * c_row * k_scale[tile]
     const float c_row = p.sm_scale_log2 * __ldg(p.q_sf + bh * p.q_nblk + min(n_row / p.q_block, p.q_nblk - 1));
-    const float *k_sf = p.k_sf + bh * p.kv_tiles;
+    const float *k_sf = p.k_sf + bh * p.k_nblk;
     const uint32_t p_row0 = sP + 2 * g * TILE_BYTES + row_l * 128;
     const uint32_t p_xor = (uint32_t)(row_l & 7) << 4;           // 128-byte swizzle: 16-byte chunk ^ (row % 8)
     const uint32_t my_s_full = s_full + 8 * g, my_p_full = p_full + 8 * g, my_o_done = o_done + 16 * g;
@@ -272,8 +275,18 @@ mha_int8_fp8_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_
           if (64 + i >= ncols) hi[i] = 0xff800000u;
         }
       }
-      // c >= 0 (scales and sm_scale are; the host rejects a negative sm_scale); the floor keeps -inf * c = -inf
-      const float c = fmaxf(c_row * __ldg(k_sf + j), 1.17549435e-38f);
+      // Scale of every 16 keys of the tile (K is quantised in blocks of 16 to 128 tokens: one to eight scales per tile).
+      // c >= 0 (scales and sm_scale are; the host rejects a negative sm_scale); the floor keeps -inf * c = -inf.
+      float c16[8];
+      if (K128) {
+        const float c = fmaxf(c_row * __ldg(k_sf + j), 1.17549435e-38f);
+#pragma unroll
+        for (int bk = 0; bk < 8; ++bk) c16[bk] = c;
+      } else {
+#pragma unroll
+        for (int bk = 0; bk < 8; ++bk)
+          c16[bk] = fmaxf(c_row * __ldg(k_sf + min((j * BKV + 16 * bk) >> p.k_shift, p.k_nblk - 1)), 1.17549435e-38f);
+      }
       float bs[8];
 #pragma unroll
       for (int bk = 0; bk < 8; ++bk) {
@@ -283,8 +296,10 @@ mha_int8_fp8_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_
         const float t0 = max3(v[0], v[1], v[2]), t1 = max3(v[3], v[4], v[5]), t2 = max3(v[6], v[7], v[8]);
         const float t3 = max3(v[9], v[10], v[11]), t4 = max3(v[12], v[13], v[14]);
         bs[bk] = fmaxf(max3(t0, t1, t2), max3(t3, t4, v[15]));
+        if (!K128) bs[bk] *= c16[bk];
       }
-      const float rowmax = fmaxf(max3(bs[0], bs[1], bs[2]), max3(bs[3], bs[4], max3(bs[5], bs[6], bs[7]))) * c;
+      float rowmax = fmaxf(max3(bs[0], bs[1], bs[2]), max3(bs[3], bs[4], max3(bs[5], bs[6], bs[7])));
+      if (K128) rowmax *= c16[0];
       const float m_new = fmaxf(m, rowmax - kExpOffset);
       if (j > 0 && __any_sync(0xffffffffu, m_new != m)) {
         // a maximum of this warp's rows moved: O is rescaled, once the previous tile's P V is complete
@@ -317,7 +332,7 @@ mha_int8_fp8_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_
       // holds key ((n / 2) % 2 * 4 + n / 4) * 2 + n % 2.
       const uint32_t p_row = p_row0 + (j & 1) * TILE_BYTES;
       float2 lsum[4];
-      const float2 c2 = make_float2(c, c), negm2 = make_float2(-m, -m);
+      const float2 negm2 = make_float2(-m, -m);
 #pragma unroll
       for (int gg = 0; gg < 4; ++gg) {          // 32 keys = two 16-byte chunks of P
         float2 pr[16];
@@ -326,7 +341,8 @@ mha_int8_fp8_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_
         for (int n = 0; n < 32; n += 2) {
           const int n16 = n & 15;
           const int i = 32 * gg + (n & 16) + (((n16 >> 1) & 1) * 4 + (n16 >> 2)) * 2;     // keys held at positions n, n + 1
-          const float2 e = ffma2(make_float2(__uint_as_float(AC4K_S(i)), __uint_as_float(AC4K_S(i + 1))), c2, negm2);
+          const float cc = c16[2 * gg + (n >> 4)];
+          const float2 e = ffma2(make_float2(__uint_as_float(AC4K_S(i)), __uint_as_float(AC4K_S(i + 1))), make_float2(cc, cc), negm2);
           // every fourth pair on the FMA pipe, the others on the ex2 pipe
           pr[n >> 1] = ((n >> 1) & 3) == 1 ? exp2_fma_pipe(e) : make_float2(ex2_approx(e.x), ex2_approx(e.y));
           lsum[gg] = fadd2(lsum[gg], pr[n >> 1]);
@@ -412,9 +428,9 @@ extern "C" int ac4k_mha_int8_x_fp8_fwd(void *O, const int64_t o_stride[4], const
   if (!(sm_scale >= 0.0f)) return fail(AC4K_ERR_UNSUPPORTED, "sm_scale must be >= 0 (the row maximum is taken before scaling)");
   if (Dqk <= 0 || Dqk > 128 || Dv <= 0 || Dv > 128)
     return fail(AC4K_ERR_UNSUPPORTED, "head dimensions up to 128 are built (Dqk = %lld, Dv = %lld)", (long long)Dqk, (long long)Dv);
-  if (k_block != 128) return fail(AC4K_ERR_UNSUPPORTED, "K must be quantised in blocks of 128 tokens (the key tile), got %lld", (long long)k_block);
-  if (q_block < 16 || q_block > 128 || (q_block & (q_block - 1)))
-    return fail(AC4K_ERR_UNSUPPORTED, "Q must be quantised in blocks of 16, 32, 64 or 128 tokens, got %lld", (long long)q_block);
+  if (k_block < 16 || k_block > 128 || (k_block & (k_block - 1)) || q_block < 16 || q_block > 128 || (q_block & (q_block - 1)))
+    return fail(AC4K_ERR_UNSUPPORTED, "Q and K must be quantised in blocks of 16, 32, 64 or 128 tokens, got %lld and %lld", (long long)q_block,
+                (long long)k_block);
   if (B > 65535 || H > 65535 || B * H * Nq > (1ll << 31) - 256 || B * H * Nkv > (1ll << 31) - 256) return fail(AC4K_ERR_SHAPE, "dimension too large");
   for (const void *ptr : {Q, K, V})
     if (reinterpret_cast<uintptr_t>(ptr) & 15) return fail(AC4K_ERR_ALIGN, "Q, K and V must be 16-byte aligned");
@@ -439,13 +455,16 @@ extern "C" int ac4k_mha_int8_x_fp8_fwd(void *O, const int64_t o_stride[4], const
   a.q_block = (int)q_block;
   a.q_nblk = (int)ceil_div(Nq, q_block);
   a.v_pad = (int)align_up(Dv, 16);
+  a.k_shift = k_block == 16 ? 4 : (k_block == 32 ? 5 : (k_block == 64 ? 6 : 7));
+  a.k_nblk = (int)ceil_div(Nkv, k_block);
   a.sm_scale_log2 = sm_scale * 1.4426950408889634f;
   a.status = status;
   a.wait_ns = kWaitTimeoutNs;
   static PerDevice<int> attr_set;
   int unused = 0;
   if (int e = attr_set.get(&unused, [&](int &v) {
-        AC4K_CUDA_TRY(cudaFuncSetAttribute(mha_int8_fp8_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mha8::SMEM_BYTES));
+        AC4K_CUDA_TRY(cudaFuncSetAttribute(mha_int8_fp8_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, mha8::SMEM_BYTES));
+        AC4K_CUDA_TRY(cudaFuncSetAttribute(mha_int8_fp8_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, mha8::SMEM_BYTES));
         v = 1;
         return 0;
       }))
@@ -460,6 +479,9 @@ extern "C" int ac4k_mha_int8_x_fp8_fwd(void *O, const int64_t o_stride[4], const
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  AC4K_CUDA_TRY(cudaLaunchKernelEx(&cfg, mha_int8_fp8_fwd_kernel, tq, tk, tv, a));
+  if (k_block == 128)
+    AC4K_CUDA_TRY(cudaLaunchKernelEx(&cfg, mha_int8_fp8_fwd_kernel<true>, tq, tk, tv, a));
+  else
+    AC4K_CUDA_TRY(cudaLaunchKernelEx(&cfg, mha_int8_fp8_fwd_kernel<false>, tq, tk, tv, a));
   return 0;
 }

@@ -27,7 +27,7 @@
 // group starts the exponentials of a tile only when the other group is at least half way through its own.
 // Tensor memory: S 128 + O_A 128 + O_B 128 + scales 40 columns of 512.
 //
-// Supported: head dimensions in (64, 128] (padded to 128 by the quantiser); block scales in the tiled layout
+// Supported: head dimensions up to 128 (padded to 64 or 128 by the quantiser); block scales in the tiled layout
 // [.., 128-row block, K/64, 32 x 16 B] or in the reference's [.., K/64, align16(rows), 4]; V quantised along the keys (cross dimension = head dimension) with the
 // reference's K permutation (quantize(v, 3, N_dim, swizzle=True), python/ac4k_kernel/ops/attention.py:113-118):
 // P is written in the same key order, so scale blocks of P and V cover the same 16 keys as in the reference.
@@ -66,6 +66,7 @@ struct MhaArgs {
   int B, H, Nq, Nkv, Dv;
   int q_blocks, kv_tiles;               // ceil(Nq / 128), ceil(Nkv / 128): 128-row blocks of Q and of the keys
   int v_k64;                            // align64(Nkv) / 64: K = 64 steps of V^T that exist
+  int nkq;                              // align64(Dqk) / 64: K = 64 steps of the head dimension (1 or 2)
   int q_pad, k_pad, v_pad;              // align16 of Nq, Nkv, Dv: scale rows per K step in the reference's layout
   float sm_scale;
   unsigned int *status;
@@ -183,11 +184,11 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     // ------------------------------------------------------------------ TMA producer
     const uint32_t el = elect_one();
     const int ng = both ? 2 : 1;
-    mbar_arrive_expect_tx_if(el, q_full, ng * (Q_BYTES + (SF_TILED ? SF_BYTES : 0)));
+    mbar_arrive_expect_tx_if(el, q_full, ng * (Q_BYTES + (SF_TILED ? p.nkq * 512 : 0)));
     for (int g = 0; g < ng; ++g) {
       tma_load_2d_if(el, sQ + g * Q_BYTES, &tma_q, 0, q_row0 + g * BQ, q_full);
       if (SF_TILED)
-        bulk_load_1d_if(el, sSFQ + g * SF_BYTES, p.sfq + ((bh * p.q_blocks + 2 * qt + g) * 2) * 512, SF_BYTES, q_full);
+        bulk_load_1d_if(el, sSFQ + g * SF_BYTES, p.sfq + ((bh * p.q_blocks + 2 * qt + g) * p.nkq) * 512, p.nkq * 512, q_full);
     }
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
@@ -197,11 +198,11 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       const uint32_t st = sKV + s * STAGE_BYTES, fb = kv_full + 8 * s;
       // V^T: D rows x 128 keys; of the tile's two K = 64 steps only those below align64(Nkv) exist
       const int nk = min(2, p.v_k64 - 2 * j);
-      mbar_arrive_expect_tx_if(el, fb, K_BYTES + V_BYTES + (SF_TILED ? SF_BYTES + nk * 512 : 0));
+      mbar_arrive_expect_tx_if(el, fb, K_BYTES + V_BYTES + (SF_TILED ? (p.nkq + nk) * 512 : 0));
       tma_load_2d_if(el, st, &tma_k, 0, k_row0 + j * BKV, fb);
       tma_load_2d_if(el, st + K_BYTES, &tma_v, j * 64, v_row0, fb);
       if (SF_TILED) {
-        bulk_load_1d_if(el, st + K_BYTES + V_BYTES, p.sfk + ((bh * p.kv_tiles + j) * 2) * 512, SF_BYTES, fb);
+        bulk_load_1d_if(el, st + K_BYTES + V_BYTES, p.sfk + ((bh * p.kv_tiles + j) * p.nkq) * 512, p.nkq * 512, fb);
         bulk_load_1d_if(el, st + K_BYTES + V_BYTES + SF_BYTES, p.sfv + (bh * p.v_k64 + 2 * j) * 512, nk * 512, fb);
       }
     }
@@ -221,13 +222,13 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       const uint64_t sfqdesc = make_smem_desc(sSFQ + g * SF_BYTES, 0, 128, kSwizzleNone);
       const uint64_t sfkdesc = make_smem_desc(st + K_BYTES + V_BYTES, 0, 128, kSwizzleNone);
       const uint32_t t_sfq = tmem_base + SFQ_COL + 8 * g;
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
+      // (a head dimension of 64 or less is one K step: the rows are 32 bytes, the upper half of the 64-byte tile rows is
+      // filled with zeros by TMA and never multiplied)
+      for (int i = 0; i < p.nkq; ++i) {
         if (j == 0) tmem_cp_32x128b_warpx4_if(el, t_sfq + 4 * i, sfqdesc + 32 * i);
         tmem_cp_32x128b_warpx4_if(el, tmem_base + SFK_COL + 4 * i, sfkdesc + 32 * i);
       }
-#pragma unroll
-      for (int i = 0; i < 2; ++i)
+      for (int i = 0; i < p.nkq; ++i)
         mma_mxf4nvf4_if(el, t_s, qdesc + 2 * i, kdesc + 2 * i, idesc, t_sfq + 4 * i, tmem_base + SFK_COL + 4 * i, i > 0 ? 1u : 0u);
       tc_commit_if(el, s_full + 8 * g);
     };
@@ -313,11 +314,11 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         }
         st_shared_v4u(dst + lane * 16, w[0], w[1], w[2], w[3]);
       };
-      const uint8_t *q_base = p.sfq + bh * 2 * (int64_t)p.q_pad * 4;
-      const uint8_t *k_base = p.sfk + bh * 2 * (int64_t)p.k_pad * 4;
+      const uint8_t *q_base = p.sfq + bh * p.nkq * (int64_t)p.q_pad * 4;
+      const uint8_t *k_base = p.sfk + bh * p.nkq * (int64_t)p.k_pad * 4;
       const uint8_t *v_base = p.sfv + bh * (int64_t)p.v_k64 * p.v_pad * 4;
       for (int g = 0; g < (both ? 2 : 1); ++g)
-        for (int i = 0; i < 2; ++i) put_chunk(sSFQ + g * SF_BYTES + i * 512, q_base, i, p.q_pad, (2 * qt + g) * BQ);
+        for (int i = 0; i < p.nkq; ++i) put_chunk(sSFQ + g * SF_BYTES + i * 512, q_base, i, p.q_pad, (2 * qt + g) * BQ);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(q_full);
@@ -328,7 +329,7 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         if (!ok) break;
         const uint32_t st = sKV + s * STAGE_BYTES + K_BYTES + V_BYTES;
         const int nk = min(2, p.v_k64 - 2 * j);
-        for (int i = 0; i < 2; ++i) put_chunk(st + i * 512, k_base, i, p.k_pad, j * BKV);
+        for (int i = 0; i < p.nkq; ++i) put_chunk(st + i * 512, k_base, i, p.k_pad, j * BKV);
         for (int i = 0; i < nk; ++i) put_chunk(st + SF_BYTES + i * 512, v_base, 2 * j + i, p.v_pad, 0);
         fence_proxy_async_smem();
         __syncwarp();
@@ -552,8 +553,8 @@ extern "C" int ac4k_mha_nvfp4_fwd(void *O, const int64_t o_stride[4], const void
   if (B == 0 || H == 0 || Nq == 0) return 0;
   if (Nkv == 0) return fail(AC4K_ERR_SHAPE, "attention over zero keys");
   if (!(sm_scale >= 0.0f)) return fail(AC4K_ERR_UNSUPPORTED, "sm_scale must be >= 0 (the row maximum is taken before scaling)");
-  if (Dqk <= 64 || Dqk > 128 || Dv <= 64 || Dv > 128)
-    return fail(AC4K_ERR_UNSUPPORTED, "head dimensions in (64, 128] are built (Dqk = %lld, Dv = %lld)", (long long)Dqk, (long long)Dv);
+  if (Dqk <= 0 || Dqk > 128 || Dv <= 0 || Dv > 128)
+    return fail(AC4K_ERR_UNSUPPORTED, "head dimensions up to 128 are built (Dqk = %lld, Dv = %lld)", (long long)Dqk, (long long)Dv);
   if (sf_layout != AC4K_SF_TILE128X4 && sf_layout != AC4K_SF_AC4K) return fail(AC4K_ERR_ENUM, "unknown scale layout %d", sf_layout);
   if (B > 65535 || H > 65535 || B * H * Nq > (1ll << 31) - 256 || B * H * Nkv > (1ll << 31) - 256)
     return fail(AC4K_ERR_SHAPE, "dimension too large");
@@ -566,9 +567,10 @@ extern "C" int ac4k_mha_nvfp4_fwd(void *O, const int64_t o_stride[4], const void
   if (!status) return fail(AC4K_ERR_DEVICE, "cannot resolve the device status word");
   const int64_t v_k64 = ceil_div(Nkv, 64);
   CUtensorMap tq, tk, tv;
-  // Q, K: [B*H*N, 64 bytes] (head dimension padded to 128 by the quantiser); V^T: [B*H*Dv, align64(Nkv)/2 bytes]
-  if (int e = get_tmap64(Q, B * H * Nq, 64, mha::BQ, &tq)) return e;
-  if (int e = get_tmap64(K, B * H * Nkv, 64, mha::BKV, &tk)) return e;
+  // Q, K: [B*H*N, 32 or 64 bytes] (head dimension padded to 64 or 128 by the quantiser); V^T: [B*H*Dv, align64(Nkv)/2 bytes]
+  const int64_t nkq = ceil_div(Dqk, 64);
+  if (int e = get_tmap64(Q, B * H * Nq, nkq * 32, mha::BQ, &tq)) return e;
+  if (int e = get_tmap64(K, B * H * Nkv, nkq * 32, mha::BKV, &tk)) return e;
   if (int e = get_tmap64(V, B * H * Dv, v_k64 * 32, 128, &tv)) return e;
   MhaArgs a = {};
   a.sfq = static_cast<const uint8_t *>(Q_sf);
@@ -581,6 +583,7 @@ extern "C" int ac4k_mha_nvfp4_fwd(void *O, const int64_t o_stride[4], const void
   a.q_blocks = (int)ceil_div(Nq, 128);
   a.kv_tiles = (int)ceil_div(Nkv, 128);
   a.v_k64 = (int)v_k64;
+  a.nkq = (int)nkq;
   a.q_pad = (int)align_up(Nq, 16);
   a.k_pad = (int)align_up(Nkv, 16);
   a.v_pad = (int)align_up(Dv, 16);

@@ -169,8 +169,7 @@ int ac4k_linear_nvfp4_requant(void *out_fp4, void *out_sf, const float *out_gs, 
  *   copied as it is; the reference's is re-ordered by one more warp of the kernel);
  *   *_gs: device fp32 scalars; O: bf16, element (b, h, n, d) at O + b*o_stride[0] + h*o_stride[1] + n*o_stride[2] +
  *   d*o_stride[3] (elements), so both the [B, H, N, D] and the permuted [B, N, H, D] outputs of the reference work.
- * Built for 64 < Dqk <= 128 and 64 < Dv <= 128 (the reference allows up to 128) and sm_scale >= 0; other head
- * dimensions return AC4K_ERR_UNSUPPORTED. */
+ * Built for Dqk, Dv <= 128 (as the reference) and sm_scale >= 0. */
 int ac4k_mha_nvfp4_fwd(void *O, const int64_t o_stride[4], const void *Q, const void *Q_sf, const float *Q_gs,
                        const void *K, const void *K_sf, const float *K_gs, const void *V, const void *V_sf,
                        const float *V_gs, int64_t B, int64_t H, int64_t Nq, int64_t Nkv, int64_t Dqk, int64_t Dv,
@@ -193,7 +192,7 @@ int ac4k_quantize_int8_block(void *out, float *scale, const void *in, const int6
  *   K_sf: fp32 [B, H, ceil(Nkv / k_block)]; V: e4m3 [B, H, Dv, align16(Nkv)], quantised along the keys with the FP8 K
  *   permutation (swizzle = 1) and max_scale 2.25, V_sf: fp32 [B, H, align16(Dv)]; O: bf16 by element strides as in
  *   ac4k_mha_nvfp4_fwd.
- * Built for Dqk, Dv <= 128, k_block = 128 (the reference's default), q_block in {16, 32, 64, 128}, sm_scale >= 0; the
+ * Built for Dqk, Dv <= 128, q_block and k_block in {16, 32, 64, 128} (the reference's defaults: 64 and 128), sm_scale >= 0; the
  * P V products accumulate in fp32 (the reference: fp16 within a key tile). */
 int ac4k_mha_int8_x_fp8_fwd(void *O, const int64_t o_stride[4], const void *Q, const float *Q_sf, int64_t q_block,
                             const void *K, const float *K_sf, int64_t k_block, const void *V, const float *V_sf,

@@ -59,6 +59,7 @@ SDP_CASES = [
     (1, 1, 2, 128, "BNHD"),
     (1, 1000, 2, 100, "BNHD"),
     (1, 4096, 2, 128, "BHND"),
+    (2, 512, 4, 64, "BNHD"),
 ]
 
 
@@ -83,6 +84,9 @@ ORACLE_CASES = [
     (1, 1, 40, 64, 128, 128),        # a single key tile, half of it
     (1, 2, 130, 190, 96, 80),        # head dimensions below 128 (padded by the quantiser)
     (1, 1, 128, 2048, 128, 128),
+    (2, 2, 150, 300, 64, 64),        # one K = 64 step over the head dimension
+    (1, 3, 100, 100, 48, 16),
+    (1, 2, 260, 140, 128, 32),
 ]
 
 
@@ -162,8 +166,8 @@ def test_argument_checks():
     with pytest.raises(RuntimeError):      # scale layouts must agree
         q5 = quantize(q, 2, 3)[1]
         ops.mha_nvfp4_fwd(o, qq, q5, qg, kq, ks, kg, vq, vs, vg, 0.1)
-    with pytest.raises(RuntimeError):      # head dimension 64: a valid call in the reference, not built here
-        q64, k64, v64 = _qkv(1, 64, 64, 1, 64, 64, "BHND", seed=2)
-        attention(q64, k64, v64, layout="BHND", precision="nvfp4")
+    with pytest.raises(RuntimeError):      # head dimension above 128
+        q256, k256, v256 = _qkv(1, 64, 64, 1, 256, 256, "BHND", seed=2)
+        attention(q256, k256, v256, layout="BHND", precision="nvfp4")
     with pytest.raises(AssertionError):
         attention(q, k, v, layout="BHND", precision="fp16")

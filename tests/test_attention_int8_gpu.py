@@ -120,6 +120,21 @@ def test_kernel_against_oracle_on_the_same_operands(B, H, Nq, Nkv, Dqk, Dv, layo
     torch.testing.assert_close(got, want.float(), atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("q_block,k_block", [(16, 16), (32, 64), (128, 32), (64, 64)])
+def test_other_quantisation_block_sizes(q_block, k_block):
+    ops, _, quantize, int8_quantize = _ops()
+    q, k, v = _qkv(2, 300, 333, 2, 128, 128, "BHND", seed=q_block + k_block)
+    k = k * torch.linspace(0.2, 3.0, 333, device="cuda").bfloat16()[None, None, :, None]     # scales that differ along the keys
+    qq, qs = int8_quantize(q, "BHND", 2, BLOCK_SIZE=q_block)
+    kq, ks = int8_quantize(k, "BHND", 2, BLOCK_SIZE=k_block)
+    vq, vs = quantize(v, 3, 2, swizzle=True, max_scale=2.25, precision="fp8e4m3")
+    out = torch.empty((2, 2, 300, 128), dtype=torch.bfloat16, device="cuda")
+    ops.mha_int8_x_fp8_fwd(out, qq, qs, q_block, kq, ks, k_block, vq, vs, 128 ** -0.5)
+    want = E.mha_int8_x_fp8_ref(qq, qs, q_block, kq, ks, k_block, vq, vs, 128 ** -0.5)
+    rel = ((out.float() - want.float()).norm() / want.float().norm()).item()
+    assert rel < 2e-3, rel
+
+
 def test_fp16_tile_accumulation_of_the_reference_is_within_the_same_bound():
     """The reference rounds each key tile's P V to fp16 before adding it to O; the restatement can do both."""
     g = torch.Generator().manual_seed(5)
@@ -145,9 +160,8 @@ def test_out_argument_repeatability_and_checks():
     o = torch.empty((2, 2, 256, 128), dtype=torch.bfloat16, device="cuda")
     with pytest.raises(RuntimeError):      # scale count does not match the block size
         ops.mha_int8_x_fp8_fwd(o, qq, qs, 128, kq, ks, 128, vq, vs, 0.1)
-    with pytest.raises(RuntimeError):      # K in blocks of 64: valid in the reference, not built here
-        k64, ks64 = int8_quantize(k, "BNHD", 1, BLOCK_SIZE=64)
-        ops.mha_int8_x_fp8_fwd(o, qq, qs, 64, k64, ks64, 64, vq, vs, 0.1)
+    with pytest.raises(RuntimeError):      # a block size that is not a power of two
+        ops.mha_int8_x_fp8_fwd(o, qq, qs, 64, kq, ks[..., :1].expand(2, 2, 6).contiguous(), 48, vq, vs, 0.1)
     with pytest.raises(RuntimeError):
         ops.mha_int8_x_fp8_fwd(o.float(), qq, qs, 64, kq, ks, 128, vq, vs, 0.1)
     with pytest.raises(RuntimeError):

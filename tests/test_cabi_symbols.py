@@ -64,9 +64,9 @@ def test_argument_errors_without_gpu():
     assert LIB.ac4k_quantize_int8_block(8, 8, 8, sh, sh, 48, None) == -2         # block not a power of two
     assert LIB.ac4k_quantize_int8_block(None, 8, 8, sh, sh, 64, None) == -1
     o4 = (ctypes.c_int64 * 4)(1, 1, 1, 1)
-    assert LIB.ac4k_mha_int8_x_fp8_fwd(16, o4, 16, 16, 64, 16, 16, 64, 16, 16, 1, 1, 8, 8, 128, 128, 0.1, None) == -5   # K block 64
+    assert LIB.ac4k_mha_int8_x_fp8_fwd(16, o4, 16, 16, 64, 16, 16, 48, 16, 16, 1, 1, 8, 8, 128, 128, 0.1, None) == -5   # K block 48
     assert LIB.ac4k_mha_int8_x_fp8_fwd(16, o4, 16, 16, 64, 16, 16, 128, 16, 16, 1, 1, 8, 8, 256, 128, 0.1, None) == -5  # head dim 256
-    assert LIB.ac4k_mha_nvfp4_fwd(16, o4, 16, 16, 16, 16, 16, 16, 16, 16, 16, 1, 1, 8, 8, 64, 128, 0.1, 1, None) == -5
+    assert LIB.ac4k_mha_nvfp4_fwd(16, o4, 16, 16, 16, 16, 16, 16, 16, 16, 16, 1, 1, 8, 8, 192, 128, 0.1, 1, None) == -5
     assert LIB.ac4k_mha_nvfp4_fwd(16, o4, 16, 16, 16, 16, 16, 16, 16, 16, 16, 1, 1, 8, 0, 128, 128, 0.1, 1, None) == -2
     assert LIB.ac4k_mha_nvfp4_fwd(16, o4, 16, 16, 16, 16, 16, 16, 16, 16, 16, 1, 1, 8, 8, 128, 128, -1.0, 1, None) == -5
     bad = (ctypes.c_int64 * 4)(1, 1, -3, 64)
