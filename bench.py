@@ -804,6 +804,20 @@ def run_profile_case(case):
         out = torch.empty_like(x)
         for _ in range(3):
             ops.rope3d(x, grid, freqs, out)
+    elif case in ("mha-int8", "quant-attn"):
+        import math
+        from ac4k_kernel_b200.ops.attention import _int8_quantize
+        g = torch.Generator(device="cuda").manual_seed(9567)
+        n, h = (8192, 16) if case == "mha-int8" else (75600, 40)
+        q, k, v = (torch.randn((1, n, h, 128), dtype=torch.bfloat16, device="cuda", generator=g) for _ in range(3))
+        for _ in range(3):
+            q8, q8s = _int8_quantize(q, "BNHD", 1, BLOCK_SIZE=64)
+            k8, k8s = _int8_quantize(k, "BNHD", 1, BLOCK_SIZE=128)
+            v8, v8s = ops.quantize(v, 3, 1, swizzle=True, max_scale=2.25, precision="fp8e4m3")
+        if case == "mha-int8":
+            out = torch.empty_like(q)
+            for _ in range(3):
+                _cuda_ops.mha_int8_x_fp8_fwd(out.permute(0, 2, 1, 3), q8, q8s, 64, k8, k8s, 128, v8, v8s, 1 / math.sqrt(128))
     elif case == "mha":
         import math
         g = torch.Generator(device="cuda").manual_seed(9567)
@@ -835,7 +849,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--profile-case", default=None,
-                    choices=["gemm-c2", "gemm-8k", "gemm-decode", "mha", "rope3d", "quant-c4", "quant-c4-fp8", "quant-c4-int8"],
+                    choices=["gemm-c2", "gemm-8k", "gemm-decode", "mha", "mha-int8", "quant-attn", "rope3d", "quant-c4", "quant-c4-fp8", "quant-c4-int8"],
                     help="run one small workload three times and exit (for ncu)")
     args = ap.parse_args()
     if args.profile_case:
