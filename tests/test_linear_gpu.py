@@ -295,13 +295,14 @@ def test_repeatable_under_requantisation(ops):
 
 
 @pytest.mark.parametrize("layout", ["ac4k", "128x4"])
-@pytest.mark.parametrize("m,n,k,ldd,col_off,odt,with_bias", [
-    (512, 512, 1024, 1536, 512, torch.bfloat16, False),
-    (300, 264, 256, 800, 8, torch.bfloat16, True),        # ragged tiles, 16-byte aligned rows only
-    (128, 256, 512, 256, 0, torch.float16, False),        # M of a single row tile, dense destination
+@pytest.mark.parametrize("m,n,k,ldd,col_off,odt,with_bias,n_dst", [
+    (512, 512, 1024, 1536, 512, torch.bfloat16, False, 3),
+    (300, 264, 256, 800, 8, torch.bfloat16, True, 3),        # ragged tiles, 16-byte aligned rows only
+    (128, 256, 512, 256, 0, torch.float16, False, 3),        # M of a single row tile, dense destination
+    (1024, 512, 512, 4096, 3584, torch.bfloat16, False, 8),  # the largest number of destinations (an 8-GPU node), last column block
 ])
-def test_gather_epilogue_on_one_gpu(ops, layout, m, n, k, ldd, col_off, odt, with_bias):
-    """The fused all-gather epilogue with all destinations on one GPU: three [M, ldd] buffers get
+def test_gather_epilogue_on_one_gpu(ops, layout, m, n, k, ldd, col_off, odt, with_bias, n_dst):
+    """The fused all-gather epilogue with all destinations on one GPU: n_dst [M, ldd] buffers get
     columns [col_off, col_off + N) equal to the plain GEMM's output; the other columns stay as
     they were."""
     from ac4k_kernel_b200 import _cuda_ops
@@ -312,7 +313,7 @@ def test_gather_epilogue_on_one_gpu(ops, layout, m, n, k, ldd, col_off, odt, wit
     bias = gaussian((1, n), seed=5).to(odt).cuda() if with_bias else None
     plain = torch.empty((m, n), dtype=odt, device="cuda")
     _cuda_ops.linear_nvfp4(plain, a4, asf, ag, b4, bsf, bg, bias)
-    bufs = [torch.full((m, ldd), -7.0, dtype=odt, device="cuda") for _ in range(3)]
+    bufs = [torch.full((m, ldd), -7.0, dtype=odt, device="cuda") for _ in range(n_dst)]
     _cuda_ops.linear_nvfp4_gather([t.data_ptr() for t in bufs], ldd, col_off, bufs[0], a4, asf, ag, b4, bsf, bg, bias)
     torch.cuda.synchronize()
     for t in bufs:
