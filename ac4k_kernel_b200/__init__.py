@@ -1,5 +1,6 @@
-"""ac4k_kernel_b200: the NVFP4 linear path of ac4k_kernel (quantize -> block-scaled GEMM),
-written for B200 (sm_100a).  Layout of this module mirrors python/ac4k_kernel/__init__.py.
+"""ac4k_kernel_b200: the operators of ac4k_kernel written for B200 (sm_100a): the NVFP4 linear path
+(quantize -> block-scaled GEMM), NVFP4 and INT8 x FP8 attention, 3-D RoPE.  Layout of this module mirrors
+python/ac4k_kernel/__init__.py.
 
 The compiled backend is the C-ABI library `libac4k_b200.so`; importing this package fails
 if it is not built (there is no other backend and no CPU fallback).

@@ -1,5 +1,5 @@
-"""Operators of the NVFP4 linear path and NVFP4 attention (mirrors python/ac4k_kernel/ops/__init__.py
-for the names this build covers)."""
+"""quantize, linear, attention, rope3d: mirrors python/ac4k_kernel/ops/__init__.py (SparseLinearAttention, a
+Triton/PyTorch module on top of `attention`, is not part of this package)."""
 from .attention import attention
 from .linear import linear, linear_nvfp4, linear_requant
 from .rope_3d import rope3d

@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the NVFP4 linear path on B200.
+"""Benchmark of the NVFP4 linear path on B200 (headline), with legs for the attention kernels and RoPE.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--profile-case NAME]
 

@@ -1,8 +1,9 @@
 /*
- * ac4k_b200.h - C ABI of the B200 (sm_100a) NVFP4 linear path.
+ * ac4k_b200.h - C ABI of ac4k_kernel's operators on B200 (sm_100a): the NVFP4 linear path
+ * (quantisers and block-scaled GEMM), the two attention kernels and 3-D RoPE.
  *
  * A shared library exporting these symbols replaces the compiled half of ac4k_kernel's
- * `_cuda_ops` extension for the quantise -> NVFP4 GEMM path.  Every entry point takes raw
+ * `_cuda_ops` extension (all seven functions of lib/cuda_bindings.cc:37-97).  Every entry point takes raw
  * device pointers, sizes and a CUDA stream; no torch types cross the boundary.  The file
  * and line given with each declaration is the reference interface it stands in for
  * (paths inside the ac4k_kernel project).
