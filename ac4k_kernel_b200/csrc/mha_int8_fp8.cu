@@ -14,8 +14,7 @@
 // S by four tcgen05.mma kind::i8 (M 128, N 128, K 32) into int32 columns, P V by four kind::f8f6f4 from the P tile the
 // group wrote to shared memory (128-byte-swizzled K-major, in the key order of the reference's V quantiser: every 16
 // keys viewed as [2, 4, 2] and transposed to [4, 2, 2]).  The exponentials bound the kernel (16 ex2 per clock per SM);
-// the groups are kept out of step by the same token, and a quarter of the exponentials run as a polynomial on the
-// FMA pipe.  Because of the 7.5 offset a row's maximum rarely moves after the first tiles, so O is rarely rescaled.
+// a quarter of the exponentials run as a polynomial on the FMA pipe.  Because of the 7.5 offset a row's maximum rarely moves after the first tiles, so O is rarely rescaled.
 //
 // Supported: head dimensions up to 128 for Q/K (rows padded to a multiple of 16 bytes by the quantiser) and up to 128
 // for V; Q and K quantised in blocks of 16, 32, 64 or 128 tokens (the reference's defaults: 64 and 128).
@@ -98,8 +97,7 @@ mha_int8_fp8_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_
   const uint32_t s_free = s_full + 16;
   const uint32_t p_full = s_free + 8;                // [group]
   const uint32_t o_done = p_full + 16;               // [group][P buffer]
-  const uint32_t tok = o_done + 32;                  // [group]: the group may start its exponentials
-  const uint32_t tmem_slot = tok + 16;
+  const uint32_t tmem_slot = o_done + 32;
   uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -122,7 +120,6 @@ mha_int8_fp8_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_
       mbar_init(p_full + 8 * g, 4);     // the group's four warps have written P
       mbar_init(o_done + 16 * g, 1);
       mbar_init(o_done + 16 * g + 8, 1);
-      mbar_init(tok + 8 * g, 4);
     }
     mbar_init(s_free, 4);               // the four warps of the group whose turn it is hold S in registers
     fence_barrier_init();
@@ -244,7 +241,6 @@ mha_int8_fp8_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_
     const uint32_t p_row0 = sP + 2 * g * TILE_BYTES + row_l * 128;
     const uint32_t p_xor = (uint32_t)(row_l & 7) << 4;           // 128-byte swizzle: 16-byte chunk ^ (row % 8)
     const uint32_t my_s_full = s_full + 8 * g, my_p_full = p_full + 8 * g, my_o_done = o_done + 16 * g;
-    const uint32_t my_tok = tok + 8 * g, other_tok = tok + 8 * (1 - g);
     float m = -INFINITY, l = 0.0f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
@@ -321,11 +317,6 @@ mha_int8_fp8_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_
         l *= a;
       }
       m = m_new;
-      // the exponential phases of the two groups take turns
-      if (both) {
-        ok = warp_all(mbar_wait(my_tok, g == 0 ? ((j & 1) ^ 1) : (j & 1), p.wait_ns));
-        if (!ok) break;
-      }
       // This tile's P buffer was last read by the P V of two tiles ago, which was issued before this tile's S: s_full
       // of this tile implies that it is complete (the tensor pipe completes MMAs and commits in issue order).
       // Probabilities, row sum, P to e4m3 in the key order of the reference's V quantiser: position n of every 16 keys
@@ -353,11 +344,6 @@ mha_int8_fp8_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_
           st_shared_v4u(p_row + (((uint32_t)(2 * gg + ch) << 4) ^ p_xor), e4m3x4(q8[0].x, q8[0].y, q8[1].x, q8[1].y),
                         e4m3x4(q8[2].x, q8[2].y, q8[3].x, q8[3].y), e4m3x4(q8[4].x, q8[4].y, q8[5].x, q8[5].y),
                         e4m3x4(q8[6].x, q8[6].y, q8[7].x, q8[7].y));
-        }
-        if (gg == 1 && both) {
-          // half of this tile's exponentials are issued: the other group may start its own
-          __syncwarp();
-          if (lane == 0) mbar_arrive(other_tok);
         }
       }
 #undef AC4K_S

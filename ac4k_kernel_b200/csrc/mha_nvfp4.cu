@@ -23,8 +23,9 @@
 // The softmax bounds this kernel: an SM retires 16 ex2 per clock, 1024 cycles for 128 x 128 scores against 330 for the
 // four-bit MMAs.  One warp per scheduler keeps the ex2 pipe ~65 % busy, two keep it full, but two groups that run in
 // step also sit together in the phases that do not use it (wait for S, copy it out, maxima, rescale, fences, barrier
-// traffic: ~800 cycles per key tile).  So the groups are kept out of step by a token passed through two mbarriers: a
-// group starts the exponentials of a tile only when the other group is at least half way through its own.
+// traffic: ~800 cycles per key tile).  Sharing one score buffer keeps the groups a few hundred cycles apart (group B's S
+// is issued when group A has copied its own out); an explicit token that made a group wait until the other was half way
+// through its exponentials helped earlier versions of this kernel and costs 3 % in this one.
 // Tensor memory: S 128 + O_A 128 + O_B 128 + scales 40 columns of 512.
 //
 // Supported: head dimensions up to 128 (padded to 64 or 128 by the quantiser); block scales in the tiled layout
@@ -129,8 +130,7 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   const uint32_t s_free = s_full + 16;
   const uint32_t p_full = s_free + 8;                // [group]
   const uint32_t o_done = p_full + 16;               // [group][P buffer]
-  const uint32_t tok = o_done + 32;                  // [group]: the group may start its exponentials
-  const uint32_t tmem_slot = tok + 16;
+  const uint32_t tmem_slot = o_done + 32;
   uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -153,7 +153,6 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       mbar_init(p_full + 8 * g, 4);     // the group's four warps have written P and its scales
       mbar_init(o_done + 16 * g, 1);
       mbar_init(o_done + 16 * g + 8, 1);
-      mbar_init(tok + 8 * g, 4);
     }
     mbar_init(s_free, 4);               // the four warps of the group whose turn it is hold S in registers
     fence_barrier_init();
@@ -352,7 +351,6 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     const uint32_t p_xor = (uint32_t)((row_l >> 1) & 3) << 4;       // 64-byte swizzle: 16-byte chunk ^ ((row / 2) % 4)
     const uint32_t sfp0 = sSFP + 2 * g * SF_BYTES + lane * 16 + q * 4;
     const uint32_t my_s_full = s_full + 8 * g, my_p_full = p_full + 8 * g, my_o_done = o_done + 16 * g;
-    const uint32_t my_tok = tok + 8 * g, other_tok = tok + 8 * (1 - g);
     const bool tracer = (q == 0 && lane == 0);
     float m = -INFINITY, l = 0.0f;
     bool ok = true;
@@ -422,11 +420,6 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       }
       m = m_new;
       if (tracer) AC4K_TRM(2 * g, j, 3);
-      // the exponential phases of the two groups take turns
-      if (both) {
-        ok = warp_all(mbar_wait(my_tok, g == 0 ? ((j & 1) ^ 1) : (j & 1), p.wait_ns));
-        if (!ok) break;
-      }
       if (tracer) AC4K_TRM(2 * g, j, 4);
       // This tile's P buffer was last read by the P V of two tiles ago.  That MMA was issued before this tile's S, and
       // the tensor pipe completes MMAs (and the commits behind them) in issue order: s_full of this tile, seen above,
@@ -476,11 +469,6 @@ mha_nvfp4_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
           codes[hh] = f32x8_to_e2m1x8(x);
         }
         st_shared_v4u(p_row + (((uint32_t)gg << 4) ^ p_xor), codes[0], codes[1], codes[2], codes[3]);
-        if (gg == 1 && both) {
-          // half of this tile's exponentials are issued: the other group may start its own
-          __syncwarp();
-          if (lane == 0) mbar_arrive(other_tok);
-        }
       }
 #undef AC4K_S
       l += (lsum[0].x + lsum[0].y) + (lsum[1].x + lsum[1].y) + ((lsum[2].x + lsum[2].y) + (lsum[3].x + lsum[3].y));
