@@ -406,10 +406,12 @@ def mha_int8_x_fp8_fwd(o, q, q_sf, q_quantize_block_size, k, k_sf, k_quantize_bl
               "mha_int8_x_fp8_fwd")
 
 
-def quantize_int8_block(out, scale, input, layout, block_size):
+def quantize_int8_block(out, scale, input, layout, block_size, sub=None):
     """INT8 quantisation in blocks of `block_size` tokens (all features of a head share the block's scale); stands in
     for the reference's Triton kernel (python/ac4k_kernel/ops/attention.py:18-99).  input: bf16 [B, N, H, D] ("BNHD")
-    or [B, H, N, D] ("BHND"), any strides; out: int8 [B, H, N, align16(D)]; scale: fp32 [B, H, ceil(N / block_size)]."""
+    or [B, H, N, D] ("BHND"), any strides; out: int8 [B, H, N, align16(D)]; scale: fp32 [B, H, ceil(N / block_size)].
+    sub: None, or a bf16 tensor of input's layout with one token ([B, 1, H, D] / [B, H, 1, D]): input - sub (a bf16 tensor
+    subtraction) is quantised, without that tensor being written."""
     _require(layout in ("BNHD", "BHND"), f"Unsupported layout: {layout}")
     _require(isinstance(input, torch.Tensor) and input.is_cuda and input.dtype == torch.bfloat16 and input.dim() == 4,
              "in must be a 4D bfloat16 CUDA tensor")
@@ -419,7 +421,13 @@ def quantize_int8_block(out, scale, input, layout, block_size):
     _check_tensor(scale, torch.float32, "scale")
     _require(list(out.shape) == [B, H, N, _align_up(D, 16)], "out has an invalid shape")
     _require(list(scale.shape) == [B, H, _ceil_div(N, int(block_size))], "scale has an invalid shape")
+    sub_ptr, sub_strides = None, None
+    if sub is not None:
+        u = sub.permute(0, 2, 1, 3) if layout == "BNHD" else sub
+        _require(u.is_cuda and u.dtype == torch.bfloat16 and list(u.shape) == [B, H, 1, D] and u.stride(3) == 1,
+                 "sub must be a bfloat16 CUDA tensor with one token and contiguous features")
+        sub_ptr, sub_strides = u.data_ptr(), (ctypes.c_int64 * 2)(u.stride(0), u.stride(1))
     with torch.cuda.device(input.device):
         check(LIB.ac4k_quantize_int8_block(out.data_ptr(), scale.data_ptr(), x.data_ptr(), _I64x4(B, H, N, D),
-                                           _I64x4(*x.stride()), int(block_size), _stream(input)),
+                                           _I64x4(*x.stride()), int(block_size), sub_ptr, sub_strides, _stream(input)),
               "quantize_int8_block")

@@ -42,7 +42,7 @@ SIGNATURES = {
     "ac4k_mha_nvfp4_fwd": (ctypes.c_int, [_vp, _c_i64p, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                           ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                           ctypes.c_int64, ctypes.c_int64, ctypes.c_float, ctypes.c_int, _vp]),
-    "ac4k_quantize_int8_block": (ctypes.c_int, [_vp, _vp, _vp, _c_i64p, _c_i64p, ctypes.c_int64, _vp]),
+    "ac4k_quantize_int8_block": (ctypes.c_int, [_vp, _vp, _vp, _c_i64p, _c_i64p, ctypes.c_int64, _vp, _c_i64p, _vp]),
     "ac4k_mha_int8_x_fp8_fwd": (ctypes.c_int, [_vp, _c_i64p, _vp, _vp, ctypes.c_int64, _vp, _vp, ctypes.c_int64, _vp, _vp,
                                                ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                                ctypes.c_int64, ctypes.c_int64, ctypes.c_float, _vp]),

@@ -1,6 +1,8 @@
 // Block-of-tokens INT8 quantiser of the INT8 x FP8 attention path: x[b, h, n, :] bf16 (any strides) ->
 // y[b, h, n, align16(D)] int8 and one fp32 scale per block of `block` consecutive tokens (all D features):
 //   scale = max|x| / 127 over the block,  y = trunc(x / scale)  (0 when the block is all zero), padding columns 0.
+// Optionally x is first reduced by a bf16 vector per head, x - sub rounded to bf16 (the reference takes the mean over
+// the tokens off K with a tensor subtraction of its own, attention.py:157: one pass over K less).
 // Stands in for the Triton kernel and its wrapper in ac4k_kernel's python/ac4k_kernel/ops/attention.py:18-48 and
 // :51-99 (`tl.cast(fp32 -> int8)` truncates toward zero; the division is a true fp32 division).
 //
@@ -20,7 +22,7 @@ static constexpr int kQ8MaxElemsPerThread = 128;     // 128 tokens x 256 feature
 template <int EPT>
 __global__ void __launch_bounds__(kQ8Threads) quantize_int8_block_kernel(
     int8_t *__restrict__ y, float *__restrict__ scale, const uint16_t *__restrict__ x, int N, int D, int Dp, int block, int nblk,
-    int64_t sb, int64_t sh, int64_t sn, int64_t sd, int H) {
+    int64_t sb, int64_t sh, int64_t sn, int64_t sd, int H, const uint16_t *__restrict__ sub, int64_t ub, int64_t uh) {
   __shared__ float red[kQ8Threads / 32];
   const int blk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int n0 = blk * block;
@@ -38,6 +40,8 @@ __global__ void __launch_bounds__(kQ8Threads) quantize_int8_block_kernel(
       const int r = e / Dp, c = e - r * Dp;
       if (r < rows && c < D) {
         v[i] = __uint_as_float((uint32_t)__ldg(src + (int64_t)(n0 + r) * sn + (int64_t)c * sd) << 16);
+        if (sub != nullptr)      // x - sub rounded to bf16, as a bf16 tensor subtraction gives it
+          v[i] = __bfloat162float(__float2bfloat16_rn(v[i] - __uint_as_float((uint32_t)__ldg(sub + b * ub + h * uh + c) << 16)));
         amax = fmaxf(amax, fabsf(v[i]));
       }
     }
@@ -66,7 +70,7 @@ __global__ void __launch_bounds__(kQ8Threads) quantize_int8_block_kernel(
 template <int VPT>
 __global__ void __launch_bounds__(kQ8Threads) quantize_int8_block_vec_kernel(
     int8_t *__restrict__ y, float *__restrict__ scale, const uint16_t *__restrict__ x, int N, int D, int Dp, int block, int nblk,
-    int64_t sb, int64_t sh, int64_t sn, int H) {
+    int64_t sb, int64_t sh, int64_t sn, int H, const uint16_t *__restrict__ sub, int64_t ub, int64_t uh) {
   __shared__ float red[kQ8Threads / 32];
   const int blk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int n0 = blk * block;
@@ -85,7 +89,13 @@ __global__ void __launch_bounds__(kQ8Threads) quantize_int8_block_vec_kernel(
       const int r = e / vpr_out, c = e - r * vpr_out;
       if (c < vpr) {
         v[i] = __ldcs(reinterpret_cast<const uint4 *>(src + (int64_t)r * sn) + c);
-        const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&v[i]);
+        __nv_bfloat162 *h2 = reinterpret_cast<__nv_bfloat162 *>(&v[i]);
+        if (sub != nullptr) {      // x - sub rounded to bf16, as a bf16 tensor subtraction gives it
+          const uint4 u = __ldg(reinterpret_cast<const uint4 *>(sub + b * ub + h * uh) + c);
+          const __nv_bfloat162 *u2 = reinterpret_cast<const __nv_bfloat162 *>(&u);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) h2[k] = __hsub2(h2[k], u2[k]);
+        }
 #pragma unroll
         for (int k = 0; k < 4; ++k) am2 = __hmax2(am2, __habs2(h2[k]));
       }
@@ -126,7 +136,7 @@ __global__ void __launch_bounds__(kQ8Threads) quantize_int8_block_vec_kernel(
 using namespace ac4k;
 
 extern "C" int ac4k_quantize_int8_block(void *out, float *scale, const void *in, const int64_t shape[4], const int64_t stride[4],
-                                        int64_t block, ac4k_stream_t stream_) {
+                                        int64_t block, const void *sub, const int64_t sub_stride[2], ac4k_stream_t stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (!shape || !stride) return fail(AC4K_ERR_NULL, "shape/stride is NULL");
   const int64_t B = shape[0], H = shape[1], N = shape[2], D = shape[3];
@@ -140,16 +150,20 @@ extern "C" int ac4k_quantize_int8_block(void *out, float *scale, const void *in,
                 (long long)block, (long long)Dp);
   if (H > 65535 || B > 65535 || N > INT32_MAX) return fail(AC4K_ERR_SHAPE, "dimension too large");
   if ((reinterpret_cast<uintptr_t>(in) & 1) || (reinterpret_cast<uintptr_t>(scale) & 3)) return fail(AC4K_ERR_ALIGN, "in must be 2-byte and scale 4-byte aligned");
+  if (sub && !sub_stride) return fail(AC4K_ERR_NULL, "sub_stride is NULL");
+  const uint16_t *subp = static_cast<const uint16_t *>(sub);
+  const int64_t ub = sub ? sub_stride[0] : 0, uh = sub ? sub_stride[1] : 0;
   const int64_t nblk = ceil_div(N, block);
   dim3 grid((unsigned)nblk, (unsigned)H, (unsigned)B);
   const bool vec = stride[3] == 1 && D % 8 == 0 && stride[0] % 8 == 0 && stride[1] % 8 == 0 && stride[2] % 8 == 0 &&
-                   (reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 7) == 0;
+                   (reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 7) == 0 &&
+                   (!sub || ((reinterpret_cast<uintptr_t>(sub) & 15) == 0 && ub % 8 == 0 && uh % 8 == 0));
   if (vec) {
     const int64_t vpt = ceil_div(block * (Dp / 8), kQ8Threads);
 #define AC4K_Q8V_LAUNCH(V)                                                                                                            \
   quantize_int8_block_vec_kernel<V><<<grid, kQ8Threads, 0, stream>>>(static_cast<int8_t *>(out), scale, static_cast<const uint16_t *>(in), \
                                                                       (int)N, (int)D, (int)Dp, (int)block, (int)nblk, stride[0], stride[1],  \
-                                                                      stride[2], (int)H)
+                                                                      stride[2], (int)H, subp, ub, uh)
     if (vpt <= 2) AC4K_Q8V_LAUNCH(2);
     else if (vpt <= 4) AC4K_Q8V_LAUNCH(4);
     else if (vpt <= 8) AC4K_Q8V_LAUNCH(8);
@@ -162,7 +176,7 @@ extern "C" int ac4k_quantize_int8_block(void *out, float *scale, const void *in,
 #define AC4K_Q8_LAUNCH(E)                                                                                                          \
   quantize_int8_block_kernel<E><<<grid, kQ8Threads, 0, stream>>>(static_cast<int8_t *>(out), scale, static_cast<const uint16_t *>(in), \
                                                                   (int)N, (int)D, (int)Dp, (int)block, (int)nblk, stride[0], stride[1],  \
-                                                                  stride[2], stride[3], (int)H)
+                                                                  stride[2], stride[3], (int)H, subp, ub, uh)
   if (ept <= 16) AC4K_Q8_LAUNCH(16);
   else if (ept <= 32) AC4K_Q8_LAUNCH(32);
   else if (ept <= 64) AC4K_Q8_LAUNCH(64);

@@ -18,9 +18,10 @@ mha_nvfp4_fwd = _cuda_ops.mha_nvfp4_fwd
 mha_int8_x_fp8_fwd = _cuda_ops.mha_int8_x_fp8_fwd
 
 
-def _int8_quantize(x, layout, dim, type="token", BLOCK_SIZE=64, HDIM_ALIGN=16):
+def _int8_quantize(x, layout, dim, type="token", BLOCK_SIZE=64, HDIM_ALIGN=16, sub=None):
     """(int8 [B, H, N, align_up(D, 16)], fp32 scale [B, H, ceil(N / BLOCK_SIZE)]) as the reference's helper of the
-    same name (attention.py:51-99)."""
+    same name (attention.py:51-99).  `sub` (one token per head, x's layout): x - sub is quantised, bit for bit what
+    quantising the bf16 tensor `x - sub` gives."""
     assert HDIM_ALIGN == 16, "HDIM_ALIGN other than 16 is not built"
     assert type == "token", "Only support token quantization yet."
     assert BLOCK_SIZE >= 16 and (BLOCK_SIZE & (BLOCK_SIZE - 1)) == 0
@@ -33,7 +34,7 @@ def _int8_quantize(x, layout, dim, type="token", BLOCK_SIZE=64, HDIM_ALIGN=16):
         assert dim in [2, 3]
     scale = torch.empty([B, H, (x.shape[dim] + BLOCK_SIZE - 1) // BLOCK_SIZE], device=x.device, dtype=torch.float32)
     y = torch.empty([B, H, N, (D + 15) // 16 * 16], device=x.device, dtype=torch.int8)
-    _cuda_ops.quantize_int8_block(y, scale, x, layout, BLOCK_SIZE)
+    _cuda_ops.quantize_int8_block(y, scale, x, layout, BLOCK_SIZE, sub)
     return y, scale
 
 
@@ -46,9 +47,11 @@ def _int8_x_fp8_attention(q, k, v, layout, Q_QUANTIZE_BLOCK_SIZE=64, K_QUANTIZE_
     else:
         H, Nq = q.shape[1], q.shape[2]
     n_dim = 1 if layout == "BNHD" else 2
-    k = k - k.mean(dim=n_dim, keepdim=True)          # softmax is invariant to it; it shrinks the range INT8 has to cover
+    # k - mean(k): softmax is invariant to it and it shrinks the range INT8 has to cover (attention.py:157); the
+    # subtraction happens inside the K quantiser
+    k_mean = k.mean(dim=n_dim, keepdim=True)
     q_int8, q_sf = _int8_quantize(q, layout, n_dim, BLOCK_SIZE=Q_QUANTIZE_BLOCK_SIZE)
-    k_int8, k_sf = _int8_quantize(k, layout, n_dim, BLOCK_SIZE=K_QUANTIZE_BLOCK_SIZE)
+    k_int8, k_sf = _int8_quantize(k, layout, n_dim, BLOCK_SIZE=K_QUANTIZE_BLOCK_SIZE, sub=k_mean)
     v_fp8, v_sf = quantize(v, 3, n_dim, swizzle=True, max_scale=2.25, precision="fp8e4m3")
     if out is None:
         out_shape = (B, Nq, H, Dv) if layout == "BNHD" else (B, H, Nq, Dv)

@@ -182,9 +182,12 @@ int ac4k_mha_nvfp4_fwd(void *O, const int64_t o_stride[4], const void *Q, const 
  * python/ac4k_kernel/ops/attention.py:18-48, :51-99.
  *   in: bf16, logical [B, H, N, D] given by shape[4] = {B, H, N, D} and element strides stride[4] (so both tensor
  *   layouts of the reference work); out: int8 [B, H, N, align16(D)] contiguous; scale: fp32 [B, H, ceil(N / block)].
- *   block: power of two in [16, 128], block * align16(D) <= 32768. */
+ *   block: power of two in [16, 128], block * align16(D) <= 32768.
+ *   sub: NULL, or bf16 vectors of D contiguous features, one per head at sub + b * sub_stride[0] + h * sub_stride[1]
+ *   (elements): x - sub, rounded to bf16 as a bf16 tensor subtraction rounds it, is quantised instead of x (the
+ *   reference subtracts the mean over the tokens from K with a torch operation first, attention.py:157). */
 int ac4k_quantize_int8_block(void *out, float *scale, const void *in, const int64_t shape[4], const int64_t stride[4],
-                             int64_t block, ac4k_stream_t stream);
+                             int64_t block, const void *sub, const int64_t sub_stride[2], ac4k_stream_t stream);
 
 /* O = softmax(sm_scale * Q K^T) V with Q, K in INT8 (scales per block of tokens), P and V in FP8 e4m3 (V with one scale
  * per channel), bf16 output.  Replaces ac4k::mha_int8_x_fp8_fwd, include/ac4k_kernel/ops.h:19-25,

@@ -58,6 +58,20 @@ def test_block_quantiser_bit_exact(B, N, H, D, layout, block):
     assert torch.equal(y, ry)
 
 
+@pytest.mark.parametrize("layout,D", [("BNHD", 128), ("BHND", 100), ("BNHD", 12)])
+def test_block_quantiser_with_subtraction(layout, D):
+    """x - mean inside the quantiser = the quantiser on the bf16 tensor x - mean."""
+    _, _, _, int8_quantize = _ops()
+    g = torch.Generator(device="cuda").manual_seed(D)
+    shape = (2, 300, 3, D) if layout == "BNHD" else (2, 3, 300, D)
+    n_dim = 1 if layout == "BNHD" else 2
+    x = torch.randn(shape, dtype=torch.bfloat16, device="cuda", generator=g) + 0.7
+    mean = x.mean(dim=n_dim, keepdim=True)
+    y0, s0 = int8_quantize(x - mean, layout, n_dim, BLOCK_SIZE=128)
+    y1, s1 = int8_quantize(x, layout, n_dim, BLOCK_SIZE=128, sub=mean)
+    assert torch.equal(y0, y1) and torch.equal(s0, s1)
+
+
 # the shapes of the reference's test (the 75 600-token one with one head: 732 ms of fp32 SDPA, fine)
 REF_CASES = [
     (1, 75600, 1, 128, "BNHD"), (1, 100, 1, 128, "BNHD"), (11, 100, 12, 12, "BNHD"), (11, 100, 12, 65, "BNHD"),

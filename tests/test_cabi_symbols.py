@@ -61,8 +61,8 @@ def test_argument_errors_without_gpu():
     assert LIB.ac4k_rope3d(None, 8, 8, 16, 1, 4, 2, 8, 4, None) == -1
     assert LIB.ac4k_rope3d(8, 8, 8, 16, 1, 4, 2, 4096, 4, None) == -5       # feature dimension above what is built
     sh = (ctypes.c_int64 * 4)(1, 1, 8, 16)
-    assert LIB.ac4k_quantize_int8_block(8, 8, 8, sh, sh, 48, None) == -2         # block not a power of two
-    assert LIB.ac4k_quantize_int8_block(None, 8, 8, sh, sh, 64, None) == -1
+    assert LIB.ac4k_quantize_int8_block(8, 8, 8, sh, sh, 48, None, None, None) == -2         # block not a power of two
+    assert LIB.ac4k_quantize_int8_block(None, 8, 8, sh, sh, 64, None, None, None) == -1
     o4 = (ctypes.c_int64 * 4)(1, 1, 1, 1)
     assert LIB.ac4k_mha_int8_x_fp8_fwd(16, o4, 16, 16, 64, 16, 16, 48, 16, 16, 1, 1, 8, 8, 128, 128, 0.1, None) == -5   # K block 48
     assert LIB.ac4k_mha_int8_x_fp8_fwd(16, o4, 16, 16, 64, 16, 16, 128, 16, 16, 1, 1, 8, 8, 256, 128, 0.1, None) == -5  # head dim 256
