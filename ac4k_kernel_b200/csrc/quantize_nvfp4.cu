@@ -5,8 +5,9 @@
 // approximate reciprocals replaced by correctly rounded fp32 operations:
 //     alpha = 1 / g ;  sf = e4m3(alpha * (amax16 * fp32(1/6))) ;
 //     r = sf ? alpha * (1 / float(sf)) : 0 ;  code = e2m1(float(x) * r)
-// Two kernels: a tiled one for rows that are contiguous along K (the linear path), and a
-// strided one (any cross/reduce strides, optional K permutation) for the other callers.
+// Three kernels: a tiled one for rows that are contiguous along K (the linear path), a transposing one
+// for rows that are contiguous along the cross dimension (attention's V), and a strided one (any
+// cross/reduce strides, optional K permutation) for everything else.
 #include "common.cuh"
 
 namespace ac4k {
@@ -224,6 +225,91 @@ nvfp4_quantize_strided_kernel(uint8_t *__restrict__ out, uint8_t *__restrict__ s
 }
 
 // ----------------------------------------------------------------------------------------
+// Transposing kernel: rows contiguous in memory along the CROSS dimension (stride_m == 1) and strided
+// along K -- attention's V, quantised along the keys with the head dimension as output rows.  The
+// strided kernel above reads 64 bytes per warp load there and writes 8-byte pieces 'Kp / 2' apart.
+// Here one CTA takes 128 K-elements x 128 rows: a thread loads 32 words (two neighbouring rows x 32
+// consecutive K-elements; a warp reads 128 contiguous bytes per load), quantises its four blocks of
+// 16 in registers, and codes and scale bytes go through shared memory so that each output row leaves
+// as 64 contiguous bytes and the scales as whole words.
+// ----------------------------------------------------------------------------------------
+template <int SF_LAYOUT, bool PERMUTE>
+__global__ void __launch_bounds__(256)
+nvfp4_quantize_transposed_kernel(uint8_t *__restrict__ out, uint8_t *__restrict__ sf, const uint16_t *__restrict__ in,
+                                 const float *__restrict__ gscale, int64_t M, int64_t K, int64_t d1, int64_t stride0,
+                                 int64_t stride1, int64_t stride_k) {
+  __shared__ uint4 s_codes[128][4 + 1];          // [row][32-element group of the tile], padded
+  __shared__ uint32_t s_sf[2][128];              // [K = 64 step of the tile][row]: four scale bytes
+  const int64_t Kp = align_up(K, 64), KT = Kp / 64, M16 = align_up(M, 16), MT = ceil_div(M, 128);
+  const int64_t batch = blockIdx.z;
+  const int64_t k0 = (int64_t)blockIdx.x * 128, m0 = (int64_t)blockIdx.y * 128;
+  const int cx = threadIdx.x & 63, kg = threadIdx.x >> 6;
+  const int64_t m = m0 + 2 * cx, kb = k0 + 32 * kg;           // this thread: rows m, m + 1; K-elements kb .. kb + 31
+  const uint16_t *base = in + (batch / d1) * stride0 + (batch % d1) * stride1;
+  const float alpha = load_alpha(gscale);
+
+  uint32_t w[32];                                // w[j]: element kb + j of row m (low half) and of row m + 1 (high half)
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    w[j] = 0u;
+    if (m < M && kb + j < K) w[j] = __ldg(reinterpret_cast<const uint32_t *>(base + (kb + j) * stride_k + m));
+  }
+  uint32_t bytes[2] = {0u, 0u};                  // the two block scales of this group, for row m and row m + 1
+  uint4 codes[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    // pairs of consecutive K-elements of row m + r, in output order: position pair j holds elements src(2 j), src(2 j) + 1
+    uint32_t pr[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      int e = 2 * j;
+      if (PERMUTE) e = 8 * (((2 * j) & 7) >> 1) + 2 * ((2 * j) >> 3);
+      pr[j] = __byte_perm(w[e], w[e + 1], r == 0 ? 0x5410 : 0x7632);
+    }
+    uint32_t cw[4];
+#pragma unroll
+    for (int blk = 0; blk < 2; ++blk) {
+      uint32_t amax = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t a = pr[8 * blk + j] & 0x7FFF7FFFu;
+        amax = max(amax, max(a & 0xFFFFu, a >> 16));
+      }
+      const BlockScale bs = block_scale(bf16_bits_to_f32(amax), alpha);
+      cw[2 * blk] = quantize8(make_uint4(pr[8 * blk], pr[8 * blk + 1], pr[8 * blk + 2], pr[8 * blk + 3]), bs.r);
+      cw[2 * blk + 1] = quantize8(make_uint4(pr[8 * blk + 4], pr[8 * blk + 5], pr[8 * blk + 6], pr[8 * blk + 7]), bs.r);
+      bytes[r] |= (uint32_t)((m + r < M) ? bs.byte : (uint8_t)0) << (8 * blk);
+    }
+    codes[r] = make_uint4(cw[0], cw[1], cw[2], cw[3]);
+  }
+  s_codes[2 * cx][kg] = codes[0];
+  s_codes[2 * cx + 1][kg] = codes[1];
+  // scale bytes: group kg covers blocks 2 (kg & 1), 2 (kg & 1) + 1 of K = 64 step kg >> 1
+  reinterpret_cast<uint16_t *>(&s_sf[kg >> 1][2 * cx])[kg & 1] = (uint16_t)bytes[0];
+  reinterpret_cast<uint16_t *>(&s_sf[kg >> 1][2 * cx + 1])[kg & 1] = (uint16_t)bytes[1];
+  __syncthreads();
+  // codes: 128 rows x 64 bytes, four threads per row
+  for (int v = threadIdx.x; v < 512; v += 256) {
+    const int row = v >> 2, g = v & 3;
+    if (m0 + row < M && k0 + 32 * g < Kp)
+      *reinterpret_cast<uint4 *>(out + (batch * M + m0 + row) * (Kp / 2) + (k0 + 32 * g) / 2) = s_codes[row][g];
+  }
+  // scales: one word per row and K = 64 step
+  {
+    const int row = threadIdx.x & 127, ks = threadIdx.x >> 7;
+    const int64_t k64 = k0 / 64 + ks, rg = m0 + row;
+    const int64_t rows_sf = (SF_LAYOUT == AC4K_SF_AC4K) ? M16 : MT * 128;
+    if (k64 < KT && rg < rows_sf) {
+      uint32_t *sfw = reinterpret_cast<uint32_t *>(sf);
+      if (SF_LAYOUT == AC4K_SF_AC4K)
+        sfw[(batch * KT + k64) * M16 + rg] = s_sf[ks][row];
+      else
+        sfw[((batch * MT + blockIdx.y) * KT + k64) * 128 + (row & 31) * 4 + (row >> 5)] = s_sf[ks][row];
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------
 // Global scale: max|x| / max_scale.  Division is monotonic, so each CTA divides its own
 // maximum and combines with an integer atomicMax on the (non-negative) float bits, the
 // same scheme as the reference's Triton kernel (python/ac4k_kernel/ops/quant.py:21-46).
@@ -357,6 +443,24 @@ extern "C" int ac4k_quantize_nvfp4(void *out, void *sf, const void *in, const fl
 
   const int64_t rows_sf = (sf_layout == AC4K_SF_AC4K) ? align_up(M, 16) : align_up(M, 128);
   const bool row_fastest = stride[2] < stride[3];
+  // rows contiguous along the cross dimension, K strided: the transposing kernel
+  const bool tr_ok = stride[2] == 1 && M % 2 == 0 && stride[3] % 2 == 0 && stride[0] % 2 == 0 && stride[1] % 2 == 0 &&
+                     ((reinterpret_cast<uintptr_t>(in) & 3) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
+                     ceil_div(M, 128) <= 65535;
+  if (tr_ok) {
+    dim3 g((unsigned)ceil_div(Kp, 128), (unsigned)ceil_div(M, 128), (unsigned)nbatch);
+#define AC4K_LAUNCH_TR(L, P)                                                                                        \
+  nvfp4_quantize_transposed_kernel<L, P><<<g, 256, 0, stream>>>(static_cast<uint8_t *>(out), static_cast<uint8_t *>(sf), inp, \
+                                                                global_scale, M, K, d1, stride[0], stride[1], stride[3])
+    if (sf_layout == AC4K_SF_AC4K) {
+      if (swizzle) AC4K_LAUNCH_TR(AC4K_SF_AC4K, true); else AC4K_LAUNCH_TR(AC4K_SF_AC4K, false);
+    } else {
+      if (swizzle) AC4K_LAUNCH_TR(AC4K_SF_TILE128X4, true); else AC4K_LAUNCH_TR(AC4K_SF_TILE128X4, false);
+    }
+#undef AC4K_LAUNCH_TR
+    AC4K_LAUNCH_CHECK("nvfp4_quantize_transposed_kernel");
+    return 0;
+  }
   dim3 grid;
   if (row_fastest)
     grid = dim3((unsigned)ceil_div(Kp / 16, 8), (unsigned)ceil_div(rows_sf, 32), (unsigned)nbatch);
