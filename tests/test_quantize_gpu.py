@@ -60,6 +60,19 @@ def test_strided_and_permuted(ops, shape, cd, rd, sw, layout):
     _check_nvfp4(ops, gaussian(shape, seed=7), cd, rd, sw, layout)
 
 
+@pytest.mark.parametrize("layout", ["ac4k", "128x4"])
+@pytest.mark.parametrize("sw", [False, True])
+@pytest.mark.parametrize("shape,cd,rd", [
+    ((300, 130), 1, 0),            # rows contiguous, K strided: the transposing kernel, ragged in both directions
+    ((64, 2), 1, 0),               # two rows
+    ((2, 200, 3, 96), 3, 1),       # attention's V: [B, N, H, D] reduced over the keys
+    ((1, 1000, 2, 128), 3, 1),
+    ((1, 129, 1, 256), 3, 1),      # two row tiles, K one past a tile
+])
+def test_contiguous_rows_strided_k(ops, shape, cd, rd, sw, layout):
+    _check_nvfp4(ops, gaussian(shape, seed=11, outlier_frac=0.01, outlier_mul=30.0), cd, rd, sw, layout)
+
+
 def test_golden_known_answers_through_cuda(ops, golden_dir):
     """The reference's known-answer construction ({+-1,+-2,+-4,+-6} inputs, get_ref outputs)."""
     z = np.load(os.path.join(golden_dir, "nvfp4_quantize_known_answer.npz"))
