@@ -147,14 +147,25 @@ __device__ __forceinline__ void store_row32(void *D, int64_t off, const float (&
 // host helpers (linear_nvfp4.cu)
 // 2-D byte tensor map [rows, row_bytes] with a (128 B x box_rows) box and 128-byte swizzle
 int get_tmap(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUtensorMap *out);
-// 2-CTA kernel launcher (linear_nvfp4_2cta.cu); D must be bf16/fp16 with N % 8 == 0
-// tsa / tsb: tensor maps of tiled scales (get_tmap_sf_tiled); scales in the row layout are read with plain loads
+// same bytes with the rows as (row / 4, row % 4): a box of 128 B x 32 x 4 brings rows 4 l + q of a 128-row block to
+// shared-memory row q * 32 + l; rows must be a multiple of 4
+int get_tmap_rows4(const void *ptr, int64_t rows, int64_t row_bytes, CUtensorMap *out);
+// tiled scales [row blocks][K/64][512 B] as a matrix of 512-byte rows, boxes of box_ksteps rows
 int get_tmap_sf_tiled(const void *ptr, int64_t row_blocks, int64_t kt, int box_ksteps, CUtensorMap *out);
-// 16-bit output [rows, cols] with a row pitch of ld elements: boxes of 64 columns x 32 rows, 128-byte swizzle
+// scales in the row layout [K/64][rows] words: boxes of 128 words (the rows of a 128-row block) x 4 K steps
+int get_tmap_sf_rows(const void *ptr, int64_t rows, int64_t kt, CUtensorMap *out);
+// 2-D byte tensor map with a (64 B x box_rows) box and 64-byte swizzle
 int get_tmap64(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUtensorMap *out);
 unsigned long long *debug_trace_ptr();
+// 16-bit output [rows, cols] with a row pitch of ld elements: boxes of 64 columns x 32 rows, 128-byte swizzle
 int get_tmap_out16(const void *ptr, int64_t rows, int64_t cols, int64_t ld, CUtensorMap *out);
-int launch_linear_2cta(int d_dtype, bool sf_tiled, const CUtensorMap &ta, const CUtensorMap &tb,
+// the same output with the rows as (row / 4, row % 4): boxes of 64 columns x 32 x 1; rows must be a multiple of 4
+int get_tmap_out16_rows4(const void *ptr, int64_t rows, int64_t cols, int64_t ld, CUtensorMap *out);
+// 2-CTA kernel launcher (linear_nvfp4_2cta.cu); D must be bf16/fp16 with N % 8 == 0.  sf_mode 0: scales in the row
+// layout read with plain loads (ta, tb, dm from get_tmap / get_tmap_out16); 1: tiled scales (tsa, tsb from
+// get_tmap_sf_tiled); 2: scales in the row layout by TMA (tsa, tsb from get_tmap_sf_rows; ta, tb from get_tmap_rows4,
+// dm from get_tmap_out16_rows4)
+int launch_linear_2cta(int d_dtype, int sf_mode, const CUtensorMap &ta, const CUtensorMap &tb,
                        const CUtensorMap &tsa, const CUtensorMap &tsb, const DstMaps &dm, GemmArgs args, cudaStream_t stream);
 
 // decode-shape kernel (linear_nvfp4_skinny.cu): M <= nt activation rows, nt in {16, 32, 64}

@@ -418,9 +418,11 @@ struct TmapKey {
   const void *ptr;
   int64_t d0, d1, pitch;   // extents: innermost (elements), outer; row pitch in elements
   int box0, box1, kind, dev;
+  bool rows4;              // rank 3: the d1 rows as (row / 4, row % 4), box {box0, box1, box2}
+  int box2;
   bool operator==(const TmapKey &o) const {
     return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && pitch == o.pitch && box0 == o.box0 && box1 == o.box1 &&
-           kind == o.kind && dev == o.dev;
+           kind == o.kind && dev == o.dev && rows4 == o.rows4 && box2 == o.box2;
   }
 };
 struct TmapEntry { TmapKey key; CUtensorMap map; };
@@ -428,13 +430,15 @@ enum { kTmapOperand = 0, kTmapWords = 1, kTmapOut16 = 2, kTmapOperand64 = 3 };
 
 // kind kTmapOperand / kTmapOperand64: bytes, 128- / 64-byte swizzle; kTmapWords: 32-bit words, not swizzled;
 // kTmapOut16: 16-bit elements, 128-byte swizzle.
+// rows4: a rank-3 map {d0, d1 / 4, 4} with strides {4 * pitch, pitch}: coordinate (x, i, q) is row 4 i + q, and a box
+// {box0, box1, box2} lands in shared memory with q outermost.
 static int encode_cached(int kind, const void *ptr, int64_t d0, int64_t d1, int64_t pitch, int box0, int box1,
-                         CUtensorMap *out) {
+                         CUtensorMap *out, bool rows4 = false, int box2 = 1) {
   static std::mutex mu;
   static std::vector<TmapEntry> cache;
   int dev = 0;
   cudaGetDevice(&dev);
-  TmapKey key{ptr, d0, d1, pitch, box0, box1, kind, dev};
+  TmapKey key{ptr, d0, d1, pitch, box0, box1, kind, dev, rows4, box2};
   {
     std::lock_guard<std::mutex> lk(mu);
     for (auto &e : cache)
@@ -448,12 +452,18 @@ static int encode_cached(int kind, const void *ptr, int64_t d0, int64_t d1, int6
                                  : (kind == kTmapOperand64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE);
   const CUtensorMapDataType dt = bytes ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                  : (kind == kTmapWords ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16);
-  cuuint64_t gdim[2] = {(cuuint64_t)d0, (cuuint64_t)d1};
-  cuuint64_t gstride[1] = {(cuuint64_t)pitch * esize};
-  cuuint32_t box[2] = {(cuuint32_t)box0, (cuuint32_t)box1};
-  cuuint32_t estr[2] = {1, 1};
+  cuuint64_t gdim[3] = {(cuuint64_t)d0, (cuuint64_t)d1, 1};
+  cuuint64_t gstride[2] = {(cuuint64_t)pitch * esize, 0};
+  cuuint32_t box[3] = {(cuuint32_t)box0, (cuuint32_t)box1, (cuuint32_t)box2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  if (rows4) {
+    gdim[1] = (cuuint64_t)(d1 / 4);
+    gdim[2] = 4;
+    gstride[0] = (cuuint64_t)pitch * esize * 4;
+    gstride[1] = (cuuint64_t)pitch * esize;
+  }
   CUtensorMap m;
-  CUresult r = enc(&m, dt, 2,
+  CUresult r = enc(&m, dt, rows4 ? 3 : 2,
                    const_cast<void *>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    swz,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -481,6 +491,20 @@ int get_tmap_sf_tiled(const void *ptr, int64_t row_blocks, int64_t kt, int box_k
 
 int get_tmap_out16(const void *ptr, int64_t rows, int64_t cols, int64_t ld, CUtensorMap *out) {
   return encode_cached(kTmapOut16, ptr, cols, rows, ld, 64, 32, out);
+}
+
+int get_tmap_rows4(const void *ptr, int64_t rows, int64_t row_bytes, CUtensorMap *out) {
+  return encode_cached(kTmapOperand, ptr, row_bytes, rows, row_bytes, BKB, 32, out, true, 4);
+}
+
+int get_tmap_out16_rows4(const void *ptr, int64_t rows, int64_t cols, int64_t ld, CUtensorMap *out) {
+  return encode_cached(kTmapOut16, ptr, cols, rows, ld, 64, 32, out, true, 1);
+}
+
+// Scale factors in the row layout [K/64][rows][4 bytes] seen as a [K/64, rows] matrix of words: the 128 words of a
+// 128-row block at 4 K steps.  Words past the rows or the K steps read as zero.
+int get_tmap_sf_rows(const void *ptr, int64_t rows, int64_t kt, CUtensorMap *out) {
+  return encode_cached(kTmapWords, ptr, rows, kt, rows, 128, 4, out);
 }
 
 // packed operand [rows, row_bytes] whose contraction rows are 64 bytes: boxes of 64 bytes x box_rows rows, 64-byte swizzle
@@ -737,24 +761,33 @@ static int linear_impl(void *D, int d_dtype, const void *A, const void *A_sf, co
                 pl.ws_bytes, ws_capacity);
   const bool tiled = sf_layout == AC4K_SF_TILE128X4;
   if (use_pair) {
-    // scales in the reference's row layout are fed by two more tensor maps (one box per operand and stage)
-    CUtensorMap tsa = ta, tsb = tb;      // placeholders for scales in the row layout (read with plain loads)
+    // Scales in the reference's row layout: with M and N multiples of 4 the operands are loaded with their rows
+    // permuted inside each 128-row block, so that the scales can be used as they lie in memory (rank-3 maps; a
+    // row count that is no multiple of 4 would let such a map reach up to 3 rows past the tensor); otherwise
+    // warps of the kernel re-order the scales.  g_dbg bit 0x200 keeps the re-ordering warps (measurement).
+    const bool perm = !tiled && M % 4 == 0 && N % 4 == 0 && !(g_dbg & 0x200);
+    const int sf_mode = tiled ? 1 : (perm ? 2 : 0);
+    CUtensorMap tsa = ta, tsb = tb;      // placeholders when the scales are read with plain loads
     if (tiled) {
       if (int e = get_tmap_sf_tiled(A_sf, a.rows_sfa / 128, a.KT, 4, &tsa)) return e;
       if (int e = get_tmap_sf_tiled(B_sf, a.rows_sfb / 128, a.KT, 4, &tsb)) return e;
+    } else if (perm) {
+      if (int e = get_tmap_rows4(A, M, K / 2, &ta)) return e;
+      if (int e = get_tmap_rows4(B, N, K / 2, &tb)) return e;
+      if (int e = get_tmap_sf_rows(A_sf, a.rows_sfa, a.KT, &tsa)) return e;
+      if (int e = get_tmap_sf_rows(B_sf, a.rows_sfb, a.KT, &tsb)) return e;
     }
     // destinations of the epilogue's TMA stores: columns [0, col_off + N) of each [M, ldd] buffer, so that the
     // stores are clipped at this launch's last column
     DstMaps dm;
     for (int i = 0; i < kMaxDst; ++i) dm.m[i] = ta;
-    if (!requant && a.n_dst == 1) {
-      if (int e = get_tmap_out16(D, M, a.col_off + N, a.ldd, &dm.m[0])) return e;
-    } else if (!requant) {
-      if (int e = get_tmap_out16(D, M, a.col_off + N, a.ldd, &dm.m[0])) return e;
+    if (!requant) {
+      auto out_map = perm ? get_tmap_out16_rows4 : get_tmap_out16;
+      if (int e = out_map(D, M, a.col_off + N, a.ldd, &dm.m[0])) return e;
       for (int i = 1; i < a.n_dst; ++i)
-        if (int e = get_tmap_out16(a.D_more[i - 1], M, a.col_off + N, a.ldd, &dm.m[i])) return e;
+        if (int e = out_map(a.D_more[i - 1], M, a.col_off + N, a.ldd, &dm.m[i])) return e;
     }
-    return launch_linear_2cta(d_dtype, tiled, ta, tb, tsa, tsb, dm, a, stream);
+    return launch_linear_2cta(d_dtype, sf_mode, ta, tb, tsa, tsb, dm, a, stream);
   }
   if (pl.splits > 1) {
     if (ws_mode == 1) {

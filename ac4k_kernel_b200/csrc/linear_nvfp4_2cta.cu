@@ -19,11 +19,19 @@
 //   warp 0      TMA producer: A, B and - for tiled scales - three scale boxes per stage, all
 //               completing on the leader CTA's barrier of the stage
 //   warp 1      MMA issuer (leader CTA only): per stage 12 scale copies, 4 MMAs, 1 commit
-//   warps 2-5   only for scales in the row layout [K/64][rows][4]: each warp takes every fourth
-//               stage, reads the stage's scale words from global memory and writes them to shared
-//               memory in the 32 x 16-byte order tcgen05.cp wants
+//   warps 2-5   only for scales in the row layout [K/64][rows][4] when M or N is not a multiple of 4:
+//               each warp takes every fourth stage, reads the stage's scale words from global
+//               memory and writes them to shared memory in the 32 x 16-byte order tcgen05.cp wants
 //   warps 6-13  epilogue: tcgen05.ld of 128 accumulator columns per warp into registers
 //               (* alpha, + bias, packed to 16 bit), hand the accumulator back, then store
+// Scales in the row layout, M and N multiples of 4 (SF_MODE == kSfPerm): tcgen05.cp puts word w of a 512-byte
+// chunk on lane w / 4, column w % 4, and the MMA takes the scales of its row q * 32 + l from lane l, column q.
+// So the 512 bytes that hold the scale words of 128 consecutive rows in row order are the chunk of those rows in
+// the order (4 l + q -> q * 32 + l): the operand boxes are loaded with their rows in that order (rank-3 tensor
+// maps: bytes, row / 4, row % 4), the scales arrive by TMA as they lie in memory, and nothing is re-ordered by
+// threads (the generic-proxy stores of the scale warps slow the tensor pipe down by 12 - 30 % per stage).  The
+// accumulator's rows and columns come out in the same order; the epilogue maps its lane to row 4 l + q, pairs
+// the columns back in registers and stores through a rank-3 map of the output.
 // Barriers that gate the MMA live in the leader CTA and are signalled by both CTAs; barriers that
 // release stages / publish the accumulator exist in both CTAs and are signalled by one
 // tcgen05.commit whose arrival fans out to both.
@@ -110,12 +118,78 @@ __device__ __forceinline__ void pack_cols(const uint32_t (&r)[N], uint32_t (&w)[
   }
 }
 
-template <bool SF_TILED, int OUT_DT, int EPI>
+// One output word of the row-permuted variant: accumulator values of output columns col, col + 1 of this thread's
+// 128-column segment.
+template <int OUT_DT, bool BIAS>
+__device__ __forceinline__ uint32_t pack_pair(uint32_t lo, uint32_t hi, float alpha, uint32_t bias_s, int col) {
+  if (!BIAS) return (OUT_DT == AC4K_DT_BF16) ? scale_pack_bf16x2(lo, hi, alpha) : scale_pack_f16x2(lo, hi, alpha);
+  const float2 bb = ld_shared_v2f(bias_s + col * 4);
+  return (OUT_DT == AC4K_DT_BF16) ? scale_bias_pack_bf16x2(lo, hi, alpha, bb.x, bb.y) : scale_bias_pack_f16x2(lo, hi, alpha, bb.x, bb.y);
+}
+
+// Drain of this warp's 128 accumulator columns in the row-permuted variant.  Column c holds output column
+// 4 (c % 32) + c / 32 of the segment: output columns 4 l, 4 l + 1 (word 2 l) come from columns l and 32 + l, output
+// columns 4 l + 2, 4 l + 3 (word 2 l + 1) from 64 + l and 96 + l.  Step S = 2 u + v reads columns 64 u + 16 v + [0, 16)
+// and the 16 columns 32 further on and packs words 2 l + u, l = 16 v + [0, 16); the first two steps are read together,
+// later ones are in flight while a step is packed.
+template <int S>
+__device__ __forceinline__ void drain_issue(uint32_t t_row, uint32_t (&lo)[16], uint32_t (&hi)[16]) {
+  tmem_ld_32x32b_x16(t_row + (S >> 1) * 64 + (S & 1) * 16, lo);
+  tmem_ld_32x32b_x16(t_row + (S >> 1) * 64 + (S & 1) * 16 + 32, hi);
+}
+template <int OUT_DT, bool BIAS, int S>
+__device__ __forceinline__ void drain_pack(uint32_t (&w)[64], const uint32_t (&lo)[16], const uint32_t (&hi)[16], float alpha,
+                                           uint32_t bias_s) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    constexpr int u = S >> 1, v = S & 1;
+    w[2 * (16 * v + i) + u] = pack_pair<OUT_DT, BIAS>(lo[i], hi[i], alpha, bias_s, 4 * (16 * v + i) + 2 * u);
+  }
+}
+// Steps in the order S0 .. S3; after the first two (which must cover the columns both accumulators share, if this
+// warp has any of them: `arrive`) the shared columns are reported free.
+template <int OUT_DT, bool BIAS, int S0, int S1, int S2, int S3>
+__device__ __forceinline__ void drain_permuted(uint32_t (&w)[64], uint32_t t_row, bool arrive, float alpha, uint32_t bias_s,
+                                               int lane, uint32_t leader_shared_free) {
+  uint32_t a_lo[16], a_hi[16], b_lo[16], b_hi[16];
+  drain_issue<S0>(t_row, a_lo, a_hi);
+  drain_issue<S1>(t_row, b_lo, b_hi);
+  tmem_ld_wait();
+  tmem_pin(a_lo);
+  tmem_pin(a_hi);
+  tmem_pin(b_lo);
+  tmem_pin(b_hi);
+  if (arrive) {
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive_cluster(leader_shared_free);
+  }
+  drain_pack<OUT_DT, BIAS, S0>(w, a_lo, a_hi, alpha, bias_s);
+  drain_issue<S2>(t_row, a_lo, a_hi);
+  drain_pack<OUT_DT, BIAS, S1>(w, b_lo, b_hi, alpha, bias_s);
+  tmem_ld_wait();
+  tmem_pin(a_lo);
+  tmem_pin(a_hi);
+  drain_issue<S3>(t_row, b_lo, b_hi);
+  drain_pack<OUT_DT, BIAS, S2>(w, a_lo, a_hi, alpha, bias_s);
+  tmem_ld_wait();
+  tmem_pin(b_lo);
+  tmem_pin(b_hi);
+  drain_pack<OUT_DT, BIAS, S3>(w, b_lo, b_hi, alpha, bias_s);
+}
+
+// where the block scales come from: kSfWarps - row layout, re-ordered by warps 2-5; kSfTiled - 128x4 tiles by TMA;
+// kSfPerm - row layout by TMA, operand rows permuted instead
+enum { kSfWarps = 0, kSfTiled = 1, kSfPerm = 2 };
+
+template <int SF_MODE, int OUT_DT, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreadsPair, 1)
 linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                          const __grid_constant__ CUtensorMap tma_sfa, const __grid_constant__ CUtensorMap tma_sfb,
                          const __grid_constant__ DstMaps dmaps, const GemmArgs p) {
   using namespace pair;
+  constexpr bool SF_TILED = SF_MODE != kSfWarps;      // the scales arrive by TMA, laid out for tcgen05.cp
+  constexpr bool PERM = SF_MODE == kSfPerm;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = smem_u32(smem_raw);
   if (smem_base & 1023u) {      // the swizzled boxes need 1024-byte alignment; never seen, but not promised either
@@ -192,8 +266,13 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     const int m0 = tm * BMP + (int)rank * 128, nb0 = tn * BN + (int)rank * 128;
     const int npre = k_tiles < STAGES ? k_tiles : STAGES;
     for (int kt = 0; kt < npre; ++kt) {
-      tma_prefetch_2d_if(el, &tma_a, kt * BKB, m0);
-      tma_prefetch_2d_if(el, &tma_b, kt * BKB, nb0);
+      if (PERM) {
+        tma_prefetch_3d_if(el, &tma_a, kt * BKB, m0 >> 2, 0);
+        tma_prefetch_3d_if(el, &tma_b, kt * BKB, nb0 >> 2, 0);
+      } else {
+        tma_prefetch_2d_if(el, &tma_a, kt * BKB, m0);
+        tma_prefetch_2d_if(el, &tma_b, kt * BKB, nb0);
+      }
     }
   }
   grid_dependency_wait();
@@ -228,6 +307,17 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         // the leader announces the bytes of both CTAs; K steps past the end of K arrive as zeros
         // (or as the next row block's scales, unused) and count all the same
         if (rank == 0) mbar_arrive_expect_tx_if(el, full_bar + 8 * s, 2 * (SF_TILED ? STAGE_TX : A_BYTES + B_BYTES));
+        if (PERM) {
+          // rows 4 l + q of the 128-row block land on shared-memory row q * 32 + l; the scale words of K step k lie
+          // in row order at word k * rows + row: one box of 128 words x 4 K steps per 128-row block
+          tma_load_3d_pair_if(el, sA + s * A_BYTES, &tma_a, kt * BKB, m0 >> 2, 0, lf);
+          tma_load_3d_pair_if(el, sB + s * B_BYTES, &tma_b, kt * BKB, nb0 >> 2, 0, lf);
+          tma_load_2d_pair_if(el, sSFA + s * SFA_BYTES, &tma_sfa, m0, kt * KS, lf);
+          tma_load_2d_pair_if(el, sSFB + s * SFB_BYTES, &tma_sfb, tn * BN, kt * KS, lf);
+          tma_load_2d_pair_if(el, sSFB + s * SFB_BYTES + KS * 512, &tma_sfb, tn * BN + 128, kt * KS, lf);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+          continue;
+        }
         tma_load_2d_pair_if(el, sA + s * A_BYTES, &tma_a, kt * BKB, m0, lf);
         tma_load_2d_pair_if(el, sB + s * B_BYTES, &tma_b, kt * BKB, nb0, lf);
         if (SF_TILED) {
@@ -379,7 +469,7 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     for (int t = cluster_id; t < num_tiles; t += num_clusters) {
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
-      const int row = tm * BMP + (int)rank * 128 + q * 32 + lane;
+      const int row = tm * BMP + (int)rank * 128 + (PERM ? 4 * lane + q : q * 32 + lane);
       const int col0 = tn * BN + half * 128;
       const uint32_t bias_s = sBias + (uint32_t)(half * 4 + q) * 512u;
       const uint32_t acc = ti & 1;
@@ -401,7 +491,18 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       tc_fence_after();
       if (warp == 6 && lane == 0) AC4K_TR(1, ti, 0);
       uint32_t w[64];
-      if (half == (int)acc) {
+      if (PERM) {
+        // the columns both accumulators share are the first 48 of accumulator 1's columns 0 - 127 and the last 48 of
+        // accumulator 0's columns 128 - 255: the first two steps cover them
+        const bool shared = half != (int)acc;
+        if (shared && half == 1) {
+          if (has_bias) drain_permuted<OUT_DT, true, 3, 2, 0, 1>(w, t_row, true, alpha, bias_s, lane, leader_shared_free);
+          else drain_permuted<OUT_DT, false, 3, 2, 0, 1>(w, t_row, true, alpha, bias_s, lane, leader_shared_free);
+        } else {
+          if (has_bias) drain_permuted<OUT_DT, true, 0, 1, 2, 3>(w, t_row, shared, alpha, bias_s, lane, leader_shared_free);
+          else drain_permuted<OUT_DT, false, 0, 1, 2, 3>(w, t_row, shared, alpha, bias_s, lane, leader_shared_free);
+        }
+      } else if (half == (int)acc) {
         // none of the shared columns: columns 0 - 127 of accumulator 0 or 128 - 255 of accumulator 1
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -520,7 +621,8 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         // all-gather: this GPU's buffer and the peers', reached over NVLink) the same buffer is stored
         // once per destination.
         const uint32_t stage_buf = sOut + (uint32_t)(half * 4 + q) * OUT_STAGE_BYTES;
-        const int y0 = tm * BMP + (int)rank * 128 + q * 32;
+        // (row-permuted variant: this warp's lanes hold rows y0 + q, y0 + q + 4, ...: box {64, 32, 1} at {x, y0 / 4, q})
+        const int y0 = tm * BMP + (int)rank * 128 + (PERM ? 0 : q * 32);
 #pragma unroll
         for (int h2 = 0; h2 < 2; ++h2) {
           const int x0 = (int)col_base + 64 * h2;
@@ -534,10 +636,14 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&dmaps.m[0], x0, y0, stage_buf);
+            if (PERM) tma_store_3d(&dmaps.m[0], x0, y0 >> 2, q, stage_buf);
+            else tma_store_2d(&dmaps.m[0], x0, y0, stage_buf);
             if (EPI == EPI_GATHER) {
               // peers in turn, starting behind this rank, so that the ranks do not all write to the same GPU at once
-              for (int d = 1; d < p.n_dst; ++d) tma_store_2d(&dmaps.m[d], x0, y0, stage_buf);
+              for (int d = 1; d < p.n_dst; ++d) {
+                if (PERM) tma_store_3d(&dmaps.m[d], x0, y0 >> 2, q, stage_buf);
+                else tma_store_2d(&dmaps.m[d], x0, y0, stage_buf);
+              }
             }
             bulk_commit_group();
           }
@@ -565,10 +671,10 @@ linear_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   AC4K_TR_LAUNCH(false);
 }
 
-template <bool SF_TILED, int OUT_DT, int EPI>
+template <int SF_MODE, int OUT_DT, int EPI>
 static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tsa, const CUtensorMap &tsb,
                        const DstMaps &dm, const GemmArgs &args, int sms, cudaStream_t stream) {
-  auto kern = linear_nvfp4_2cta_kernel<SF_TILED, OUT_DT, EPI>;
+  auto kern = linear_nvfp4_2cta_kernel<SF_MODE, OUT_DT, EPI>;
   // Once per device: the shared-memory attribute, and how many CTA pairs can be resident at once (not every
   // SM can be paired on every part); the kernel is persistent, so launching more clusters than that would
   // serialise whole waves.
@@ -612,7 +718,17 @@ static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUten
   return 0;
 }
 
-int launch_linear_2cta(int d_dtype, bool sf_tiled, const CUtensorMap &ta, const CUtensorMap &tb,
+template <int OUT_DT, int EPI>
+static int launch_pair_mode(int sf_mode, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tsa, const CUtensorMap &tsb,
+                            const DstMaps &dm, const GemmArgs &args, int sms, cudaStream_t stream) {
+  if (sf_mode == kSfTiled) return launch_pair<kSfTiled, OUT_DT, EPI>(ta, tb, tsa, tsb, dm, args, sms, stream);
+  if (sf_mode == kSfPerm) return launch_pair<kSfPerm, OUT_DT, EPI>(ta, tb, tsa, tsb, dm, args, sms, stream);
+  return launch_pair<kSfWarps, OUT_DT, EPI>(ta, tb, tsa, tsb, dm, args, sms, stream);
+}
+
+// sf_mode: 0 - scales in the row layout, re-ordered by warps (operand and output maps of rank 2); 1 - scales in 128x4
+// tiles; 2 - scales in the row layout with the operands' and the output's maps of rank 3 (rows as row / 4, row % 4)
+int launch_linear_2cta(int d_dtype, int sf_mode, const CUtensorMap &ta, const CUtensorMap &tb,
                        const CUtensorMap &tsa, const CUtensorMap &tsb, const DstMaps &dm, GemmArgs args, cudaStream_t stream) {
   DeviceInfo di;
   if (int e = get_device_info(&di)) return e;
@@ -622,23 +738,16 @@ int launch_linear_2cta(int d_dtype, bool sf_tiled, const CUtensorMap &ta, const 
   // separate: their extra registers and code would otherwise slow the plain GEMM down
   if (args.q_out != nullptr) {
     if (d_dtype != AC4K_DT_BF16) return fail(AC4K_ERR_UNSUPPORTED, "the re-quantising epilogue rounds to bf16 first");
-    return sf_tiled ? launch_pair<true, AC4K_DT_BF16, EPI_REQUANT>(ta, tb, tsa, tsb, dm, args, di.sms, stream)
-                    : launch_pair<false, AC4K_DT_BF16, EPI_REQUANT>(ta, tb, tsa, tsb, dm, args, di.sms, stream);
+    return launch_pair_mode<AC4K_DT_BF16, EPI_REQUANT>(sf_mode, ta, tb, tsa, tsb, dm, args, di.sms, stream);
   }
   const bool gather = args.n_dst > 1;
   if (d_dtype == AC4K_DT_BF16) {
-    if (gather)
-      return sf_tiled ? launch_pair<true, AC4K_DT_BF16, EPI_GATHER>(ta, tb, tsa, tsb, dm, args, di.sms, stream)
-                      : launch_pair<false, AC4K_DT_BF16, EPI_GATHER>(ta, tb, tsa, tsb, dm, args, di.sms, stream);
-    return sf_tiled ? launch_pair<true, AC4K_DT_BF16, EPI_PLAIN>(ta, tb, tsa, tsb, dm, args, di.sms, stream)
-                    : launch_pair<false, AC4K_DT_BF16, EPI_PLAIN>(ta, tb, tsa, tsb, dm, args, di.sms, stream);
+    if (gather) return launch_pair_mode<AC4K_DT_BF16, EPI_GATHER>(sf_mode, ta, tb, tsa, tsb, dm, args, di.sms, stream);
+    return launch_pair_mode<AC4K_DT_BF16, EPI_PLAIN>(sf_mode, ta, tb, tsa, tsb, dm, args, di.sms, stream);
   }
   if (d_dtype == AC4K_DT_FP16) {
-    if (gather)
-      return sf_tiled ? launch_pair<true, AC4K_DT_FP16, EPI_GATHER>(ta, tb, tsa, tsb, dm, args, di.sms, stream)
-                      : launch_pair<false, AC4K_DT_FP16, EPI_GATHER>(ta, tb, tsa, tsb, dm, args, di.sms, stream);
-    return sf_tiled ? launch_pair<true, AC4K_DT_FP16, EPI_PLAIN>(ta, tb, tsa, tsb, dm, args, di.sms, stream)
-                    : launch_pair<false, AC4K_DT_FP16, EPI_PLAIN>(ta, tb, tsa, tsb, dm, args, di.sms, stream);
+    if (gather) return launch_pair_mode<AC4K_DT_FP16, EPI_GATHER>(sf_mode, ta, tb, tsa, tsb, dm, args, di.sms, stream);
+    return launch_pair_mode<AC4K_DT_FP16, EPI_PLAIN>(sf_mode, ta, tb, tsa, tsb, dm, args, di.sms, stream);
   }
   return fail(AC4K_ERR_UNSUPPORTED, "the CTA-pair kernel stores 16-bit outputs only");
 }

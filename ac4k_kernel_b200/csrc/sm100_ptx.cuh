@@ -108,6 +108,11 @@ __device__ __forceinline__ void tma_prefetch_2d_if(uint32_t pred, const void *tm
                "@q cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];\n}"
                ::"l"(tmap), "r"(x), "r"(y), "r"(pred) : "memory");
 }
+__device__ __forceinline__ void tma_prefetch_3d_if(uint32_t pred, const void *tmap, int x, int y, int z) {
+  asm volatile("{\n.reg .pred q;\nsetp.ne.b32 q, %4, 0;\n"
+               "@q cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];\n}"
+               ::"l"(tmap), "r"(x), "r"(y), "r"(z), "r"(pred) : "memory");
+}
 // linear form of the same hint: `bytes` (multiple of 16) from a 16-byte aligned address
 __device__ __forceinline__ void bulk_prefetch_l2_if(uint32_t pred, const void *src, uint32_t bytes) {
   asm volatile("{\n.reg .pred q;\nsetp.ne.b32 q, %2, 0;\n@q cp.async.bulk.prefetch.L2.global [%0], %1;\n}"
@@ -281,6 +286,11 @@ __device__ __forceinline__ float4 ld_shared_v4f(uint32_t addr) {
   asm volatile("ld.shared::cta.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
   return v;
 }
+__device__ __forceinline__ float2 ld_shared_v2f(uint32_t addr) {
+  float2 v;
+  asm volatile("ld.shared::cta.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
+  return v;
+}
 __device__ __forceinline__ void st_shared_release(uint32_t addr, uint32_t v) {
   asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
@@ -389,6 +399,11 @@ __device__ __forceinline__ void tma_store_2d(const void *tmap, int x, int y, uin
                ::"l"(tmap), "r"(x), "r"(y), "r"(src)
                : "memory");
 }
+__device__ __forceinline__ void tma_store_3d(const void *tmap, int x, int y, int z, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+               ::"l"(tmap), "r"(x), "r"(y), "r"(z), "r"(src)
+               : "memory");
+}
 // same, with an L2 cache policy for the written lines (from make_policy_evict_first / _last)
 __device__ __forceinline__ void tma_store_2d_hint(const void *tmap, int x, int y, uint32_t src, uint64_t policy) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group.L2::cache_hint [%0, {%1, %2}], [%3], %4;"
@@ -479,6 +494,14 @@ __device__ __forceinline__ void tma_load_2d_pair_if(uint32_t pred, uint32_t dst,
       "{\n.reg .pred q;\nsetp.ne.b32 q, %5, 0;\n"
       "@q cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n}"
       ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar_cluster_addr), "r"(pred)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair_if(uint32_t pred, uint32_t dst, const void *tmap, int x, int y, int z,
+                                                    uint32_t bar_cluster_addr) {
+  asm volatile(
+      "{\n.reg .pred q;\nsetp.ne.b32 q, %6, 0;\n"
+      "@q cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n}"
+      ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(bar_cluster_addr), "r"(pred)
       : "memory");
 }
 __device__ __forceinline__ void bulk_load_1d_if(uint32_t pred, uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {

@@ -136,6 +136,15 @@ def test_bias_and_output_dtypes(ops, m, n, k, odt, bdt):
     run_case(ops, m, n, k, seed=3, bias_dtype=bdt, out_dtype=odt)
 
 
+@pytest.mark.parametrize("m,n,k", [(260, 392, 320), (262, 392, 320), (1028, 520, 1088), (1026, 520, 1088)])
+@pytest.mark.parametrize("bdt", [None, torch.float32])
+def test_row_layout_scale_paths(ops, m, n, k, bdt):
+    """Scales in the reference's layout reach the CTA-pair kernel in two ways: with M and N multiples of 4 the
+    operand rows are permuted by the loads and the scales are used as they lie in memory; otherwise warps re-order
+    the scales.  Both against the restatement, ragged tiles in both directions."""
+    run_case(ops, m, n, k, seed=31, layout="ac4k", bias_dtype=bdt, out_dtype=torch.bfloat16)
+
+
 def test_random_shapes(ops):
     """test/test_linear_bench.py:156-161: 20 random M, N, K in [2, 555]."""
     rng = random.Random(9567)
