@@ -64,6 +64,12 @@ def _worker(rank, world, port, m, n, k, result_dir):
                     spin = spin @ spin * 0 + 1          # this rank's consumer starts late
             sums.append(full.float().sum() + spin[0, 0] * 0)      # the consumer: reads the whole gathered output
             fulls_ok.append(torch.equal(full, wholes[i]))
+        # one more step with every operand's scales in the reference's row layout: the kernel then loads the operands
+        # with permuted rows and stores through rank-3 maps of the peers' buffers
+        xr = ops.quantize(xs[0], 0, 1, sf_layout="ac4k")
+        w4r, wsfr, wgr = parallel.quantize_weight_shard(w[lo:hi].contiguous(), None, "ac4k")
+        full = parallel.column_parallel_linear_fused(xr[0], xr[1], xr[2], w4r, wsfr, wgr, peer)
+        fulls_ok.append(torch.equal(full, wholes[0]))
         torch.cuda.synchronize()
         ok = all(fulls_ok) and all(float(sums[i]) == float(wholes[i].float().sum()) for i in range(steps))
         peer.close()
