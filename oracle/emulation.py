@@ -25,7 +25,11 @@ Reference lines followed (paths inside the ac4k_kernel project):
 
 The reference kernels use `rcp.approx.ftz` and `--use_fast_math`; this restatement (and the
 CUDA kernels checked against it) use correctly rounded fp32 operations in the same order, so
-that CPU, GPU-torch and the hand-written kernels agree bit for bit.
+that CPU, GPU-torch and the hand-written kernels agree bit for bit.  How far that is from the
+reference's kernels themselves is measured, not assumed: its quantiser and RoPE kernels are built
+for sm_100a by oracle/build_ref.py and run beside the CUDA path in
+tests/test_reference_kernels_gpu.py (RoPE and, for global scales with an exactly rounded
+approximate reciprocal, the NVFP4 quantiser: every byte equal).
 """
 from __future__ import annotations
 
