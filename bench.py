@@ -308,7 +308,54 @@ def run_reference(args):
         "note": "the reference's GEMM kernel is sm_120a-only and cannot run on a B200; its CPU-runnable "
                 "form is the torch emulation from its tests, restated in oracle/emulation.py",
     }
+    gpu_side = reference_gpu_kernels() if args.gpus == 1 else None
+    if gpu_side is not None:
+        line["reference_gpu_kernels"] = gpu_side
     print(json.dumps(line))
+
+
+def reference_gpu_kernels():
+    """The part of the reference that does run on a B200: its own quantiser kernels (oracle/_ref, built unchanged
+    from the reference checkout for sm_100a), timed on the quantiser configuration of the benchmark, bf16
+    [32768, 8192].  None without a GPU or without that build."""
+    if not torch.cuda.is_available():
+        return None
+    from oracle import build_ref
+    ref = build_ref.load()
+    if ref is None:
+        return None
+    m, k = 32768, 8192
+    x = torch.randn((m, k), dtype=torch.bfloat16, device="cuda")
+    gs = (x.abs().max().float() / (6.0 * 448.0)).reshape(())
+    out4 = torch.empty((m, k // 2), dtype=torch.uint8, device="cuda")
+    sf4 = torch.empty((k // 64, m, 4), dtype=torch.float8_e4m3fn, device="cuda")
+    out8 = torch.empty((m, k), dtype=torch.float8_e4m3fn, device="cuda")
+    outi = torch.empty((m, k), dtype=torch.int8, device="cuda")
+    sf8 = torch.empty((m,), dtype=torch.float32, device="cuda")
+    smax_f = torch.tensor(448.0, device="cuda")
+    smax_i = torch.tensor(127, dtype=torch.int32, device="cuda")
+
+    def timed(fn, n=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n * 1e-3
+
+    t4 = timed(lambda: ref.quantize_nvfp4(out4, sf4, x, gs, 0, 1, False))
+    t8 = timed(lambda: ref.quantize_fp8(out8, sf8, x, smax_f, 0, 1, False))
+    ti = timed(lambda: ref.quantize_int8(outi, sf8, x, smax_i, 0, 1))
+    b4 = x.numel() * 2 + out4.numel() + sf4.numel()
+    b8 = x.numel() * 3 + sf8.numel() * 4
+    return {"workload": "bf16 [32768, 8192], the reference's own kernels compiled for sm_100a, inputs larger than L2",
+            "quantize_nvfp4_gbs": b4 / t4 / 1e9, "quantize_nvfp4_us": t4 * 1e6,
+            "quantize_fp8_gbs": b8 / t8 / 1e9, "quantize_int8_gbs": b8 / ti / 1e9,
+            "note": "given the global scale; compare with the `quantize` record of the other arm"}
 
 
 # ------------------------------------------------------------------------------------------
