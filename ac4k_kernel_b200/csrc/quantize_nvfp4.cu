@@ -38,10 +38,7 @@ __device__ __forceinline__ uint32_t quantize8(const uint4 &v, float r) {
 // instructions per 8 elements and reached 4.7 TB/s.
 // ----------------------------------------------------------------------------------------
 static constexpr int kTileRows = 128;
-static constexpr int kTileK = 256;
-static constexpr int kTileKch = kTileK / 64;
 static constexpr int kThreads = 256;
-static constexpr int kPassRows = 16;
 static constexpr int kBatch = 4;      // passes whose loads are issued together
 
 struct Block16 { uint32_t w[8]; };
@@ -63,12 +60,17 @@ __device__ __forceinline__ Block16 load_block16(const uint16_t *p) {
   return b;
 }
 
-template <int SF_LAYOUT, bool WIDE>
+// TK: K elements of a CTA's tile, 256 or - for rows of at most 128 elements (attention's q and k: one head's
+// features), where half of a 256-wide tile's threads would have nothing to load - 128.
+template <int SF_LAYOUT, bool WIDE, int TK>
 __global__ void __launch_bounds__(kThreads)
 nvfp4_quantize_tiled_kernel(uint8_t *__restrict__ out, uint32_t *__restrict__ sf,
                             const uint16_t *__restrict__ in, const float *__restrict__ gscale,
                             int64_t M, int64_t K, int64_t d1, int64_t stride0, int64_t stride1,
                             int64_t row_stride) {
+  constexpr int kTileK = TK, kTileKch = TK / 64;
+  constexpr int kRowThreads = TK / 16;                  // threads (16-element blocks) per row of the tile
+  constexpr int kPassRows = kThreads / kRowThreads;     // rows the CTA covers per pass
   __shared__ uint32_t s_sf[kTileKch * kTileRows];
   __shared__ float s_rcp[128];
 
@@ -79,7 +81,7 @@ nvfp4_quantize_tiled_kernel(uint8_t *__restrict__ out, uint32_t *__restrict__ sf
   const int64_t batch = blockIdx.z;
   const int64_t r0 = (int64_t)blockIdx.y * kTileRows;
   const int64_t k0 = (int64_t)blockIdx.x * kTileK;
-  const int blk = threadIdx.x & 15, prow = threadIdx.x >> 4;
+  const int blk = threadIdx.x % kRowThreads, prow = threadIdx.x / kRowThreads;
 
   if (threadIdx.x < 128) {
     // 1 / float(e4m3 byte), correctly rounded; entry 0 is 0 so that a zero scale zeroes the block
@@ -425,17 +427,21 @@ extern "C" int ac4k_quantize_nvfp4(void *out, void *sf, const void *in, const fl
   if (vec_ok) {
     const bool wide = (stride[2] % 16 == 0) && (stride[0] % 16 == 0) && (stride[1] % 16 == 0) &&
                       ((reinterpret_cast<uintptr_t>(in) & 31) == 0);
-    dim3 grid((unsigned)ceil_div(Kp, kTileK), (unsigned)ceil_div(M, kTileRows), (unsigned)nbatch);
+    const int tile_k = Kp <= 128 ? 128 : 256;
+    dim3 grid((unsigned)ceil_div(Kp, (int64_t)tile_k), (unsigned)ceil_div(M, kTileRows), (unsigned)nbatch);
     if (ceil_div(M, kTileRows) > 65535) return fail(AC4K_ERR_SHAPE, "M too large");
-#define AC4K_LAUNCH_TILED(L, W)                                                                   \
-  nvfp4_quantize_tiled_kernel<L, W><<<grid, kThreads, 0, stream>>>(                               \
+#define AC4K_LAUNCH_TILED(L, W, T)                                                                \
+  nvfp4_quantize_tiled_kernel<L, W, T><<<grid, kThreads, 0, stream>>>(                            \
       static_cast<uint8_t *>(out), static_cast<uint32_t *>(sf), inp, global_scale, M, K, d1,      \
       stride[0], stride[1], stride[2])
+#define AC4K_LAUNCH_TILED_K(L, W)                                                                 \
+  do { if (tile_k == 128) AC4K_LAUNCH_TILED(L, W, 128); else AC4K_LAUNCH_TILED(L, W, 256); } while (0)
     if (sf_layout == AC4K_SF_AC4K) {
-      if (wide) AC4K_LAUNCH_TILED(AC4K_SF_AC4K, true); else AC4K_LAUNCH_TILED(AC4K_SF_AC4K, false);
+      if (wide) AC4K_LAUNCH_TILED_K(AC4K_SF_AC4K, true); else AC4K_LAUNCH_TILED_K(AC4K_SF_AC4K, false);
     } else {
-      if (wide) AC4K_LAUNCH_TILED(AC4K_SF_TILE128X4, true); else AC4K_LAUNCH_TILED(AC4K_SF_TILE128X4, false);
+      if (wide) AC4K_LAUNCH_TILED_K(AC4K_SF_TILE128X4, true); else AC4K_LAUNCH_TILED_K(AC4K_SF_TILE128X4, false);
     }
+#undef AC4K_LAUNCH_TILED_K
 #undef AC4K_LAUNCH_TILED
     AC4K_LAUNCH_CHECK("nvfp4_quantize_tiled_kernel");
     return 0;

@@ -60,6 +60,27 @@ def main():
         print(f"quantize_{prec} [{m}, {k}]: reference kernel {t_ref * 1e6:.1f} us = {nb / t_ref / 1e9:.0f} GB/s; "
               f"this repository {t_own * 1e6:.1f} us = {nb / t_own / 1e9:.0f} GB/s; speed-up {t_ref / t_own:.2f}; "
               f"bytes differing (fast-math division in the reference): {diff} of {o.numel()}")
+    del x, out, sf, r_out, r_sf, o, s, ro, rs
+    # the quantisers as attention calls them (python/ac4k_kernel/ops/attention.py:102-135, 157-186): [B, N, H, D] tensors,
+    # q / k along the head dimension, V along the tokens with the K permutation
+    v = torch.randn((1, 75600, 40, 128), dtype=torch.bfloat16, device="cuda")
+    for name, cd, rd, sw in (("q / k: cross N, reduce D", 1, 3, False), ("V: cross D, reduce N, swizzle", 3, 1, True)):
+        out, sf, gs = ops.quantize(v, cd, rd, swizzle=sw)
+        r_out, r_sf = torch.empty_like(out), torch.empty_like(sf)
+        t_ref = timed(lambda: ref.quantize_nvfp4(r_out, r_sf, v, gs, cd, rd, sw), n=5)
+        t_own = timed(lambda: _cuda_ops.quantize_nvfp4(out, sf, v, gs, cd, rd, sw))
+        diff = int((out != r_out).sum()) + int((sf.view(torch.uint8) != r_sf.view(torch.uint8)).sum())
+        print(f"quantize_nvfp4 [1, 75600, 40, 128] {name}: reference kernel {t_ref * 1e6:.1f} us; this repository "
+              f"{t_own * 1e6:.1f} us; speed-up {t_ref / t_own:.2f}; bytes differing: {diff} of {out.numel() + sf.numel()}")
+    o, s = ops.quantize(v, 3, 1, swizzle=True, max_scale=2.25, precision="fp8e4m3")
+    ro, rs = torch.empty_like(o), torch.empty_like(s)
+    smax = torch.tensor(2.25, device="cuda")
+    t_ref = timed(lambda: ref.quantize_fp8(ro, rs, v, smax, 3, 1, True), n=5)
+    t_own = timed(lambda: ops.quantize(v, 3, 1, swizzle=True, max_scale=2.25, precision="fp8e4m3", output=o, sf=s))
+    diff = int((o.view(torch.uint8) != ro.view(torch.uint8)).sum())
+    print(f"quantize_fp8 [1, 75600, 40, 128] V: cross D, reduce N, swizzle, scale_max 2.25: reference kernel {t_ref * 1e6:.1f} us; "
+          f"this repository {t_own * 1e6:.1f} us; speed-up {t_ref / t_own:.2f}; bytes differing: {diff} of {o.numel()}")
+    del v, out, sf, r_out, r_sf, o, s, ro, rs
     b, f, h, w, n, d = 1, 21, 45, 80, 40, 128
     xr = torch.randn((b, f * h * w, n, d), dtype=torch.bfloat16, device="cuda")
     grid = torch.tensor([[f, h, w]], dtype=torch.int32, device="cuda")
