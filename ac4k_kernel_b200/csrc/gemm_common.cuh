@@ -157,6 +157,8 @@ int get_tmap_sf_rows(const void *ptr, int64_t rows, int64_t kt, CUtensorMap *out
 // 2-D byte tensor map with a (64 B x box_rows) box and 64-byte swizzle
 int get_tmap64(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, CUtensorMap *out);
 unsigned long long *debug_trace_ptr();
+// bf16 [B, H, N, D] by element strides (D contiguous, the others multiples of 8): boxes of D x box_rows x 1 x 1
+int get_tmap_bf16_4d(const void *ptr, const int64_t shape[4], const int64_t stride[4], int box_rows, CUtensorMap *out);
 // 16-bit output [rows, cols] with a row pitch of ld elements: boxes of 64 columns x 32 rows, 128-byte swizzle
 int get_tmap_out16(const void *ptr, int64_t rows, int64_t cols, int64_t ld, CUtensorMap *out);
 // the same output with the rows as (row / 4, row % 4): boxes of 64 columns x 32 x 1; rows must be a multiple of 4

@@ -512,6 +512,45 @@ int get_tmap64(const void *ptr, int64_t rows, int64_t row_bytes, int box_rows, C
   return encode_cached(kTmapOperand64, ptr, row_bytes, rows, row_bytes, 64, box_rows, out);
 }
 
+// bf16 tensor [B, H, N, D] given by element strides (D contiguous): boxes of D x box_rows x 1 x 1, not swizzled.  Rows
+// past N read as zero.  Kept in a small cache of its own (key: pointer, shape, strides, box).
+int get_tmap_bf16_4d(const void *ptr, const int64_t shape[4], const int64_t stride[4], int box_rows, CUtensorMap *out) {
+  struct Key { const void *ptr; int64_t sh[4], st[3]; int box, dev; };
+  struct Entry { Key k; CUtensorMap m; };
+  static std::mutex mu;
+  static std::vector<Entry> cache;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  Key key{ptr, {shape[0], shape[1], shape[2], shape[3]}, {stride[0], stride[1], stride[2]}, box_rows, dev};
+  auto same = [](const Key &a, const Key &b) {
+    return a.ptr == b.ptr && a.box == b.box && a.dev == b.dev && a.sh[0] == b.sh[0] && a.sh[1] == b.sh[1] && a.sh[2] == b.sh[2] &&
+           a.sh[3] == b.sh[3] && a.st[0] == b.st[0] && a.st[1] == b.st[1] && a.st[2] == b.st[2];
+  };
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    for (auto &e : cache)
+      if (same(e.k, key)) { *out = e.m; return 0; }
+  }
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return fail(AC4K_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[4] = {(cuuint64_t)shape[3], (cuuint64_t)shape[2], (cuuint64_t)shape[1], (cuuint64_t)shape[0]};
+  cuuint64_t gstride[3] = {(cuuint64_t)stride[2] * 2, (cuuint64_t)stride[1] * 2, (cuuint64_t)stride[0] * 2};
+  cuuint32_t box[4] = {(cuuint32_t)shape[3], (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUtensorMap m;
+  CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void *>(ptr), gdim, gstride, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail((int)r > 0 ? (int)r : 999, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    if (cache.size() >= 32) cache.erase(cache.begin());
+    cache.push_back({key, m});
+  }
+  *out = m;
+  return 0;
+}
+
 int get_device_info(DeviceInfo *out) {
   static PerDevice<DeviceInfo> info;
   return info.get(out, [](DeviceInfo &v) {

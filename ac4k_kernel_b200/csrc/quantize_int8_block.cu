@@ -11,7 +11,7 @@
 // Two kernels: 16-byte vectors when the features are contiguous and aligned, single elements otherwise.
 #include <algorithm>
 
-#include "common.cuh"
+#include "gemm_common.cuh"
 
 namespace ac4k {
 
@@ -131,6 +131,107 @@ __global__ void __launch_bounds__(kQ8Threads) quantize_int8_block_vec_kernel(
   grid_launch_dependents();
 }
 
+// trunc(RN(f / s)) for |f / s| <= 127 with rs = RN(1 / s), without a division or a conversion instruction per element
+// (both run on the 16-per-clock pipe, which bounds the kernel otherwise).  t = f * rs is within 1.5 * 2^-23 * |f / s|
+// < 2.3e-5 of the correctly rounded quotient, so the two truncate alike unless t lies that close to an integer; 1e-4
+// is the margin used, and zero, infinities and NaNs fall inside it: those elements take the true division.  The
+// integer part comes from adding 2^23 (round down: the sum's low mantissa bits are floor(|t|); round to nearest: the
+// nearest integer, for the distance).
+__device__ __forceinline__ int trunc_quotient(float f, float s, float rs) {
+  const float t = __fmul_rn(f, rs);
+  const float a = fabsf(t);
+  const float nearest = __fsub_rn(__fadd_rn(a, 8388608.0f), 8388608.0f);
+  if (fabsf(__fsub_rn(a, nearest)) > 1e-4f) {
+    const int q = (int)(__float_as_uint(__fadd_rd(a, 8388608.0f)) & 0xffu);
+    return t < 0.0f ? -q : q;
+  }
+  return __float2int_rz(__fdiv_rn(f, s));
+}
+
+// The same quantiser with the block staged in shared memory by one TMA load (a box of D features x `block` tokens of the
+// [B, H, N, D] tensor, whatever its strides; tokens past N arrive as zeros): no thread holds the block in registers
+// while it is in flight, so seven CTAs fit on an SM instead of four and the loads of all of them are outstanding at
+// once.  D a multiple of 8 and at most 256, strides multiples of 8 elements, base 16-byte aligned.
+__global__ void __launch_bounds__(kQ8Threads) quantize_int8_block_tma_kernel(
+    const __grid_constant__ CUtensorMap tmap, int8_t *__restrict__ y, float *__restrict__ scale, int N, int D, int Dp, int block,
+    int nblk, int H, const uint16_t *__restrict__ sub, int64_t ub, int64_t uh, unsigned int *status, unsigned long long wait_ns) {
+  extern __shared__ __align__(128) uint8_t q8_tile[];
+  __shared__ __align__(8) uint64_t bar_mem;
+  __shared__ float red[kQ8Threads / 32];
+  using namespace ptx;
+  const int blk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int n0 = blk * block;
+  const int rows = min(block, N - n0);
+  const uint32_t bar = smem_u32(&bar_mem), tile = smem_u32(q8_tile);
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  grid_dependency_wait();
+  if (threadIdx.x == 0) {
+    mbar_arrive_expect_tx(bar, (uint32_t)(block * D * 2));     // the whole box, rows past N included (zeros)
+    tma_load_4d(tile, &tmap, 0, n0, h, b, bar);
+  }
+  if (!mbar_wait(bar, 0, wait_ns)) {
+    if (threadIdx.x == 0) atomicExch(status, kStatusTimeoutProducer);
+    return;
+  }
+  const int vpr = D / 8, vpr_out = Dp / 8;            // vectors per input row / per output row (padding included)
+  const int nvec = rows * vpr_out;
+  const uint16_t *subp = sub != nullptr ? sub + b * ub + h * uh : nullptr;
+  auto load_vec = [&](int r, int c) {
+    uint4 v;
+    asm volatile("ld.shared::cta.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(tile + (uint32_t)(r * D + c * 8) * 2u));
+    if (subp != nullptr) {      // x - sub rounded to bf16, as a bf16 tensor subtraction gives it
+      __nv_bfloat162 *h2 = reinterpret_cast<__nv_bfloat162 *>(&v);
+      const uint4 u = __ldg(reinterpret_cast<const uint4 *>(subp) + c);
+      const __nv_bfloat162 *u2 = reinterpret_cast<const __nv_bfloat162 *>(&u);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) h2[k] = __hsub2(h2[k], u2[k]);
+    }
+    return v;
+  };
+  __nv_bfloat162 am2 = __floats2bfloat162_rn(0.0f, 0.0f);
+  for (int e = threadIdx.x; e < nvec; e += kQ8Threads) {
+    const int r = e / vpr_out, c = e - r * vpr_out;
+    if (c < vpr) {
+      const uint4 v = load_vec(r, c);
+      const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) am2 = __hmax2(am2, __habs2(h2[k]));
+    }
+  }
+  float amax = fmaxf(__low2float(am2), __high2float(am2));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int w = 1; w < kQ8Threads / 32; ++w) amax = fmaxf(amax, red[w]);
+  const float s = __fdiv_rn(amax, 127.0f);
+  const float rs = __frcp_rn(s);
+  if (threadIdx.x == 0) scale[((int64_t)b * H + h) * nblk + blk] = s;
+  uint2 *dst = reinterpret_cast<uint2 *>(y + (((int64_t)b * H + h) * N + n0) * Dp);
+  for (int e = threadIdx.x; e < nvec; e += kQ8Threads) {
+    const int r = e / vpr_out, c = e - r * vpr_out;
+    uint32_t o[2] = {0u, 0u};
+    if (c < vpr && s != 0.0f) {
+      const uint4 v = load_vec(r, c);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float f = __uint_as_float((k & 1) ? (w[k >> 1] & 0xffff0000u) : (w[k >> 1] << 16));
+        o[k >> 2] |= ((uint32_t)trunc_quotient(f, s, rs) & 0xffu) << (8 * (k & 3));
+      }
+    }
+    __stcs(dst + e, make_uint2(o[0], o[1]));
+  }
+  grid_launch_dependents();
+}
+
 }  // namespace ac4k
 
 using namespace ac4k;
@@ -158,6 +259,30 @@ extern "C" int ac4k_quantize_int8_block(void *out, float *scale, const void *in,
   const bool vec = stride[3] == 1 && D % 8 == 0 && stride[0] % 8 == 0 && stride[1] % 8 == 0 && stride[2] % 8 == 0 &&
                    (reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 7) == 0 &&
                    (!sub || ((reinterpret_cast<uintptr_t>(sub) & 15) == 0 && ub % 8 == 0 && uh % 8 == 0));
+  // the TMA-staged kernel: additionally D <= 256 (one box row), and a device of compute capability 10
+  if (vec && D <= 256 && stride[2] > 0) {
+    DeviceInfo di;
+    if (int e = get_device_info(&di)) return e;
+    CUtensorMap tm;
+    if (di.cc_major == 10 && get_tmap_bf16_4d(in, shape, stride, (int)block, &tm) == 0) {
+      unsigned int *status = device_status_ptr();
+      if (!status) return fail(AC4K_ERR_DEVICE, "cannot resolve the device status word");
+      const size_t smem = (size_t)block * D * 2;
+      static PerDevice<int> attr_set;
+      int dummy = 0;
+      if (int e = attr_set.get(&dummy, [&](int &v) {
+            AC4K_CUDA_TRY(cudaFuncSetAttribute(quantize_int8_block_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 256 * 2));
+            v = 1;
+            return 0;
+          }))
+        return e;
+      quantize_int8_block_tma_kernel<<<grid, kQ8Threads, smem, stream>>>(tm, static_cast<int8_t *>(out), scale, (int)N, (int)D, (int)Dp,
+                                                                         (int)block, (int)nblk, (int)H, subp, ub, uh, status,
+                                                                         ptx::kWaitTimeoutNs);
+      AC4K_LAUNCH_CHECK("quantize_int8_block_tma_kernel");
+      return 0;
+    }
+  }
   if (vec) {
     const int64_t vpt = ceil_div(block * (Dp / 8), kQ8Threads);
 #define AC4K_Q8V_LAUNCH(V)                                                                                                            \

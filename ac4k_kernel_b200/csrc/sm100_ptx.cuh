@@ -81,6 +81,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, int 
       ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void *tmap, int x, int y, int z, int w, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
+      : "memory");
+}
 // linear copy: src/dst 16-byte aligned, bytes a multiple of 16
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
   asm volatile(
