@@ -6,9 +6,10 @@
 // Stands in for the Triton kernel and its wrapper in ac4k_kernel's python/ac4k_kernel/ops/attention.py:18-48 and
 // :51-99 (`tl.cast(fp32 -> int8)` truncates toward zero; the division is a true fp32 division).
 //
-// One CTA per (token block, head, batch entry): the block (at most 128 x 256 bf16) is read once into registers,
+// One CTA per (token block, head, batch entry): the block (at most 128 x 256 bf16) is read once,
 // reduced to its maximum through shared memory, and written back as bytes.  HBM traffic 2 + 1 bytes per element.
-// Two kernels: 16-byte vectors when the features are contiguous and aligned, single elements otherwise.
+// Three kernels: the block staged in shared memory by a TMA load (features a multiple of 8 and at most 256, aligned
+// strides: the usual case), 16-byte vectors held in registers, single elements for anything else.
 #include <algorithm>
 
 #include "gemm_common.cuh"
@@ -131,21 +132,29 @@ __global__ void __launch_bounds__(kQ8Threads) quantize_int8_block_vec_kernel(
   grid_launch_dependents();
 }
 
-// trunc(RN(f / s)) for |f / s| <= 127 with rs = RN(1 / s), without a division or a conversion instruction per element
-// (both run on the 16-per-clock pipe, which bounds the kernel otherwise).  t = f * rs is within 1.5 * 2^-23 * |f / s|
-// < 2.3e-5 of the correctly rounded quotient, so the two truncate alike unless t lies that close to an integer; 1e-4
-// is the margin used, and zero, infinities and NaNs fall inside it: those elements take the true division.  The
-// integer part comes from adding 2^23 (round down: the sum's low mantissa bits are floor(|t|); round to nearest: the
-// nearest integer, for the distance).
-__device__ __forceinline__ int trunc_quotient(float f, float s, float rs) {
-  const float t = __fmul_rn(f, rs);
-  const float a = fabsf(t);
-  const float nearest = __fsub_rn(__fadd_rn(a, 8388608.0f), 8388608.0f);
-  if (fabsf(__fsub_rn(a, nearest)) > 1e-4f) {
-    const int q = (int)(__float_as_uint(__fadd_rd(a, 8388608.0f)) & 0xffu);
-    return t < 0.0f ? -q : q;
+// Eight elements of a 16-byte vector -> eight int8 codes trunc(RN(f / s)), |f / s| <= 127, without a division or a
+// float -> int conversion per element (both run on the 16-per-clock pipe, which bounds the kernel otherwise).  With
+// rs = RN(1 / s), t = f * rs is within 1.5 * 2^-23 * |f / s| < 2.3e-5 of the correctly rounded quotient, so the two
+// truncate alike unless t lies that close to an integer.  floor(|t|) comes from adding 2^23 with round-down, its
+// fraction is exact, and the code is the low byte of sign(t) * floor(|t|) + 1.5 * 2^23 (two's complement for free).
+// Returns false - and the caller takes the true division for the whole vector - if any fraction is within 1e-4 of an
+// integer (zero, infinities and NaNs included).
+__device__ __forceinline__ bool quantize8_by_reciprocal(const uint4 &v, float rs, uint32_t (&o)[2]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  uint32_t m[8];
+  bool ok = true;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float f = __uint_as_float((k & 1) ? (w[k >> 1] & 0xffff0000u) : (w[k >> 1] << 16));
+    const float t = __fmul_rn(f, rs);
+    const float fl = __fsub_rn(__fadd_rd(fabsf(t), 8388608.0f), 8388608.0f);
+    const float frac = __fsub_rn(fabsf(t), fl);
+    ok = ok && (fabsf(__fsub_rn(frac, 0.5f)) < 0.4999f);
+    m[k] = __float_as_uint(__fadd_rn(copysignf(fl, t), 12582912.0f));
   }
-  return __float2int_rz(__fdiv_rn(f, s));
+  o[0] = __byte_perm(__byte_perm(m[0], m[1], 0x0040), __byte_perm(m[2], m[3], 0x0040), 0x5410);
+  o[1] = __byte_perm(__byte_perm(m[4], m[5], 0x0040), __byte_perm(m[6], m[7], 0x0040), 0x5410);
+  return ok;
 }
 
 // The same quantiser with the block staged in shared memory by one TMA load (a box of D features x `block` tokens of the
@@ -179,6 +188,11 @@ __global__ void __launch_bounds__(kQ8Threads) quantize_int8_block_tma_kernel(
   }
   const int vpr = D / 8, vpr_out = Dp / 8;            // vectors per input row / per output row (padding included)
   const int nvec = rows * vpr_out;
+  const int shift = (vpr_out & (vpr_out - 1)) == 0 ? __ffs(vpr_out) - 1 : -1;     // rows of a power of two of vectors
+  auto row_col = [&](int e, int &r, int &c) {
+    if (shift >= 0) { r = e >> shift; c = e & (vpr_out - 1); }
+    else { r = e / vpr_out; c = e - r * vpr_out; }
+  };
   const uint16_t *subp = sub != nullptr ? sub + b * ub + h * uh : nullptr;
   auto load_vec = [&](int r, int c) {
     uint4 v;
@@ -195,7 +209,8 @@ __global__ void __launch_bounds__(kQ8Threads) quantize_int8_block_tma_kernel(
   };
   __nv_bfloat162 am2 = __floats2bfloat162_rn(0.0f, 0.0f);
   for (int e = threadIdx.x; e < nvec; e += kQ8Threads) {
-    const int r = e / vpr_out, c = e - r * vpr_out;
+    int r, c;
+    row_col(e, r, c);
     if (c < vpr) {
       const uint4 v = load_vec(r, c);
       const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&v);
@@ -216,15 +231,19 @@ __global__ void __launch_bounds__(kQ8Threads) quantize_int8_block_tma_kernel(
   if (threadIdx.x == 0) scale[((int64_t)b * H + h) * nblk + blk] = s;
   uint2 *dst = reinterpret_cast<uint2 *>(y + (((int64_t)b * H + h) * N + n0) * Dp);
   for (int e = threadIdx.x; e < nvec; e += kQ8Threads) {
-    const int r = e / vpr_out, c = e - r * vpr_out;
+    int r, c;
+    row_col(e, r, c);
     uint32_t o[2] = {0u, 0u};
     if (c < vpr && s != 0.0f) {
       const uint4 v = load_vec(r, c);
-      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      if (!quantize8_by_reciprocal(v, rs, o)) {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        o[0] = o[1] = 0u;
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const float f = __uint_as_float((k & 1) ? (w[k >> 1] & 0xffff0000u) : (w[k >> 1] << 16));
-        o[k >> 2] |= ((uint32_t)trunc_quotient(f, s, rs) & 0xffu) << (8 * (k & 3));
+        for (int k = 0; k < 8; ++k) {
+          const float f = __uint_as_float((k & 1) ? (w[k >> 1] & 0xffff0000u) : (w[k >> 1] << 16));
+          o[k >> 2] |= ((uint32_t)__float2int_rz(__fdiv_rn(f, s)) & 0xffu) << (8 * (k & 3));
+        }
       }
     }
     __stcs(dst + e, make_uint2(o[0], o[1]));
